@@ -1,0 +1,13 @@
+"""fused_turboquant_b200 -- B200-native (sm_100a) kernels for fused-turboquant's
+KV encode and compressed-KV decode attention, behind the reference's surfaces.
+
+Public names follow the reference package (src/fused_turboquant/__init__.py):
+``TurboQuantMSE``, ``CompressedTensor`` and the kernel-level callables in
+``fused_turboquant_b200.kernels``; ``PagedKVPool`` is the paged cache the vLLM
+attention impl drives.
+"""
+from .quantizer import CompressedTensor, TurboQuantMSE  # noqa: F401
+from .paged import PagedKVPool  # noqa: F401
+from . import kernels  # noqa: F401
+
+__version__ = "0.1.0"

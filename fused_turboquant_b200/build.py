@@ -1,0 +1,81 @@
+"""Builds libftq_b200.so (the CUDA kernels + C ABI) in-tree with nvcc for sm_100a.
+
+    python -m fused_turboquant_b200.build [--force] [--verbose]
+
+The per-head_dim translation units compile in parallel.  No fast-math flag is
+ever passed: the encode kernel's bit-exactness depends on IEEE arithmetic.
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG_DIR, "csrc")
+OBJ_DIR = os.path.join(PKG_DIR, "build")
+LIB_PATH = os.path.join(PKG_DIR, "libftq_b200.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+]
+
+# (source, object suffix, extra defines)
+UNITS = [("ftq_api.cu", "api", [])]
+for _d in (64, 128, 256):
+    UNITS.append(("ftq_encode_inst.cu", f"encode_d{_d}", [f"-DFTQ_D={_d}"]))
+    UNITS.append(("ftq_attn_inst.cu", f"attn_d{_d}", [f"-DFTQ_D={_d}"]))
+
+
+def _nvcc() -> str:
+    for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: cannot build libftq_b200.so")
+
+
+def _sources_mtime() -> float:
+    m = os.path.getmtime(os.path.join(PKG_DIR, "..", "include", "ftq_b200.h"))
+    for f in os.listdir(CSRC):
+        m = max(m, os.path.getmtime(os.path.join(CSRC, f)))
+    return m
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile and link the library if it is missing or older than its sources."""
+    if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _sources_mtime():
+        return LIB_PATH
+    nvcc = _nvcc()
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    extra = ["-Xptxas", "-v"] if verbose else []
+
+    def compile_one(unit):
+        src, tag, defs = unit
+        obj = os.path.join(OBJ_DIR, f"{tag}.o")
+        cmd = [nvcc, *NVCC_FLAGS, *extra, *defs, "-c", os.path.join(CSRC, src), "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src} {defs}:\n{r.stdout}\n{r.stderr}")
+        if verbose:
+            sys.stderr.write(r.stderr)
+        return obj
+
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        objs = list(ex.map(compile_one, UNITS))
+    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcudart"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true", help="print ptxas register/spill report")
+    a = ap.parse_args()
+    print(build(force=a.force, verbose=a.verbose))

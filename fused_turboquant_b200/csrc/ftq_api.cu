@@ -1,0 +1,586 @@
+// C ABI of libftq_b200.so: argument checking, table packing and kernel dispatch.
+// Every entry point is declared (with the reference interface it replaces) in
+// include/ftq_b200.h.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/ftq_b200.h"
+#include "ftq_dense.cuh"
+#include "ftq_launch.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(FTQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool dim_ok(int d) { return d == 64 || d == 128 || d == 256; }
+bool bits_ok(int b) { return b >= 2 && b <= 4; }
+bool dtype_ok(int t) { return t == FTQ_F32 || t == FTQ_F16 || t == FTQ_BF16; }
+size_t dtype_size(int t) { return t == FTQ_F32 ? 4 : 2; }
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// signs must be exactly +-1: the kernels flip the sign bit instead of multiplying.
+int pack_signs(const float* signs_host, int d, ftq::SignBits* out) {
+    memset(out, 0, sizeof(*out));
+    if (!signs_host) return FTQ_OK;
+    for (int i = 0; i < d; i++) {
+        const float s = signs_host[i];
+        if (s == -1.0f) out->w[i >> 5] |= 1u << (i & 31);
+        else if (s != 1.0f) return fail(FTQ_ERR_INVALID, "signs[%d] = %g is not +1 or -1", i, s);
+    }
+    return FTQ_OK;
+}
+
+int pack_levels(const float* levels_host, int bits, ftq::Codebook* out) {
+    if (!levels_host) return fail(FTQ_ERR_INVALID, "levels table is NULL");
+    memset(out, 0, sizeof(*out));
+    for (int i = 0; i < (1 << bits); i++) out->v[i] = levels_host[i];
+    return FTQ_OK;
+}
+
+float rsqrt_dim(int d) { return static_cast<float>(std::pow(static_cast<double>(d), -0.5)); }
+
+int make_encode_tables(int d, int bits, const float* signs_host, const float* boundaries_host,
+                       ftq::EncodeTables* tab) {
+    if (!boundaries_host) return fail(FTQ_ERR_INVALID, "boundaries table is NULL");
+    const int nb = (1 << bits) + 1;
+    for (int i = 1; i < nb; i++)
+        if (!(boundaries_host[i - 1] <= boundaries_host[i]))
+            return fail(FTQ_ERR_INVALID, "boundaries must be ascending");
+    memset(tab, 0, sizeof(*tab));
+    const int rc = pack_signs(signs_host, d, &tab->signs);
+    if (rc) return rc;
+    // code = clamp(#{b < x} - 1, 0, 2^bits - 1) = #{interior boundaries < x}
+    for (int j = 1; j < nb - 1; j++) tab->bounds[j - 1] = boundaries_host[j];
+    tab->rsqrt_d = rsqrt_dim(d);
+    return FTQ_OK;
+}
+
+cudaError_t dispatch_encode(int d, int bits, int dtype, const ftq::EncodeSource& src,
+                            const ftq::EncodeSink& sink, const ftq::EncodeTables& tab,
+                            int64_t n_vec, int n_layers, cudaStream_t st) {
+    switch (d) {
+        case 64: return ftq::launch_encode_d64(bits, dtype, src, sink, tab, n_vec, n_layers, st);
+        case 128: return ftq::launch_encode_d128(bits, dtype, src, sink, tab, n_vec, n_layers, st);
+        case 256: return ftq::launch_encode_d256(bits, dtype, src, sink, tab, n_vec, n_layers, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+struct ChunkPlan {
+    int chunk_tokens, n_chunks, n_hpass;
+};
+
+// Split the context so that the grid fills the GPU a few times over.
+ChunkPlan plan_chunks(int B, int Hq, int Hkv, int d, int max_seq_len, int n_layers) {
+    const int gh = 64 / (d / 8);
+    const int group = Hq / Hkv;
+    ChunkPlan pl;
+    pl.n_hpass = (group + gh - 1) / gh;
+    const int tile = ftq::kTilePages * ftq::kPageTokens;
+    const int64_t units = static_cast<int64_t>(B) * Hkv * pl.n_hpass * n_layers;
+    const int64_t target = static_cast<int64_t>(ftq::sm_count()) * 2 * 4;
+    const int max_tiles = max_seq_len > 0 ? (max_seq_len + tile - 1) / tile : 1;
+    int64_t want = (target + units - 1) / (units > 0 ? units : 1);
+    if (want < 1) want = 1;
+    if (want > max_tiles) want = max_tiles;
+    const int tiles_per_chunk = static_cast<int>((max_tiles + want - 1) / want);
+    pl.chunk_tokens = tiles_per_chunk * tile;
+    pl.n_chunks = (max_tiles + tiles_per_chunk - 1) / tiles_per_chunk;
+    return pl;
+}
+
+size_t partial_bytes(const ChunkPlan& pl, int B, int Hq, int d, int n_layers) {
+    return static_cast<size_t>(n_layers) * B * Hq * pl.n_chunks * (d + 4) * sizeof(float);
+}
+
+cudaError_t dispatch_split(int d, int bk, int bv, bool paged, const ftq::AttnParams& p, int n_lb,
+                           cudaStream_t st) {
+    switch (d) {
+        case 64: return ftq::launch_attn_split_d64(bk, bv, paged, p, n_lb, st);
+        case 128: return ftq::launch_attn_split_d128(bk, bv, paged, p, n_lb, st);
+        case 256: return ftq::launch_attn_split_d256(bk, bv, paged, p, n_lb, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t dispatch_merge(int d, int out_dtype, const float* partials, void* out,
+                           const int32_t* seq_lens, int S, int B, int Hq, const ChunkPlan& pl,
+                           int64_t n_vec, const ftq::SignBits& signs, cudaStream_t st) {
+    const float r = rsqrt_dim(d);
+    switch (d) {
+        case 64:
+            return ftq::launch_attn_merge_d64(out_dtype, partials, out, seq_lens, S, B, Hq,
+                                              pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, st);
+        case 128:
+            return ftq::launch_attn_merge_d128(out_dtype, partials, out, seq_lens, S, B, Hq,
+                                               pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, st);
+        case 256:
+            return ftq::launch_attn_merge_d256(out_dtype, partials, out, seq_lens, S, B, Hq,
+                                               pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+unsigned grid_for(int64_t n_vec, int vec_per_cta) {
+    const int64_t want = (n_vec + vec_per_cta - 1) / vec_per_cta;
+    const int64_t cap = static_cast<int64_t>(ftq::sm_count()) * 8;
+    return static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+// ---- v0 gather: one thread per output 32-bit word (codes) or norm
+__global__ void v0_gather_kernel(const uint8_t* __restrict__ kv_cache, int64_t num_blocks,
+                                 int block_size, int Hkv, int elem_size, int kv_type, int pd,
+                                 const int32_t* __restrict__ block_tables, int max_blocks,
+                                 const int32_t* __restrict__ seq_lens, int B, int max_seq_len,
+                                 uint8_t* __restrict__ out_codes, float* __restrict__ out_norms) {
+    const int wpt = pd / 4 + 1;  // words per token-head: codes then the norm
+    const int64_t total = static_cast<int64_t>(B) * Hkv * max_seq_len * wpt;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int w = static_cast<int>(i % wpt);
+        const int64_t th = i / wpt;  // (b, h, pos)
+        const int pos = static_cast<int>(th % max_seq_len);
+        const int h = static_cast<int>((th / max_seq_len) % Hkv);
+        const int b = static_cast<int>(th / (static_cast<int64_t>(max_seq_len) * Hkv));
+        uint32_t val = 0;
+        if (pos < seq_lens[b]) {
+            const int64_t blk = block_tables[static_cast<int64_t>(b) * max_blocks + pos / block_size];
+            const int off = pos % block_size;
+            const uint8_t* slot = kv_cache +
+                ((((static_cast<int64_t>(kv_type) * num_blocks + blk) * block_size + off) * Hkv + h) *
+                 elem_size);
+            val = *reinterpret_cast<const uint32_t*>(slot + 4 * w);
+        }
+        if (w < pd / 4) reinterpret_cast<uint32_t*>(out_codes + th * pd)[w] = val;
+        else out_norms[th] = __uint_as_float(val);
+    }
+}
+
+}  // namespace
+
+namespace ftq {
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+}  // namespace ftq
+
+extern "C" {
+
+int ftq_version(void) { return 100; }
+
+const char* ftq_last_error(void) { return g_err; }
+
+int ftq_packed_dim(int head_dim, int bits) {
+    if (head_dim <= 0 || head_dim % 8 || !bits_ok(bits)) return -1;
+    return head_dim * bits / 8;
+}
+
+int64_t ftq_page_bytes(int head_dim, int bits_k, int bits_v) {
+    if (!dim_ok(head_dim) || !bits_ok(bits_k) || !bits_ok(bits_v)) return -1;
+    return static_cast<int64_t>(FTQ_PAGE_TOKENS) *
+           (ftq::packed_dim(head_dim, bits_k) + ftq::packed_dim(head_dim, bits_v) + 4);
+}
+
+int ftq_encode(const void* x, int dtype, int64_t n_vec, int head_dim, int64_t row_stride, int bits,
+               const float* signs_host, const float* boundaries_host, uint8_t* packed,
+               uint16_t* norms_f16, void* stream) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!bits_ok(bits)) return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got %d", bits);
+    if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
+    if (n_vec < 0) return fail(FTQ_ERR_INVALID, "n_vec < 0");
+    if (n_vec == 0) return FTQ_OK;
+    if (!x || !packed || !norms_f16) return fail(FTQ_ERR_INVALID, "NULL tensor pointer");
+    if (row_stride < head_dim) return fail(FTQ_ERR_INVALID, "row_stride < head_dim");
+    if (!aligned(x, 16) || (row_stride * dtype_size(dtype)) % 16)
+        return fail(FTQ_ERR_INVALID, "input rows must be 16-byte aligned");
+    if (!aligned(packed, 4) || !aligned(norms_f16, 2))
+        return fail(FTQ_ERR_INVALID, "outputs must be 4-byte (codes) / 2-byte (norms) aligned");
+    ftq::EncodeTables tab;
+    int rc = make_encode_tables(head_dim, bits, signs_host, boundaries_host, &tab);
+    if (rc) return rc;
+    ftq::EncodeSource src{x, 1, row_stride, 0, 0};
+    ftq::EncodeSink sink{};
+    sink.mode = ftq::kSinkFlat;
+    sink.codes = packed;
+    sink.norms = norms_f16;
+    sink.Hkv = 1;
+    cudaError_t e = dispatch_encode(head_dim, bits, dtype, src, sink, tab, n_vec, 1,
+                                    static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_encode launch");
+}
+
+int ftq_decode_dense(const uint8_t* packed, const void* norms, int norms_dtype, int64_t n_vec,
+                     int head_dim, int bits, const float* levels_host, const float* signs_host,
+                     float* out, void* stream) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!bits_ok(bits)) return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got %d", bits);
+    if (norms_dtype != FTQ_F16 && norms_dtype != FTQ_F32)
+        return fail(FTQ_ERR_INVALID, "norms must be fp16 or fp32");
+    if (n_vec == 0) return FTQ_OK;
+    if (!packed || !norms || !out || n_vec < 0) return fail(FTQ_ERR_INVALID, "bad tensor argument");
+    if (!aligned(packed, 4) || !aligned(out, 4)) return fail(FTQ_ERR_INVALID, "misaligned tensor");
+    ftq::Codebook lv;
+    ftq::SignBits sg;
+    int rc = pack_levels(levels_host, bits, &lv);
+    if (rc) return rc;
+    rc = pack_signs(signs_host, head_dim, &sg);
+    if (rc) return rc;
+    const float r = rsqrt_dim(head_dim);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = grid_for(n_vec, 32);
+#define FTQ_DD(DD, BB)                                                                          \
+    if (norms_dtype == FTQ_F16)                                                                 \
+        ftq::decode_dense_kernel<DD, BB, __half><<<grid, 256, 0, st>>>(                          \
+            packed, static_cast<const __half*>(norms), out, lv, sg, r, n_vec);                  \
+    else                                                                                        \
+        ftq::decode_dense_kernel<DD, BB, float><<<grid, 256, 0, st>>>(                           \
+            packed, static_cast<const float*>(norms), out, lv, sg, r, n_vec);
+#define FTQ_DB(DD)                                                                              \
+    switch (bits) {                                                                             \
+        case 2: FTQ_DD(DD, 2) break;                                                            \
+        case 3: FTQ_DD(DD, 3) break;                                                            \
+        case 4: FTQ_DD(DD, 4) break;                                                            \
+    }
+    switch (head_dim) {
+        case 64: FTQ_DB(64) break;
+        case 128: FTQ_DB(128) break;
+        case 256: FTQ_DB(256) break;
+    }
+#undef FTQ_DB
+#undef FTQ_DD
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_decode_dense launch");
+}
+
+int ftq_rht(const void* x, void* y, int dtype, int64_t n_vec, int head_dim,
+            const float* signs_host, int inverse, void* stream) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
+    if (n_vec == 0) return FTQ_OK;
+    if (!x || !y || n_vec < 0) return fail(FTQ_ERR_INVALID, "bad tensor argument");
+    if (!aligned(x, 16) || !aligned(y, 4)) return fail(FTQ_ERR_INVALID, "misaligned tensor");
+    ftq::SignBits sg;
+    int rc = pack_signs(signs_host, head_dim, &sg);
+    if (rc) return rc;
+    const float r = rsqrt_dim(head_dim);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = grid_for(n_vec, 32);
+#define FTQ_RT(DD)                                                                              \
+    switch (dtype) {                                                                            \
+        case FTQ_F32:                                                                           \
+            ftq::rht_kernel<DD, float><<<grid, 256, 0, st>>>(                                    \
+                static_cast<const float*>(x), static_cast<float*>(y), sg, r, inverse, n_vec);   \
+            break;                                                                              \
+        case FTQ_F16:                                                                           \
+            ftq::rht_kernel<DD, __half><<<grid, 256, 0, st>>>(                                   \
+                static_cast<const __half*>(x), static_cast<__half*>(y), sg, r, inverse, n_vec); \
+            break;                                                                              \
+        case FTQ_BF16:                                                                          \
+            ftq::rht_kernel<DD, __nv_bfloat16><<<grid, 256, 0, st>>>(                            \
+                static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), sg, r,    \
+                inverse, n_vec);                                                                \
+            break;                                                                              \
+    }
+    switch (head_dim) {
+        case 64: FTQ_RT(64) break;
+        case 128: FTQ_RT(128) break;
+        case 256: FTQ_RT(256) break;
+    }
+#undef FTQ_RT
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_rht launch");
+}
+
+int ftq_qk_scores(const float* q_rot, const uint8_t* k_codes, const void* k_norms, int norms_dtype,
+                  const float* levels_host, float scale, int bits, int B, int Hq, int Hkv,
+                  int q_len, int S, int head_dim, float* out, void* stream) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!bits_ok(bits)) return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got %d", bits);
+    if (norms_dtype != FTQ_F16 && norms_dtype != FTQ_F32)
+        return fail(FTQ_ERR_INVALID, "norms must be fp16 or fp32");
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || q_len <= 0 || S < 0)
+        return fail(FTQ_ERR_INVALID, "bad shape B=%d Hq=%d Hkv=%d q_len=%d S=%d", B, Hq, Hkv, q_len, S);
+    if (B == 0 || S == 0) return FTQ_OK;
+    if (!q_rot || !k_codes || !k_norms || !out) return fail(FTQ_ERR_INVALID, "NULL tensor pointer");
+    if (!aligned(k_codes, 4)) return fail(FTQ_ERR_INVALID, "k_codes must be 4-byte aligned");
+    ftq::Codebook lv;
+    int rc = pack_levels(levels_host, bits, &lv);
+    if (rc) return rc;
+    const int rows = (Hq / Hkv) * q_len;
+    const size_t smem = (ftq::kMaxLevels + static_cast<size_t>(rows) * head_dim) * sizeof(float);
+    if (smem > 48 * 1024)
+        return fail(FTQ_ERR_UNSUPPORTED, "group*q_len*head_dim = %d exceeds the 48 KB query tile",
+                    rows * head_dim);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const dim3 grid((S + 63) / 64, B * Hkv);
+#define FTQ_QK(DD, BB)                                                                          \
+    if (norms_dtype == FTQ_F16)                                                                 \
+        ftq::qk_scores_kernel<DD, BB, __half><<<grid, 128, smem, st>>>(                          \
+            q_rot, k_codes, static_cast<const __half*>(k_norms), out, lv, scale, Hq, Hkv, q_len, S); \
+    else                                                                                        \
+        ftq::qk_scores_kernel<DD, BB, float><<<grid, 128, smem, st>>>(                           \
+            q_rot, k_codes, static_cast<const float*>(k_norms), out, lv, scale, Hq, Hkv, q_len, S);
+#define FTQ_QB(DD)                                                                              \
+    switch (bits) {                                                                             \
+        case 2: FTQ_QK(DD, 2) break;                                                            \
+        case 3: FTQ_QK(DD, 3) break;                                                            \
+        case 4: FTQ_QK(DD, 4) break;                                                            \
+    }
+    switch (head_dim) {
+        case 64: FTQ_QB(64) break;
+        case 128: FTQ_QB(128) break;
+        case 256: FTQ_QB(256) break;
+    }
+#undef FTQ_QB
+#undef FTQ_QK
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_qk_scores launch");
+}
+
+size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_seq_len,
+                                  int n_layers) {
+    if (!dim_ok(head_dim) || B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_layers <= 0) return 0;
+    const ChunkPlan pl = plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
+    return partial_bytes(pl, B, Hq, head_dim, n_layers);
+}
+
+static int check_attn_common(int B, int Hq, int Hkv, int head_dim, int bits_k, int bits_v,
+                             int q_dtype, int out_dtype) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!bits_ok(bits_k) || !bits_ok(bits_v))
+        return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got K=%d V=%d", bits_k, bits_v);
+    if (!dtype_ok(q_dtype) || !dtype_ok(out_dtype)) return fail(FTQ_ERR_INVALID, "bad dtype");
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv)
+        return fail(FTQ_ERR_INVALID, "bad shape B=%d Hq=%d Hkv=%d", B, Hq, Hkv);
+    return FTQ_OK;
+}
+
+int ftq_flash_decode(const void* q, int q_dtype, int q_is_rotated, const uint8_t* k_codes,
+                     const uint16_t* k_norms, const uint8_t* v_codes, const uint16_t* v_norms,
+                     const float* levels_k_host, const float* levels_v_host,
+                     const float* signs_host, float scale, int bits_k, int bits_v,
+                     const int32_t* seq_lens, int B, int Hq, int Hkv, int S, int head_dim,
+                     void* out, int out_dtype, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+    int rc = check_attn_common(B, Hq, Hkv, head_dim, bits_k, bits_v, q_dtype, out_dtype);
+    if (rc) return rc;
+    if (S < 0) return fail(FTQ_ERR_INVALID, "S < 0");
+    if (B == 0) return FTQ_OK;
+    if (!q || !out) return fail(FTQ_ERR_INVALID, "NULL q / out");
+    if (S > 0 && (!k_codes || !k_norms || !v_codes || !v_norms))
+        return fail(FTQ_ERR_INVALID, "NULL K/V tensor");
+    if (!aligned(q, 16) || !aligned(out, 4)) return fail(FTQ_ERR_INVALID, "q must be 16-byte aligned");
+    if (!aligned(k_codes, 4) || !aligned(v_codes, 4) || !aligned(k_norms, 2) || !aligned(v_norms, 2))
+        return fail(FTQ_ERR_INVALID, "misaligned K/V tensor");
+    const ChunkPlan pl = plan_chunks(B, Hq, Hkv, head_dim, S, 1);
+    const size_t need = partial_bytes(pl, B, Hq, head_dim, 1);
+    if (!workspace || workspace_bytes < need)
+        return fail(FTQ_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", need, workspace_bytes);
+    if (!aligned(workspace, 16)) return fail(FTQ_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+    ftq::AttnParams p{};
+    rc = pack_levels(levels_k_host, bits_k, &p.lk);
+    if (rc) return rc;
+    rc = pack_levels(levels_v_host, bits_v, &p.lv);
+    if (rc) return rc;
+    rc = pack_signs(signs_host, head_dim, &p.signs);
+    if (rc) return rc;
+    const int pdk = ftq::packed_dim(head_dim, bits_k), pdv = ftq::packed_dim(head_dim, bits_v);
+    p.q = q;
+    p.k_codes = k_codes; p.k_norms = k_norms; p.v_codes = v_codes; p.v_norms = v_norms;
+    p.S = S; p.seq_lens = seq_lens; p.B = B; p.Hq = Hq; p.Hkv = Hkv;
+    p.scale = scale; p.q_is_rotated = q_is_rotated; p.q_dtype = q_dtype;
+    p.cp16 = aligned(k_codes, 16) && aligned(v_codes, 16) &&
+             (static_cast<int64_t>(S) * pdk) % 16 == 0 && (static_cast<int64_t>(S) * pdv) % 16 == 0;
+    p.chunk_tokens = pl.chunk_tokens; p.n_chunks = pl.n_chunks; p.n_hpass = pl.n_hpass;
+    p.partials = static_cast<float*>(workspace);
+    p.rsqrt_d = rsqrt_dim(head_dim);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = dispatch_split(head_dim, bits_k, bits_v, false, p, B, st);
+    if (e != cudaSuccess) return cuda_fail(e, "ftq_flash_decode split launch");
+    e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, S, B, Hq, pl,
+                       static_cast<int64_t>(B) * Hq, p.signs, st);
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_flash_decode merge launch");
+}
+
+int ftq_paged_store(const void* key, const void* value, int dtype, int64_t n_tokens, int Hkv,
+                    int head_dim, int64_t token_stride, int64_t head_stride, int bits_k,
+                    int bits_v, const float* signs_host, const float* boundaries_k_host,
+                    const float* boundaries_v_host, uint8_t* pool, int64_t num_blocks,
+                    const int64_t* slot_mapping, int n_layers, int64_t kv_layer_stride,
+                    int64_t pool_layer_stride, void* stream) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!bits_ok(bits_k) || !bits_ok(bits_v))
+        return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got K=%d V=%d", bits_k, bits_v);
+    if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
+    if (n_tokens < 0 || Hkv <= 0 || n_layers <= 0 || num_blocks < 0)
+        return fail(FTQ_ERR_INVALID, "bad shape");
+    if (n_tokens == 0) return FTQ_OK;
+    if (!key || !value || !pool || !slot_mapping) return fail(FTQ_ERR_INVALID, "NULL tensor pointer");
+    const size_t es = dtype_size(dtype);
+    if (!aligned(key, 16) || !aligned(value, 16) || (token_stride * es) % 16 ||
+        (head_stride * es) % 16 || (kv_layer_stride * es) % 16)
+        return fail(FTQ_ERR_INVALID, "key/value rows must be 16-byte aligned");
+    if (!aligned(pool, 16) || pool_layer_stride % 16)
+        return fail(FTQ_ERR_INVALID, "pool must be 16-byte aligned");
+    const int pdk = ftq::packed_dim(head_dim, bits_k), pdv = ftq::packed_dim(head_dim, bits_v);
+    const int64_t page = ftq_page_bytes(head_dim, bits_k, bits_v);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int which = 0; which < 2; which++) {
+        ftq::EncodeTables tab;
+        int rc = make_encode_tables(head_dim, which ? bits_v : bits_k, signs_host,
+                                    which ? boundaries_v_host : boundaries_k_host, &tab);
+        if (rc) return rc;
+        ftq::EncodeSource src{which ? value : key, Hkv, token_stride, head_stride, kv_layer_stride};
+        ftq::EncodeSink sink{};
+        sink.mode = ftq::kSinkPaged;
+        sink.codes = pool;
+        sink.slot_mapping = slot_mapping;
+        sink.Hkv = Hkv;
+        sink.page_bytes = page;
+        sink.codes_off = which ? FTQ_PAGE_TOKENS * pdk + 2 * FTQ_PAGE_TOKENS : 0;
+        sink.norms_off = which ? FTQ_PAGE_TOKENS * (pdk + pdv) + 2 * FTQ_PAGE_TOKENS
+                               : FTQ_PAGE_TOKENS * pdk;
+        sink.layer_stride = pool_layer_stride;
+        cudaError_t e = dispatch_encode(head_dim, which ? bits_v : bits_k, dtype, src, sink, tab,
+                                        n_tokens * Hkv, n_layers, st);
+        if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_store launch");
+    }
+    return FTQ_OK;
+}
+
+int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
+                          const uint8_t* pool, int64_t num_blocks, int64_t pool_layer_stride,
+                          int n_layers, const int32_t* block_table, int max_blocks,
+                          const int32_t* seq_lens, int max_seq_len, int B, int Hq, int Hkv,
+                          int head_dim, int bits_k, int bits_v, const float* levels_k_host,
+                          const float* levels_v_host, const float* signs_host, float scale,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_attn_common(B, Hq, Hkv, head_dim, bits_k, bits_v, q_dtype, out_dtype);
+    if (rc) return rc;
+    if (n_layers <= 0 || max_blocks < 0 || max_seq_len < 0 || num_blocks < 0)
+        return fail(FTQ_ERR_INVALID, "bad shape");
+    if (B == 0) return FTQ_OK;
+    if (!q || !out || !pool || !block_table || !seq_lens)
+        return fail(FTQ_ERR_INVALID, "NULL tensor pointer");
+    if (static_cast<int64_t>(max_blocks) * FTQ_PAGE_TOKENS < max_seq_len)
+        return fail(FTQ_ERR_INVALID, "block_table too narrow: %d blocks < max_seq_len %d",
+                    max_blocks, max_seq_len);
+    if (!aligned(q, 16) || !aligned(out, 4) || !aligned(pool, 16) || pool_layer_stride % 16)
+        return fail(FTQ_ERR_INVALID, "q and pool must be 16-byte aligned");
+    const ChunkPlan pl = plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
+    const size_t need = partial_bytes(pl, B, Hq, head_dim, n_layers);
+    if (!workspace || workspace_bytes < need)
+        return fail(FTQ_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", need, workspace_bytes);
+    if (!aligned(workspace, 16)) return fail(FTQ_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+    ftq::AttnParams p{};
+    rc = pack_levels(levels_k_host, bits_k, &p.lk);
+    if (rc) return rc;
+    rc = pack_levels(levels_v_host, bits_v, &p.lv);
+    if (rc) return rc;
+    rc = pack_signs(signs_host, head_dim, &p.signs);
+    if (rc) return rc;
+    p.q = q;
+    p.pool = pool; p.pool_layer_stride = pool_layer_stride;
+    p.block_table = block_table; p.max_blocks = max_blocks;
+    p.S = 0; p.seq_lens = seq_lens; p.B = B; p.Hq = Hq; p.Hkv = Hkv;
+    p.scale = scale; p.q_is_rotated = 0; p.q_dtype = q_dtype; p.cp16 = 1;
+    p.chunk_tokens = pl.chunk_tokens; p.n_chunks = pl.n_chunks; p.n_hpass = pl.n_hpass;
+    p.partials = static_cast<float*>(workspace);
+    p.rsqrt_d = rsqrt_dim(head_dim);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = dispatch_split(head_dim, bits_k, bits_v, true, p, n_layers * B, st);
+    if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn split launch");
+    e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, 0, B, Hq, pl,
+                       static_cast<int64_t>(n_layers) * B * Hq, p.signs, st);
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_paged_decode_attn merge launch");
+}
+
+int ftq_v0_store(const void* key, const void* value, int dtype, int64_t n_tokens, int Hkv,
+                 int head_dim, int64_t token_stride, int64_t head_stride, int bits_k, int bits_v,
+                 const float* signs_host, const float* boundaries_k_host,
+                 const float* boundaries_v_host, uint8_t* kv_cache, int64_t num_blocks,
+                 int block_size, int elem_size, const int64_t* slot_mapping, void* stream) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!bits_ok(bits_k) || !bits_ok(bits_v))
+        return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got K=%d V=%d", bits_k, bits_v);
+    if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
+    if (n_tokens < 0 || Hkv <= 0 || block_size <= 0 || num_blocks < 0)
+        return fail(FTQ_ERR_INVALID, "bad shape");
+    const int pdk = ftq::packed_dim(head_dim, bits_k), pdv = ftq::packed_dim(head_dim, bits_v);
+    if (elem_size < (pdk > pdv ? pdk : pdv) + 4 || elem_size % 4)
+        return fail(FTQ_ERR_INVALID, "elem_size %d too small for packed_dim + 4", elem_size);
+    if (n_tokens == 0) return FTQ_OK;
+    if (!key || !value || !kv_cache || !slot_mapping) return fail(FTQ_ERR_INVALID, "NULL tensor pointer");
+    const size_t es = dtype_size(dtype);
+    if (!aligned(key, 16) || !aligned(value, 16) || (token_stride * es) % 16 || (head_stride * es) % 16)
+        return fail(FTQ_ERR_INVALID, "key/value rows must be 16-byte aligned");
+    if (!aligned(kv_cache, 4)) return fail(FTQ_ERR_INVALID, "kv_cache must be 4-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int which = 0; which < 2; which++) {
+        ftq::EncodeTables tab;
+        int rc = make_encode_tables(head_dim, which ? bits_v : bits_k, signs_host,
+                                    which ? boundaries_v_host : boundaries_k_host, &tab);
+        if (rc) return rc;
+        ftq::EncodeSource src{which ? value : key, Hkv, token_stride, head_stride, 0};
+        ftq::EncodeSink sink{};
+        sink.mode = ftq::kSinkV0;
+        sink.codes = kv_cache;
+        sink.slot_mapping = slot_mapping;
+        sink.Hkv = Hkv;
+        sink.block_size = block_size;
+        sink.elem_size = elem_size;
+        sink.plane_off = static_cast<int64_t>(which) * num_blocks * block_size * Hkv * elem_size;
+        cudaError_t e = dispatch_encode(head_dim, which ? bits_v : bits_k, dtype, src, sink, tab,
+                                        n_tokens * Hkv, 1, st);
+        if (e != cudaSuccess) return cuda_fail(e, "ftq_v0_store launch");
+    }
+    return FTQ_OK;
+}
+
+int ftq_v0_gather(const uint8_t* kv_cache, int64_t num_blocks, int block_size, int Hkv,
+                  int elem_size, int kv_type, int packed_dim, const int32_t* block_tables,
+                  int max_blocks, const int32_t* seq_lens, int B, int max_seq_len,
+                  uint8_t* out_codes, float* out_norms, void* stream) {
+    if (B < 0 || Hkv <= 0 || block_size <= 0 || max_seq_len < 0 || packed_dim <= 0 ||
+        packed_dim % 4 || elem_size < packed_dim + 4 || elem_size % 4 || (kv_type != 0 && kv_type != 1))
+        return fail(FTQ_ERR_INVALID, "bad shape");
+    if (B == 0 || max_seq_len == 0) return FTQ_OK;
+    if (!kv_cache || !block_tables || !seq_lens || !out_codes || !out_norms)
+        return fail(FTQ_ERR_INVALID, "NULL tensor pointer");
+    if (!aligned(kv_cache, 4) || !aligned(out_codes, 4))
+        return fail(FTQ_ERR_INVALID, "kv_cache / out_codes must be 4-byte aligned");
+    const int64_t total = static_cast<int64_t>(B) * Hkv * max_seq_len * (packed_dim / 4 + 1);
+    const int64_t want = (total + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(ftq::sm_count()) * 16;
+    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+    v0_gather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        kv_cache, num_blocks, block_size, Hkv, elem_size, kv_type, packed_dim, block_tables,
+        max_blocks, seq_lens, B, max_seq_len, out_codes, out_norms);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_v0_gather launch");
+}
+
+}  // extern "C"

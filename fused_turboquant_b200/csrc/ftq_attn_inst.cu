@@ -1,0 +1,82 @@
+// Instantiates the split-KV decode attention kernels for one head_dim (FTQ_D).
+#include "ftq_launch.h"
+
+#ifndef FTQ_D
+#error "compile with -DFTQ_D=64, 128 or 256"
+#endif
+#define FTQ_CAT2(a, b) a##b
+#define FTQ_CAT(a, b) FTQ_CAT2(a, b)
+
+namespace ftq {
+
+template <int BK, int BV, bool PAGED>
+static cudaError_t run_split(const AttnParams& p, int n_lb, cudaStream_t stream) {
+    constexpr int D = FTQ_D;
+    constexpr int GH = AttnCfg<D>::GH;
+    constexpr int page = kPageTokens * (packed_dim(D, BK) + packed_dim(D, BV) + 4);
+    constexpr int merge = 4 * GH * (D + 2) * 4;
+    constexpr int ring = ((2 * kTilePages * page > merge ? 2 * kTilePages * page : merge) + 15) / 16 * 16;
+    constexpr int smem = ring + (GH * D + 2 * kMaxLevels) * 4;
+    static_assert(smem <= 48 * 1024, "shared memory budget");
+    const dim3 grid(p.n_chunks, p.Hkv * p.n_hpass, n_lb);
+    attn_split_kernel<D, BK, BV, PAGED><<<grid, kAttnThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int BK, bool PAGED>
+static cudaError_t by_bv(int bv, const AttnParams& p, int n_lb, cudaStream_t stream) {
+    switch (bv) {
+        case 2: return run_split<BK, 2, PAGED>(p, n_lb, stream);
+        case 3: return run_split<BK, 3, PAGED>(p, n_lb, stream);
+        case 4: return run_split<BK, 4, PAGED>(p, n_lb, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <bool PAGED>
+static cudaError_t by_bk(int bk, int bv, const AttnParams& p, int n_lb, cudaStream_t stream) {
+    switch (bk) {
+        case 2: return by_bv<2, PAGED>(bv, p, n_lb, stream);
+        case 3: return by_bv<3, PAGED>(bv, p, n_lb, stream);
+        case 4: return by_bv<4, PAGED>(bv, p, n_lb, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t FTQ_CAT(launch_attn_split_d, FTQ_D)(int bits_k, int bits_v, bool paged,
+                                                const AttnParams& p, int n_lb,
+                                                cudaStream_t stream) {
+    return paged ? by_bk<true>(bits_k, bits_v, p, n_lb, stream)
+                 : by_bk<false>(bits_k, bits_v, p, n_lb, stream);
+}
+
+cudaError_t FTQ_CAT(launch_attn_merge_d, FTQ_D)(int out_dtype, const float* partials, void* out,
+                                                const int32_t* seq_lens, int S, int B, int Hq,
+                                                int n_chunks, int chunk_tokens, int64_t n_vec,
+                                                const SignBits& signs, float rsqrt_d,
+                                                cudaStream_t stream) {
+    constexpr int D = FTQ_D;
+    const unsigned grid = static_cast<unsigned>((n_vec + 15) / 16);
+    switch (out_dtype) {
+        case kF32:
+            attn_merge_kernel<D, float><<<grid, 128, 0, stream>>>(
+                partials, static_cast<float*>(out), seq_lens, S, B, Hq, n_chunks, chunk_tokens,
+                n_vec, signs, rsqrt_d);
+            break;
+        case kF16:
+            attn_merge_kernel<D, __half><<<grid, 128, 0, stream>>>(
+                partials, static_cast<__half*>(out), seq_lens, S, B, Hq, n_chunks, chunk_tokens,
+                n_vec, signs, rsqrt_d);
+            break;
+        case kBF16:
+            attn_merge_kernel<D, __nv_bfloat16><<<grid, 128, 0, stream>>>(
+                partials, static_cast<__nv_bfloat16*>(out), seq_lens, S, B, Hq, n_chunks,
+                chunk_tokens, n_vec, signs, rsqrt_d);
+            break;
+        default:
+            return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace ftq

@@ -1,0 +1,204 @@
+// Fused KV encode for sm_100a: sign flip -> Hadamard butterfly -> L2 norm ->
+// normalise -> Lloyd-Max bucketise -> bit-pack -> store (contiguous, paged pool
+// or the reference's v0 slot layout), one pass over the input, no scratch memory.
+//
+// The arithmetic restates TurboQuantMSE._encode_unfused of the reference
+// (src/fused_turboquant/core/quantizer.py:137-160) operation for operation, so
+// that the packed codes and the fp16 norms come out bit-identical:
+//   y      = fwht(x * signs) * fp32(D^-1/2)            core/hadamard.py:38-48,90
+//   norm   = sqrt(sum_l (sum_k y[l+8k]^2))             the order torch.norm uses on CPU:
+//                                                      8 strided running sums, then left to right
+//   n      = y / (norm + 1e-8)                         IEEE division
+//   code   = clamp(#{boundaries < n} - 1, 0, 2^b-1)    core/lloyd_max.py:131-132
+//   packed = pack_{nibbles,3bit,2bit}(code)            core/packing.py:14-103
+//   norm16 = fp16(norm), round to nearest even
+// No fused multiply-add may touch y or the sum of squares: every add, multiply,
+// divide and square root below is an explicitly rounded intrinsic.
+#pragma once
+
+#include "ftq_common.cuh"
+
+namespace ftq {
+
+struct EncodeTables {
+    SignBits signs;
+    float bounds[kMaxLevels - 1];  // interior boundaries b[1] .. b[2^bits - 1]
+    float rsqrt_d;                 // fp32(D ** -0.5)
+};
+
+// Where the vectors come from: vector v = (outer, inner) with inner < n_inner.
+struct EncodeSource {
+    const void* base;
+    int n_inner;           // vectors per outer index (Hkv for [tokens, Hkv, D]; 1 for flat rows)
+    int64_t outer_stride;  // elements
+    int64_t inner_stride;  // elements
+    int64_t layer_stride;  // elements, blockIdx.y advances by this
+};
+
+enum : int { kSinkFlat = 0, kSinkPaged = 1, kSinkV0 = 2 };
+
+// Where the codes and the norm of vector v go.
+struct EncodeSink {
+    int mode;
+    // flat: codes at codes + v * pd, norm (fp16) at norms + v
+    uint8_t* codes;
+    uint16_t* norms;
+    // paged pool / v0 layout: token = v / Hkv, head = v % Hkv, slot = slot_mapping[token]
+    const int64_t* slot_mapping;
+    int Hkv;
+    int64_t page_bytes;     // paged: bytes per (block, head) page
+    int codes_off;          // paged: offset of this tensor's codes inside the page
+    int norms_off;          // paged: offset of this tensor's fp16 norms inside the page
+    int block_size;         // v0: tokens per block
+    int elem_size;          // v0: bytes per (token, head) slot
+    int64_t plane_off;      // v0: byte offset of the K or V plane
+    int64_t layer_stride;   // bytes, blockIdx.y advances by this
+};
+
+// Transpose an 8-lane x (items per word) matrix of BITS-wide items: afterwards
+// lane j holds the items that had in-word position j, ordered by source lane.
+template <int BITS>
+__device__ __forceinline__ uint32_t octet_transpose_items(uint32_t w, int lane) {
+    constexpr uint32_t m0 = BITS == 4 ? 0x0F0F0F0Fu : BITS == 3 ? 0x001C71C7u : 0x33333333u;
+    constexpr uint32_t m1 = BITS == 4 ? 0x00FF00FFu : BITS == 3 ? 0x0003F03Fu : 0x0F0F0F0Fu;
+    constexpr uint32_t m2 = BITS == 4 ? 0x0000FFFFu : BITS == 3 ? 0x00000FFFu : 0x00FF00FFu;
+    constexpr int s0 = BITS, s1 = 2 * BITS, s2 = 4 * BITS;
+    uint32_t p = __shfl_xor_sync(0xffffffffu, w, 1);
+    w = (lane & 1) ? (((p >> s0) & m0) | (w & (m0 << s0))) : ((w & m0) | ((p & m0) << s0));
+    p = __shfl_xor_sync(0xffffffffu, w, 2);
+    w = (lane & 2) ? (((p >> s1) & m1) | (w & (m1 << s1))) : ((w & m1) | ((p & m1) << s1));
+    p = __shfl_xor_sync(0xffffffffu, w, 4);
+    w = (lane & 4) ? (((p >> s2) & m2) | (w & (m2 << s2))) : ((w & m2) | ((p & m2) << s2));
+    return w;
+}
+
+template <int D, int BITS, typename T>
+__global__ void __launch_bounds__(256)
+encode_kernel(EncodeSource src, EncodeSink sink, EncodeTables tab, int64_t n_vec) {
+    constexpr int E = D / kOctet;          // values per lane
+    constexpr int NCH = E / 8;             // 8-coordinate runs per lane
+    constexpr int PD = packed_dim(D, BITS);
+    constexpr int NLEV = 1 << BITS;
+    // words of packed items per lane before the transpose
+    constexpr int NW = BITS == 2 ? (E + 15) / 16 : E / 8;
+
+    const int lane = threadIdx.x & 31;
+    const int t = lane & 7;
+    const int sub = lane >> 3;  // which of the warp's 4 vectors
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+
+    const T* xbase = static_cast<const T*>(src.base) + blockIdx.y * src.layer_stride;
+    const int64_t sink_layer = blockIdx.y * sink.layer_stride;
+
+    // Per-lane sign masks in the load layout (same for every vector).
+    uint32_t sgn[E];
+#pragma unroll
+    for (int r = 0; r < E; r++) sgn[r] = sign_mask(tab.signs, load_coord(t, r));
+
+    for (int64_t base = warp * 4; base < n_vec; base += n_warps * 4) {
+        const int64_t v = base + sub;
+        const bool valid = v < n_vec;
+        const int64_t outer = valid ? v / src.n_inner : 0;
+        const int inner = valid ? static_cast<int>(v - outer * src.n_inner) : 0;
+        const T* row = xbase + outer * src.outer_stride + inner * src.inner_stride;
+
+        float y[E];
+#pragma unroll
+        for (int i = 0; i < NCH; i++) {
+            float tmp[8];
+            if (valid) {
+                load8<T>(row + 8 * (t + 8 * i), tmp);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; c++) tmp[c] = 0.f;
+            }
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                y[8 * i + c] = __uint_as_float(__float_as_uint(tmp[c]) ^ sgn[8 * i + c]);
+        }
+
+        octet_fwht<E>(y, lane);
+
+        // scale, then the 8-way strided sum of squares (lane l = running sum l)
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            y[k] = __fmul_rn(y[k], tab.rsqrt_d);
+            acc = __fadd_rn(acc, __fmul_rn(y[k], y[k]));
+        }
+        float s = __shfl_sync(0xffffffffu, acc, 0, 8);
+#pragma unroll
+        for (int l = 1; l < 8; l++) s = __fadd_rn(s, __shfl_sync(0xffffffffu, acc, l, 8));
+        const float norm = __fsqrt_rn(s);
+        const float denom = __fadd_rn(norm, 1e-8f);
+
+        // bucketise and pack this lane's codes (coordinates l + 8k)
+        uint32_t w[NW];
+#pragma unroll
+        for (int i = 0; i < NW; i++) w[i] = 0u;
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            const float nv = __fdiv_rn(y[k], denom);
+            uint32_t code = 0;
+#pragma unroll
+            for (int j = 0; j < NLEV - 1; j++) code += (tab.bounds[j] < nv) ? 1u : 0u;
+            if constexpr (BITS == 2) {
+                const int pos = ((k >> 1) & 7) | ((k & 1) << 3);
+                w[k >> 4] |= code << (2 * pos);
+            } else {
+                w[k >> 3] |= code << (BITS * (k & 7));
+            }
+        }
+
+        // destination of this vector
+        uint8_t* dst = nullptr;
+        bool store = valid;
+        if (sink.mode == kSinkFlat) {
+            dst = sink.codes + v * PD;
+        } else if (valid) {
+            const int64_t token = v / sink.Hkv;
+            const int head = static_cast<int>(v - token * sink.Hkv);
+            const int64_t slot = sink.slot_mapping[token];
+            if (slot < 0) {
+                store = false;
+            } else if (sink.mode == kSinkPaged) {
+                const int64_t blk = slot / kPageTokens;
+                const int off = static_cast<int>(slot - blk * kPageTokens);
+                uint8_t* page = sink.codes + sink_layer + (blk * sink.Hkv + head) * sink.page_bytes;
+                dst = page + sink.codes_off + off * PD;
+                if (t == 0)
+                    *reinterpret_cast<__half*>(page + sink.norms_off + 2 * off) =
+                        __float2half_rn(norm);
+            } else {
+                const int64_t blk = slot / sink.block_size;
+                const int64_t off = slot - blk * sink.block_size;
+                dst = sink.codes + sink.plane_off +
+                      ((blk * sink.block_size + off) * sink.Hkv + head) * sink.elem_size;
+                if (t == 0) *reinterpret_cast<float*>(dst + PD) = __half2float(__float2half_rn(norm));
+            }
+        }
+        if (sink.mode == kSinkFlat && valid && t == 0)
+            reinterpret_cast<__half*>(sink.norms)[v] = __float2half_rn(norm);
+
+        // transpose across the octet so that every lane owns whole output words
+#pragma unroll
+        for (int i = 0; i < NW; i++) {
+            const uint32_t o = octet_transpose_items<BITS>(w[i], lane);
+            if constexpr (BITS == 3) {
+                // lane j holds the 24-bit group j of row i; regroup 8 x 3 bytes into 6 words
+                const int g0 = (4 * t) / 3;
+                const uint32_t lo = __shfl_sync(0xffffffffu, o, g0, 8);
+                const uint32_t hi = __shfl_sync(0xffffffffu, o, g0 + 1, 8);
+                const uint64_t cat = (static_cast<uint64_t>(hi) << 24) | lo;
+                const uint32_t word = static_cast<uint32_t>(cat >> (8 * ((4 * t) % 3)));
+                if (store && t < 6) reinterpret_cast<uint32_t*>(dst + 24 * i)[t] = word;
+            } else {
+                const int widx = t + 8 * i;
+                if (store && widx < PD / 4) reinterpret_cast<uint32_t*>(dst)[widx] = o;
+            }
+        }
+    }
+}
+
+}  // namespace ftq

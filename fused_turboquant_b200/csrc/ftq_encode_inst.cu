@@ -1,0 +1,46 @@
+// Instantiates the fused encode kernel for one head_dim (FTQ_D).
+#include "ftq_launch.h"
+
+#ifndef FTQ_D
+#error "compile with -DFTQ_D=64, 128 or 256"
+#endif
+#define FTQ_CAT2(a, b) a##b
+#define FTQ_CAT(a, b) FTQ_CAT2(a, b)
+
+namespace ftq {
+
+template <int BITS, typename T>
+static cudaError_t run(const EncodeSource& src, const EncodeSink& sink, const EncodeTables& tab,
+                       int64_t n_vec, int n_layers, cudaStream_t stream) {
+    constexpr int threads = 256;                       // 8 warps, 32 vectors per CTA pass
+    const int64_t want = (n_vec + 31) / 32;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;  // persistent-style grid
+    const unsigned gx = static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
+    encode_kernel<FTQ_D, BITS, T><<<dim3(gx, n_layers), threads, 0, stream>>>(src, sink, tab, n_vec);
+    return cudaGetLastError();
+}
+
+template <int BITS>
+static cudaError_t by_dtype(int dtype, const EncodeSource& src, const EncodeSink& sink,
+                            const EncodeTables& tab, int64_t n_vec, int n_layers,
+                            cudaStream_t stream) {
+    switch (dtype) {
+        case kF32: return run<BITS, float>(src, sink, tab, n_vec, n_layers, stream);
+        case kF16: return run<BITS, __half>(src, sink, tab, n_vec, n_layers, stream);
+        case kBF16: return run<BITS, __nv_bfloat16>(src, sink, tab, n_vec, n_layers, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t FTQ_CAT(launch_encode_d, FTQ_D)(int bits, int dtype, const EncodeSource& src,
+                                            const EncodeSink& sink, const EncodeTables& tab,
+                                            int64_t n_vec, int n_layers, cudaStream_t stream) {
+    switch (bits) {
+        case 2: return by_dtype<2>(dtype, src, sink, tab, n_vec, n_layers, stream);
+        case 3: return by_dtype<3>(dtype, src, sink, tab, n_vec, n_layers, stream);
+        case 4: return by_dtype<4>(dtype, src, sink, tab, n_vec, n_layers, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace ftq

@@ -1,0 +1,214 @@
+/*
+ * ftq_b200.h -- C ABI of libftq_b200.so: fused-turboquant's KV encode and
+ * compressed-KV decode attention as hand-written CUDA for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *  - Every entry point returns 0 (FTQ_OK) or a negative ftq_status;
+ *    ftq_last_error() returns the message of the last failure on the calling thread.
+ *  - Pointers named *_host are host memory (small tables, read during the
+ *    call); every other pointer is device memory on the current device.
+ *  - No entry point allocates, frees or synchronises, except
+ *    where its comment says otherwise.  Work is enqueued on `stream`
+ *    (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *  - Tensors are dense row-major unless a stride argument says otherwise.
+ *  - head_dim must be 64, 128 or 256; bits must be 2, 3 or 4.
+ *  - Packed code formats are the reference's (core/packing.py:14-128):
+ *    4-bit: byte = code[2i] | code[2i+1] << 4; 2-bit: 4 codes per byte, LSB
+ *    first; 3-bit: 8 codes -> 24-bit little-endian stream.  Norms are IEEE fp16.
+ *
+ * Reference citations are paths inside the sudy-super/fused-turboquant project.
+ */
+#ifndef FTQ_B200_H
+#define FTQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    FTQ_OK = 0,
+    FTQ_ERR_INVALID = -1,     /* bad argument (shape, bits, alignment, NULL) */
+    FTQ_ERR_UNSUPPORTED = -2, /* valid request this build has no kernel for  */
+    FTQ_ERR_CUDA = -3,        /* a CUDA runtime call failed                  */
+    FTQ_ERR_WORKSPACE = -4    /* caller workspace missing or too small       */
+} ftq_status;
+
+typedef enum { FTQ_F32 = 0, FTQ_F16 = 1, FTQ_BF16 = 2 } ftq_dtype;
+
+/* Tokens per page of the paged KV pool (fixed). */
+#define FTQ_PAGE_TOKENS 16
+
+/* Library version (major*10000 + minor*100 + patch). */
+int ftq_version(void);
+
+/* Message of the last error raised on this thread ("" if none). */
+const char *ftq_last_error(void);
+
+/* Bytes of packed codes per vector: head_dim*bits/8; -1 if unsupported.
+ * Mirrors the packed_dim arithmetic of kernels/triton_encode.py:176-183. */
+int ftq_packed_dim(int head_dim, int bits);
+
+/* ------------------------------------------------------------------ encode */
+
+/*
+ * Fused encode: y = FWHT(x * signs) / sqrt(D); norm = ||y||2;
+ * code = #{interior boundaries < y/(norm+1e-8)}; pack; norm -> fp16.
+ * Replaces triton_fused_encode (kernels/triton_encode.py:150-209) and is
+ * bit-exact with TurboQuantMSE._encode_unfused (core/quantizer.py:137-160).
+ *   x            [n_vec, head_dim] of `dtype`, rows `row_stride` elements apart,
+ *                each row 16-byte aligned
+ *   signs_host   [head_dim] floats, each exactly +1 or -1; NULL = all +1
+ *   boundaries_host [2^bits + 1] ascending (LloydMaxQuantizer.boundaries)
+ *   packed       [n_vec, packed_dim] u8 out;  norms_f16 [n_vec] out
+ */
+int ftq_encode(const void *x, int dtype, int64_t n_vec, int head_dim, int64_t row_stride,
+               int bits, const float *signs_host, const float *boundaries_host,
+               uint8_t *packed, uint16_t *norms_f16, void *stream);
+
+/*
+ * Dense dequantisation: unpack -> levels[code] * norm -> FWHT -> * signs.
+ * Replaces triton_fused_decode (kernels/triton_decode.py:104-155);
+ * same arithmetic as TurboQuantMSE._decode_unfused (core/quantizer.py:191-205).
+ *   norms: fp16 ([n_vec]) when norms_dtype == FTQ_F16, fp32 when FTQ_F32.
+ *   out   [n_vec, head_dim] fp32
+ */
+int ftq_decode_dense(const uint8_t *packed, const void *norms, int norms_dtype, int64_t n_vec,
+                     int head_dim, int bits, const float *levels_host, const float *signs_host,
+                     float *out, void *stream);
+
+/*
+ * Randomized Hadamard transform, forward (FWHT(x*signs)) or inverse
+ * (FWHT(x)*signs), output dtype = input dtype.
+ * Replaces triton_rht (kernels/triton_rht.py:82-121); arithmetic of
+ * randomized_hadamard / inverse_randomized_hadamard (core/hadamard.py:70-100).
+ */
+int ftq_rht(const void *x, void *y, int dtype, int64_t n_vec, int head_dim,
+            const float *signs_host, int inverse, void *stream);
+
+/* ------------------------------------------------------- attention (dense) */
+
+/*
+ * Scores from packed keys: out[b,hq,t,s] = norm[b,hkv,s] * scale *
+ * sum_d q_rot[b,hq,t,d] * levels[code[b,hkv,s,d]],  hkv = hq / (Hq/Hkv).
+ * Replaces fused_qk_scores_rht (kernels/triton_attention.py:158-225).
+ *   q_rot [B,Hq,q_len,D] fp32 (already rotated); k_codes [B,Hkv,S,packed_dim];
+ *   k_norms [B,Hkv,S] fp16 or fp32 (norms_dtype); out [B,Hq,q_len,S] fp32.
+ */
+int ftq_qk_scores(const float *q_rot, const uint8_t *k_codes, const void *k_norms,
+                  int norms_dtype, const float *levels_host, float scale, int bits, int B, int Hq,
+                  int Hkv, int q_len, int S, int head_dim, float *out, void *stream);
+
+/*
+ * Bytes of caller workspace ftq_flash_decode / ftq_paged_decode_attn need for
+ * a batch of B sequences (per layer) whose longest context is max_seq_len.
+ */
+size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_seq_len,
+                                  int n_layers);
+
+/*
+ * Single-pass decode attention over CONTIGUOUS compressed K/V (one query
+ * token per sequence): rotated-space Q.K, online softmax, V accumulation,
+ * inverse rotation of the output.  Fills the slot of flash_decode_compressed
+ * (kernels/triton_flash_decode.py:224-324); unlike the reference it honours
+ * seq_lens.
+ *   q [B,Hq,D] of q_dtype; q_is_rotated != 0 means q is already RHT-rotated
+ *   (the reference's calling convention), 0 means the kernel rotates it.
+ *   k_codes [B,Hkv,S,pdk], k_norms [B,Hkv,S] fp16, same for v.
+ *   seq_lens [B] int32 device or NULL (= S everywhere).
+ *   out [B,Hq,D] of out_dtype, in the ORIGINAL (un-rotated) space.
+ *   workspace: device scratch of ftq_decode_workspace_bytes(B,Hq,Hkv,D,S,1) bytes.
+ */
+int ftq_flash_decode(const void *q, int q_dtype, int q_is_rotated, const uint8_t *k_codes,
+                     const uint16_t *k_norms, const uint8_t *v_codes, const uint16_t *v_norms,
+                     const float *levels_k_host, const float *levels_v_host,
+                     const float *signs_host, float scale, int bits_k, int bits_v,
+                     const int32_t *seq_lens, int B, int Hq, int Hkv, int S, int head_dim,
+                     void *out, int out_dtype, void *workspace, size_t workspace_bytes,
+                     void *stream);
+
+/* ------------------------------------------------------------- paged pool */
+
+/*
+ * Page layout of the paged KV pool (one pool per layer):
+ *   pool u8 [num_blocks, Hkv, page_bytes]; a (block, head) page holds 16 tokens:
+ *     [ K codes 16 x pdk | K norms 16 x fp16 | V codes 16 x pdv | V norms 16 x fp16 ]
+ *   page_bytes = 16 * (pdk + pdv + 4); every sub-array starts 16-byte aligned.
+ * The pool plays the role of the kv_cache tensor whose shape the backend
+ * defines (vllm_plugin/backend.py:107-124); slots hold the same code bytes
+ * and fp16 norms the reference stores, grouped per (block, head) so that one
+ * page is a single contiguous span.
+ */
+int64_t ftq_page_bytes(int head_dim, int bits_k, int bits_v);
+
+/*
+ * Fused encode + scatter of new K and V vectors into the paged pool.
+ * Replaces FusedTurboQuantImpl._compress_and_write_to_cache
+ * (vllm_plugin/attention_impl.py:190-254): tq.encode(K), tq_v.encode(V), then
+ * the per-token slot writes; tokens with slot_mapping < 0 are skipped.
+ *   key, value   [n_tokens, Hkv, D] of `dtype`; token_stride / head_stride in elements
+ *   slot_mapping [n_tokens] int64 device: slot = block * 16 + offset
+ *   n_layers > 1 batches layers: key/value/pool advance by *_layer_stride
+ *   (elements for key/value, bytes for the pool); slot_mapping is shared.
+ */
+int ftq_paged_store(const void *key, const void *value, int dtype, int64_t n_tokens, int Hkv,
+                    int head_dim, int64_t token_stride, int64_t head_stride, int bits_k,
+                    int bits_v, const float *signs_host, const float *boundaries_k_host,
+                    const float *boundaries_v_host, uint8_t *pool, int64_t num_blocks,
+                    const int64_t *slot_mapping, int n_layers, int64_t kv_layer_stride,
+                    int64_t pool_layer_stride, void *stream);
+
+/*
+ * Paged decode attention, one query token per sequence, straight from the
+ * packed pool through the block table (no gather, no dense K/V).
+ * Replaces FusedTurboQuantImpl._forward_decode (vllm_plugin/attention_impl.py:431-521:
+ * gather_compressed_kv_batched -> randomized_hadamard(q) -> fused_qk_scores_rht ->
+ * softmax -> gather + decode V -> matmul) with one split-KV kernel plus a merge.
+ *   q   [n_layers, B, Hq, D] of q_dtype, NOT rotated (rotation is fused)
+ *   out [n_layers, B, Hq, D] of out_dtype, original space
+ *   block_table [B, max_blocks] int32 device; seq_lens [B] int32 device
+ *   (both shared by all layers); pool advances pool_layer_stride bytes per layer.
+ *   max_seq_len: upper bound on seq_lens (host value; sizes the grid).
+ *   workspace: ftq_decode_workspace_bytes(B,Hq,Hkv,D,max_seq_len,n_layers) bytes.
+ */
+int ftq_paged_decode_attn(const void *q, int q_dtype, void *out, int out_dtype,
+                          const uint8_t *pool, int64_t num_blocks, int64_t pool_layer_stride,
+                          int n_layers, const int32_t *block_table, int max_blocks,
+                          const int32_t *seq_lens, int max_seq_len, int B, int Hq, int Hkv,
+                          int head_dim, int bits_k, int bits_v, const float *levels_k_host,
+                          const float *levels_v_host, const float *signs_host, float scale,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------- reference v0 layout adaptors */
+
+/*
+ * Same fused encode, written into the reference's own v0 paged layout
+ * kv_cache u8 [2, num_blocks, block_size, Hkv, packed_dim + 4] (plane 0 = K,
+ * 1 = V; slot = codes then the norm widened to 4 fp32 bytes), as
+ * compute_compressed_elem_size / write_compressed_to_slot define it
+ * (vllm_plugin/cache_ops.py:64-108).  Requires bits_k == bits_v or
+ * elem_size >= max(pdk, pdv) + 4; `elem_size` is the last dimension.
+ */
+int ftq_v0_store(const void *key, const void *value, int dtype, int64_t n_tokens, int Hkv,
+                 int head_dim, int64_t token_stride, int64_t head_stride, int bits_k, int bits_v,
+                 const float *signs_host, const float *boundaries_k_host,
+                 const float *boundaries_v_host, uint8_t *kv_cache, int64_t num_blocks,
+                 int block_size, int elem_size, const int64_t *slot_mapping, void *stream);
+
+/*
+ * Gather from the v0 layout into contiguous tensors, the job of
+ * gather_compressed_kv_batched (vllm_plugin/cache_ops.py:151-205), without the
+ * per-token host loop: out_codes [B,Hkv,max_seq_len,pd] u8 (zero beyond
+ * seq_len), out_norms [B,Hkv,max_seq_len] fp32.
+ */
+int ftq_v0_gather(const uint8_t *kv_cache, int64_t num_blocks, int block_size, int Hkv,
+                  int elem_size, int kv_type, int packed_dim, const int32_t *block_tables,
+                  int max_blocks, const int32_t *seq_lens, int B, int max_seq_len,
+                  uint8_t *out_codes, float *out_norms, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTQ_B200_H */

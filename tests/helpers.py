@@ -1,0 +1,76 @@
+"""numpy helpers shared by the tests: the page layout restated on the host, input generators."""
+import numpy as np
+
+PAGE = 16
+
+
+def pd(d, bits):
+    return d * bits // 8
+
+
+def page_offsets(d, bk, bv):
+    off_kn = PAGE * pd(d, bk)
+    off_vc = off_kn + 2 * PAGE
+    off_vn = off_vc + PAGE * pd(d, bv)
+    return off_kn, off_vc, off_vn, off_vn + 2 * PAGE
+
+
+def pool_from_contiguous(k_idx, k_norms, v_idx, v_norms, block_table, num_blocks, d, bk, bv,
+                         seq_lens=None, base=None):
+    """Lay contiguous [B,Hkv,S,*] codes / fp16 norms out as pool u8 [num_blocks, Hkv, page_bytes].
+    Slots of tokens beyond seq_len keep the bytes of `base` (zeros when None)."""
+    B, Hkv, S, _ = k_idx.shape
+    off_kn, off_vc, off_vn, pbytes = page_offsets(d, bk, bv)
+    pool = np.zeros((num_blocks, Hkv, pbytes), np.uint8) if base is None else base.copy()
+    kn = np.ascontiguousarray(k_norms, np.float16).view(np.uint16)
+    vn = np.ascontiguousarray(v_norms, np.float16).view(np.uint16)
+    for b in range(B):
+        n = S if seq_lens is None else int(seq_lens[b])
+        for s in range(n):
+            blk, t = int(block_table[b, s // PAGE]), s % PAGE
+            for h in range(Hkv):
+                page = pool[blk, h]
+                page[t * pd(d, bk):(t + 1) * pd(d, bk)] = k_idx[b, h, s]
+                page[off_kn + 2 * t:off_kn + 2 * t + 2] = np.frombuffer(kn[b, h, s].tobytes(), np.uint8)
+                page[off_vc + t * pd(d, bv):off_vc + (t + 1) * pd(d, bv)] = v_idx[b, h, s]
+                page[off_vn + 2 * t:off_vn + 2 * t + 2] = np.frombuffer(vn[b, h, s].tobytes(), np.uint8)
+    return pool
+
+
+def contiguous_from_pool(pool, block_table, seq_lens, S, d, bk, bv):
+    """Inverse of pool_from_contiguous (positions >= seq_len stay zero)."""
+    B = block_table.shape[0]
+    Hkv = pool.shape[1]
+    off_kn, off_vc, off_vn, _ = page_offsets(d, bk, bv)
+    k_idx = np.zeros((B, Hkv, S, pd(d, bk)), np.uint8)
+    v_idx = np.zeros((B, Hkv, S, pd(d, bv)), np.uint8)
+    k_n = np.zeros((B, Hkv, S), np.uint16)
+    v_n = np.zeros((B, Hkv, S), np.uint16)
+    for b in range(B):
+        for s in range(int(seq_lens[b])):
+            blk, t = int(block_table[b, s // PAGE]), s % PAGE
+            for h in range(Hkv):
+                page = pool[blk, h]
+                k_idx[b, h, s] = page[t * pd(d, bk):(t + 1) * pd(d, bk)]
+                v_idx[b, h, s] = page[off_vc + t * pd(d, bv):off_vc + (t + 1) * pd(d, bv)]
+                k_n[b, h, s] = page[off_kn + 2 * t:off_kn + 2 * t + 2].view(np.uint16)[0]
+                v_n[b, h, s] = page[off_vn + 2 * t:off_vn + 2 * t + 2].view(np.uint16)[0]
+    return k_idx, k_n.view(np.float16), v_idx, v_n.view(np.float16)
+
+
+def shuffled_block_table(rng, B, max_blocks, num_blocks):
+    perm = rng.permutation(num_blocks)[:B * max_blocks]
+    return perm.reshape(B, max_blocks).astype(np.int32)
+
+
+def boundary_exempt(normalized, boundaries, tol=1e-6):
+    """Mask of coordinates whose normalised rotated value lies within tol of a decision boundary."""
+    dist = np.abs(normalized[..., None] - np.asarray(boundaries, np.float32)[None, :]).min(-1)
+    return dist <= tol
+
+
+def gate(out, ref, rtol=2e-3, atol=1e-3):
+    """Number of elements violating |out - ref| <= atol + rtol * |ref|."""
+    out = np.asarray(out, np.float64)
+    ref = np.asarray(ref, np.float64)
+    return int((np.abs(out - ref) > atol + rtol * np.abs(ref)).sum())

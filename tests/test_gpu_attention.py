@@ -1,0 +1,232 @@
+"""GPU parity of the decode attention kernels (contiguous and paged) against the oracle.
+
+Tolerance: the north-star gate |out - ref| <= 1e-3 + 2e-3 * |ref| for bf16 outputs;
+fp32 outputs are held to 1e-4 + 2e-4 * |ref| (the kernel accumulates in fp32).
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import contiguous_from_pool, gate, pool_from_contiguous, shuffled_block_table
+
+pytestmark = pytest.mark.gpu
+
+
+def _lv(tables, d, b):
+    return tables[f"levels_d{d}_b{b}"]
+
+
+def _rand_case(oracle, tables, B, Hkv, G, S, d, bk, bv, seed, outliers=False):
+    rng = np.random.default_rng(seed)
+    K = rng.standard_normal((B, Hkv, S, d)).astype(np.float32)
+    V = rng.standard_normal((B, Hkv, S, d)).astype(np.float32)
+    if outliers:
+        K[..., :4] *= 20.0
+        V[..., :4] *= 20.0
+    q = rng.standard_normal((B, Hkv * G, d)).astype(np.float32)
+    signs = tables[f"signs_d{d}"]
+    k_idx, k_n = oracle.encode(K, signs, tables[f"boundaries_d{d}_b{bk}"], bk)
+    v_idx, v_n = oracle.encode(V, signs, tables[f"boundaries_d{d}_b{bv}"], bv)
+    return q, k_idx, k_n, v_idx, v_n, signs
+
+
+@pytest.mark.parametrize("name", ["cfg1small", "d64_g7_k3v3", "d256_g2_k4v2"])
+def test_flash_decode_vs_reference_golden(golden, tables, name):
+    """Against the reference's own composed unfused output (committed fixture)."""
+    from fused_turboquant_b200 import kernels
+    g = golden("attention.npz")
+    B, Hkv, G, S, d, bk, bv = (int(v) for v in g[f"{name}_meta"])
+    cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    common = (cu(g[f"{name}_k_idx"]), cu(g[f"{name}_k_norms"]), cu(g[f"{name}_v_idx"]),
+              cu(g[f"{name}_v_norms"]), _lv(tables, d, bk), _lv(tables, d, bv),
+              tables[f"signs_d{d}"], d ** -0.5, bk, bv)
+    # reference calling convention: pre-rotated query
+    out = kernels.flash_decode_compressed(cu(g[f"{name}_q_rot"]), *common)
+    assert out.shape == (B, Hkv * G, 1, d) and out.dtype == torch.float32
+    assert gate(out.cpu().numpy(), g[f"{name}_out_full"], 2e-4, 1e-4) == 0
+    # fused query rotation + seq_lens masking
+    out_m = kernels.flash_decode_compressed(cu(g[f"{name}_q"]), *common,
+                                            seq_lens=cu(g[f"{name}_seq_lens"]), q_is_rotated=False)
+    assert gate(out_m.cpu().numpy(), g[f"{name}_out_masked"], 2e-4, 1e-4) == 0
+    # bf16 in / bf16 out under the north-star gate
+    qb = cu(g[f"{name}_q"]).bfloat16()
+    ref = None
+    out_b = kernels.flash_decode_compressed(qb, *common, q_is_rotated=False,
+                                            out_dtype=torch.bfloat16)
+    assert out_b.dtype == torch.bfloat16
+    # the oracle is re-run on the bf16-rounded query so only the kernel's error is measured
+    from oracle import oracle as orc
+    ref = orc.decode_attn(qb.float().cpu().numpy()[:, :, 0], g[f"{name}_k_idx"], g[f"{name}_k_norms"],
+                          g[f"{name}_v_idx"], g[f"{name}_v_norms"], _lv(tables, d, bk),
+                          _lv(tables, d, bv), tables[f"signs_d{d}"], d ** -0.5, bk, bv)
+    ref_b = torch.from_numpy(ref).bfloat16().float().numpy()
+    viol = gate(out_b.float().cpu().numpy()[:, :, 0], ref_b)
+    # a violation can only be a one-ulp bf16 rounding flip (1 ulp is up to 7.8e-3 relative)
+    assert viol <= max(1, out_b.numel() // 500), viol
+
+
+@pytest.mark.parametrize("S", [1, 15, 16, 17, 63, 64, 65, 200, 1000])
+def test_flash_decode_lengths(oracle, tables, S):
+    from fused_turboquant_b200 import kernels
+    B, Hkv, G, d, bk, bv = 2, 2, 4, 128, 4, 4
+    q, k_idx, k_n, v_idx, v_n, signs = _rand_case(oracle, tables, B, Hkv, G, S, d, bk, bv, S)
+    ref = oracle.decode_attn(q, k_idx, k_n, v_idx, v_n, _lv(tables, d, bk), _lv(tables, d, bv), signs,
+                             d ** -0.5, bk, bv)
+    cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    out = kernels.flash_decode_compressed(cu(q)[:, :, None], cu(k_idx), cu(k_n), cu(v_idx), cu(v_n),
+                                          _lv(tables, d, bk), _lv(tables, d, bv), signs, d ** -0.5,
+                                          bk, bv, q_is_rotated=False)
+    assert gate(out.cpu().numpy()[:, :, 0], ref, 2e-4, 1e-4) == 0
+
+
+@pytest.mark.parametrize("d,G,bk,bv", [(64, 7, 3, 3), (128, 4, 4, 4), (128, 8, 3, 3), (256, 2, 4, 2),
+                                       (128, 1, 2, 2), (64, 16, 4, 3), (256, 4, 3, 4), (128, 5, 2, 4)])
+def test_paged_decode_vs_oracle(oracle, tables, d, G, bk, bv):
+    """Ragged batch through shuffled page tables; covers every bit width, GQA groups that need
+    several head passes, empty and one-token sequences."""
+    from fused_turboquant_b200 import PagedKVPool
+    B, Hkv = 5, 2
+    seq_lens = np.array([0, 1, 16, 77, 300], np.int32)
+    S = int(seq_lens.max())
+    max_blocks = (S + 15) // 16
+    num_blocks = B * max_blocks + 3
+    rng = np.random.default_rng(d + G + bk + bv)
+    q, k_idx, k_n, v_idx, v_n, signs = _rand_case(oracle, tables, B, Hkv, G, S, d, bk, bv, d * G + bk)
+    bt = shuffled_block_table(rng, B, max_blocks, num_blocks)
+    # unused token slots hold garbage (NaN / Inf norm patterns included): the kernel must mask by length
+    from helpers import page_offsets
+    garbage = rng.integers(0, 256, (num_blocks, Hkv, page_offsets(d, bk, bv)[3]), dtype=np.uint8)
+    pool_np = pool_from_contiguous(k_idx, k_n, v_idx, v_n, bt, num_blocks, d, bk, bv, seq_lens,
+                                   base=garbage)
+    back = contiguous_from_pool(pool_np, bt, seq_lens, S, d, bk, bv)
+    for b in range(B):
+        n = int(seq_lens[b])
+        np.testing.assert_array_equal(back[0][b, :, :n], k_idx[b, :, :n])
+        np.testing.assert_array_equal(back[3][b, :, :n].view(np.uint16), v_n[b, :, :n].view(np.uint16))
+    ref = oracle.decode_attn(q, k_idx, k_n, v_idx, v_n, _lv(tables, d, bk), _lv(tables, d, bv), signs,
+                             d ** -0.5, bk, bv, seq_lens=seq_lens)
+    kv = PagedKVPool(num_blocks, Hkv, d, bk, bv, n_layers=1)
+    kv.pool[0].copy_(torch.from_numpy(pool_np))
+    out = kv.decode_attention(torch.from_numpy(q).cuda(), torch.from_numpy(bt).cuda(),
+                              torch.from_numpy(seq_lens).cuda(), S, layer=0)
+    out = out.cpu().numpy()
+    assert np.isfinite(out).all()
+    assert np.abs(out[0]).max() == 0.0          # empty sequence -> zeros
+    assert gate(out, ref, 2e-4, 1e-4) == 0
+    # bf16 query / output under the north-star gate
+    qb = torch.from_numpy(q).cuda().bfloat16()
+    out_b = kv.decode_attention(qb, torch.from_numpy(bt).cuda(), torch.from_numpy(seq_lens).cuda(),
+                                S, layer=0)
+    ref_b = oracle.decode_attn(qb.float().cpu().numpy(), k_idx, k_n, v_idx, v_n, _lv(tables, d, bk),
+                               _lv(tables, d, bv), signs, d ** -0.5, bk, bv, seq_lens=seq_lens)
+    ref_b = torch.from_numpy(ref_b).bfloat16().float().numpy()
+    assert gate(out_b.float().cpu().numpy(), ref_b) <= max(1, out_b.numel() // 500)
+
+
+@pytest.mark.parametrize("d,bk,bv,dtype", [(128, 4, 4, torch.bfloat16), (64, 3, 3, torch.bfloat16),
+                                           (256, 4, 2, torch.float16), (128, 2, 3, torch.float32)])
+def test_paged_store_then_decode_end_to_end(oracle, tables, d, bk, bv, dtype):
+    """store (fused encode + scatter) -> pool bytes bit-exact vs the oracle's codes -> decode."""
+    from fused_turboquant_b200 import PagedKVPool
+    B, Hkv, G, L = 3, 2, 4, 2
+    seq_lens = np.array([5, 40, 129], np.int32)
+    S = int(seq_lens.max())
+    max_blocks = (S + 15) // 16
+    num_blocks = B * max_blocks + 2
+    rng = np.random.default_rng(11 + d)
+    bt = shuffled_block_table(rng, B, max_blocks, num_blocks)
+    g = torch.Generator("cpu").manual_seed(d + bk)
+    n_tok = int(seq_lens.sum())
+    key = torch.randn(L, n_tok, Hkv, d, generator=g).to(dtype)
+    val = torch.randn(L, n_tok, Hkv, d, generator=g).to(dtype)
+    slots, owner = [], []
+    for b in range(B):
+        for s in range(int(seq_lens[b])):
+            slots.append(int(bt[b, s // 16]) * 16 + s % 16)
+            owner.append((b, s))
+    slots = np.array(slots, np.int64)
+    # a few padding tokens with negative slots must be skipped
+    pad = 3
+    key = torch.cat([key, torch.randn(L, pad, Hkv, d).to(dtype)], 1)
+    val = torch.cat([val, torch.randn(L, pad, Hkv, d).to(dtype)], 1)
+    slots_p = np.concatenate([slots, -np.ones(pad, np.int64)])
+    kv = PagedKVPool(num_blocks, Hkv, d, bk, bv, n_layers=L)
+    kv.store(key.cuda(), val.cuda(), torch.from_numpy(slots_p).cuda())
+    signs = tables[f"signs_d{d}"]
+    q = torch.randn(L, B, Hkv * G, d, generator=g)
+    out = kv.decode_attention(q.cuda(), torch.from_numpy(bt).cuda(), torch.from_numpy(seq_lens).cuda(), S)
+    for layer in range(L):
+        k_idx = np.zeros((B, Hkv, S, d * bk // 8), np.uint8)
+        v_idx = np.zeros((B, Hkv, S, d * bv // 8), np.uint8)
+        k_n = np.zeros((B, Hkv, S), np.float16)
+        v_n = np.zeros((B, Hkv, S), np.float16)
+        ek, enk = oracle.encode(key[layer, :n_tok].float().numpy(), signs, tables[f"boundaries_d{d}_b{bk}"], bk)
+        ev, env = oracle.encode(val[layer, :n_tok].float().numpy(), signs, tables[f"boundaries_d{d}_b{bv}"], bv)
+        for i, (b, s) in enumerate(owner):
+            k_idx[b, :, s], k_n[b, :, s] = ek[i], enk[i]
+            v_idx[b, :, s], v_n[b, :, s] = ev[i], env[i]
+        expect_pool = pool_from_contiguous(k_idx, k_n, v_idx, v_n, bt, num_blocks, d, bk, bv, seq_lens)
+        np.testing.assert_array_equal(kv.pool[layer].cpu().numpy(), expect_pool)   # bit-exact bytes
+        ref = oracle.decode_attn(q[layer].numpy(), k_idx, k_n, v_idx, v_n, tables[f"levels_d{d}_b{bk}"],
+                                 tables[f"levels_d{d}_b{bv}"], signs, d ** -0.5, bk, bv, seq_lens=seq_lens)
+        assert gate(out[layer].cpu().numpy(), ref, 2e-4, 1e-4) == 0
+
+
+def test_qk_scores_vs_golden_and_oracle(oracle, golden, tables):
+    from fused_turboquant_b200 import kernels
+    g = golden("attention.npz")
+    for name in ["cfg1small", "d64_g7_k3v3", "d256_g2_k4v2"]:
+        B, Hkv, G, S, d, bk, bv = (int(v) for v in g[f"{name}_meta"])
+        cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        for norms in (g[f"{name}_k_norms"], g[f"{name}_k_norms"].astype(np.float32)):
+            s = kernels.fused_qk_scores_rht(cu(g[f"{name}_q_rot"]), cu(g[f"{name}_k_idx"]), cu(norms),
+                                            _lv(tables, d, bk), d ** -0.5, bits=bk)
+            assert s.shape == (B, Hkv * G, 1, S)
+            np.testing.assert_allclose(s.cpu().numpy(), g[f"{name}_scores_rot"], rtol=1e-4, atol=1e-4)
+    # q_len > 1
+    rng = np.random.default_rng(3)
+    q, k_idx, k_n, _, _, signs = _rand_case(oracle, tables, 2, 2, 2, 70, 128, 3, 3, 9)
+    q3 = rng.standard_normal((2, 4, 3, 128)).astype(np.float32)
+    s = kernels.fused_qk_scores_rht(torch.from_numpy(q3).cuda(), torch.from_numpy(k_idx).cuda(),
+                                    torch.from_numpy(k_n).cuda(), _lv(tables, 128, 3), 0.1, bits=3).cpu().numpy()
+    for t in range(3):
+        ref = oracle.qk_scores(q3[:, :, t], k_idx, k_n.astype(np.float32), _lv(tables, 128, 3), 0.1, 3)
+        np.testing.assert_allclose(s[:, :, t], ref, rtol=1e-4, atol=1e-4)
+
+
+def test_v0_layout_store_and_gather(oracle, golden, tables):
+    """The reference's v0 slot layout, written by the fused encode and gathered in one launch."""
+    from fused_turboquant_b200 import paged
+    g = golden("v0_layout.npz")
+    d, b, Hkv, bs, nb, es, n_tok = (int(v) for v in g["meta"])
+    cache = torch.zeros(2, nb, bs, Hkv, es, dtype=torch.uint8, device="cuda")
+    K = torch.from_numpy(g["K"]).cuda()
+    paged.v0_store(cache, K, K, torch.from_numpy(g["slots"]).cuda(), b, b, tables[f"signs_d{d}"],
+                   tables[f"boundaries_d{d}_b{b}"], tables[f"boundaries_d{d}_b{b}"])
+    got = cache.cpu().numpy()
+    np.testing.assert_array_equal(got[0], g["cache"][0])       # K plane == reference bytes
+    np.testing.assert_array_equal(got[1], g["cache"][0])       # V plane written with the same data
+    gp, gn = paged.gather_compressed_kv_batched(cache, torch.from_numpy(g["block_table"]).cuda(),
+                                                torch.tensor([n_tok]).cuda(), 0, d // 2, 48)
+    np.testing.assert_array_equal(gp.cpu().numpy(), g["gathered_packed"])
+    np.testing.assert_array_equal(gn.cpu().numpy(), g["gathered_norms"])
+
+
+def test_errors_surface_as_exceptions(tables):
+    from fused_turboquant_b200 import PagedKVPool, kernels
+    with pytest.raises(ValueError):
+        PagedKVPool(4, 2, 96, 4)
+    with pytest.raises(ValueError):
+        PagedKVPool(4, 2, 128, 5)
+    kv = PagedKVPool(4, 2, 128, 4)
+    q = torch.randn(1, 8, 128).cuda()
+    with pytest.raises(RuntimeError):          # block table too narrow for max_seq_len
+        kv.decode_attention(q, torch.zeros(1, 1, dtype=torch.int32).cuda(),
+                            torch.tensor([40], dtype=torch.int32).cuda(), 40, layer=0)
+    with pytest.raises(RuntimeError):          # workspace too small
+        kv.decode_attention(q, torch.zeros(1, 4, dtype=torch.int32).cuda(),
+                            torch.tensor([40], dtype=torch.int32).cuda(), 40, layer=0,
+                            workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+    with pytest.raises(RuntimeError):
+        kernels.fused_encode(torch.randn(2, 128).cuda(), np.full(128, 0.5, np.float32),
+                             tables["boundaries_d128_b4"], 4)   # signs must be +-1
