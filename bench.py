@@ -1,0 +1,450 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: paged compressed-KV decode attention (+ fused KV encode).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3] [--impl ours|reference]
+
+One "step" is one decode step of the whole model shape: for every layer, one
+paged decode-attention call over that layer's own compressed KV pool (distinct
+pools, so every byte comes from HBM; a layer's pool is far larger than L2).
+`value` is whole-job packed-KV bandwidth: algorithmic bytes of all ranks / the
+slowest rank's device time.  Under torchrun every rank owns its own batch of
+sequences (sequence sharding, no data-path collective; weak scaling), except
+--workload cfg4, which shards KV heads and all-gathers the outputs.
+
+--impl reference times the CPU arm: the oracle's restatement of the reference's
+unfused path on the host cores (OpenMP over all cores), on a bounded sample of
+the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+METRIC = "tq_paged_decode_attn_hbm_gbs"
+UNIT = "GB/s"
+
+# BASELINE configs 2..5 (config 1 is the CPU-runnable parity case, not a bench line).
+WORKLOADS = {
+    # name: layers, B, ctx, Hq, Hkv, D, bits_k, bits_v, ragged
+    "cfg2": dict(desc="qwen2.5-0.5b-shaped decode, K3V3", layers=24, B=32, ctx=4096, Hq=14, Hkv=2,
+                 D=64, bk=3, bv=3, ragged=False),
+    "cfg3": dict(desc="llama-3-8b-shaped decode, K4V4", layers=32, B=64, ctx=8192, Hq=32, Hkv=8,
+                 D=128, bk=4, bv=4, ragged=False),
+    "cfg4": dict(desc="long-context decode, K3V3, KV heads sharded", layers=32, B=4, ctx=131072,
+                 Hq=64, Hkv=8, D=128, bk=3, bv=3, ragged=False),
+    "cfg5": dict(desc="mixed-bit ragged serving batch, K4V2", layers=4, B=256, ctx=32768, Hq=16,
+                 Hkv=8, D=256, bk=4, bv=2, ragged=True),
+}
+
+
+def packed_dim(d, bits):
+    return d * bits // 8
+
+
+def decode_bytes(seq_lens, Hq, Hkv, D, bk, bv):
+    """Algorithmic bytes of one layer's decode call: packed K/V + fp16 norms once per KV head,
+    page ids, q in, out (bf16)."""
+    tok_head = packed_dim(D, bk) + 2 + packed_dim(D, bv) + 2
+    kv = int(sum(int(s) for s in seq_lens)) * Hkv * tok_head
+    pages = int(sum((int(s) + 15) // 16 for s in seq_lens)) * 4
+    qo = 2 * len(seq_lens) * Hq * D * 2
+    return kv + pages + qo
+
+
+def encode_bytes(n_vec, D, bits, in_bytes=2):
+    return n_vec * (D * in_bytes + packed_dim(D, bits) + 2)
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampler running beside the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu_index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), f[5:9]):
+                if val.lower() == "active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_seq_lens(w, rank, gen):
+    if not w["ragged"]:
+        return np.full(w["B"], w["ctx"], np.int32)
+    # config 5: log-uniform context lengths in [128, 32768]
+    u = torch.rand(w["B"], generator=gen).numpy()
+    return np.floor(np.exp(math.log(128) + u * (math.log(32768) - math.log(128)))).astype(np.int32)
+
+
+def synth_kv(n_tok, Hkv, D, cfg_name, gen_dev, device):
+    """Synthetic K or V [n_tok, Hkv, D] bf16 with the value distribution the config names."""
+    x = torch.randn(n_tok, Hkv, D, device=device, generator=gen_dev, dtype=torch.float32)
+    if cfg_name == "cfg2":      # per-head lognormal(0, 0.5) channel scales
+        sc = torch.exp(0.5 * torch.randn(Hkv, D, device=device, generator=gen_dev))
+        x = x * sc
+    elif cfg_name == "cfg3":    # 1% of channels x10
+        mask = torch.rand(Hkv, D, device=device, generator=gen_dev) < 0.01
+        x = torch.where(mask, x * 10.0, x)
+    elif cfg_name == "cfg5":    # Student-t(nu=5)
+        chi = torch.randn(5, n_tok, Hkv, D, device=device, generator=gen_dev).pow(2).sum(0) / 5.0
+        x = x / chi.sqrt()
+    return x.to(torch.bfloat16)
+
+
+def build_pool(w, cfg_name, seq_lens, layers, Hkv_local, device, seed):
+    """Allocate and fill the per-layer pools through the library's own fused store."""
+    from fused_turboquant_b200 import PagedKVPool
+
+    B = len(seq_lens)
+    max_blocks = int((int(seq_lens.max()) + 15) // 16)
+    blocks_needed = int(sum((int(s) + 15) // 16 for s in seq_lens))
+    num_blocks = blocks_needed
+    pool = PagedKVPool(num_blocks, Hkv_local, w["D"], w["bk"], w["bv"], n_layers=layers,
+                       device=device)
+    gcpu = torch.Generator("cpu").manual_seed(seed)
+    perm = torch.randperm(num_blocks, generator=gcpu).numpy().astype(np.int32)
+    bt = np.zeros((B, max_blocks), np.int32)
+    pos = 0
+    for b in range(B):
+        nb = (int(seq_lens[b]) + 15) // 16
+        bt[b, :nb] = perm[pos:pos + nb]
+        pos += nb
+    bt_dev = torch.from_numpy(bt).to(device)
+    gdev = torch.Generator(device=device).manual_seed(seed + 1)
+    # fill sequence by sequence group so the fp32 staging tensors stay small
+    tok_budget = 1 << 17
+    for layer in range(layers):
+        b0 = 0
+        while b0 < B:
+            b1, ntok = b0, 0
+            while b1 < B and (ntok == 0 or ntok + int(seq_lens[b1]) <= tok_budget):
+                ntok += int(seq_lens[b1]); b1 += 1
+            slots = torch.cat([
+                bt_dev[b, torch.arange(int(seq_lens[b]), device=device) // 16].long() * 16 +
+                torch.arange(int(seq_lens[b]), device=device) % 16 for b in range(b0, b1)])
+            k = synth_kv(ntok, Hkv_local, w["D"], cfg_name, gdev, device)
+            v = synth_kv(ntok, Hkv_local, w["D"], cfg_name, gdev, device)
+            pool.store(k, v, slots, layer=layer)
+            del k, v
+            b0 = b1
+    return pool, bt_dev
+
+
+def cpu_arm(w, seconds_target: float, threads: int):
+    """Time the oracle's unfused decode attention on a bounded sample of the workload.
+
+    Returns (GB/s on the same algorithmic bytes, description of the sample)."""
+    from fused_turboquant_b200 import codebook
+    from oracle import oracle as orc
+
+    orc.set_threads(threads)
+    D, bk, bv, Hq, Hkv = w["D"], w["bk"], w["bv"], w["Hq"], w["Hkv"]
+    ctx = min(w["ctx"], 8192)
+    rng = np.random.default_rng(0)
+    signs = codebook.rht_signs(D, 42)
+    _, lk = codebook.codebook_f32(D, bk)
+    _, lv = codebook.codebook_f32(D, bv)
+
+    def run(B):
+        k_idx = rng.integers(0, 256, (B, Hkv, ctx, packed_dim(D, bk)), dtype=np.uint8)
+        v_idx = rng.integers(0, 256, (B, Hkv, ctx, packed_dim(D, bv)), dtype=np.uint8)
+        k_n = (rng.random((B, Hkv, ctx)) * 4 + 9).astype(np.float16)
+        v_n = (rng.random((B, Hkv, ctx)) * 4 + 9).astype(np.float16)
+        q = rng.standard_normal((B, Hq, D)).astype(np.float32)
+        t = time.perf_counter()
+        orc.decode_attn(q, k_idx, k_n, v_idx, v_n, lk, lv, signs, D ** -0.5, bk, bv)
+        dt = time.perf_counter() - t
+        return dt, decode_bytes([ctx] * B, Hq, Hkv, D, bk, bv)
+
+    dt, nbytes = run(1)                       # calibration (also the warm-up)
+    B = int(max(1, min(64, seconds_target / max(dt, 1e-3))))
+    dt, nbytes = run(B)
+    sample = (f"1 layer, {B} sequences x {Hkv} KV heads x ctx {ctx} of the workload shape, "
+              f"oracle decode_attn, {dt:.2f} s")
+    return nbytes / dt / 1e9, sample
+
+
+def run_reference_arm(args, w, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    vals = []
+    sample = ""
+    per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        v, sample = cpu_arm(w, per_step, threads)
+        if i >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {w['desc']}"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-encode", action="store_true", help="skip the encode measurement")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    w = dict(WORKLOADS[args.workload])
+    if args.layers:
+        w["layers"] = args.layers
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, rank)
+        return
+
+    import torch.distributed as dist
+    from fused_turboquant_b200 import _lib, sharding
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (no CPU fallback in the product path)")
+    _lib.load()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    head_sharded = args.workload == "cfg4" and world > 1
+    Hkv_local, Hq_local = w["Hkv"], w["Hq"]
+    if head_sharded:
+        kvr, qr = sharding.shard_kv_heads(w["Hkv"], w["Hq"], world, rank)
+        Hkv_local, Hq_local = len(kvr), len(qr)
+    L, D = w["layers"], w["D"]
+    gen = torch.Generator("cpu").manual_seed(20250 + int(args.workload[-1]) + 1000 * rank)
+    seq_lens = make_seq_lens(w, rank, gen)
+    B = len(seq_lens)
+    max_seq = int(seq_lens.max())
+
+    pool, bt = build_pool(w, args.workload, seq_lens, L, Hkv_local, device, seed=7 + rank)
+    sl = torch.from_numpy(seq_lens).to(device)
+    q_host = torch.randn(L, B, Hq_local, D, generator=gen).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty_like(q_host).pin_memory()
+    q_dev = q_host.to(device)
+    out_dev = torch.empty_like(q_dev)
+    ws = torch.empty(pool.workspace_bytes(B, Hq_local, max_seq, 1), dtype=torch.uint8, device=device)
+    gathered = None
+
+    def step(qd, od):
+        for layer in range(L):
+            pool.decode_attention(qd[layer], bt, sl, max_seq, layer=layer, out=od[layer],
+                                  workspace=ws)
+        if head_sharded:
+            return sharding.all_gather_heads(od)
+        return od
+
+    bytes_layer = decode_bytes(seq_lens, Hq_local, Hkv_local, D, w["bk"], w["bv"])
+    bytes_step = bytes_layer * L
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        gathered = step(q_dev, out_dev)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # ---- device-resident timing: K steps between two events
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        gathered = step(q_dev, out_dev)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+
+    # ---- per-call timing of the decode call (split-KV kernel + merge) for the roofline
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(L)]
+    call_ms = []
+    for _ in range(min(args.steps, 5)):
+        for layer in range(L):
+            evs[layer][0].record()
+            pool.decode_attention(q_dev[layer], bt, sl, max_seq, layer=layer, out=out_dev[layer],
+                                  workspace=ws)
+            evs[layer][1].record()
+        torch.cuda.synchronize()
+        call_ms += [a.elapsed_time(b) for a, b in evs]
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the public API with host buffers (pinned), copies inside the region
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        q_dev.copy_(q_host, non_blocking=True)
+        res = step(q_dev, out_dev)
+        if head_sharded:
+            out_host_g = res.to("cpu", non_blocking=True)
+        else:
+            out_host.copy_(res, non_blocking=True)
+    e3.record()
+    barrier()
+    ms_e2e = e2.elapsed_time(e3)
+
+    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=device)
+    nb = torch.tensor([float(bytes_step)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nb, op=dist.ReduceOp.SUM)
+    ms_total, ms_e2e = float(t[0]), float(t[1])
+    total_bytes_step = float(nb[0])
+
+    # ---- encode throughput (prefill encode of the same shape), rank-local, summed over ranks
+    enc = None
+    if not args.no_encode:
+        n_tok = min(int(seq_lens.sum()), 1 << 19)
+        gdev = torch.Generator(device=device).manual_seed(99)
+        k = synth_kv(n_tok, Hkv_local, D, args.workload, gdev, device)
+        v = synth_kv(n_tok, Hkv_local, D, args.workload, gdev, device)
+        nblk = (n_tok + 15) // 16
+        from fused_turboquant_b200 import PagedKVPool
+        epool = PagedKVPool(nblk, Hkv_local, D, w["bk"], w["bv"], n_layers=1, device=device)
+        slots = torch.randperm(nblk, device=device).repeat_interleave(16)[:n_tok] * 16 + \
+            torch.arange(n_tok, device=device) % 16
+        for _ in range(3):
+            epool.store(k, v, slots, layer=0)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        barrier()
+        a.record()
+        for _ in range(reps):
+            epool.store(k, v, slots, layer=0)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        eb = encode_bytes(n_tok * Hkv_local, D, w["bk"]) + encode_bytes(n_tok * Hkv_local, D, w["bv"])
+        et = torch.tensor([ms, float(n_tok)], dtype=torch.float64, device=device)
+        if world > 1:
+            mx = et.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+            sm = et.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+            ms, tok_total = float(mx[0]), float(sm[1])
+        else:
+            tok_total = float(n_tok)
+        enc = {"tokens_per_s": tok_total / (ms * 1e-3), "ms": ms, "tokens": int(tok_total),
+               "vectors_per_token": 2 * Hkv_local, "gbs_per_gpu": eb / (ms * 1e-3) / 1e9,
+               "launches": 2}
+        del k, v, epool
+
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+
+    if rank == 0:
+        ms_step = ms_total / args.steps
+        value = total_bytes_step / (ms_step * 1e-3) / 1e9
+        call = float(np.mean(call_ms))
+        achieved = bytes_layer / (call * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['desc']}", "layers": L, "batch_per_gpu": B,
+                       "ctx": int(max_seq), "q_heads": w["Hq"], "kv_heads": w["Hkv"], "head_dim": D,
+                       "key_bits": w["bk"], "value_bits": w["bv"], "page_tokens": 16,
+                       "activations": "bf16",
+                       "sharding": "kv-heads+allgather" if head_sharded else "sequences",
+                       "l2": "inputs larger than L2 (distinct pool per layer)"},
+            "pct_of_nominal_8000": 100.0 * value / world / 8000.0,
+            "decode_tokens_per_s": B * world / (ms_step * 1e-3),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "attn_split_kernel + attn_merge_kernel (one call)",
+                         "bytes_per_launch": bytes_layer, "ms_per_launch": call},
+            "e2e": {"value": total_bytes_step / (ms_e2e / args.steps * 1e-3) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": int(q_host.numel() * 2),
+                    "d2h_bytes_per_step": int(q_host.numel() * 2 * (world if head_sharded else 1)),
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": int(args.steps * L * 2),
+            "clocks": clocks,
+            "encode": enc,
+        }
+        if world == 1 and not args.no_cpu:
+            v, sample = cpu_arm(w, 12.0, os.cpu_count() or 1)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": os.cpu_count() or 1,
+                                    "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
