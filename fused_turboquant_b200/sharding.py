@@ -77,8 +77,10 @@ def all_gather_heads(out_local: torch.Tensor, group=None) -> torch.Tensor:
     if world == 1:
         return out_local
     local = out_local.contiguous()
-    gathered = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(gathered, local, group=group)
+    flat = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype,
+                       device=local.device)
+    dist.all_gather_into_tensor(flat, local, group=group)
+    gathered = flat.view((world,) + tuple(local.shape))
     # [world, ..., B, Hl, D] -> [..., B, world, Hl, D] -> merge
     nd = local.dim()
     perm = list(range(1, nd - 1)) + [0, nd - 1, nd]
