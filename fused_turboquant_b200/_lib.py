@@ -35,6 +35,8 @@ SIGNATURES = {
                              _i64, _vp, _i, _i64, _i64, _vp]),
     "ftq_paged_decode_attn": (_i, [_vp, _i, _vp, _i, _vp, _i64, _i64, _i, _vp, _i, _vp, _i, _i,
                                    _i, _i, _i, _i, _i, _fp, _fp, _fp, _f, _vp, _sz, _vp]),
+    "ftq_paged_decode_attn_static": (_i, [_vp, _i, _vp, _i, _vp, _i64, _i64, _i, _vp, _i, _vp, _i,
+                                          _i, _i, _i, _i, _i, _i, _fp, _fp, _fp, _f, _vp]),
     "ftq_v0_store": (_i, [_vp, _vp, _i, _i64, _i, _i, _i64, _i64, _i, _i, _fp, _fp, _fp, _vp,
                           _i64, _i, _i, _vp, _vp]),
     "ftq_v0_gather": (_i, [_vp, _i64, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp]),

@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/ftq_b200.h"
 #include "ftq_dense.cuh"
@@ -584,3 +585,63 @@ int ftq_v0_gather(const uint8_t* kv_cache, int64_t num_blocks, int block_size, i
 }
 
 }  // extern "C"
+
+// --------------------------------------------------------------------------
+// Paged decode attention without a caller workspace.
+//
+// Some callers have no memory to give and cannot get any: an inference engine
+// that has already handed (nearly) all of the device to its own KV block
+// manager, a plugin that is entered in a context where cudaMalloc is not
+// allowed or would stall the device (it synchronises), or a host that simply
+// forbids allocation after start-up.  For them the split-KV partials live in a
+// fixed array inside the library image instead.  The price: the array occupies
+// FTQ_STATIC_SCRATCH_BYTES on every GPU that loads the library, for the life
+// of the process, and it caps the problem size.
+static __device__ __align__(256) unsigned char g_static_scratch[FTQ_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_addr[64] = {nullptr};
+
+// In host code `g_static_scratch` is only a handle for the symbol; the device
+// address has to be asked for, once per device, with that device current.
+int static_scratch_address(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(FTQ_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_addr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        if (!p) return fail(FTQ_ERR_CUDA, "static scratch has no device address");
+        g_static_addr[dev] = p;
+    }
+    *out = g_static_addr[dev];
+    return FTQ_OK;
+}
+}  // namespace
+
+extern "C" int ftq_paged_decode_attn_static(
+    const void* q, int q_dtype, void* out, int out_dtype, const uint8_t* pool, int64_t num_blocks,
+    int64_t pool_layer_stride, int n_layers, const int32_t* block_table, int max_blocks,
+    const int32_t* seq_lens, int max_seq_len, int B, int Hq, int Hkv, int head_dim, int bits_k,
+    int bits_v, const float* levels_k_host, const float* levels_v_host, const float* signs_host,
+    float scale, void* stream) {
+    // Shape errors are reported by the shared path below; only the size limit is checked here.
+    const size_t need = ftq_decode_workspace_bytes(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
+    if (need > static_cast<size_t>(FTQ_STATIC_SCRATCH_BYTES))
+        return fail(FTQ_ERR_WORKSPACE,
+                    "this batch needs %zu bytes of split-KV scratch but the built-in scratch holds "
+                    "%zu; call ftq_paged_decode_attn with your own workspace, or pass fewer "
+                    "sequences / layers per call",
+                    need, static_cast<size_t>(FTQ_STATIC_SCRATCH_BYTES));
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    return ftq_paged_decode_attn(q, q_dtype, out, out_dtype, pool, num_blocks, pool_layer_stride,
+                                 n_layers, block_table, max_blocks, seq_lens, max_seq_len, B, Hq,
+                                 Hkv, head_dim, bits_k, bits_v, levels_k_host, levels_v_host,
+                                 signs_host, scale, scratch, FTQ_STATIC_SCRATCH_BYTES, stream);
+}

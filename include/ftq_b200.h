@@ -181,6 +181,43 @@ int ftq_paged_decode_attn(const void *q, int q_dtype, void *out, int out_dtype,
                           const float *levels_v_host, const float *signs_host, float scale,
                           void *workspace, size_t workspace_bytes, void *stream);
 
+/* ------------------------------------------- decode without a workspace */
+
+/* Size of the scratch array built into the library (bytes, per GPU). */
+#define FTQ_STATIC_SCRATCH_BYTES (8u << 20)
+
+/*
+ * ftq_paged_decode_attn for callers that cannot provide a workspace because
+ * they cannot allocate device memory at all: engines that gave the whole
+ * device to their own block manager, code entered where cudaMalloc is not
+ * permitted or would stall every stream, hosts that forbid allocation after
+ * start-up.  It has no counterpart in the reference (which allocates freely
+ * through torch); it exists only for such embedders.
+ *
+ * Same arguments and results as ftq_paged_decode_attn, minus the workspace:
+ * the split-KV partials go to an 8 MiB array that is part of the library
+ * image.  Consequences to know about:
+ *   - every GPU that loads the library holds those 8 MiB until the process ends;
+ *   - a batch whose partials exceed FTQ_STATIC_SCRATCH_BYTES
+ *     (ftq_decode_workspace_bytes tells) is rejected with FTQ_ERR_WORKSPACE;
+ *   - all calls on one GPU share the array and it keeps whatever the last call
+ *     left (nothing in it has to start at zero: every row that is read is
+ *     written first by the same call), so two calls that may run at the same
+ *     time on one GPU (different streams) corrupt each other: serialise them;
+ *   - the first call on each device looks up the array's device address
+ *     (one cudaGetSymbolAddress, no allocation); make that first call outside
+ *     any stream capture.
+ * The call itself allocates nothing and frees nothing.
+ */
+int ftq_paged_decode_attn_static(const void *q, int q_dtype, void *out, int out_dtype,
+                                 const uint8_t *pool, int64_t num_blocks,
+                                 int64_t pool_layer_stride, int n_layers,
+                                 const int32_t *block_table, int max_blocks,
+                                 const int32_t *seq_lens, int max_seq_len, int B, int Hq, int Hkv,
+                                 int head_dim, int bits_k, int bits_v, const float *levels_k_host,
+                                 const float *levels_v_host, const float *signs_host, float scale,
+                                 void *stream);
+
 /* ------------------------------------------- reference v0 layout adaptors */
 
 /*
