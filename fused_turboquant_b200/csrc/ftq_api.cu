@@ -104,6 +104,28 @@ ChunkPlan plan_chunks(int B, int Hq, int Hkv, int d, int max_seq_len, int n_laye
     return pl;
 }
 
+// Chunking of the tensor-core path: chunks of at least 2048 tokens (the per-CTA table build and
+// query rotation must stay small against the streaming work), at most 16384 (block ids of a
+// chunk are staged in shared memory), otherwise enough chunks for ~4 waves of 2 CTAs per SM.
+ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers) {
+    ChunkPlan pl;
+    pl.n_hpass = 1;
+    const int64_t units = static_cast<int64_t>(B) * Hkv * n_layers;
+    const int64_t target = static_cast<int64_t>(ftq::sm_count()) * 2 * 4;
+    int64_t want = (target + units - 1) / (units > 0 ? units : 1);
+    if (want < 1) want = 1;
+    const int seq = max_seq_len > 0 ? max_seq_len : 1;
+    int64_t ct = (seq + want - 1) / want;
+    ct = (ct + 63) / 64 * 64;
+    if (ct < 2048) ct = 2048;
+    if (ct > 16384) ct = 16384;
+    pl.chunk_tokens = static_cast<int>(ct);
+    pl.n_chunks = static_cast<int>((seq + ct - 1) / ct);
+    return pl;
+}
+
+bool use_mma_path(int Hq, int Hkv, int q_dtype) { return Hq / Hkv <= 8 && q_dtype != FTQ_F32; }
+
 size_t partial_bytes(const ChunkPlan& pl, int B, int Hq, int d, int n_layers) {
     return static_cast<size_t>(n_layers) * B * Hq * pl.n_chunks * (d + 4) * sizeof(float);
 }
@@ -114,6 +136,16 @@ cudaError_t dispatch_split(int d, int bk, int bv, bool paged, const ftq::AttnPar
         case 64: return ftq::launch_attn_split_d64(bk, bv, paged, p, n_lb, st);
         case 128: return ftq::launch_attn_split_d128(bk, bv, paged, p, n_lb, st);
         case 256: return ftq::launch_attn_split_d256(bk, bv, paged, p, n_lb, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t dispatch_mma(int d, int bk, int bv, bool shared_lut, const ftq::AttnParams& p, int n_lb,
+                         cudaStream_t st) {
+    switch (d) {
+        case 64: return ftq::launch_attn_mma_d64(bk, bv, shared_lut, p, n_lb, st);
+        case 128: return ftq::launch_attn_mma_d128(bk, bv, shared_lut, p, n_lb, st);
+        case 256: return ftq::launch_attn_mma_d256(bk, bv, shared_lut, p, n_lb, st);
     }
     return cudaErrorInvalidValue;
 }
@@ -364,8 +396,12 @@ int ftq_qk_scores(const float* q_rot, const uint8_t* k_codes, const void* k_norm
 size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_seq_len,
                                   int n_layers) {
     if (!dim_ok(head_dim) || B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_layers <= 0) return 0;
-    const ChunkPlan pl = plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
-    return partial_bytes(pl, B, Hq, head_dim, n_layers);
+    // the larger of the two paths' needs, so one buffer serves whichever kernel runs
+    const ChunkPlan a = plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
+    const ChunkPlan m = plan_chunks_mma(B, Hkv, max_seq_len, n_layers);
+    const size_t na = partial_bytes(a, B, Hq, head_dim, n_layers);
+    const size_t nm = partial_bytes(m, B, Hq, head_dim, n_layers);
+    return na > nm ? na : nm;
 }
 
 static int check_attn_common(int B, int Hq, int Hkv, int head_dim, int bits_k, int bits_v,
@@ -491,8 +527,12 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
                     max_blocks, max_seq_len);
     if (!aligned(q, 16) || !aligned(out, 4) || !aligned(pool, 16) || pool_layer_stride % 16)
         return fail(FTQ_ERR_INVALID, "q and pool must be 16-byte aligned");
-    const ChunkPlan pl = plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
-    const size_t need = partial_bytes(pl, B, Hq, head_dim, n_layers);
+    // 16-bit queries with a GQA group of at most 8 take the tensor-core kernel; fp32 queries
+    // (and larger groups) take the fp32 kernel.
+    const bool mma = use_mma_path(Hq, Hkv, q_dtype);
+    const ChunkPlan pl = mma ? plan_chunks_mma(B, Hkv, max_seq_len, n_layers)
+                             : plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
+    const size_t need = ftq_decode_workspace_bytes(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     if (!workspace || workspace_bytes < need)
         return fail(FTQ_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", need, workspace_bytes);
     if (!aligned(workspace, 16)) return fail(FTQ_ERR_WORKSPACE, "workspace must be 16-byte aligned");
@@ -512,7 +552,14 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     p.partials = static_cast<float*>(workspace);
     p.rsqrt_d = rsqrt_dim(head_dim);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    cudaError_t e = dispatch_split(head_dim, bits_k, bits_v, true, p, n_layers * B, st);
+    cudaError_t e;
+    if (mma) {
+        const bool shared_lut = bits_k == bits_v &&
+            memcmp(levels_k_host, levels_v_host, sizeof(float) << bits_k) == 0;
+        e = dispatch_mma(head_dim, bits_k, bits_v, shared_lut, p, n_layers * B, st);
+    } else {
+        e = dispatch_split(head_dim, bits_k, bits_v, true, p, n_layers * B, st);
+    }
     if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn split launch");
     e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, 0, B, Hq, pl,
                        static_cast<int64_t>(n_layers) * B * Hq, p.signs, st);

@@ -1,4 +1,5 @@
 // Instantiates the split-KV decode attention kernels for one head_dim (FTQ_D).
+#include "ftq_attn_mma.cuh"
 #include "ftq_launch.h"
 
 #ifndef FTQ_D
@@ -48,6 +49,47 @@ cudaError_t FTQ_CAT(launch_attn_split_d, FTQ_D)(int bits_k, int bits_v, bool pag
                                                 cudaStream_t stream) {
     return paged ? by_bk<true>(bits_k, bits_v, p, n_lb, stream)
                  : by_bk<false>(bits_k, bits_v, p, n_lb, stream);
+}
+
+template <int BK, int BV, bool SHARED, int NH>
+static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream) {
+    constexpr int D = FTQ_D;
+    constexpr int smem = MmaCfg<D, BK, BV>::smem_bytes(SHARED);
+    static_assert(smem <= 227 * 1024, "shared memory budget");
+    auto kern = attn_mma_kernel<D, BK, BV, SHARED, NH>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    const dim3 grid(p.n_chunks, p.Hkv, n_lb);
+    kern<<<grid, kMmaThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int BK, int BV, bool SHARED>
+static cudaError_t run_mma(const AttnParams& p, int n_lb, cudaStream_t stream) {
+    return p.Hq / p.Hkv <= 4 ? run_mma_nh<BK, BV, SHARED, 1>(p, n_lb, stream)
+                             : run_mma_nh<BK, BV, SHARED, 2>(p, n_lb, stream);
+}
+
+template <int BK>
+static cudaError_t mma_by_bv(int bv, bool shared_lut, const AttnParams& p, int n_lb,
+                             cudaStream_t stream) {
+    if (shared_lut && bv == BK) return run_mma<BK, BK, true>(p, n_lb, stream);
+    switch (bv) {
+        case 2: return run_mma<BK, 2, false>(p, n_lb, stream);
+        case 3: return run_mma<BK, 3, false>(p, n_lb, stream);
+        case 4: return run_mma<BK, 4, false>(p, n_lb, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t FTQ_CAT(launch_attn_mma_d, FTQ_D)(int bits_k, int bits_v, bool shared_lut,
+                                              const AttnParams& p, int n_lb, cudaStream_t stream) {
+    switch (bits_k) {
+        case 2: return mma_by_bv<2>(bits_v, shared_lut, p, n_lb, stream);
+        case 3: return mma_by_bv<3>(bits_v, shared_lut, p, n_lb, stream);
+        case 4: return mma_by_bv<4>(bits_v, shared_lut, p, n_lb, stream);
+    }
+    return cudaErrorInvalidValue;
 }
 
 cudaError_t FTQ_CAT(launch_attn_merge_d, FTQ_D)(int out_dtype, const float* partials, void* out,

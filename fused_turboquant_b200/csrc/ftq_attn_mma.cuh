@@ -1,0 +1,459 @@
+// Paged split-KV decode attention, fast path: packed codes go straight from
+// HBM to registers, are dequantised through a bank-conflict-free shared-memory
+// table, and feed warp-level m16n8k16 fp16 MMAs (fp32 accumulate).  With a GQA
+// group of G query heads the products are skinny GEMMs (G x D x tokens), so the
+// per-element work no longer grows with G and every packed byte is dequantised
+// exactly once per KV head.
+//
+// Same mathematics as attn_split_kernel (ftq_attn.cuh), i.e. the fused
+// formulation of src/fused_turboquant/kernels/triton_flash_decode.py:33-324 in the
+// reference; centroids, the rotated query and the softmax weights are rounded
+// to fp16 before the MMAs, accumulation is fp32.
+//
+// Work split: CTA = (KV chunk, KV head, sequence x layer), 8 warps; each warp
+// walks pages warp, warp+8, ... of the chunk with its own online-softmax state;
+// the states are merged through shared memory at the end and written as one
+// partial row per query head (same workspace format as attn_split_kernel, so
+// attn_merge_kernel finishes both).
+//
+// Fragment maps for one 16-token page (lane = 4*g + tg), query heads handled in
+// halves of 4 (NH = 1 for a GQA group <= 4, else 2):
+//   S = K.Q^T :  A = K [16 tokens x 16 coords]: rows g / g+8 = page tokens rho(g) / rho(g)+2,
+//                    k-block kb covers coordinates (D/4)*tg + 4*kb + {0..3}
+//                B = Q^T[16 coords x 8]: column n = head n>>1 (each head twice)
+//                C[token][head tg]  (columns 2tg and 2tg+1 are the same head)
+//   the weights p*vnorm are rounded to fp16 and transposed with movmatrix, which
+//   hands lane (g, tg) the weights of head g>>1 for page tokens 4tg .. 4tg+3;
+//   O^T = V^T.P^T with reduction index k = (token, parity of d), so that the fp16
+//   pair a table lookup returns, (V[t,d], V[t,d+1]), is directly an A register:
+//                A[row = d-pair][k = (token, parity)] = V[token][2*pair + parity]
+//                B[k = (token, parity)][n = (head n>>1, parity n&1)] = p or 0
+//                C[d-pair][(head tg, parity)]: lane (g,tg) owns O[head tg][(D/8)g .. +D/8)
+//   so a lane dequantises the K slices (D/4 coordinates) of two tokens and the V
+//   slices (D/8 coordinates) of four tokens per page, all contiguous bytes, every
+//   code exactly once per KV head.
+#pragma once
+
+#include "ftq_attn.cuh"
+
+namespace ftq {
+
+constexpr int kMmaWarps = 8;
+constexpr int kMmaThreads = 32 * kMmaWarps;
+constexpr int kMmaMaxChunkPages = 1024;  // block ids of one chunk are staged in shared memory
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t ldg_nc32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];\n" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_nc64(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];\n"
+                 : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg_nc128(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// Load slice `idx` (SB bytes each, slices back to back starting at `row`, which
+// is 4-byte aligned) into ceil(SB/4) words.  Slices whose size is not a
+// multiple of 4 are cut out of the enclosing aligned chunk with funnel shifts.
+template <int SB>
+__device__ __forceinline__ void load_slice(const uint8_t* row, int idx, uint32_t (&w)[(SB + 3) / 4]) {
+    if constexpr (SB % 16 == 0) {
+#pragma unroll
+        for (int i = 0; i < SB / 16; i++) {
+            const uint4 v = ldg_nc128(row + idx * SB + 16 * i);
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    } else if constexpr (SB % 8 == 0) {
+#pragma unroll
+        for (int i = 0; i < SB / 8; i++) {
+            const uint2 v = ldg_nc64(row + idx * SB + 8 * i);
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
+    } else if constexpr (SB % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < SB / 4; i++) w[i] = ldg_nc32(row + idx * SB + 4 * i);
+    } else if constexpr (SB == 6) {  // two slices per aligned 12-byte chunk
+        const uint8_t* c = row + (idx >> 1) * 12;
+        const uint32_t x0 = ldg_nc32(c), x1 = ldg_nc32(c + 4), x2 = ldg_nc32(c + 8);
+        const bool odd = idx & 1;
+        w[0] = odd ? __funnelshift_r(x1, x2, 16) : x0;
+        w[1] = odd ? (x2 >> 16) : (x1 & 0xffffu);
+    } else if constexpr (SB == 3) {  // four slices per aligned 12-byte chunk
+        const uint8_t* c = row + (idx >> 2) * 12;
+        const uint32_t x0 = ldg_nc32(c), x1 = ldg_nc32(c + 4), x2 = ldg_nc32(c + 8);
+        const int q = idx & 3;
+        const uint32_t lo = q == 0 ? x0 : (q == 1 ? __funnelshift_r(x0, x1, 24)
+                                                  : (q == 2 ? __funnelshift_r(x1, x2, 16) : (x2 >> 8)));
+        w[0] = lo & 0xffffffu;
+    } else {
+        static_assert(SB == 2, "unsupported slice size");
+        const uint32_t x = ldg_nc32(row + (idx >> 1) * 4);
+        w[0] = (idx & 1) ? (x >> 16) : (x & 0xffffu);
+    }
+}
+
+// Shared-memory byte offset (entry * 128) of the table entry for code pair `pair`
+// of a slice: bits [pair*IW, pair*IW + IW) of the little-endian stream in w[].
+template <int IW, int NW>
+__device__ __forceinline__ uint32_t pair_index(const uint32_t (&w)[NW], int pair) {
+    constexpr uint32_t mask = ((1u << IW) - 1u) << 7;
+    const int bo = pair * IW;
+    const int j = bo >> 5, sh = bo & 31;
+    uint32_t x;
+    if (sh + IW <= 32) x = sh >= 7 ? (w[j] >> (sh - 7)) : (w[j] << (7 - sh));
+    else x = __funnelshift_r(w[j], w[j + 1 < NW ? j + 1 : j], sh - 7);
+    return x & mask;
+}
+
+template <int D, int BK, int BV>
+struct MmaCfg {
+    static constexpr int NKB = D / 16;                 // k-blocks of QK^T = n-tiles of P.V
+    static constexpr int PDK = packed_dim(D, BK), PDV = packed_dim(D, BV);
+    static constexpr int KSB = PDK / 4, VSB = PDV / 8;  // slice bytes per lane
+    static constexpr int IWK = 2 * BK, IWV = 2 * BV;    // table index width (two codes)
+    static constexpr int TKB = (1 << IWK) * 128, TVB = (1 << IWV) * 128;  // table bytes
+    static constexpr int OFF_KN = kPageTokens * PDK;
+    static constexpr int OFF_VC = OFF_KN + 2 * kPageTokens;
+    static constexpr int OFF_VN = OFF_VC + kPageTokens * PDV;
+    static constexpr int PAGE_BYTES = OFF_VN + 2 * kPageTokens;
+    static constexpr int DP = D + 4;                    // padded head stride of the merge area
+    static constexpr int MERGE_BYTES = (kMmaWarps * 8 * DP + 2 * kMmaWarps * 8) * 4;
+    static constexpr int ALIGN = TKB > TVB ? TKB : TVB;
+    __host__ __device__ static constexpr int region_bytes(bool shared_lut) {
+        const int t = shared_lut ? TKB : TKB + TVB;
+        return t > MERGE_BYTES ? t : MERGE_BYTES;
+    }
+    // dynamic shared memory: alignment slack + tables/merge region + queries + block ids
+    __host__ __device__ static constexpr int smem_bytes(bool shared_lut) {
+        return ALIGN + region_bytes(shared_lut) + 8 * D * 4 + kMmaMaxChunkPages * 4;
+    }
+};
+
+// One page worth of packed data in registers (per lane).
+template <int D, int BK, int BV>
+struct PageRegs {
+    using C = MmaCfg<D, BK, BV>;
+    uint32_t k[2][(C::KSB + 3) / 4];  // K slice tg of page tokens rho(g), rho(g) + 2
+    uint32_t v[4][(C::VSB + 3) / 4];  // V slice g of page tokens 4tg .. 4tg+3
+    uint2 kn, vn;                     // fp16 norms of page tokens 4(g>>1) .. 4(g>>1)+3
+};
+
+template <int D, int BK, int BV>
+__device__ __forceinline__ void load_page(PageRegs<D, BK, BV>& r, const uint8_t* page, int g,
+                                          int tg) {
+    using C = MmaCfg<D, BK, BV>;
+    const int ktok = 4 * (g >> 1) + (g & 1);  // rho(g)
+    load_slice<C::KSB>(page + ktok * C::PDK, tg, r.k[0]);
+    load_slice<C::KSB>(page + (ktok + 2) * C::PDK, tg, r.k[1]);
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        load_slice<C::VSB>(page + C::OFF_VC + (4 * tg + j) * C::PDV, g, r.v[j]);
+    r.kn = ldg_nc64(page + C::OFF_KN + 8 * (g >> 1));
+    r.vn = ldg_nc64(page + C::OFF_VN + 8 * (g >> 1));
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h16)));
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// NH: query-head halves (4 heads each) = ceil(group / 4).
+template <int D, int BK, int BV, bool SHARED_LUT, int NH>
+__global__ void __launch_bounds__(kMmaThreads, D == 256 ? 1 : 2)
+attn_mma_kernel(const AttnParams p) {
+    using C = MmaCfg<D, BK, BV>;
+    constexpr int NKB = C::NKB;
+    constexpr int NMT = D / 32;  // m-tiles of O^T (16 d-pairs each)
+    constexpr int E = D / kOctet;
+    constexpr int ROW = D + 4;
+    constexpr int DP = C::DP;
+
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
+    const uint32_t region = (sbase + C::ALIGN - 1) & ~static_cast<uint32_t>(C::ALIGN - 1);
+    // the larger table first, so that both start on a multiple of their own size
+    const uint32_t tk_addr = (SHARED_LUT || C::TKB >= C::TVB) ? region : region + C::TVB;
+    const uint32_t tv_addr = SHARED_LUT ? tk_addr : (C::TKB >= C::TVB ? region + C::TKB : region);
+    uint8_t* region_ptr = smem_raw + (region - sbase);
+    float* qs = reinterpret_cast<float*>(region_ptr + C::region_bytes(SHARED_LUT));  // [8][D]
+    int32_t* sblk = reinterpret_cast<int32_t*>(qs + 8 * D);                         // block ids
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, tg = lane & 3;
+
+    const int chunk = blockIdx.x;
+    const int hkv = blockIdx.y;
+    const int lb = blockIdx.z;
+    const int layer = lb / p.B;
+    const int b = lb - layer * p.B;
+    const int group = p.Hq / p.Hkv;  // <= 4 * NH
+
+    const int seq_len = p.seq_lens[b];
+    const int t0 = chunk * p.chunk_tokens;
+    const int t1 = min(seq_len, t0 + p.chunk_tokens);
+    float* prow = p.partials +
+                  ((static_cast<int64_t>(lb) * p.Hq + hkv * group) * p.n_chunks + chunk) * ROW;
+    const int64_t prow_head_stride = static_cast<int64_t>(p.n_chunks) * ROW;
+    if (t0 >= t1) {
+        if (tid < group) {
+            prow[tid * prow_head_stride + D] = -INFINITY;
+            prow[tid * prow_head_stride + D + 1] = 0.f;
+        }
+        return;
+    }
+    const int n_pages = (t1 - t0 + kPageTokens - 1) / kPageTokens;
+
+    // ---- prologue: block ids, dequantisation tables, rotated queries
+    {
+        const int32_t* btab = p.block_table + static_cast<int64_t>(b) * p.max_blocks + t0 / kPageTokens;
+        for (int i = tid; i < n_pages; i += kMmaThreads) sblk[i] = btab[i];
+        uint32_t* tk = reinterpret_cast<uint32_t*>(smem_raw + (tk_addr - sbase));
+        for (int i = tid; i < (1 << C::IWK) * 32; i += kMmaThreads) {
+            const int e = i >> 5;
+            const __half2 h = __floats2half2_rn(p.lk.v[e & ((1 << BK) - 1)],
+                                                p.lk.v[(e >> BK) & ((1 << BK) - 1)]);
+            tk[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        if constexpr (!SHARED_LUT) {
+            uint32_t* tv = reinterpret_cast<uint32_t*>(smem_raw + (tv_addr - sbase));
+            for (int i = tid; i < (1 << C::IWV) * 32; i += kMmaThreads) {
+                const int e = i >> 5;
+                const __half2 h = __floats2half2_rn(p.lv.v[e & ((1 << BV) - 1)],
+                                                    p.lv.v[(e >> BV) & ((1 << BV) - 1)]);
+                tv[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+        // one octet rotates one query head: RHT in fp32, then the softmax scale
+        const int t8 = lane & 7, o = lane >> 3;
+        const int hh = warp * 4 + o;
+        if (warp < 2) {  // 8 octets cover the (at most) 8 heads; warp-uniform
+            const bool hv = hh < group;
+            const int64_t qoff =
+                (static_cast<int64_t>(lb) * p.Hq + hkv * group + (hv ? hh : 0)) * D;
+            float a[E];
+#pragma unroll
+            for (int i = 0; i < E / 8; i++) {
+                float tmp[8];
+                const int64_t eo = qoff + 8 * (t8 + 8 * i);
+                if (p.q_dtype == kF32) load8<float>(static_cast<const float*>(p.q) + eo, tmp);
+                else if (p.q_dtype == kBF16)
+                    load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.q) + eo, tmp);
+                else load8<__half>(static_cast<const __half*>(p.q) + eo, tmp);
+#pragma unroll
+                for (int c = 0; c < 8; c++)
+                    a[8 * i + c] = __uint_as_float(__float_as_uint(tmp[c]) ^
+                                                   sign_mask(p.signs, load_coord(t8, 8 * i + c)));
+            }
+            octet_fwht<E>(a, lane);
+#pragma unroll
+            for (int k = 0; k < E; k++)
+                qs[hh * D + t8 + 8 * k] = hv ? a[k] * p.rsqrt_d * p.scale : 0.f;
+        }
+    }
+    __syncthreads();
+
+    // Q^T fragments: column n = g is head 4*hh + (g >> 1); k-block kb covers coordinates
+    // (D/4)*tg + 4*kb + {0,1} (b0) and + {2,3} (b1)
+    uint32_t qb[NH][NKB][2];
+#pragma unroll
+    for (int hh = 0; hh < NH; hh++)
+#pragma unroll
+        for (int kb = 0; kb < NKB; kb++) {
+            const float* q4 = qs + (4 * hh + (g >> 1)) * D + (D / 4) * tg + 4 * kb;
+            const __half2 lo = __floats2half2_rn(q4[0], q4[1]);
+            const __half2 hi = __floats2half2_rn(q4[2], q4[3]);
+            qb[hh][kb][0] = *reinterpret_cast<const uint32_t*>(&lo);
+            qb[hh][kb][1] = *reinterpret_cast<const uint32_t*>(&hi);
+        }
+
+    const uint32_t lk_lane = tk_addr + lane * 4;
+    const uint32_t lv_lane = tv_addr + lane * 4;
+    const uint8_t* pool = p.pool + layer * p.pool_layer_stride;
+    const bool odd = g & 1;
+
+    // per lane: softmax state of head 4*hh + tg, O[head][(D/8)*g .. + D/8)
+    float m_run[NH], l_run[NH], oacc[NH][NMT][4];
+#pragma unroll
+    for (int hh = 0; hh < NH; hh++) {
+        m_run[hh] = -INFINITY;
+        l_run[hh] = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < NMT; mt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) oacc[hh][mt][i] = 0.f;
+    }
+
+    auto page_ptr = [&](int pg) {
+        return pool + (static_cast<int64_t>(sblk[pg]) * p.Hkv + hkv) * C::PAGE_BYTES;
+    };
+
+    auto compute = [&](const PageRegs<D, BK, BV>& r, int pg) {
+        const int ntok = min(kPageTokens, t1 - t0 - pg * kPageTokens);
+        const int tokA = 4 * (g >> 1) + (g & 1), tokB = tokA + 2;  // rows g, g+8 of S
+        const bool okA = tokA < ntok, okB = tokB < ntok;
+
+        // ---- S = K.Q^T (two accumulator chains per head half)
+        float c[NH][2][4];
+#pragma unroll
+        for (int hh = 0; hh < NH; hh++)
+#pragma unroll
+            for (int z = 0; z < 2; z++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) c[hh][z][i] = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < NKB; kb++) {
+            const uint32_t a0 = lds32(lk_lane | pair_index<C::IWK>(r.k[0], 2 * kb));
+            const uint32_t a1 = lds32(lk_lane | pair_index<C::IWK>(r.k[1], 2 * kb));
+            const uint32_t a2 = lds32(lk_lane | pair_index<C::IWK>(r.k[0], 2 * kb + 1));
+            const uint32_t a3 = lds32(lk_lane | pair_index<C::IWK>(r.k[1], 2 * kb + 1));
+#pragma unroll
+            for (int hh = 0; hh < NH; hh++)
+                mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qb[hh][kb][0], qb[hh][kb][1]);
+        }
+        const float kna = half_bits_to_float(odd ? r.kn.x >> 16 : r.kn.x & 0xffffu);
+        const float knb = half_bits_to_float(odd ? r.kn.y >> 16 : r.kn.y & 0xffffu);
+        const float vna = okA ? half_bits_to_float(odd ? r.vn.x >> 16 : r.vn.x & 0xffffu) : 0.f;
+        const float vnb = okB ? half_bits_to_float(odd ? r.vn.y >> 16 : r.vn.y & 0xffffu) : 0.f;
+
+        // ---- online softmax per head (4*hh + tg); weights to fp16, transposed for P.V
+        uint32_t pb[NH][2][2];  // [hh][k-step][b0/b1]
+#pragma unroll
+        for (int hh = 0; hh < NH; hh++) {
+            const float sa = okA ? (c[hh][0][0] + c[hh][1][0]) * kna : -INFINITY;
+            const float sb = okB ? (c[hh][0][2] + c[hh][1][2]) * knb : -INFINITY;
+            float mx = fmaxf(sa, sb);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[hh], mx);  // finite: page token 0 is valid
+            if (m_new != m_run[hh]) {                  // same decision in all lanes of a head
+                const float corr = m_run[hh] == -INFINITY ? 0.f : __expf(m_run[hh] - m_new);
+                l_run[hh] *= corr;
+#pragma unroll
+                for (int mt = 0; mt < NMT; mt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) oacc[hh][mt][i] *= corr;
+                m_run[hh] = m_new;
+            }
+            const float pa = okA ? __expf(sa - m_new) : 0.f;
+            const float pbv = okB ? __expf(sb - m_new) : 0.f;
+            l_run[hh] += pa + pbv;
+            const uint32_t ha = __half_as_ushort(__float2half_rn(pa * vna));
+            const uint32_t hb = __half_as_ushort(__float2half_rn(pbv * vnb));
+            // M[token row][column n] with both columns of a head equal; transposed, lane (g, tg)
+            // receives head g>>1, page tokens 4tg, 4tg+1 (first) and 4tg+2, 4tg+3 (second)
+            const uint32_t t0w = movmatrix_trans(ha | (ha << 16));
+            const uint32_t t1w = movmatrix_trans(hb | (hb << 16));
+            pb[hh][0][0] = odd ? (t0w << 16) : (t0w & 0xffffu);
+            pb[hh][0][1] = odd ? (t0w & 0xffff0000u) : (t0w >> 16);
+            pb[hh][1][0] = odd ? (t1w << 16) : (t1w & 0xffffu);
+            pb[hh][1][1] = odd ? (t1w & 0xffff0000u) : (t1w >> 16);
+        }
+
+        // ---- O^T += V^T.P^T : rows = d-pairs (D/16)*g + 2*mt + {0,1}, k = (token, parity)
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+            for (int mt = 0; mt < NMT; mt++) {
+                const uint32_t a0 = lds32(lv_lane | pair_index<C::IWV>(r.v[2 * ks], 2 * mt));
+                const uint32_t a1 = lds32(lv_lane | pair_index<C::IWV>(r.v[2 * ks], 2 * mt + 1));
+                const uint32_t a2 = lds32(lv_lane | pair_index<C::IWV>(r.v[2 * ks + 1], 2 * mt));
+                const uint32_t a3 = lds32(lv_lane | pair_index<C::IWV>(r.v[2 * ks + 1], 2 * mt + 1));
+#pragma unroll
+                for (int hh = 0; hh < NH; hh++)
+                    mma_16816(oacc[hh][mt], a0, a1, a2, a3, pb[hh][ks][0], pb[hh][ks][1]);
+            }
+    };
+
+    // ---- main loop: the warp's pages, next page's loads in flight during the math
+    PageRegs<D, BK, BV> ra, rb;
+    int pg = warp;
+    if (pg < n_pages) load_page<D, BK, BV>(ra, page_ptr(pg), g, tg);
+    while (pg < n_pages) {
+        if (pg + kMmaWarps < n_pages) load_page<D, BK, BV>(rb, page_ptr(pg + kMmaWarps), g, tg);
+        compute(ra, pg);
+        pg += kMmaWarps;
+        if (pg >= n_pages) break;
+        if (pg + kMmaWarps < n_pages) load_page<D, BK, BV>(ra, page_ptr(pg + kMmaWarps), g, tg);
+        compute(rb, pg);
+        pg += kMmaWarps;
+    }
+
+    // ---- merge the warps through shared memory (the tables are dead now)
+#pragma unroll
+    for (int hh = 0; hh < NH; hh++) {
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
+    }
+    __syncthreads();
+    float* wacc = reinterpret_cast<float*>(region_ptr);  // [warps][8][DP]
+    float* wm = wacc + kMmaWarps * 8 * DP;               // [warps][8]
+    float* wl = wm + kMmaWarps * 8;                      // [warps][8]
+#pragma unroll
+    for (int hh = 0; hh < NH; hh++) {
+        const int h = 4 * hh + tg;
+        float* dst = wacc + (warp * 8 + h) * DP + (D / 8) * g;
+#pragma unroll
+        for (int mt = 0; mt < NMT; mt++)
+            *reinterpret_cast<float4*>(dst + 4 * mt) =
+                make_float4(oacc[hh][mt][0], oacc[hh][mt][1], oacc[hh][mt][2], oacc[hh][mt][3]);
+        if (g == 0) {
+            wm[warp * 8 + h] = m_run[hh];
+            wl[warp * 8 + h] = l_run[hh];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < group * D; idx += kMmaThreads) {
+        const int h = idx / D, d = idx - h * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w2 = 0; w2 < kMmaWarps; w2++) M = fmaxf(M, wm[w2 * 8 + h]);
+        float a = 0.f, l = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < kMmaWarps; w2++) {
+            const float mw = wm[w2 * 8 + h];
+            if (mw != -INFINITY) {
+                const float f = __expf(mw - M);
+                a = fmaf(wacc[(w2 * 8 + h) * DP + d], f, a);
+                l = fmaf(wl[w2 * 8 + h], f, l);
+            }
+        }
+        prow[h * prow_head_stride + d] = a;
+        if (d == 0) {
+            prow[h * prow_head_stride + D] = M;
+            prow[h * prow_head_stride + D + 1] = l;
+        }
+    }
+}
+
+}  // namespace ftq

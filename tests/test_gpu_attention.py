@@ -119,8 +119,22 @@ def test_paged_decode_vs_oracle(oracle, tables, d, G, bk, bv):
                                 S, layer=0)
     ref_b = oracle.decode_attn(qb.float().cpu().numpy(), k_idx, k_n, v_idx, v_n, _lv(tables, d, bk),
                                _lv(tables, d, bv), signs, d ** -0.5, bk, bv, seq_lens=seq_lens)
-    ref_b = torch.from_numpy(ref_b).bfloat16().float().numpy()
-    assert gate(out_b.float().cpu().numpy(), ref_b) <= max(1, out_b.numel() // 500)
+    # 16-bit queries run the tensor-core kernel (fp16 centroids / weights, fp32 accumulate):
+    # with an fp32 output buffer its own error is visible without the bf16 output rounding
+    out32 = kv.decode_attention(qb, torch.from_numpy(bt).cuda(), torch.from_numpy(seq_lens).cuda(),
+                                S, layer=0, out=torch.empty(q.shape, dtype=torch.float32, device="cuda"))
+    assert gate(out32.cpu().numpy(), ref_b) == 0, np.abs(out32.cpu().numpy() - ref_b).max()
+    # the bf16 output is exactly the rounding of that fp32 result; what is left against the
+    # bf16-rounded oracle are single-ulp rounding flips (1 bf16 ulp is up to 7.8e-3 relative)
+    assert torch.equal(out_b, out32.bfloat16())
+    ref_r = torch.from_numpy(ref_b).bfloat16().float().numpy()
+    ob = out_b.float().cpu().numpy()
+    tol = 1e-3 + 2e-3 * np.abs(ref_r)
+    viol = np.abs(ob - ref_r) > tol
+    ulp = np.abs(ref_r) * 2.0 ** -7 + 1e-30          # upper bound of one bf16 ulp
+    # two roundings (ours and the oracle's) can add at most one ulp to an in-gate difference
+    assert (np.abs(ob - ref_r) <= tol + ulp).all(), "bf16 output off by more than rounding"
+    assert viol.mean() < 0.05
 
 
 @pytest.mark.parametrize("d,bk,bv,dtype", [(128, 4, 4, torch.bfloat16), (64, 3, 3, torch.bfloat16),
