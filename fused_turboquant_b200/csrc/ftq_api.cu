@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cfloat>
 #include <cstring>
 #include <mutex>
 
@@ -70,13 +71,51 @@ int make_encode_tables(int d, int bits, const float* signs_host, const float* bo
     return FTQ_OK;
 }
 
+// Table quantizer of the throughput encode kernel: x is mapped to a cell of [-1, 1] by
+// the same single-precision FMA the kernel uses; usable when no cell holds two boundaries
+// and no boundary is so close to zero that a 2^100 scaling cannot separate it from x.
+uint32_t quant_cell(float x) {
+    const float v = fmaf(x, ftq::kCellScale, ftq::kCellMagic);
+    uint32_t bits;
+    memcpy(&bits, &v, 4);
+    return (bits & 0xFF80u) >> 7;
+}
+
+bool make_encode2_tables(const ftq::EncodeTables& tab, int bits, ftq::Encode2Tables* out) {
+    const int nb = (1 << bits) - 1;  // interior boundaries, ascending
+    out->signs = tab.signs;
+    out->rsqrt_d = tab.rsqrt_d;
+    for (int c = 0; c < ftq::kQuantCells; c++) {
+        out->cells[c].neg_thr_scaled = -FLT_MAX;
+        out->cells[c].base = 0.f;
+    }
+    uint32_t prev = 0xffffffffu;
+    for (int j = 0; j < nb; j++) {
+        const float b = tab.bounds[j];
+        if (!(b > -1.0f && b < 1.0f) || (j > 0 && !(tab.bounds[j - 1] < b))) return false;
+        if (std::fabs(b) < 1e-20f) return false;
+        const uint32_t c = quant_cell(b);
+        if (c == prev || c >= static_cast<uint32_t>(ftq::kQuantCells)) return false;
+        prev = c;
+        out->cells[c].neg_thr_scaled = -b * ftq::kStepScale;
+        for (uint32_t k = c + 1; k < static_cast<uint32_t>(ftq::kQuantCells); k++)
+            out->cells[k].base += 1.f;
+    }
+    return true;
+}
+
 cudaError_t dispatch_encode(int d, int bits, int dtype, const ftq::EncodeSource& src,
                             const ftq::EncodeSink& sink, const ftq::EncodeTables& tab,
                             int64_t n_vec, int n_layers, cudaStream_t st) {
+    // A handful of vectors (a decode step) is launch-bound either way: the simple kernel
+    // skips the table set-up.  Bulk encodes take the throughput kernel when the codebook allows.
+    ftq::Encode2Tables tab2;
+    const bool fast = n_vec >= 2048 && make_encode2_tables(tab, bits, &tab2);
+    const ftq::Encode2Tables* t2 = fast ? &tab2 : nullptr;
     switch (d) {
-        case 64: return ftq::launch_encode_d64(bits, dtype, src, sink, tab, n_vec, n_layers, st);
-        case 128: return ftq::launch_encode_d128(bits, dtype, src, sink, tab, n_vec, n_layers, st);
-        case 256: return ftq::launch_encode_d256(bits, dtype, src, sink, tab, n_vec, n_layers, st);
+        case 64: return ftq::launch_encode_d64(bits, dtype, src, sink, tab, t2, n_vec, n_layers, st);
+        case 128: return ftq::launch_encode_d128(bits, dtype, src, sink, tab, t2, n_vec, n_layers, st);
+        case 256: return ftq::launch_encode_d256(bits, dtype, src, sink, tab, t2, n_vec, n_layers, st);
     }
     return cudaErrorInvalidValue;
 }
@@ -104,23 +143,32 @@ ChunkPlan plan_chunks(int B, int Hq, int Hkv, int d, int max_seq_len, int n_laye
     return pl;
 }
 
-// Chunking of the tensor-core path: chunks of at least 2048 tokens (the per-CTA table build and
-// query rotation must stay small against the streaming work), at most 16384 (block ids of a
-// chunk are staged in shared memory), otherwise enough chunks for ~4 waves of 2 CTAs per SM.
-ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers) {
+// Chunking of the tensor-core path (persistent CTAs): few, large chunks keep the per-item
+// prologue and merge small; the chunk count is the smallest one whose item count fills the
+// CTA slots in whole waves to >= 95 % (else the best found).  Chunks hold at most 16384 tokens
+// (the block ids of a chunk are staged in shared memory) and at least 1024.
+ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers, int ctas_per_sm) {
     ChunkPlan pl;
     pl.n_hpass = 1;
     const int64_t units = static_cast<int64_t>(B) * Hkv * n_layers;
-    const int64_t target = static_cast<int64_t>(ftq::sm_count()) * 2 * 4;
-    int64_t want = (target + units - 1) / (units > 0 ? units : 1);
-    if (want < 1) want = 1;
+    const int64_t slots = static_cast<int64_t>(ftq::sm_count()) * ctas_per_sm;
     const int seq = max_seq_len > 0 ? max_seq_len : 1;
-    int64_t ct = (seq + want - 1) / want;
-    ct = (ct + 63) / 64 * 64;
-    if (ct < 2048) ct = 2048;
-    if (ct > 16384) ct = 16384;
-    pl.chunk_tokens = static_cast<int>(ct);
-    pl.n_chunks = static_cast<int>((seq + ct - 1) / ct);
+    const int c_min = (seq + 16383) / 16384;
+    const int c_max = (seq + 1023) / 1024 > c_min ? (seq + 1023) / 1024 : c_min;
+    int best_nc = c_min, best_ct = 0;
+    double best_eff = -1.0;
+    for (int nc = c_min; nc <= c_max && nc < c_min + 64; nc++) {
+        int ct = ((seq + nc - 1) / nc + 63) / 64 * 64;
+        if (ct > 16384) ct = 16384;
+        const int real_nc = (seq + ct - 1) / ct;
+        const int64_t items = units * real_nc;
+        const int64_t waves = (items + slots - 1) / slots;
+        const double eff = static_cast<double>(items) / static_cast<double>(waves * slots);
+        if (eff > best_eff + 1e-9) { best_eff = eff; best_nc = real_nc; best_ct = ct; }
+        if (eff >= 0.95) { best_nc = real_nc; best_ct = ct; break; }
+    }
+    pl.chunk_tokens = best_ct;
+    pl.n_chunks = best_nc;
     return pl;
 }
 
@@ -398,10 +446,14 @@ size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_
     if (!dim_ok(head_dim) || B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_layers <= 0) return 0;
     // the larger of the two paths' needs, so one buffer serves whichever kernel runs
     const ChunkPlan a = plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
-    const ChunkPlan m = plan_chunks_mma(B, Hkv, max_seq_len, n_layers);
-    const size_t na = partial_bytes(a, B, Hq, head_dim, n_layers);
-    const size_t nm = partial_bytes(m, B, Hq, head_dim, n_layers);
-    return na > nm ? na : nm;
+    const ChunkPlan m1 = plan_chunks_mma(B, Hkv, max_seq_len, n_layers, 1);
+    const ChunkPlan m2 = plan_chunks_mma(B, Hkv, max_seq_len, n_layers, 2);
+    size_t n = partial_bytes(a, B, Hq, head_dim, n_layers);
+    const size_t n1 = partial_bytes(m1, B, Hq, head_dim, n_layers);
+    const size_t n2 = partial_bytes(m2, B, Hq, head_dim, n_layers);
+    if (n1 > n) n = n1;
+    if (n2 > n) n = n2;
+    return n;
 }
 
 static int check_attn_common(int B, int Hq, int Hkv, int head_dim, int bits_k, int bits_v,
@@ -530,7 +582,9 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     // 16-bit queries with a GQA group of at most 8 take the tensor-core kernel; fp32 queries
     // (and larger groups) take the fp32 kernel.
     const bool mma = use_mma_path(Hq, Hkv, q_dtype);
-    const ChunkPlan pl = mma ? plan_chunks_mma(B, Hkv, max_seq_len, n_layers)
+    // one CTA per SM when a 4-bit byte table is in use (or head_dim 256), else two
+    const int mma_ctas = (bits_k == 4 || bits_v == 4 || head_dim == 256) ? 1 : 2;
+    const ChunkPlan pl = mma ? plan_chunks_mma(B, Hkv, max_seq_len, n_layers, mma_ctas)
                              : plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     const size_t need = ftq_decode_workspace_bytes(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     if (!workspace || workspace_bytes < need)

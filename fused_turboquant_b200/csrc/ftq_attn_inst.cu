@@ -54,13 +54,16 @@ cudaError_t FTQ_CAT(launch_attn_split_d, FTQ_D)(int bits_k, int bits_v, bool pag
 template <int BK, int BV, bool SHARED, int NH>
 static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream) {
     constexpr int D = FTQ_D;
-    constexpr int smem = MmaCfg<D, BK, BV>::smem_bytes(SHARED);
-    static_assert(smem <= 227 * 1024, "shared memory budget");
+    using C = MmaCfg<D, BK, BV, NH>;
+    static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory budget");
     auto kern = attn_mma_kernel<D, BK, BV, SHARED, NH>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    const dim3 grid(p.n_chunks, p.Hkv, n_lb);
-    kern<<<grid, kMmaThreads, smem, stream>>>(p);
+    const int64_t items = static_cast<int64_t>(p.n_chunks) * p.Hkv * n_lb;
+    const int64_t slots = static_cast<int64_t>(sm_count()) * C::CTAS_PER_SM;
+    const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
+    kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, static_cast<int>(items));
     return cudaGetLastError();
 }
 

@@ -10,11 +10,20 @@
 // reference; centroids, the rotated query and the softmax weights are rounded
 // to fp16 before the MMAs, accumulation is fp32.
 //
-// Work split: CTA = (KV chunk, KV head, sequence x layer), 8 warps; each warp
-// walks pages warp, warp+8, ... of the chunk with its own online-softmax state;
-// the states are merged through shared memory at the end and written as one
-// partial row per query head (same workspace format as attn_split_kernel, so
-// attn_merge_kernel finishes both).
+// Work split: persistent CTAs (one per SM with 16 warps when a 4-bit byte table
+// is in use, else two per SM with 8 warps) loop over work items
+// (KV chunk, KV head, sequence x layer); the dequantisation tables are built once
+// per CTA.  Within an item each warp walks pages warp, warp+W, ... with its own
+// online-softmax state; the states are merged pairwise (registers + a small
+// shared exchange area) and warp 0 writes one partial row per query head (same
+// workspace format as attn_split_kernel, so attn_merge_kernel finishes both).
+//
+// Tables: an entry holds the fp16 centroids of two adjacent codes, replicated
+// for the 32 lanes so that bank = lane (no conflicts whatever the codes are).
+// 4-bit codes index by byte: the table occupies a 64 KB-aligned window with
+// 256-byte rows, so that the address is one byte-permute -- the code byte
+// dropped into bits 8..15 of the lane's base address.  3- and 2-bit codes use
+// 128-byte rows in a table aligned to its own size (shift + and/or).
 //
 // Fragment maps for one 16-token page (lane = 4*g + tg), query heads handled in
 // halves of 4 (NH = 1 for a GQA group <= 4, else 2):
@@ -38,8 +47,6 @@
 
 namespace ftq {
 
-constexpr int kMmaWarps = 8;
-constexpr int kMmaThreads = 32 * kMmaWarps;
 constexpr int kMmaMaxChunkPages = 1024;  // block ids of one chunk are staged in shared memory
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -128,52 +135,54 @@ __device__ __forceinline__ uint32_t pair_index(const uint32_t (&w)[NW], int pair
     return x & mask;
 }
 
-template <int D, int BK, int BV>
+// Shared-memory address of the table entry for code pair `pair` of a slice.
+//   IW == 8 (4-bit): lane_base = window | table half | lane*4; the code byte becomes byte 1.
+//   IW  < 8        : lane_base = table | lane*4; entry * 128 is or-ed in.
+template <int IW, int NW>
+__device__ __forceinline__ uint32_t entry_addr(const uint32_t (&w)[NW], int pair, uint32_t lane_base) {
+    if constexpr (IW == 8) {
+        const int j = pair >> 2, k = pair & 3;
+        return __byte_perm(w[j], lane_base, 0x7604u | (static_cast<uint32_t>(k) << 4));
+    } else {
+        return lane_base | pair_index<IW>(w, pair);
+    }
+}
+
+template <int D, int BK, int BV, int NH>
 struct MmaCfg {
-    static constexpr int NKB = D / 16;                 // k-blocks of QK^T = n-tiles of P.V
+    static constexpr int NKB = D / 16;                  // k-blocks of K.Q^T
+    static constexpr int NMT = D / 32;                  // m-tiles of O^T
     static constexpr int PDK = packed_dim(D, BK), PDV = packed_dim(D, BV);
     static constexpr int KSB = PDK / 4, VSB = PDV / 8;  // slice bytes per lane
     static constexpr int IWK = 2 * BK, IWV = 2 * BV;    // table index width (two codes)
-    static constexpr int TKB = (1 << IWK) * 128, TVB = (1 << IWV) * 128;  // table bytes
+    static constexpr bool BYTE = BK == 4 || BV == 4;    // a 64 KB byte-indexed window is used
+    // head_dim 256 needs > 128 registers per thread: 8 warps, one CTA per SM
+    static constexpr int WARPS = (BYTE && D != 256) ? 16 : 8;
+    static constexpr int THREADS = 32 * WARPS;
+    static constexpr int CTAS_PER_SM = (BYTE || D == 256) ? 1 : 2;
     static constexpr int OFF_KN = kPageTokens * PDK;
     static constexpr int OFF_VC = OFF_KN + 2 * kPageTokens;
     static constexpr int OFF_VN = OFF_VC + kPageTokens * PDV;
     static constexpr int PAGE_BYTES = OFF_VN + 2 * kPageTokens;
-    static constexpr int DP = D + 4;                    // padded head stride of the merge area
-    static constexpr int MERGE_BYTES = (kMmaWarps * 8 * DP + 2 * kMmaWarps * 8) * 4;
-    static constexpr int ALIGN = TKB > TVB ? TKB : TVB;
-    __host__ __device__ static constexpr int region_bytes(bool shared_lut) {
-        const int t = shared_lut ? TKB : TKB + TVB;
-        return t > MERGE_BYTES ? t : MERGE_BYTES;
-    }
-    // dynamic shared memory: alignment slack + tables/merge region + queries + block ids
-    __host__ __device__ static constexpr int smem_bytes(bool shared_lut) {
-        return ALIGN + region_bytes(shared_lut) + 8 * D * 4 + kMmaMaxChunkPages * 4;
-    }
+    // small (non-byte) tables, each aligned to its own size
+    static constexpr int TKS = BK == 4 ? 0 : (1 << IWK) * 128;
+    static constexpr int TVS = BV == 4 ? 0 : (1 << IWV) * 128;
+    static constexpr int SMALL_ALIGN = TKS > TVS ? TKS : TVS;
+    static constexpr int SMALL_BYTES = TKS + TVS + SMALL_ALIGN;  // incl. alignment slack
+    // exchange area of the pairwise merge: WARPS/2 slots x 32 lanes x state
+    static constexpr int STATE_F4 = NH * NMT;                    // float4 items per lane
+    static constexpr int XCHG_BYTES = (WARPS / 2) * 32 * (STATE_F4 * 16 + NH * 8);
+    static constexpr int AUX_BYTES = SMALL_BYTES + XCHG_BYTES + 8 * D * 4 + kMmaMaxChunkPages * 4 + 64;
+    static constexpr int SMEM_BYTES = BYTE ? 2 * 65536 + AUX_BYTES : AUX_BYTES;
 };
 
 // One page worth of packed data in registers (per lane).
-template <int D, int BK, int BV>
+template <int KSB, int VSB>
 struct PageRegs {
-    using C = MmaCfg<D, BK, BV>;
-    uint32_t k[2][(C::KSB + 3) / 4];  // K slice tg of page tokens rho(g), rho(g) + 2
-    uint32_t v[4][(C::VSB + 3) / 4];  // V slice g of page tokens 4tg .. 4tg+3
-    uint2 kn, vn;                     // fp16 norms of page tokens 4(g>>1) .. 4(g>>1)+3
+    uint32_t k[2][(KSB + 3) / 4];  // K slice tg of page tokens rho(g), rho(g) + 2
+    uint32_t v[4][(VSB + 3) / 4];  // V slice g of page tokens 4tg .. 4tg+3
+    uint2 kn, vn;                  // fp16 norms of page tokens 4(g>>1) .. 4(g>>1)+3
 };
-
-template <int D, int BK, int BV>
-__device__ __forceinline__ void load_page(PageRegs<D, BK, BV>& r, const uint8_t* page, int g,
-                                          int tg) {
-    using C = MmaCfg<D, BK, BV>;
-    const int ktok = 4 * (g >> 1) + (g & 1);  // rho(g)
-    load_slice<C::KSB>(page + ktok * C::PDK, tg, r.k[0]);
-    load_slice<C::KSB>(page + (ktok + 2) * C::PDK, tg, r.k[1]);
-#pragma unroll
-    for (int j = 0; j < 4; j++)
-        load_slice<C::VSB>(page + C::OFF_VC + (4 * tg + j) * C::PDV, g, r.v[j]);
-    r.kn = ldg_nc64(page + C::OFF_KN + 8 * (g >> 1));
-    r.vn = ldg_nc64(page + C::OFF_VN + 8 * (g >> 1));
-}
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h16)));
@@ -185,274 +194,334 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     return d;
 }
 
-// NH: query-head halves (4 heads each) = ceil(group / 4).
 template <int D, int BK, int BV, bool SHARED_LUT, int NH>
-__global__ void __launch_bounds__(kMmaThreads, D == 256 ? 1 : 2)
-attn_mma_kernel(const AttnParams p) {
-    using C = MmaCfg<D, BK, BV>;
-    constexpr int NKB = C::NKB;
-    constexpr int NMT = D / 32;  // m-tiles of O^T (16 d-pairs each)
+__global__ void __launch_bounds__(MmaCfg<D, BK, BV, NH>::THREADS, MmaCfg<D, BK, BV, NH>::CTAS_PER_SM)
+attn_mma_kernel(const AttnParams p, int n_items) {
+    using C = MmaCfg<D, BK, BV, NH>;
+    constexpr int NKB = C::NKB, NMT = C::NMT, WARPS = C::WARPS, THREADS = C::THREADS;
     constexpr int E = D / kOctet;
     constexpr int ROW = D + 4;
-    constexpr int DP = C::DP;
+    using Regs = PageRegs<C::KSB, C::VSB>;
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
-    const uint32_t region = (sbase + C::ALIGN - 1) & ~static_cast<uint32_t>(C::ALIGN - 1);
-    // the larger table first, so that both start on a multiple of their own size
-    const uint32_t tk_addr = (SHARED_LUT || C::TKB >= C::TVB) ? region : region + C::TVB;
-    const uint32_t tv_addr = SHARED_LUT ? tk_addr : (C::TKB >= C::TVB ? region + C::TKB : region);
-    uint8_t* region_ptr = smem_raw + (region - sbase);
-    float* qs = reinterpret_cast<float*>(region_ptr + C::region_bytes(SHARED_LUT));  // [8][D]
-    int32_t* sblk = reinterpret_cast<int32_t*>(qs + 8 * D);                         // block ids
+    // ---- carve shared memory (addresses in the shared window)
+    uint32_t window = 0, aux = sbase;
+    if constexpr (C::BYTE) {
+        window = (sbase + 65535u) & ~65535u;
+        aux = (window - sbase >= static_cast<uint32_t>(C::AUX_BYTES)) ? sbase : window + 65536u;
+    }
+    uint32_t tk_small = 0, tv_small = 0, cur = aux;
+    if constexpr (C::SMALL_ALIGN > 0) {
+        cur = (aux + C::SMALL_ALIGN - 1) & ~static_cast<uint32_t>(C::SMALL_ALIGN - 1);
+        if (C::TKS >= C::TVS) { tk_small = cur; tv_small = cur + C::TKS; }
+        else { tv_small = cur; tk_small = cur + C::TVS; }
+        cur += C::TKS + C::TVS;
+        if (SHARED_LUT) tv_small = tk_small;
+    }
+    cur = (cur + 15u) & ~15u;
+    auto gptr = [&](uint32_t saddr) { return smem_raw + (saddr - sbase); };
+    float4* xchg = reinterpret_cast<float4*>(gptr(cur));  // [WARPS/2][STATE_F4][32] then m/l
+    float* xml = reinterpret_cast<float*>(gptr(cur + (WARPS / 2) * 32 * C::STATE_F4 * 16));
+    float* qs = reinterpret_cast<float*>(gptr(cur + C::XCHG_BYTES));  // [8][D]
+    int32_t* sblk = reinterpret_cast<int32_t*>(qs + 8 * D);           // block ids of the chunk
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tg = lane & 3;
-
-    const int chunk = blockIdx.x;
-    const int hkv = blockIdx.y;
-    const int lb = blockIdx.z;
-    const int layer = lb / p.B;
-    const int b = lb - layer * p.B;
+    const bool odd = g & 1;
     const int group = p.Hq / p.Hkv;  // <= 4 * NH
 
-    const int seq_len = p.seq_lens[b];
-    const int t0 = chunk * p.chunk_tokens;
-    const int t1 = min(seq_len, t0 + p.chunk_tokens);
-    float* prow = p.partials +
-                  ((static_cast<int64_t>(lb) * p.Hq + hkv * group) * p.n_chunks + chunk) * ROW;
-    const int64_t prow_head_stride = static_cast<int64_t>(p.n_chunks) * ROW;
-    if (t0 >= t1) {
-        if (tid < group) {
-            prow[tid * prow_head_stride + D] = -INFINITY;
-            prow[tid * prow_head_stride + D + 1] = 0.f;
+    // ---- once per CTA: dequantisation tables
+    if constexpr (C::BYTE) {
+        uint32_t* tb = reinterpret_cast<uint32_t*>(gptr(window));
+        for (int i = tid; i < 256 * 64; i += THREADS) {
+            const int e = i >> 6, col = i & 63;
+            if (col < 32) {
+                if constexpr (BK == 4) {
+                    const __half2 h = __floats2half2_rn(p.lk.v[e & 15], p.lk.v[e >> 4]);
+                    tb[i] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+            } else if constexpr (BV == 4 && !SHARED_LUT) {
+                const __half2 h = __floats2half2_rn(p.lv.v[e & 15], p.lv.v[e >> 4]);
+                tb[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
         }
-        return;
     }
-    const int n_pages = (t1 - t0 + kPageTokens - 1) / kPageTokens;
-
-    // ---- prologue: block ids, dequantisation tables, rotated queries
-    {
-        const int32_t* btab = p.block_table + static_cast<int64_t>(b) * p.max_blocks + t0 / kPageTokens;
-        for (int i = tid; i < n_pages; i += kMmaThreads) sblk[i] = btab[i];
-        uint32_t* tk = reinterpret_cast<uint32_t*>(smem_raw + (tk_addr - sbase));
-        for (int i = tid; i < (1 << C::IWK) * 32; i += kMmaThreads) {
+    if constexpr (BK != 4) {
+        uint32_t* t = reinterpret_cast<uint32_t*>(gptr(tk_small));
+        for (int i = tid; i < (1 << C::IWK) * 32; i += THREADS) {
             const int e = i >> 5;
-            const __half2 h = __floats2half2_rn(p.lk.v[e & ((1 << BK) - 1)],
-                                                p.lk.v[(e >> BK) & ((1 << BK) - 1)]);
-            tk[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        if constexpr (!SHARED_LUT) {
-            uint32_t* tv = reinterpret_cast<uint32_t*>(smem_raw + (tv_addr - sbase));
-            for (int i = tid; i < (1 << C::IWV) * 32; i += kMmaThreads) {
-                const int e = i >> 5;
-                const __half2 h = __floats2half2_rn(p.lv.v[e & ((1 << BV) - 1)],
-                                                    p.lv.v[(e >> BV) & ((1 << BV) - 1)]);
-                tv[i] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-        }
-        // one octet rotates one query head: RHT in fp32, then the softmax scale
-        const int t8 = lane & 7, o = lane >> 3;
-        const int hh = warp * 4 + o;
-        if (warp < 2) {  // 8 octets cover the (at most) 8 heads; warp-uniform
-            const bool hv = hh < group;
-            const int64_t qoff =
-                (static_cast<int64_t>(lb) * p.Hq + hkv * group + (hv ? hh : 0)) * D;
-            float a[E];
-#pragma unroll
-            for (int i = 0; i < E / 8; i++) {
-                float tmp[8];
-                const int64_t eo = qoff + 8 * (t8 + 8 * i);
-                if (p.q_dtype == kF32) load8<float>(static_cast<const float*>(p.q) + eo, tmp);
-                else if (p.q_dtype == kBF16)
-                    load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.q) + eo, tmp);
-                else load8<__half>(static_cast<const __half*>(p.q) + eo, tmp);
-#pragma unroll
-                for (int c = 0; c < 8; c++)
-                    a[8 * i + c] = __uint_as_float(__float_as_uint(tmp[c]) ^
-                                                   sign_mask(p.signs, load_coord(t8, 8 * i + c)));
-            }
-            octet_fwht<E>(a, lane);
-#pragma unroll
-            for (int k = 0; k < E; k++)
-                qs[hh * D + t8 + 8 * k] = hv ? a[k] * p.rsqrt_d * p.scale : 0.f;
+            const __half2 h = __floats2half2_rn(p.lk.v[e & ((1 << BK) - 1)], p.lk.v[e >> BK]);
+            t[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
     }
-    __syncthreads();
-
-    // Q^T fragments: column n = g is head 4*hh + (g >> 1); k-block kb covers coordinates
-    // (D/4)*tg + 4*kb + {0,1} (b0) and + {2,3} (b1)
-    uint32_t qb[NH][NKB][2];
-#pragma unroll
-    for (int hh = 0; hh < NH; hh++)
-#pragma unroll
-        for (int kb = 0; kb < NKB; kb++) {
-            const float* q4 = qs + (4 * hh + (g >> 1)) * D + (D / 4) * tg + 4 * kb;
-            const __half2 lo = __floats2half2_rn(q4[0], q4[1]);
-            const __half2 hi = __floats2half2_rn(q4[2], q4[3]);
-            qb[hh][kb][0] = *reinterpret_cast<const uint32_t*>(&lo);
-            qb[hh][kb][1] = *reinterpret_cast<const uint32_t*>(&hi);
+    if constexpr (BV != 4 && !SHARED_LUT) {
+        uint32_t* t = reinterpret_cast<uint32_t*>(gptr(tv_small));
+        for (int i = tid; i < (1 << C::IWV) * 32; i += THREADS) {
+            const int e = i >> 5;
+            const __half2 h = __floats2half2_rn(p.lv.v[e & ((1 << BV) - 1)], p.lv.v[e >> BV]);
+            t[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
-
-    const uint32_t lk_lane = tk_addr + lane * 4;
-    const uint32_t lv_lane = tv_addr + lane * 4;
-    const uint8_t* pool = p.pool + layer * p.pool_layer_stride;
-    const bool odd = g & 1;
-
-    // per lane: softmax state of head 4*hh + tg, O[head][(D/8)*g .. + D/8)
-    float m_run[NH], l_run[NH], oacc[NH][NMT][4];
-#pragma unroll
-    for (int hh = 0; hh < NH; hh++) {
-        m_run[hh] = -INFINITY;
-        l_run[hh] = 0.f;
-#pragma unroll
-        for (int mt = 0; mt < NMT; mt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) oacc[hh][mt][i] = 0.f;
     }
+    const uint32_t lk_lane = (BK == 4 ? window : tk_small) | (lane * 4);
+    const uint32_t lv_lane = (BV == 4 ? (window | (SHARED_LUT ? 0u : 128u)) : tv_small) | (lane * 4);
 
-    auto page_ptr = [&](int pg) {
-        return pool + (static_cast<int64_t>(sblk[pg]) * p.Hkv + hkv) * C::PAGE_BYTES;
-    };
+    // ---- persistent loop over work items
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const int chunk = item % p.n_chunks;
+        const int rest = item / p.n_chunks;
+        const int hkv = rest % p.Hkv;
+        const int lb = rest / p.Hkv;
+        const int layer = lb / p.B;
+        const int b = lb - layer * p.B;
 
-    auto compute = [&](const PageRegs<D, BK, BV>& r, int pg) {
-        const int ntok = min(kPageTokens, t1 - t0 - pg * kPageTokens);
-        const int tokA = 4 * (g >> 1) + (g & 1), tokB = tokA + 2;  // rows g, g+8 of S
-        const bool okA = tokA < ntok, okB = tokB < ntok;
+        const int seq_len = p.seq_lens[b];
+        const int t0 = chunk * p.chunk_tokens;
+        const int t1 = min(seq_len, t0 + p.chunk_tokens);
+        float* prow = p.partials +
+                      ((static_cast<int64_t>(lb) * p.Hq + hkv * group) * p.n_chunks + chunk) * ROW;
+        const int64_t prow_head_stride = static_cast<int64_t>(p.n_chunks) * ROW;
+        if (t0 >= t1) {  // CTA-uniform
+            if (tid < group) {
+                prow[tid * prow_head_stride + D] = -INFINITY;
+                prow[tid * prow_head_stride + D + 1] = 0.f;
+            }
+            continue;
+        }
+        const int n_pages = (t1 - t0 + kPageTokens - 1) / kPageTokens;
 
-        // ---- S = K.Q^T (two accumulator chains per head half)
-        float c[NH][2][4];
+        // ---- item prologue: block ids and the rotated, pre-scaled queries
+        {
+            const int32_t* btab =
+                p.block_table + static_cast<int64_t>(b) * p.max_blocks + t0 / kPageTokens;
+            for (int i = tid; i < n_pages; i += THREADS) sblk[i] = btab[i];
+            if (warp < 2) {  // 8 octets rotate the (at most) 8 heads; warp-uniform
+                const int t8 = lane & 7, o = lane >> 3;
+                const int hh = warp * 4 + o;
+                const bool hv = hh < group;
+                const int64_t qoff =
+                    (static_cast<int64_t>(lb) * p.Hq + hkv * group + (hv ? hh : 0)) * D;
+                float a[E];
+#pragma unroll
+                for (int i = 0; i < E / 8; i++) {
+                    float tmp[8];
+                    const int64_t eo = qoff + 8 * (t8 + 8 * i);
+                    if (p.q_dtype == kF32) load8<float>(static_cast<const float*>(p.q) + eo, tmp);
+                    else if (p.q_dtype == kBF16)
+                        load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.q) + eo, tmp);
+                    else load8<__half>(static_cast<const __half*>(p.q) + eo, tmp);
+#pragma unroll
+                    for (int c = 0; c < 8; c++)
+                        a[8 * i + c] = __uint_as_float(
+                            __float_as_uint(tmp[c]) ^ sign_mask(p.signs, load_coord(t8, 8 * i + c)));
+                }
+                octet_fwht<E>(a, lane);
+#pragma unroll
+                for (int k = 0; k < E; k++)
+                    qs[hh * D + t8 + 8 * k] = hv ? a[k] * p.rsqrt_d * p.scale : 0.f;
+            }
+        }
+        __syncthreads();
+
+        // Q^T fragments: column n = g is head 4*hh + (g >> 1); k-block kb covers coordinates
+        // (D/4)*tg + 4*kb + {0,1} (b0) and + {2,3} (b1)
+        uint32_t qb[NH][NKB][2];
 #pragma unroll
         for (int hh = 0; hh < NH; hh++)
 #pragma unroll
-            for (int z = 0; z < 2; z++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) c[hh][z][i] = 0.f;
-#pragma unroll
-        for (int kb = 0; kb < NKB; kb++) {
-            const uint32_t a0 = lds32(lk_lane | pair_index<C::IWK>(r.k[0], 2 * kb));
-            const uint32_t a1 = lds32(lk_lane | pair_index<C::IWK>(r.k[1], 2 * kb));
-            const uint32_t a2 = lds32(lk_lane | pair_index<C::IWK>(r.k[0], 2 * kb + 1));
-            const uint32_t a3 = lds32(lk_lane | pair_index<C::IWK>(r.k[1], 2 * kb + 1));
-#pragma unroll
-            for (int hh = 0; hh < NH; hh++)
-                mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qb[hh][kb][0], qb[hh][kb][1]);
-        }
-        const float kna = half_bits_to_float(odd ? r.kn.x >> 16 : r.kn.x & 0xffffu);
-        const float knb = half_bits_to_float(odd ? r.kn.y >> 16 : r.kn.y & 0xffffu);
-        const float vna = okA ? half_bits_to_float(odd ? r.vn.x >> 16 : r.vn.x & 0xffffu) : 0.f;
-        const float vnb = okB ? half_bits_to_float(odd ? r.vn.y >> 16 : r.vn.y & 0xffffu) : 0.f;
+            for (int kb = 0; kb < NKB; kb++) {
+                const float4 q4 = *reinterpret_cast<const float4*>(
+                    qs + (4 * hh + (g >> 1)) * D + (D / 4) * tg + 4 * kb);
+                const __half2 lo = __floats2half2_rn(q4.x, q4.y);
+                const __half2 hi = __floats2half2_rn(q4.z, q4.w);
+                qb[hh][kb][0] = *reinterpret_cast<const uint32_t*>(&lo);
+                qb[hh][kb][1] = *reinterpret_cast<const uint32_t*>(&hi);
+            }
 
-        // ---- online softmax per head (4*hh + tg); weights to fp16, transposed for P.V
-        uint32_t pb[NH][2][2];  // [hh][k-step][b0/b1]
+        const uint8_t* pool = p.pool + layer * p.pool_layer_stride;
+        const int64_t head_off = static_cast<int64_t>(hkv) * C::PAGE_BYTES;
+        const int64_t blk_stride = static_cast<int64_t>(p.Hkv) * C::PAGE_BYTES;
+
+        // per lane: softmax state of head 4*hh + tg, O[head][(D/8)*g .. + D/8)
+        float m_run[NH], l_run[NH], oacc[NH][NMT][4];
 #pragma unroll
         for (int hh = 0; hh < NH; hh++) {
-            const float sa = okA ? (c[hh][0][0] + c[hh][1][0]) * kna : -INFINITY;
-            const float sb = okB ? (c[hh][0][2] + c[hh][1][2]) * knb : -INFINITY;
-            float mx = fmaxf(sa, sb);
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-            const float m_new = fmaxf(m_run[hh], mx);  // finite: page token 0 is valid
-            if (m_new != m_run[hh]) {                  // same decision in all lanes of a head
-                const float corr = m_run[hh] == -INFINITY ? 0.f : __expf(m_run[hh] - m_new);
-                l_run[hh] *= corr;
+            m_run[hh] = -INFINITY;
+            l_run[hh] = 0.f;
 #pragma unroll
-                for (int mt = 0; mt < NMT; mt++)
+            for (int mt = 0; mt < NMT; mt++)
 #pragma unroll
-                    for (int i = 0; i < 4; i++) oacc[hh][mt][i] *= corr;
-                m_run[hh] = m_new;
-            }
-            const float pa = okA ? __expf(sa - m_new) : 0.f;
-            const float pbv = okB ? __expf(sb - m_new) : 0.f;
-            l_run[hh] += pa + pbv;
-            const uint32_t ha = __half_as_ushort(__float2half_rn(pa * vna));
-            const uint32_t hb = __half_as_ushort(__float2half_rn(pbv * vnb));
-            // M[token row][column n] with both columns of a head equal; transposed, lane (g, tg)
-            // receives head g>>1, page tokens 4tg, 4tg+1 (first) and 4tg+2, 4tg+3 (second)
-            const uint32_t t0w = movmatrix_trans(ha | (ha << 16));
-            const uint32_t t1w = movmatrix_trans(hb | (hb << 16));
-            pb[hh][0][0] = odd ? (t0w << 16) : (t0w & 0xffffu);
-            pb[hh][0][1] = odd ? (t0w & 0xffff0000u) : (t0w >> 16);
-            pb[hh][1][0] = odd ? (t1w << 16) : (t1w & 0xffffu);
-            pb[hh][1][1] = odd ? (t1w & 0xffff0000u) : (t1w >> 16);
+                for (int i = 0; i < 4; i++) oacc[hh][mt][i] = 0.f;
         }
 
-        // ---- O^T += V^T.P^T : rows = d-pairs (D/16)*g + 2*mt + {0,1}, k = (token, parity)
+        auto load_page = [&](Regs& r, int pg) {
+            const uint8_t* page = pool + sblk[pg] * blk_stride + head_off;
+            const int ktok = 4 * (g >> 1) + (g & 1);  // rho(g)
+            load_slice<C::KSB>(page + ktok * C::PDK, tg, r.k[0]);
+            load_slice<C::KSB>(page + (ktok + 2) * C::PDK, tg, r.k[1]);
 #pragma unroll
-        for (int ks = 0; ks < 2; ks++)
+            for (int j = 0; j < 4; j++)
+                load_slice<C::VSB>(page + C::OFF_VC + (4 * tg + j) * C::PDV, g, r.v[j]);
+            r.kn = ldg_nc64(page + C::OFF_KN + 8 * (g >> 1));
+            r.vn = ldg_nc64(page + C::OFF_VN + 8 * (g >> 1));
+        };
+
+        auto compute = [&](const Regs& r, int pg) {
+            const int ntok = min(kPageTokens, t1 - t0 - pg * kPageTokens);
+            const int tokA = 4 * (g >> 1) + (g & 1), tokB = tokA + 2;  // rows g, g+8 of S
+            const bool okA = tokA < ntok, okB = tokB < ntok;
+
+            // ---- S = K.Q^T (two accumulator chains per head half)
+            float c[NH][2][4];
 #pragma unroll
-            for (int mt = 0; mt < NMT; mt++) {
-                const uint32_t a0 = lds32(lv_lane | pair_index<C::IWV>(r.v[2 * ks], 2 * mt));
-                const uint32_t a1 = lds32(lv_lane | pair_index<C::IWV>(r.v[2 * ks], 2 * mt + 1));
-                const uint32_t a2 = lds32(lv_lane | pair_index<C::IWV>(r.v[2 * ks + 1], 2 * mt));
-                const uint32_t a3 = lds32(lv_lane | pair_index<C::IWV>(r.v[2 * ks + 1], 2 * mt + 1));
+            for (int hh = 0; hh < NH; hh++)
+#pragma unroll
+                for (int z = 0; z < 2; z++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) c[hh][z][i] = 0.f;
+#pragma unroll
+            for (int kb = 0; kb < NKB; kb++) {
+                const uint32_t a0 = lds32(entry_addr<C::IWK>(r.k[0], 2 * kb, lk_lane));
+                const uint32_t a1 = lds32(entry_addr<C::IWK>(r.k[1], 2 * kb, lk_lane));
+                const uint32_t a2 = lds32(entry_addr<C::IWK>(r.k[0], 2 * kb + 1, lk_lane));
+                const uint32_t a3 = lds32(entry_addr<C::IWK>(r.k[1], 2 * kb + 1, lk_lane));
 #pragma unroll
                 for (int hh = 0; hh < NH; hh++)
-                    mma_16816(oacc[hh][mt], a0, a1, a2, a3, pb[hh][ks][0], pb[hh][ks][1]);
+                    mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qb[hh][kb][0], qb[hh][kb][1]);
             }
-    };
+            const float kna = half_bits_to_float(odd ? r.kn.x >> 16 : r.kn.x & 0xffffu);
+            const float knb = half_bits_to_float(odd ? r.kn.y >> 16 : r.kn.y & 0xffffu);
+            const float vna = okA ? half_bits_to_float(odd ? r.vn.x >> 16 : r.vn.x & 0xffffu) : 0.f;
+            const float vnb = okB ? half_bits_to_float(odd ? r.vn.y >> 16 : r.vn.y & 0xffffu) : 0.f;
 
-    // ---- main loop: the warp's pages, next page's loads in flight during the math
-    PageRegs<D, BK, BV> ra, rb;
-    int pg = warp;
-    if (pg < n_pages) load_page<D, BK, BV>(ra, page_ptr(pg), g, tg);
-    while (pg < n_pages) {
-        if (pg + kMmaWarps < n_pages) load_page<D, BK, BV>(rb, page_ptr(pg + kMmaWarps), g, tg);
-        compute(ra, pg);
-        pg += kMmaWarps;
-        if (pg >= n_pages) break;
-        if (pg + kMmaWarps < n_pages) load_page<D, BK, BV>(ra, page_ptr(pg + kMmaWarps), g, tg);
-        compute(rb, pg);
-        pg += kMmaWarps;
-    }
+            // ---- online softmax per head (4*hh + tg); weights to fp16, transposed for P.V
+            uint32_t pb[NH][2][2];  // [hh][k-step][b0/b1]
+#pragma unroll
+            for (int hh = 0; hh < NH; hh++) {
+                const float sa = okA ? (c[hh][0][0] + c[hh][1][0]) * kna : -INFINITY;
+                const float sb = okB ? (c[hh][0][2] + c[hh][1][2]) * knb : -INFINITY;
+                float mx = fmaxf(sa, sb);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float m_new = fmaxf(m_run[hh], mx);  // finite: page token 0 is valid
+                if (m_new != m_run[hh]) {                  // same decision in all lanes of a head
+                    const float corr = m_run[hh] == -INFINITY ? 0.f : __expf(m_run[hh] - m_new);
+                    l_run[hh] *= corr;
+#pragma unroll
+                    for (int mt = 0; mt < NMT; mt++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) oacc[hh][mt][i] *= corr;
+                    m_run[hh] = m_new;
+                }
+                const float pa = okA ? __expf(sa - m_new) : 0.f;
+                const float pbv = okB ? __expf(sb - m_new) : 0.f;
+                l_run[hh] += pa + pbv;
+                const uint32_t ha = __half_as_ushort(__float2half_rn(pa * vna));
+                const uint32_t hb = __half_as_ushort(__float2half_rn(pbv * vnb));
+                // M[token row][column n], both columns of a head equal; transposed, lane (g, tg)
+                // receives head g>>1, page tokens 4tg, 4tg+1 (first) and 4tg+2, 4tg+3 (second)
+                const uint32_t t0w = movmatrix_trans(ha | (ha << 16));
+                const uint32_t t1w = movmatrix_trans(hb | (hb << 16));
+                pb[hh][0][0] = odd ? (t0w << 16) : (t0w & 0xffffu);
+                pb[hh][0][1] = odd ? (t0w & 0xffff0000u) : (t0w >> 16);
+                pb[hh][1][0] = odd ? (t1w << 16) : (t1w & 0xffffu);
+                pb[hh][1][1] = odd ? (t1w & 0xffff0000u) : (t1w >> 16);
+            }
 
-    // ---- merge the warps through shared memory (the tables are dead now)
+            // ---- O^T += V^T.P^T : rows = d-pairs (D/16)*g + 2*mt + {0,1}, k = (token, parity)
 #pragma unroll
-    for (int hh = 0; hh < NH; hh++) {
-        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
-        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
-        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
-    }
-    __syncthreads();
-    float* wacc = reinterpret_cast<float*>(region_ptr);  // [warps][8][DP]
-    float* wm = wacc + kMmaWarps * 8 * DP;               // [warps][8]
-    float* wl = wm + kMmaWarps * 8;                      // [warps][8]
+            for (int ks = 0; ks < 2; ks++)
 #pragma unroll
-    for (int hh = 0; hh < NH; hh++) {
-        const int h = 4 * hh + tg;
-        float* dst = wacc + (warp * 8 + h) * DP + (D / 8) * g;
+                for (int mt = 0; mt < NMT; mt++) {
+                    const uint32_t a0 = lds32(entry_addr<C::IWV>(r.v[2 * ks], 2 * mt, lv_lane));
+                    const uint32_t a1 = lds32(entry_addr<C::IWV>(r.v[2 * ks], 2 * mt + 1, lv_lane));
+                    const uint32_t a2 = lds32(entry_addr<C::IWV>(r.v[2 * ks + 1], 2 * mt, lv_lane));
+                    const uint32_t a3 = lds32(entry_addr<C::IWV>(r.v[2 * ks + 1], 2 * mt + 1, lv_lane));
 #pragma unroll
-        for (int mt = 0; mt < NMT; mt++)
-            *reinterpret_cast<float4*>(dst + 4 * mt) =
-                make_float4(oacc[hh][mt][0], oacc[hh][mt][1], oacc[hh][mt][2], oacc[hh][mt][3]);
-        if (g == 0) {
-            wm[warp * 8 + h] = m_run[hh];
-            wl[warp * 8 + h] = l_run[hh];
-        }
-    }
-    __syncthreads();
-    for (int idx = tid; idx < group * D; idx += kMmaThreads) {
-        const int h = idx / D, d = idx - h * D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w2 = 0; w2 < kMmaWarps; w2++) M = fmaxf(M, wm[w2 * 8 + h]);
-        float a = 0.f, l = 0.f;
-#pragma unroll
-        for (int w2 = 0; w2 < kMmaWarps; w2++) {
-            const float mw = wm[w2 * 8 + h];
-            if (mw != -INFINITY) {
-                const float f = __expf(mw - M);
-                a = fmaf(wacc[(w2 * 8 + h) * DP + d], f, a);
-                l = fmaf(wl[w2 * 8 + h], f, l);
+                    for (int hh = 0; hh < NH; hh++)
+                        mma_16816(oacc[hh][mt], a0, a1, a2, a3, pb[hh][ks][0], pb[hh][ks][1]);
+                }
+        };
+
+        // ---- main loop: the warp's pages, next page's loads in flight during the math
+        {
+            Regs ra, rb;
+            int pg = warp;
+            if (pg < n_pages) load_page(ra, pg);
+            while (pg < n_pages) {
+                if (pg + WARPS < n_pages) load_page(rb, pg + WARPS);
+                compute(ra, pg);
+                pg += WARPS;
+                if (pg >= n_pages) break;
+                if (pg + WARPS < n_pages) load_page(ra, pg + WARPS);
+                compute(rb, pg);
+                pg += WARPS;
             }
         }
-        prow[h * prow_head_stride + d] = a;
-        if (d == 0) {
-            prow[h * prow_head_stride + D] = M;
-            prow[h * prow_head_stride + D + 1] = l;
+
+        // ---- pairwise merge of the warps' states: upper half writes, lower half folds in
+#pragma unroll
+        for (int s = WARPS / 2; s >= 1; s >>= 1) {
+            __syncthreads();
+            if (warp >= s && warp < 2 * s) {
+                const int slot = warp - s;
+#pragma unroll
+                for (int hh = 0; hh < NH; hh++) {
+#pragma unroll
+                    for (int mt = 0; mt < NMT; mt++)
+                        xchg[(slot * C::STATE_F4 + hh * NMT + mt) * 32 + lane] = make_float4(
+                            oacc[hh][mt][0], oacc[hh][mt][1], oacc[hh][mt][2], oacc[hh][mt][3]);
+                    xml[((slot * NH + hh) * 2 + 0) * 32 + lane] = m_run[hh];
+                    xml[((slot * NH + hh) * 2 + 1) * 32 + lane] = l_run[hh];
+                }
+            }
+            __syncthreads();
+            if (warp < s) {
+                const int slot = warp;
+#pragma unroll
+                for (int hh = 0; hh < NH; hh++) {
+                    const float m2 = xml[((slot * NH + hh) * 2 + 0) * 32 + lane];
+                    const float l2 = xml[((slot * NH + hh) * 2 + 1) * 32 + lane];
+                    const float mn = fmaxf(m_run[hh], m2);
+                    const float f1 = m_run[hh] == -INFINITY ? 0.f : __expf(m_run[hh] - mn);
+                    const float f2 = m2 == -INFINITY ? 0.f : __expf(m2 - mn);
+                    l_run[hh] = l_run[hh] * f1 + l2 * f2;
+                    m_run[hh] = mn;
+#pragma unroll
+                    for (int mt = 0; mt < NMT; mt++) {
+                        const float4 o2 = xchg[(slot * C::STATE_F4 + hh * NMT + mt) * 32 + lane];
+                        oacc[hh][mt][0] = oacc[hh][mt][0] * f1 + o2.x * f2;
+                        oacc[hh][mt][1] = oacc[hh][mt][1] * f1 + o2.y * f2;
+                        oacc[hh][mt][2] = oacc[hh][mt][2] * f1 + o2.z * f2;
+                        oacc[hh][mt][3] = oacc[hh][mt][3] * f1 + o2.w * f2;
+                    }
+                }
+            }
         }
+        if (warp == 0) {
+#pragma unroll
+            for (int hh = 0; hh < NH; hh++) {
+                float l = l_run[hh];
+                l += __shfl_xor_sync(0xffffffffu, l, 4);
+                l += __shfl_xor_sync(0xffffffffu, l, 8);
+                l += __shfl_xor_sync(0xffffffffu, l, 16);
+                const int h = 4 * hh + tg;
+                if (h < group) {
+                    float* dst = prow + h * prow_head_stride;
+#pragma unroll
+                    for (int mt = 0; mt < NMT; mt++)
+                        *reinterpret_cast<float4*>(dst + (D / 8) * g + 4 * mt) = make_float4(
+                            oacc[hh][mt][0], oacc[hh][mt][1], oacc[hh][mt][2], oacc[hh][mt][3]);
+                    if (g == 0) {
+                        dst[D] = m_run[hh];
+                        dst[D + 1] = l;
+                    }
+                }
+            }
+        }
+        __syncthreads();  // qs / sblk / exchange area are reused by the next item
     }
 }
 

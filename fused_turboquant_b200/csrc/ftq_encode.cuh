@@ -72,6 +72,64 @@ __device__ __forceinline__ uint32_t octet_transpose_items(uint32_t w, int lane) 
     return w;
 }
 
+// Store one encoded vector: `w` holds this lane's codes (coordinates l + 8k) packed as
+// octet_transpose_items expects; the octet transposes them so that every lane owns whole
+// output words, then writes codes and norm to the sink.  Must be called by all 32 lanes.
+template <int D, int BITS, int NW>
+__device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm, bool valid,
+                                            int64_t v, const EncodeSink& sink, int64_t sink_layer,
+                                            int lane) {
+    constexpr int PD = packed_dim(D, BITS);
+    const int t = lane & 7;
+    // destination of this vector
+    uint8_t* dst = nullptr;
+    bool store = valid;
+    if (sink.mode == kSinkFlat) {
+        dst = sink.codes + v * PD;
+    } else if (valid) {
+        const int64_t token = v / sink.Hkv;
+        const int head = static_cast<int>(v - token * sink.Hkv);
+        const int64_t slot = sink.slot_mapping[token];
+        if (slot < 0) {
+            store = false;
+        } else if (sink.mode == kSinkPaged) {
+            const int64_t blk = slot / kPageTokens;
+            const int off = static_cast<int>(slot - blk * kPageTokens);
+            uint8_t* page = sink.codes + sink_layer + (blk * sink.Hkv + head) * sink.page_bytes;
+            dst = page + sink.codes_off + off * PD;
+            if (t == 0)
+                *reinterpret_cast<__half*>(page + sink.norms_off + 2 * off) =
+                    __float2half_rn(norm);
+        } else {
+            const int64_t blk = slot / sink.block_size;
+            const int64_t off = slot - blk * sink.block_size;
+            dst = sink.codes + sink.plane_off +
+                  ((blk * sink.block_size + off) * sink.Hkv + head) * sink.elem_size;
+            if (t == 0) *reinterpret_cast<float*>(dst + PD) = __half2float(__float2half_rn(norm));
+        }
+    }
+    if (sink.mode == kSinkFlat && valid && t == 0)
+        reinterpret_cast<__half*>(sink.norms)[v] = __float2half_rn(norm);
+
+    // transpose across the octet so that every lane owns whole output words
+#pragma unroll
+    for (int i = 0; i < NW; i++) {
+        const uint32_t o = octet_transpose_items<BITS>(w[i], lane);
+        if constexpr (BITS == 3) {
+            // lane j holds the 24-bit group j of row i; regroup 8 x 3 bytes into 6 words
+            const int g0 = (4 * t) / 3;
+            const uint32_t lo = __shfl_sync(0xffffffffu, o, g0, 8);
+            const uint32_t hi = __shfl_sync(0xffffffffu, o, g0 + 1, 8);
+            const uint64_t cat = (static_cast<uint64_t>(hi) << 24) | lo;
+            const uint32_t word = static_cast<uint32_t>(cat >> (8 * ((4 * t) % 3)));
+            if (store && t < 6) reinterpret_cast<uint32_t*>(dst + 24 * i)[t] = word;
+        } else {
+            const int widx = t + 8 * i;
+            if (store && widx < PD / 4) reinterpret_cast<uint32_t*>(dst)[widx] = o;
+        }
+    }
+}
+
 template <int D, int BITS, typename T>
 __global__ void __launch_bounds__(256)
 encode_kernel(EncodeSource src, EncodeSink sink, EncodeTables tab, int64_t n_vec) {
@@ -151,53 +209,7 @@ encode_kernel(EncodeSource src, EncodeSink sink, EncodeTables tab, int64_t n_vec
             }
         }
 
-        // destination of this vector
-        uint8_t* dst = nullptr;
-        bool store = valid;
-        if (sink.mode == kSinkFlat) {
-            dst = sink.codes + v * PD;
-        } else if (valid) {
-            const int64_t token = v / sink.Hkv;
-            const int head = static_cast<int>(v - token * sink.Hkv);
-            const int64_t slot = sink.slot_mapping[token];
-            if (slot < 0) {
-                store = false;
-            } else if (sink.mode == kSinkPaged) {
-                const int64_t blk = slot / kPageTokens;
-                const int off = static_cast<int>(slot - blk * kPageTokens);
-                uint8_t* page = sink.codes + sink_layer + (blk * sink.Hkv + head) * sink.page_bytes;
-                dst = page + sink.codes_off + off * PD;
-                if (t == 0)
-                    *reinterpret_cast<__half*>(page + sink.norms_off + 2 * off) =
-                        __float2half_rn(norm);
-            } else {
-                const int64_t blk = slot / sink.block_size;
-                const int64_t off = slot - blk * sink.block_size;
-                dst = sink.codes + sink.plane_off +
-                      ((blk * sink.block_size + off) * sink.Hkv + head) * sink.elem_size;
-                if (t == 0) *reinterpret_cast<float*>(dst + PD) = __half2float(__float2half_rn(norm));
-            }
-        }
-        if (sink.mode == kSinkFlat && valid && t == 0)
-            reinterpret_cast<__half*>(sink.norms)[v] = __float2half_rn(norm);
-
-        // transpose across the octet so that every lane owns whole output words
-#pragma unroll
-        for (int i = 0; i < NW; i++) {
-            const uint32_t o = octet_transpose_items<BITS>(w[i], lane);
-            if constexpr (BITS == 3) {
-                // lane j holds the 24-bit group j of row i; regroup 8 x 3 bytes into 6 words
-                const int g0 = (4 * t) / 3;
-                const uint32_t lo = __shfl_sync(0xffffffffu, o, g0, 8);
-                const uint32_t hi = __shfl_sync(0xffffffffu, o, g0 + 1, 8);
-                const uint64_t cat = (static_cast<uint64_t>(hi) << 24) | lo;
-                const uint32_t word = static_cast<uint32_t>(cat >> (8 * ((4 * t) % 3)));
-                if (store && t < 6) reinterpret_cast<uint32_t*>(dst + 24 * i)[t] = word;
-            } else {
-                const int widx = t + 8 * i;
-                if (store && widx < PD / 4) reinterpret_cast<uint32_t*>(dst)[widx] = o;
-            }
-        }
+        emit_vector<D, BITS>(w, norm, valid, v, sink, sink_layer, lane);
     }
 }
 

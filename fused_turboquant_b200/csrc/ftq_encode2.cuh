@@ -1,0 +1,268 @@
+// Fused KV encode, throughput version.  Same arithmetic, bit for bit, as
+// encode_kernel (ftq_encode.cuh) -- which restates TurboQuantMSE._encode_unfused of
+// the reference (src/fused_turboquant/core/quantizer.py:137-160) -- with the
+// instruction count cut to what the B200 issue slots allow:
+//
+//  * every lane carries TWO vectors packed into 64-bit register pairs and runs
+//    the butterfly, scaling, squares, running sums and the division on
+//    Blackwell's packed fp32 instructions (add/sub/mul/fma .f32x2, round to
+//    nearest, each half an ordinary IEEE operation);
+//  * the lane<->register transposition between butterfly stage h=4 and h=8
+//    goes once through shared memory (conflict-free) instead of three rounds of
+//    shuffles and selects;
+//  * y / denom is q = y*r refined twice with exact FMA residuals (r the correctly
+//    rounded reciprocal), which yields the correctly rounded quotient that
+//    __fdiv_rn returns;
+//  * bucketisation is one table lookup: x is mapped to one of 257 cells of
+//    [-1, 1] with a single FMA (monotone in x); a cell contains at most one
+//    decision boundary (checked on the host), so
+//    code = codes below the cell + [x > boundary in the cell], the comparison
+//    done as a saturating FMA; codes are accumulated into the packed word in
+//    floating point (exact below 2^24).
+#pragma once
+
+#include "ftq_encode.cuh"
+
+namespace ftq {
+
+constexpr int kQuantCells = 257;
+constexpr float kCellScale = 128.0f;                 // cells per unit of x
+constexpr float kCellMagic = 98304.0f + 128.0f;      // 1.5 * 2^16 + scale: ulp = 2^-7
+constexpr float kStepScale = 1.2676506002282294e30f; // 2^100
+
+struct QuantCell {
+    float neg_thr_scaled;  // -boundary * 2^100, or -FLT_MAX when the cell holds no boundary
+    float base;            // number of interior boundaries in lower cells
+};
+
+struct Encode2Tables {
+    SignBits signs;
+    float rsqrt_d;
+    QuantCell cells[kQuantCells];
+};
+
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 pk2(float lo, float hi) {
+    u64 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void upk2(u64 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ u64 add2(u64 a, u64 b) {
+    u64 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 sub2(u64 a, u64 b) {
+    u64 r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
+    u64 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
+    u64 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {
+    float r;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// In-lane butterfly stage on register-index bit B of packed pairs.
+template <int E, int B>
+__device__ __forceinline__ void stage2(u64 (&p)[E]) {
+#pragma unroll
+    for (int r = 0; r < E; r++) {
+        if ((r & (1 << B)) == 0) {
+            const u64 a = p[r], b = p[r | (1 << B)];
+            p[r] = add2(a, b);
+            p[r | (1 << B)] = sub2(a, b);
+        }
+    }
+}
+
+// Physical float index of logical coordinate (run m, element c) in a transpose slot:
+// the two float4 halves of a run are swapped for runs 4..7 (mod 8) so that the eight
+// 16-byte stores of an octet cover all 32 banks.
+__device__ __forceinline__ constexpr int slot_index(int m, int c) {
+    return 8 * m + (c ^ (4 * ((m >> 2) & 1)));
+}
+
+template <int D, int BITS, typename T>
+__global__ void __launch_bounds__(256, 2)
+encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64_t n_vec) {
+    constexpr int E = D / kOctet;
+    constexpr int NCH = E / 8;
+    constexpr int SLOT = D + 8;  // floats per transpose slot (+8: the 4 octets hit distinct banks)
+    constexpr int NW = BITS == 2 ? (E + 15) / 16 : E / 8;  // packed words per lane
+    constexpr int IPW = BITS == 2 ? 16 : 8;                 // items per word
+    constexpr int CPF = 24 / BITS;                          // codes per fp32 accumulator
+    constexpr int FPW = (IPW + CPF - 1) / CPF;              // accumulators per word
+
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float2* lut = reinterpret_cast<float2*>(smem_raw);                 // [257][16]
+    float* tbuf = reinterpret_cast<float*>(smem_raw + kQuantCells * 128);  // [warps][8][SLOT]
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, wip = tid >> 5;
+    const int t = lane & 7, sub = lane >> 3;
+    for (int i = tid; i < kQuantCells * 16; i += blockDim.x)
+        lut[i] = make_float2(tab.cells[i >> 4].neg_thr_scaled, tab.cells[i >> 4].base);
+    __syncthreads();
+    const uint32_t lut_lane =
+        static_cast<uint32_t>(__cvta_generic_to_shared(lut)) + (lane & 15) * 8;
+    float* slotA = tbuf + (wip * 8 + sub) * SLOT;
+    float* slotB = slotA + 4 * SLOT;
+
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + tid) >> 5;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    const T* xbase = static_cast<const T*>(src.base) + blockIdx.y * src.layer_stride;
+    const int64_t sink_layer = blockIdx.y * sink.layer_stride;
+
+    uint32_t sgn[E];
+#pragma unroll
+    for (int r = 0; r < E; r++) sgn[r] = sign_mask(tab.signs, load_coord(t, r));
+    const u64 scale2 = pk2(tab.rsqrt_d, tab.rsqrt_d);
+    const u64 cs2 = pk2(kCellScale, kCellScale), cm2 = pk2(kCellMagic, kCellMagic);
+
+    for (int64_t base = warp * 8; base < n_vec; base += n_warps * 8) {
+        const int64_t vA = base + sub, vB = base + 4 + sub;
+        const bool okA = vA < n_vec, okB = vB < n_vec;
+        u64 p[E];
+        {
+            const int64_t oA = okA ? vA / src.n_inner : 0, oB = okB ? vB / src.n_inner : 0;
+            const T* rowA = xbase + oA * src.outer_stride +
+                            (okA ? vA - oA * src.n_inner : 0) * src.inner_stride;
+            const T* rowB = xbase + oB * src.outer_stride +
+                            (okB ? vB - oB * src.n_inner : 0) * src.inner_stride;
+#pragma unroll
+            for (int i = 0; i < NCH; i++) {
+                float a[8], b[8];
+                if (okA) load8<T>(rowA + 8 * (t + 8 * i), a);
+                if (okB) load8<T>(rowB + 8 * (t + 8 * i), b);
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    const float fa = okA ? __uint_as_float(__float_as_uint(a[c]) ^ sgn[8 * i + c]) : 0.f;
+                    const float fb = okB ? __uint_as_float(__float_as_uint(b[c]) ^ sgn[8 * i + c]) : 0.f;
+                    p[8 * i + c] = pk2(fa, fb);
+                }
+            }
+        }
+        // stages h = 1, 2, 4 on the coordinates inside a run
+        stage2<E, 0>(p);
+        stage2<E, 1>(p);
+        stage2<E, 2>(p);
+
+        // lane <-> register transposition through shared memory:
+        // (lane t, register c + 8i) = coordinate 8(t + 8i) + c   ->   (lane l, register k) = l + 8k
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < NCH; i++) {
+            const int m = t + 8 * i;
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                float a[4], b[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) upk2(p[8 * i + 4 * j + c], a[c], b[c]);
+                const int off = slot_index(m, 4 * j);
+                *reinterpret_cast<float4*>(slotA + off) = make_float4(a[0], a[1], a[2], a[3]);
+                *reinterpret_cast<float4*>(slotB + off) = make_float4(b[0], b[1], b[2], b[3]);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            const int off = 8 * k + (t ^ (4 * ((k >> 2) & 1)));
+            p[k] = pk2(slotA[off], slotB[off]);
+        }
+
+        // stages h = 8, 16, ... : register bits 0.. of the new layout
+        stage2<E, 0>(p);
+        stage2<E, 1>(p);
+        stage2<E, 2>(p);
+        if constexpr (E >= 16) stage2<E, 3>(p);
+        if constexpr (E >= 32) stage2<E, 4>(p);
+
+        // scale, 8-way strided sum of squares (lane l = running sum l), ordered octet sum
+        u64 acc = pk2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            p[k] = mul2(p[k], scale2);
+            // the squares are rounded on their own (scalar mul.rn): a packed multiply feeding a
+            // packed add may be contracted into a fused multiply-add, which changes the norm
+            float ya, yb;
+            upk2(p[k], ya, yb);
+            acc = add2(acc, pk2(__fmul_rn(ya, ya), __fmul_rn(yb, yb)));
+        }
+        u64 s = __shfl_sync(0xffffffffu, acc, 0, 8);
+#pragma unroll
+        for (int l = 1; l < 8; l++) s = add2(s, __shfl_sync(0xffffffffu, acc, l, 8));
+        float sA, sB;
+        upk2(s, sA, sB);
+        const float normA = __fsqrt_rn(sA), normB = __fsqrt_rn(sB);
+        const float dA = __fadd_rn(normA, 1e-8f), dB = __fadd_rn(normB, 1e-8f);
+        const u64 r2 = pk2(__frcp_rn(dA), __frcp_rn(dB));
+        const u64 nd2 = pk2(-dA, -dB);
+
+        // normalise, bucketise, accumulate the packed words in floating point
+        u64 wf[NW * FPW];
+#pragma unroll
+        for (int i = 0; i < NW * FPW; i++) wf[i] = pk2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            u64 q = mul2(p[k], r2);
+            u64 e = fma2(nd2, q, p[k]);
+            q = fma2(e, r2, q);
+            e = fma2(nd2, q, p[k]);
+            q = fma2(e, r2, q);
+            // cell = floor((x + 1) * 128 rounded to 1/128); row = cell * 128 bytes
+            const u64 cv = fma2(q, cs2, cm2);
+            float cA, cB, qA, qB;
+            upk2(cv, cA, cB);
+            upk2(q, qA, qB);
+            float2 eA, eB;
+            {
+                const uint32_t aA = lut_lane + (__float_as_uint(cA) & 0xFF80u);
+                const uint32_t aB = lut_lane + (__float_as_uint(cB) & 0xFF80u);
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(eA.x), "=f"(eA.y) : "r"(aA));
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(eB.x), "=f"(eB.y) : "r"(aB));
+            }
+            const float stA = fma_sat(qA, kStepScale, eA.x);
+            const float stB = fma_sat(qB, kStepScale, eB.x);
+            const u64 code = add2(pk2(eA.y, eB.y), pk2(stA, stB));
+            // position of code k inside its word (see encode_kernel)
+            const int word = BITS == 2 ? (k >> 4) : (k >> 3);
+            const int pos = BITS == 2 ? (((k >> 1) & 7) | ((k & 1) << 3)) : (k & 7);
+            const int fi = word * FPW + pos / CPF;
+            const float sc = static_cast<float>(1u << (BITS * (pos % CPF)));
+            wf[fi] = fma2(code, pk2(sc, sc), wf[fi]);
+        }
+        uint32_t wA[NW], wB[NW];
+#pragma unroll
+        for (int i = 0; i < NW; i++) {
+            float a0, b0;
+            upk2(wf[i * FPW], a0, b0);
+            wA[i] = __float2uint_rn(a0);
+            wB[i] = __float2uint_rn(b0);
+            if constexpr (FPW == 2) {
+                float a1, b1;
+                upk2(wf[i * FPW + 1], a1, b1);
+                wA[i] |= __float2uint_rn(a1) << (BITS * CPF);
+                wB[i] |= __float2uint_rn(b1) << (BITS * CPF);
+            }
+        }
+        emit_vector<D, BITS>(wA, normA, okA, vA, sink, sink_layer, lane);
+        emit_vector<D, BITS>(wB, normB, okB, vB, sink, sink_layer, lane);
+    }
+}
+
+}  // namespace ftq

@@ -5,14 +5,15 @@
 #include <cuda_runtime.h>
 
 #include "ftq_attn.cuh"
-#include "ftq_encode.cuh"
+#include "ftq_encode2.cuh"
 
 namespace ftq {
 
 #define FTQ_DECLARE_LAUNCHERS(DD)                                                              \
     cudaError_t launch_encode_d##DD(int bits, int dtype, const EncodeSource& src,               \
                                     const EncodeSink& sink, const EncodeTables& tab,            \
-                                    int64_t n_vec, int n_layers, cudaStream_t stream);          \
+                                    const Encode2Tables* tab2, int64_t n_vec, int n_layers,     \
+                                    cudaStream_t stream);                                       \
     cudaError_t launch_attn_split_d##DD(int bits_k, int bits_v, bool paged, const AttnParams& p, \
                                         int n_lb, cudaStream_t stream);                         \
     cudaError_t launch_attn_mma_d##DD(int bits_k, int bits_v, bool shared_lut, const AttnParams& p, \
