@@ -553,6 +553,7 @@ int ftq_paged_store(const void* key, const void* value, int dtype, int64_t n_tok
         sink.norms_off = which ? FTQ_PAGE_TOKENS * (pdk + pdv) + 2 * FTQ_PAGE_TOKENS
                                : FTQ_PAGE_TOKENS * pdk;
         sink.layer_stride = pool_layer_stride;
+        sink.swap_halves = which;  // V rows only (see the page layout in ftq_b200.h)
         cudaError_t e = dispatch_encode(head_dim, which ? bits_v : bits_k, dtype, src, sink, tab,
                                         n_tokens * Hkv, n_layers, st);
         if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_store launch");

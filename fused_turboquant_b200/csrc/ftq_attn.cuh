@@ -344,7 +344,9 @@ attn_split_kernel(const AttnParams p) {
             for (int step = 0; step < 4; step++) {
                 const int tk = step * 4 + o;
                 uint32_t w[(NBV + 3) / 4];
-                load_code_bytes<NBV>(page + OFF_VC + tk * PDV + t * NBV, w);
+                // pool pages store a V row with its halves exchanged for tokens with bit 1 set
+                const int vt = PAGED ? (t ^ ((tk & 2) << 1)) : t;
+                load_code_bytes<NBV>(page + OFF_VC + tk * PDV + vt * NBV, w);
                 const float vn = tk < ntok
                     ? __half2float(reinterpret_cast<const __half*>(page + OFF_VN)[tk]) : 0.f;
                 float vv[E];

@@ -260,14 +260,14 @@ struct MmaCfg {
     static constexpr int TVS = BV == 4 ? 0 : (1 << IWV) * 128;
     static constexpr int SMALL_ALIGN = TKS > TVS ? TKS : TVS;
     static constexpr int SMALL_BYTES = TKS + TVS + SMALL_ALIGN;  // incl. alignment slack
-    // exchange area of the pairwise merge: WARPS/2 slots x 32 lanes x state
+    // exchange area of the end-of-item merge: every warp's (O, m, l)
     static constexpr int STATE_F4 = NH * NMT;                    // float4 items per lane
-    static constexpr int XCHG_BYTES = (WARPS / 2) * 32 * (STATE_F4 * 16 + NH * 8);
+    static constexpr int XCHG_BYTES = WARPS * (32 * STATE_F4 * 16 + NH * 2 * 4 * 4);
     // per-warp ring of pages staged by bulk copies (TMA), one mbarrier per buffer
     static constexpr int RING = 2;
     // two groups of shared-memory objects, placed first-fit around the 64 KB table window
     // (the merge exchange area aliases the page ring, which is idle during the merge)
-    static constexpr int GROUP_A = SMALL_BYTES + 8 * D * 4 + kMmaMaxChunkPages * 4 + 64;
+    static constexpr int GROUP_A = SMALL_BYTES + 8 * (D + 16) * 4 + kMmaMaxChunkPages * 4 + 64;
     static constexpr int RING_BYTES = WARPS * RING * PAGE_BYTES;
     static constexpr int GROUP_B =
         (RING_BYTES > XCHG_BYTES ? RING_BYTES : XCHG_BYTES) + WARPS * RING * 8 + 256;
@@ -333,15 +333,15 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         if (SHARED_LUT) tv_small = tk_small;
     }
     cur = (cur + 15u) & ~15u;
-    float* qs = reinterpret_cast<float*>(gptr(cur));                  // [8][D]
-    int32_t* sblk = reinterpret_cast<int32_t*>(qs + 8 * D);           // block ids of the chunk
+    float* qs = reinterpret_cast<float*>(gptr(cur));                  // [8][D + 16]
+    int32_t* sblk = reinterpret_cast<int32_t*>(qs + 8 * (D + 16));    // block ids of the chunk
     // group B: page ring + mbarriers
     const uint32_t grp_b = take(C::GROUP_B, 128);
     const uint32_t bars = grp_b;                              // [WARPS][RING] x 8 bytes
     const uint32_t ring = (grp_b + WARPS * C::RING * 8 + 127u) & ~127u;
     // merge exchange area: aliases the ring (no copy is in flight when the merge runs)
-    float4* xchg = reinterpret_cast<float4*>(gptr(ring));  // [WARPS/2][STATE_F4][32] then m/l
-    float* xml = reinterpret_cast<float*>(gptr(ring + (WARPS / 2) * 32 * C::STATE_F4 * 16));
+    float4* xchg = reinterpret_cast<float4*>(gptr(ring));  // [WARPS][NH][NMT][32]
+    float* xml = reinterpret_cast<float*>(gptr(ring + WARPS * 32 * C::STATE_F4 * 16));  // [WARPS][NH][2][4]
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -394,62 +394,88 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     uint32_t phase = 0;   // bit r = parity the next wait on ring buffer r expects
     bool stalled = false; // a bulk copy never arrived: stop waiting, poison the result
 
+    // rotated queries in shared memory: head rows of D + 16 floats, each quarter of a row
+    // padded by 4, so that the 16 distinct float4 a fragment load touches are 2-way at worst
+    auto qs_index = [](int head, int coord) {
+        return head * (D + 16) + (coord / (D / 4)) * (D / 4 + 4) + coord % (D / 4);
+    };
     // ---- persistent loop over work items
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const int chunk = item % p.n_chunks;
+    struct Item { int chunk, hkv, lb, layer, b, t0, t1, n_pages; };
+    auto item_info = [&](int item) {
+        Item it;
+        it.chunk = item % p.n_chunks;
         const int rest = item / p.n_chunks;
-        const int hkv = rest % p.Hkv;
-        const int lb = rest / p.Hkv;
-        const int layer = lb / p.B;
-        const int b = lb - layer * p.B;
-
-        const int seq_len = p.seq_lens[b];
-        const int t0 = chunk * p.chunk_tokens;
-        const int t1 = min(seq_len, t0 + p.chunk_tokens);
-        float* prow = p.partials +
-                      ((static_cast<int64_t>(lb) * p.Hq + hkv * group) * p.n_chunks + chunk) * ROW;
-        const int64_t prow_head_stride = static_cast<int64_t>(p.n_chunks) * ROW;
-        if (t0 >= t1) {  // CTA-uniform
+        it.hkv = rest % p.Hkv;
+        it.lb = rest / p.Hkv;
+        it.layer = it.lb / p.B;
+        it.b = it.lb - it.layer * p.B;
+        it.t0 = it.chunk * p.chunk_tokens;
+        it.t1 = min(p.seq_lens[it.b], it.t0 + p.chunk_tokens);
+        it.n_pages = (it.t1 - it.t0 + kPageTokens - 1) / kPageTokens;
+        return it;
+    };
+    const int64_t prow_head_stride = static_cast<int64_t>(p.n_chunks) * ROW;
+    auto partial_row = [&](const Item& it) {
+        return p.partials +
+               ((static_cast<int64_t>(it.lb) * p.Hq + it.hkv * group) * p.n_chunks + it.chunk) * ROW;
+    };
+    // first non-empty item at or after `item` (CTA-uniform); empty ones get (-inf, 0) rows
+    auto skip_empty = [&](int item) {
+        while (item < n_items) {
+            const Item it = item_info(item);
+            if (it.t0 < it.t1) break;
             if (tid < group) {
+                float* prow = partial_row(it);
                 prow[tid * prow_head_stride + D] = -INFINITY;
                 prow[tid * prow_head_stride + D + 1] = 0.f;
             }
-            continue;
+            item += gridDim.x;
         }
-        const int n_pages = (t1 - t0 + kPageTokens - 1) / kPageTokens;
-
-        // ---- item prologue: block ids and the rotated, pre-scaled queries
-        {
-            const int32_t* btab =
-                p.block_table + static_cast<int64_t>(b) * p.max_blocks + t0 / kPageTokens;
-            for (int i = tid; i < n_pages; i += THREADS) sblk[i] = btab[i];
-            if (warp < 2) {  // 8 octets rotate the (at most) 8 heads; warp-uniform
-                const int t8 = lane & 7, o = lane >> 3;
-                const int hh = warp * 4 + o;
-                const bool hv = hh < group;
-                const int64_t qoff =
-                    (static_cast<int64_t>(lb) * p.Hq + hkv * group + (hv ? hh : 0)) * D;
-                float a[E];
+        return item;
+    };
+    // item prologue, run by warps [w0, w0 + nw): block ids of the chunk and the rotated,
+    // pre-scaled queries (8 octets of the first two warps rotate the at most 8 heads)
+    auto prologue = [&](const Item& it, int w0, int nw) {
+        const int32_t* btab =
+            p.block_table + static_cast<int64_t>(it.b) * p.max_blocks + it.t0 / kPageTokens;
+        for (int i = tid - w0 * 32; i < it.n_pages; i += nw * 32) sblk[i] = btab[i];
+        if (warp - w0 < 2) {  // warp-uniform
+            const int t8 = lane & 7, o = lane >> 3;
+            const int hh = (warp - w0) * 4 + o;
+            const bool hv = hh < group;
+            const int64_t qoff =
+                (static_cast<int64_t>(it.lb) * p.Hq + it.hkv * group + (hv ? hh : 0)) * D;
+            float a[E];
 #pragma unroll
-                for (int i = 0; i < E / 8; i++) {
-                    float tmp[8];
-                    const int64_t eo = qoff + 8 * (t8 + 8 * i);
-                    if (p.q_dtype == kF32) load8<float>(static_cast<const float*>(p.q) + eo, tmp);
-                    else if (p.q_dtype == kBF16)
-                        load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.q) + eo, tmp);
-                    else load8<__half>(static_cast<const __half*>(p.q) + eo, tmp);
+            for (int i = 0; i < E / 8; i++) {
+                float tmp[8];
+                const int64_t eo = qoff + 8 * (t8 + 8 * i);
+                if (p.q_dtype == kF32) load8<float>(static_cast<const float*>(p.q) + eo, tmp);
+                else if (p.q_dtype == kBF16)
+                    load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.q) + eo, tmp);
+                else load8<__half>(static_cast<const __half*>(p.q) + eo, tmp);
 #pragma unroll
-                    for (int c = 0; c < 8; c++)
-                        a[8 * i + c] = __uint_as_float(
-                            __float_as_uint(tmp[c]) ^ sign_mask(p.signs, load_coord(t8, 8 * i + c)));
-                }
-                octet_fwht<E>(a, lane);
-#pragma unroll
-                for (int k = 0; k < E; k++)
-                    qs[hh * D + t8 + 8 * k] = hv ? a[k] * p.rsqrt_d * p.scale : 0.f;
+                for (int c = 0; c < 8; c++)
+                    a[8 * i + c] = __uint_as_float(
+                        __float_as_uint(tmp[c]) ^ sign_mask(p.signs, load_coord(t8, 8 * i + c)));
             }
+            octet_fwht<E>(a, lane);
+#pragma unroll
+            for (int k = 0; k < E; k++)
+                qs[qs_index(hh, t8 + 8 * k)] = hv ? a[k] * p.rsqrt_d * p.scale : 0.f;
         }
-        __syncthreads();
+    };
+    // warps that fold the per-warp states into the partial rows; when at least two warps are
+    // left over they run the next item's prologue at the same time
+    constexpr int NRED = (NH * NMT <= WARPS - 2) ? NH * NMT : WARPS;
+
+    int item = skip_empty(blockIdx.x);
+    if (item < n_items) prologue(item_info(item), 0, WARPS);
+    while (item < n_items) {
+        const Item cur = item_info(item);
+        const int hkv = cur.hkv, layer = cur.layer;
+        const int t0 = cur.t0, t1 = cur.t1, n_pages = cur.n_pages;
+        __syncthreads();  // prologue of this item visible; ring and exchange area free
 
         // Q^T fragments: column n = g is head 4*hh + (g >> 1); k-block kb covers coordinates
         // (D/4)*tg + 4*kb + {0,1} (b0) and + {2,3} (b1)
@@ -459,7 +485,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
 #pragma unroll
             for (int kb = 0; kb < NKB; kb++) {
                 const float4 q4 = *reinterpret_cast<const float4*>(
-                    qs + (4 * hh + (g >> 1)) * D + (D / 4) * tg + 4 * kb);
+                    qs + qs_index(4 * hh + (g >> 1), (D / 4) * tg + 4 * kb));
                 const __half2 lo = __floats2half2_rn(q4.x, q4.y);
                 const __half2 hi = __floats2half2_rn(q4.z, q4.w);
                 qb[hh][kb][0] = *reinterpret_cast<const uint32_t*>(&lo);
@@ -500,9 +526,13 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             // rows of alternating parity in one instruction (2-way instead of 4-way bank conflict);
             // the P.V k-slots of a lane may hold its tokens in any order as long as the weights
             // follow (see the rotation of the transposed weights below)
+            // the pool stores a V row with its two halves exchanged for tokens with bit 1 set, so
+            // that the four rows a quad reads in one instruction fall into distinct bank groups
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-                lds_slice<C::VSB>(page + C::OFF_VC + (4 * tg + ((j + tg) & 3)) * C::PDV, g, r.v[j]);
+            for (int j = 0; j < 4; j++) {
+                const int u = (j + tg) & 3;
+                lds_slice<C::VSB>(page + C::OFF_VC + (4 * tg + u) * C::PDV, g ^ ((u & 2) << 1), r.v[j]);
+            }
             r.kn = lds64(page + C::OFF_KN + 8 * (g >> 1));
             r.vn = lds64(page + C::OFF_VN + 8 * (g >> 1));
         };
@@ -617,69 +647,71 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             }
         }
 
-        // ---- pairwise merge of the warps' states: upper half writes, lower half folds in
+        // ---- fold the warps' states: every warp publishes (m, l, O), NRED warps reduce
 #pragma unroll
-        for (int s = WARPS / 2; s >= 1; s >>= 1) {
-            __syncthreads();
-            if (warp >= s && warp < 2 * s) {
-                const int slot = warp - s;
+        for (int hh = 0; hh < NH; hh++) {
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
+        }
+        // a warp whose copy never arrived poisons its state (NaN propagates to the output)
+        if (stalled) m_run[0] = __int_as_float(0x7fc00000);
+        __syncthreads();  // every warp is done with the ring: it becomes the exchange area
 #pragma unroll
-                for (int hh = 0; hh < NH; hh++) {
+        for (int hh = 0; hh < NH; hh++) {
 #pragma unroll
-                    for (int mt = 0; mt < NMT; mt++)
-                        xchg[(slot * C::STATE_F4 + hh * NMT + mt) * 32 + lane] = make_float4(
-                            oacc[hh][mt][0], oacc[hh][mt][1], oacc[hh][mt][2], oacc[hh][mt][3]);
-                    xml[((slot * NH + hh) * 2 + 0) * 32 + lane] = m_run[hh];
-                    xml[((slot * NH + hh) * 2 + 1) * 32 + lane] = l_run[hh];
-                }
-            }
-            __syncthreads();
-            if (warp < s) {
-                const int slot = warp;
-#pragma unroll
-                for (int hh = 0; hh < NH; hh++) {
-                    const float m2 = xml[((slot * NH + hh) * 2 + 0) * 32 + lane];
-                    const float l2 = xml[((slot * NH + hh) * 2 + 1) * 32 + lane];
-                    const float mn = fmaxf(m_run[hh], m2);
-                    const float f1 = m_run[hh] == -INFINITY ? 0.f : __expf(m_run[hh] - mn);
-                    const float f2 = m2 == -INFINITY ? 0.f : __expf(m2 - mn);
-                    l_run[hh] = l_run[hh] * f1 + l2 * f2;
-                    m_run[hh] = mn;
-#pragma unroll
-                    for (int mt = 0; mt < NMT; mt++) {
-                        const float4 o2 = xchg[(slot * C::STATE_F4 + hh * NMT + mt) * 32 + lane];
-                        oacc[hh][mt][0] = oacc[hh][mt][0] * f1 + o2.x * f2;
-                        oacc[hh][mt][1] = oacc[hh][mt][1] * f1 + o2.y * f2;
-                        oacc[hh][mt][2] = oacc[hh][mt][2] * f1 + o2.z * f2;
-                        oacc[hh][mt][3] = oacc[hh][mt][3] * f1 + o2.w * f2;
-                    }
-                }
+            for (int mt = 0; mt < NMT; mt++)
+                xchg[((warp * NH + hh) * NMT + mt) * 32 + lane] = make_float4(
+                    oacc[hh][mt][0], oacc[hh][mt][1], oacc[hh][mt][2], oacc[hh][mt][3]);
+            if (g == 0) {
+                xml[((warp * NH + hh) * 2 + 0) * 4 + tg] = m_run[hh];
+                xml[((warp * NH + hh) * 2 + 1) * 4 + tg] = l_run[hh];
             }
         }
-        // a warp whose copy never arrived poisons the row (NaN propagates through the merge)
-        if (stalled) m_run[0] = __int_as_float(0x7fc00000);
-        if (warp == 0) {
+        __syncthreads();
+        const int next = skip_empty(item + gridDim.x);
+        if (warp < NRED) {
+            float* prow = partial_row(cur);
+            for (int j = tid; j < NH * NMT * 32; j += NRED * 32) {
+                const int ln = j & 31, mt = (j >> 5) % NMT, hh = j / (32 * NMT);
+                const int tg_ = ln & 3, g_ = ln >> 2;
+                float M = -INFINITY;
 #pragma unroll
-            for (int hh = 0; hh < NH; hh++) {
-                float l = l_run[hh];
-                l += __shfl_xor_sync(0xffffffffu, l, 4);
-                l += __shfl_xor_sync(0xffffffffu, l, 8);
-                l += __shfl_xor_sync(0xffffffffu, l, 16);
-                const int h = 4 * hh + tg;
+                for (int w2 = 0; w2 < WARPS; w2++)
+                    M = fmaxf(M, xml[((w2 * NH + hh) * 2 + 0) * 4 + tg_]);
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                float l = 0.f;
+#pragma unroll
+                for (int w2 = 0; w2 < WARPS; w2++) {
+                    const float mw = xml[((w2 * NH + hh) * 2 + 0) * 4 + tg_];
+                    if (mw != -INFINITY) {  // (NaN compares unequal: poison goes through)
+                        const float f = __expf(mw - M);
+                        const float4 o = xchg[((w2 * NH + hh) * NMT + mt) * 32 + ln];
+                        a.x = fmaf(o.x, f, a.x);
+                        a.y = fmaf(o.y, f, a.y);
+                        a.z = fmaf(o.z, f, a.z);
+                        a.w = fmaf(o.w, f, a.w);
+                        l = fmaf(xml[((w2 * NH + hh) * 2 + 1) * 4 + tg_], f, l);
+                    }
+                }
+                const int h = 4 * hh + tg_;
                 if (h < group) {
                     float* dst = prow + h * prow_head_stride;
-#pragma unroll
-                    for (int mt = 0; mt < NMT; mt++)
-                        *reinterpret_cast<float4*>(dst + (D / 8) * g + 4 * mt) = make_float4(
-                            oacc[hh][mt][0], oacc[hh][mt][1], oacc[hh][mt][2], oacc[hh][mt][3]);
-                    if (g == 0) {
-                        dst[D] = m_run[hh];
+                    *reinterpret_cast<float4*>(dst + (D / 8) * g_ + 4 * mt) = a;
+                    if (g_ == 0 && mt == 0) {
+                        dst[D] = M;
                         dst[D + 1] = l;
                     }
                 }
             }
         }
-        __syncthreads();  // qs / sblk / exchange area are reused by the next item
+        if constexpr (NRED < WARPS) {
+            if (warp >= NRED && next < n_items) prologue(item_info(next), NRED, WARPS - NRED);
+        } else {
+            __syncthreads();
+            if (next < n_items) prologue(item_info(next), 0, WARPS);
+        }
+        item = next;
     }
 }
 

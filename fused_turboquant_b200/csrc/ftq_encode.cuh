@@ -49,6 +49,7 @@ struct EncodeSink {
     int64_t page_bytes;     // paged: bytes per (block, head) page
     int codes_off;          // paged: offset of this tensor's codes inside the page
     int norms_off;          // paged: offset of this tensor's fp16 norms inside the page
+    int swap_halves;        // paged: store the row's two halves exchanged for tokens with bit 1 set
     int block_size;         // v0: tokens per block
     int elem_size;          // v0: bytes per (token, head) slot
     int64_t plane_off;      // v0: byte offset of the K or V plane
@@ -84,6 +85,7 @@ __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm,
     // destination of this vector
     uint8_t* dst = nullptr;
     bool store = valid;
+    int rot = 0;  // word rotation inside the row (half swap of the paged V rows)
     if (sink.mode == kSinkFlat) {
         dst = sink.codes + v * PD;
     } else if (valid) {
@@ -97,6 +99,7 @@ __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm,
             const int off = static_cast<int>(slot - blk * kPageTokens);
             uint8_t* page = sink.codes + sink_layer + (blk * sink.Hkv + head) * sink.page_bytes;
             dst = page + sink.codes_off + off * PD;
+            if (sink.swap_halves && (off & 2)) rot = PD / 8;
             if (t == 0)
                 *reinterpret_cast<__half*>(page + sink.norms_off + 2 * off) =
                     __float2half_rn(norm);
@@ -122,10 +125,17 @@ __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm,
             const uint32_t hi = __shfl_sync(0xffffffffu, o, g0 + 1, 8);
             const uint64_t cat = (static_cast<uint64_t>(hi) << 24) | lo;
             const uint32_t word = static_cast<uint32_t>(cat >> (8 * ((4 * t) % 3)));
-            if (store && t < 6) reinterpret_cast<uint32_t*>(dst + 24 * i)[t] = word;
+            if (store && t < 6) {
+                int widx = 6 * i + t;
+                widx = widx + rot < PD / 4 ? widx + rot : widx + rot - PD / 4;
+                reinterpret_cast<uint32_t*>(dst)[widx] = word;
+            }
         } else {
-            const int widx = t + 8 * i;
-            if (store && widx < PD / 4) reinterpret_cast<uint32_t*>(dst)[widx] = o;
+            int widx = t + 8 * i;
+            if (store && widx < PD / 4) {
+                widx = widx + rot < PD / 4 ? widx + rot : widx + rot - PD / 4;
+                reinterpret_cast<uint32_t*>(dst)[widx] = o;
+            }
         }
     }
 }

@@ -136,6 +136,10 @@ int ftq_flash_decode(const void *q, int q_dtype, int q_is_rotated, const uint8_t
  *   pool u8 [num_blocks, Hkv, page_bytes]; a (block, head) page holds 16 tokens:
  *     [ K codes 16 x pdk | K norms 16 x fp16 | V codes 16 x pdv | V norms 16 x fp16 ]
  *   page_bytes = 16 * (pdk + pdv + 4); every sub-array starts 16-byte aligned.
+ *   K rows and all norms are in token order.  A V row (pdv bytes) is stored with its two
+ *   halves exchanged when the token's offset in the page has bit 1 set (tokens 2, 3, 6, 7,
+ *   10, 11, 14, 15): the decode kernel reads four rows per instruction and this spreads them
+ *   over the shared-memory banks.  The bytes themselves are the reference's packed codes.
  * The pool plays the role of the kv_cache tensor whose shape the backend
  * defines (vllm_plugin/backend.py:107-124); slots hold the same code bytes
  * and fp16 norms the reference stores, grouped per (block, head) so that one

@@ -15,6 +15,14 @@ def page_offsets(d, bk, bv):
     return off_kn, off_vc, off_vn, off_vn + 2 * PAGE
 
 
+def v_row(row, t):
+    """V rows are stored with their halves exchanged for page tokens with bit 1 set."""
+    if t & 2:
+        h = row.shape[-1] // 2
+        return np.concatenate([row[..., h:], row[..., :h]], axis=-1)
+    return row
+
+
 def pool_from_contiguous(k_idx, k_norms, v_idx, v_norms, block_table, num_blocks, d, bk, bv,
                          seq_lens=None, base=None):
     """Lay contiguous [B,Hkv,S,*] codes / fp16 norms out as pool u8 [num_blocks, Hkv, page_bytes].
@@ -32,7 +40,7 @@ def pool_from_contiguous(k_idx, k_norms, v_idx, v_norms, block_table, num_blocks
                 page = pool[blk, h]
                 page[t * pd(d, bk):(t + 1) * pd(d, bk)] = k_idx[b, h, s]
                 page[off_kn + 2 * t:off_kn + 2 * t + 2] = np.frombuffer(kn[b, h, s].tobytes(), np.uint8)
-                page[off_vc + t * pd(d, bv):off_vc + (t + 1) * pd(d, bv)] = v_idx[b, h, s]
+                page[off_vc + t * pd(d, bv):off_vc + (t + 1) * pd(d, bv)] = v_row(v_idx[b, h, s], t)
                 page[off_vn + 2 * t:off_vn + 2 * t + 2] = np.frombuffer(vn[b, h, s].tobytes(), np.uint8)
     return pool
 
@@ -52,7 +60,7 @@ def contiguous_from_pool(pool, block_table, seq_lens, S, d, bk, bv):
             for h in range(Hkv):
                 page = pool[blk, h]
                 k_idx[b, h, s] = page[t * pd(d, bk):(t + 1) * pd(d, bk)]
-                v_idx[b, h, s] = page[off_vc + t * pd(d, bv):off_vc + (t + 1) * pd(d, bv)]
+                v_idx[b, h, s] = v_row(page[off_vc + t * pd(d, bv):off_vc + (t + 1) * pd(d, bv)], t)
                 k_n[b, h, s] = page[off_kn + 2 * t:off_kn + 2 * t + 2].view(np.uint16)[0]
                 v_n[b, h, s] = page[off_vn + 2 * t:off_vn + 2 * t + 2].view(np.uint16)[0]
     return k_idx, k_n.view(np.float16), v_idx, v_n.view(np.float16)
