@@ -120,6 +120,61 @@ cudaError_t dispatch_encode(int d, int bits, int dtype, const ftq::EncodeSource&
     return cudaErrorInvalidValue;
 }
 
+// fp32 -> fp16 -> fp32 with round to nearest even (host side).
+float round_to_half(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    const uint32_t sign = x & 0x80000000u;
+    uint32_t a = x & 0x7fffffffu;
+    if (a >= 0x477ff000u) a = 0x7f800000u;           // overflow -> inf
+    else if (a < 0x38800000u) {                      // half subnormal range: quantum 2^-24
+        float v;
+        memcpy(&v, &a, 4);
+        v = std::nearbyint(v * 16777216.0f) / 16777216.0f;
+        memcpy(&a, &v, 4);
+    } else {
+        const uint32_t rem = a & 0x1fffu;
+        a &= ~0x1fffu;
+        if (rem > 0x1000u || (rem == 0x1000u && (a & 0x2000u))) a += 0x2000u;
+    }
+    a |= sign;
+    float r;
+    memcpy(&r, &a, 4);
+    return r;
+}
+
+// Factor s in [1, 2) for the V centroids of the tensor-core path: fp16(s * level) / s should
+// have no common bias.  The bias is weighted with the cell probabilities of N(0, 1/D) (cell
+// edges = level midpoints); a small share of the mean absolute error keeps s from trading a
+// zero bias against large individual errors.
+float choose_v_scale(const float* levels, int bits, int head_dim) {
+    const int n = 1 << bits;
+    double prob[16];
+    const double inv_sigma = std::sqrt(static_cast<double>(head_dim));
+    double prev = 0.0;
+    for (int c = 0; c < n; c++) {
+        const double cdf = c == n - 1 ? 1.0
+            : 0.5 * std::erfc(-0.5 * (static_cast<double>(levels[c]) + levels[c + 1]) * inv_sigma /
+                              std::sqrt(2.0));
+        prob[c] = cdf - prev;
+        prev = cdf;
+    }
+    float best = 1.0f;
+    double best_cost = 1e30;
+    for (int i = 0; i < 8192; i++) {
+        const float sc = 1.0f + static_cast<float>(i) / 8192.0f;
+        double bias = 0.0, mad = 0.0;
+        for (int c = 0; c < n; c++) {
+            const double err = static_cast<double>(round_to_half(levels[c] * sc)) / sc - levels[c];
+            bias += prob[c] * err;
+            mad += prob[c] * std::fabs(err);
+        }
+        const double cost = std::fabs(bias) + 0.05 * mad;
+        if (cost < best_cost) { best_cost = cost; best = sc; }
+    }
+    return best;
+}
+
 struct ChunkPlan {
     int chunk_tokens, n_chunks, n_hpass;
 };
@@ -609,8 +664,12 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if (mma) {
+        const float vs = choose_v_scale(levels_v_host, bits_v, head_dim);
+        for (int i = 0; i < (1 << bits_v); i++) p.lv_scaled.v[i] = levels_v_host[i] * vs;
+        p.inv_v_scale = 1.0f / vs;
+        // K and V can share one table only when the scaled V levels equal the K levels
         const bool shared_lut = bits_k == bits_v &&
-            memcmp(levels_k_host, levels_v_host, sizeof(float) << bits_k) == 0;
+            memcmp(p.lk.v, p.lv_scaled.v, sizeof(float) << bits_k) == 0;
         e = dispatch_mma(head_dim, bits_k, bits_v, shared_lut, p, n_layers * B, st);
     } else {
         e = dispatch_split(head_dim, bits_k, bits_v, true, p, n_layers * B, st);

@@ -48,6 +48,10 @@ struct AttnParams {
     Codebook lk, lv;
     SignBits signs;
     float rsqrt_d;
+    // tensor-core path: V centroids pre-multiplied by v_scale before the fp16 rounding
+    // (lv_scaled), undone through the weights (inv_v_scale)
+    Codebook lv_scaled;
+    float inv_v_scale;
 };
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, int src_bytes) {

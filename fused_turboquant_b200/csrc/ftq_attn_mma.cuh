@@ -8,7 +8,10 @@
 // Same mathematics as attn_split_kernel (ftq_attn.cuh), i.e. the fused
 // formulation of src/fused_turboquant/kernels/triton_flash_decode.py:33-324 in the
 // reference; centroids, the rotated query and the softmax weights are rounded
-// to fp16 before the MMAs, accumulation is fp32.
+// to fp16 before the MMAs, accumulation is fp32.  The V centroids are multiplied
+// by a host-chosen factor in [1, 2) before the rounding (and the weights divided
+// by it): a common rounding bias of the centroids would otherwise add up over
+// all coordinates into one output element through the inverse rotation.
 //
 // Work split: persistent CTAs (one per SM with 16 warps when a 4-bit byte table
 // is in use, else two per SM with 8 warps) loop over work items
@@ -360,7 +363,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                     tb[i] = *reinterpret_cast<const uint32_t*>(&h);
                 }
             } else if constexpr (BV == 4 && !SHARED_LUT) {
-                const __half2 h = __floats2half2_rn(p.lv.v[e & 15], p.lv.v[e >> 4]);
+                const __half2 h = __floats2half2_rn(p.lv_scaled.v[e & 15], p.lv_scaled.v[e >> 4]);
                 tb[i] = *reinterpret_cast<const uint32_t*>(&h);
             }
         }
@@ -377,7 +380,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         uint32_t* t = reinterpret_cast<uint32_t*>(gptr(tv_small));
         for (int i = tid; i < (1 << C::IWV) * 32; i += THREADS) {
             const int e = i >> 5;
-            const __half2 h = __floats2half2_rn(p.lv.v[e & ((1 << BV) - 1)], p.lv.v[e >> BV]);
+            const __half2 h = __floats2half2_rn(p.lv_scaled.v[e & ((1 << BV) - 1)], p.lv_scaled.v[e >> BV]);
             t[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
     }
@@ -562,8 +565,10 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             }
             const float kna = half_bits_to_float(odd ? r.kn.x >> 16 : r.kn.x & 0xffffu);
             const float knb = half_bits_to_float(odd ? r.kn.y >> 16 : r.kn.y & 0xffffu);
-            const float vna = okA ? half_bits_to_float(odd ? r.vn.x >> 16 : r.vn.x & 0xffffu) : 0.f;
-            const float vnb = okB ? half_bits_to_float(odd ? r.vn.y >> 16 : r.vn.y & 0xffffu) : 0.f;
+            const float vna =
+                okA ? half_bits_to_float(odd ? r.vn.x >> 16 : r.vn.x & 0xffffu) * p.inv_v_scale : 0.f;
+            const float vnb =
+                okB ? half_bits_to_float(odd ? r.vn.y >> 16 : r.vn.y & 0xffffu) * p.inv_v_scale : 0.f;
 
             // ---- online softmax per head (4*hh + tg); weights to fp16, transposed for P.V
             uint32_t pb[NH][2][2];  // [hh][k-step][b0/b1]
