@@ -147,7 +147,34 @@ float round_to_half(float f) {
 // have no common bias.  The bias is weighted with the cell probabilities of N(0, 1/D) (cell
 // edges = level midpoints); a small share of the mean absolute error keeps s from trading a
 // zero bias against large individual errors.
+float search_v_scale(const float* levels, int bits, int head_dim);
+
+// The search costs ~1 ms of host time: results are remembered per (levels, bits, head_dim).
 float choose_v_scale(const float* levels, int bits, int head_dim) {
+    struct Entry { float levels[16]; int bits, head_dim; float scale; };
+    static std::mutex mu;
+    static Entry cache[16];
+    static int n_cached = 0, next_slot = 0;
+    const size_t nbytes = sizeof(float) << bits;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < n_cached; i++)
+            if (cache[i].bits == bits && cache[i].head_dim == head_dim &&
+                memcmp(cache[i].levels, levels, nbytes) == 0)
+                return cache[i].scale;
+    }
+    const float sc = search_v_scale(levels, bits, head_dim);
+    std::lock_guard<std::mutex> lock(mu);
+    Entry& e = cache[next_slot];
+    memset(&e, 0, sizeof(e));
+    memcpy(e.levels, levels, nbytes);
+    e.bits = bits; e.head_dim = head_dim; e.scale = sc;
+    next_slot = (next_slot + 1) % 16;
+    if (n_cached < 16) n_cached++;
+    return sc;
+}
+
+float search_v_scale(const float* levels, int bits, int head_dim) {
     const int n = 1 << bits;
     double prob[16];
     const double inv_sigma = std::sqrt(static_cast<double>(head_dim));
