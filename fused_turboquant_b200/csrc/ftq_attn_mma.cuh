@@ -269,15 +269,25 @@ struct MmaCfg {
     // per-warp ring of pages staged by bulk copies (TMA), one mbarrier per buffer
     static constexpr int RING = 2;
     // two groups of shared-memory objects, placed first-fit around the 64 KB table window
-    // (the merge exchange area aliases the page ring, which is idle during the merge)
-    static constexpr int GROUP_A = SMALL_BYTES + 8 * (D + 16) * 4 + kMmaMaxChunkPages * 4 + 64;
+    // With one head half the merge exchange area gets its own space when it fits, so that the
+    // first pages of the NEXT item can already be copied into the ring while the merge runs;
+    // otherwise it aliases the ring (idle during the merge).
     static constexpr int RING_BYTES = WARPS * RING * PAGE_BYTES;
-    static constexpr int GROUP_B =
-        (RING_BYTES > XCHG_BYTES ? RING_BYTES : XCHG_BYTES) + WARPS * RING * 8 + 256;
-    static constexpr int MIN_AB = GROUP_A < GROUP_B ? GROUP_A : GROUP_B;
-    static constexpr int WORST = (65536 + GROUP_B > MIN_AB + GROUP_A + GROUP_B)
-                                     ? 65536 + GROUP_B : MIN_AB + GROUP_A + GROUP_B;
-    static constexpr int SMEM_BYTES = BYTE ? 65536 + WORST : GROUP_A + GROUP_B;
+    static constexpr int BASE_A = SMALL_BYTES + 8 * (D + 16) * 4 + kMmaMaxChunkPages * 4 + 64;
+    static constexpr int BARS = WARPS * RING * 8 + 256;
+    __host__ __device__ static constexpr int total(bool sep) {
+        const int a = BASE_A + (sep ? XCHG_BYTES + 16 : 0);
+        const int b = ((sep || RING_BYTES > XCHG_BYTES) ? RING_BYTES : XCHG_BYTES) + BARS;
+        if (!BYTE) return a + b;
+        // objects are placed first-fit before / after the 64 KB-aligned table window
+        const int mn = a < b ? a : b;
+        const int worst = (65536 + b > mn + a + b) ? 65536 + b : mn + a + b;
+        return 65536 + worst;
+    }
+    static constexpr bool SEP = NH == 1 && total(true) <= 227 * 1024;
+    static constexpr int GROUP_A = BASE_A + (SEP ? XCHG_BYTES + 16 : 0);
+    static constexpr int GROUP_B = ((SEP || RING_BYTES > XCHG_BYTES) ? RING_BYTES : XCHG_BYTES) + BARS;
+    static constexpr int SMEM_BYTES = total(SEP);
 };
 
 // One page worth of packed data in registers (per lane).
@@ -342,9 +352,10 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     const uint32_t grp_b = take(C::GROUP_B, 128);
     const uint32_t bars = grp_b;                              // [WARPS][RING] x 8 bytes
     const uint32_t ring = (grp_b + WARPS * C::RING * 8 + 127u) & ~127u;
-    // merge exchange area: aliases the ring (no copy is in flight when the merge runs)
-    float4* xchg = reinterpret_cast<float4*>(gptr(ring));  // [WARPS][NH][NMT][32]
-    float* xml = reinterpret_cast<float*>(gptr(ring + WARPS * 32 * C::STATE_F4 * 16));  // [WARPS][NH][2][4]
+    // merge exchange area: own space after the block ids, or aliasing the ring
+    const uint32_t xaddr = C::SEP ? ((cur + 8 * (D + 16) * 4 + kMmaMaxChunkPages * 4 + 15u) & ~15u) : ring;
+    float4* xchg = reinterpret_cast<float4*>(gptr(xaddr));  // [WARPS][NH][NMT][32]
+    float* xml = reinterpret_cast<float*>(gptr(xaddr + WARPS * 32 * C::STATE_F4 * 16));  // [WARPS][NH][2][4]
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -395,6 +406,8 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     mbar_fence_init();
     __syncthreads();
     uint32_t phase = 0;   // bit r = parity the next wait on ring buffer r expects
+    int ring_it = 0;      // pages this warp has taken from its ring so far (buffer = ring_it % RING)
+    bool primed = false;  // the first RING pages of the current item were requested early
     bool stalled = false; // a bulk copy never arrived: stop waiting, poison the result
 
     // rotated queries in shared memory: head rows of D + 16 floats, each quarter of a row
@@ -519,6 +532,15 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             mbar_expect_tx(my_bars + rb * 8, C::PAGE_BYTES);
             bulk_g2s(my_ring + rb * C::PAGE_BYTES, page, C::PAGE_BYTES, my_bars + rb * 8);
         };
+        // same, for the first pages of a later item, whose block ids are not staged yet
+        auto issue_page_of = [&](const Item& it2, int pg, int rb) {
+            const int32_t blk = p.block_table[static_cast<int64_t>(it2.b) * p.max_blocks +
+                                              it2.t0 / kPageTokens + pg];
+            const uint8_t* page = p.pool + it2.layer * p.pool_layer_stride + blk * blk_stride +
+                                  static_cast<int64_t>(it2.hkv) * C::PAGE_BYTES;
+            mbar_expect_tx(my_bars + rb * 8, C::PAGE_BYTES);
+            bulk_g2s(my_ring + rb * C::PAGE_BYTES, page, C::PAGE_BYTES, my_bars + rb * 8);
+        };
         // every lane copies its slices of the staged page into registers
         auto read_page = [&](Regs& r, int rb) {
             const uint32_t page = my_ring + rb * C::PAGE_BYTES;
@@ -540,13 +562,8 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             r.vn = lds64(page + C::OFF_VN + 8 * (g >> 1));
         };
 
-        auto compute = [&](const Regs& r, int pg) {
-            const int ntok = min(kPageTokens, t1 - t0 - pg * kPageTokens);
-            const int tokA = 4 * (g >> 1) + (g & 1), tokB = tokA + 2;  // rows g, g+8 of S
-            const bool okA = tokA < ntok, okB = tokB < ntok;
-
-            // ---- S = K.Q^T (two accumulator chains per head half)
-            float c[NH][2][4];
+        // S = K.Q^T of one page (two accumulator chains per head half)
+        auto qk_scores = [&](const Regs& r, float (&c)[NH][2][4]) {
 #pragma unroll
             for (int hh = 0; hh < NH; hh++)
 #pragma unroll
@@ -563,15 +580,21 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 for (int hh = 0; hh < NH; hh++)
                     mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qb[hh][kb][0], qb[hh][kb][1]);
             }
+        };
+
+        // online softmax per head (4*hh + tg) over the page's scores; the weights p * vnorm are
+        // rounded to fp16 and transposed into the B operand of P.V
+        auto softmax_update = [&](const Regs& r, int pg, const float (&c)[NH][2][4],
+                                  uint32_t (&pb)[NH][2][2]) {
+            const int ntok = min(kPageTokens, t1 - t0 - pg * kPageTokens);
+            const int tokA = 4 * (g >> 1) + (g & 1), tokB = tokA + 2;  // rows g, g+8 of S
+            const bool okA = tokA < ntok, okB = tokB < ntok;
             const float kna = half_bits_to_float(odd ? r.kn.x >> 16 : r.kn.x & 0xffffu);
             const float knb = half_bits_to_float(odd ? r.kn.y >> 16 : r.kn.y & 0xffffu);
             const float vna =
                 okA ? half_bits_to_float(odd ? r.vn.x >> 16 : r.vn.x & 0xffffu) * p.inv_v_scale : 0.f;
             const float vnb =
                 okB ? half_bits_to_float(odd ? r.vn.y >> 16 : r.vn.y & 0xffffu) * p.inv_v_scale : 0.f;
-
-            // ---- online softmax per head (4*hh + tg); weights to fp16, transposed for P.V
-            uint32_t pb[NH][2][2];  // [hh][k-step][b0/b1]
 #pragma unroll
             for (int hh = 0; hh < NH; hh++) {
                 const float sa = okA ? (c[hh][0][0] + c[hh][1][0]) * kna : -INFINITY;
@@ -613,42 +636,97 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 pb[hh][1][0] = odd ? (t1w << 16) : (t1w & 0xffffu);
                 pb[hh][1][1] = odd ? (t1w & 0xffff0000u) : (t1w >> 16);
             }
+        };
 
-            // ---- O^T += V^T.P^T : rows = d-pairs (D/16)*g + 2*mt + {0,1}, k = (token, parity)
+        // O^T += V^T.P^T : rows = d-pairs (D/16)*g + 2*mt + {0,1}, k = (token, parity)
+        auto pv_accum = [&](const uint32_t (&v)[4][(C::VSB + 3) / 4], const uint32_t (&pb)[NH][2][2]) {
 #pragma unroll
             for (int ks = 0; ks < 2; ks++)
 #pragma unroll
                 for (int mt = 0; mt < NMT; mt++) {
-                    const uint32_t a0 = lut32(entry_addr<C::IWV>(r.v[2 * ks], 2 * mt, lv_lane));
-                    const uint32_t a1 = lut32(entry_addr<C::IWV>(r.v[2 * ks], 2 * mt + 1, lv_lane));
-                    const uint32_t a2 = lut32(entry_addr<C::IWV>(r.v[2 * ks + 1], 2 * mt, lv_lane));
-                    const uint32_t a3 = lut32(entry_addr<C::IWV>(r.v[2 * ks + 1], 2 * mt + 1, lv_lane));
+                    const uint32_t a0 = lut32(entry_addr<C::IWV>(v[2 * ks], 2 * mt, lv_lane));
+                    const uint32_t a1 = lut32(entry_addr<C::IWV>(v[2 * ks], 2 * mt + 1, lv_lane));
+                    const uint32_t a2 = lut32(entry_addr<C::IWV>(v[2 * ks + 1], 2 * mt, lv_lane));
+                    const uint32_t a3 = lut32(entry_addr<C::IWV>(v[2 * ks + 1], 2 * mt + 1, lv_lane));
 #pragma unroll
                     for (int hh = 0; hh < NH; hh++)
                         mma_16816(oacc[hh][mt], a0, a1, a2, a3, pb[hh][ks][0], pb[hh][ks][1]);
                 }
         };
 
-        // ---- main loop: the warp's pages; RING bulk copies stay in flight during the math
+        // ---- main loop: the warp's pages; RING bulk copies stay in flight during the math.
+        // Software pipeline: K.Q^T of page i+1 and P.V of page i are independent and sit in one
+        // straight-line block, so their look-ups and MMAs overlap each other's latencies.
         {
-            if (lane == 0) {
-                // the previous item's merge wrote the ring with ordinary stores
+            if (lane == 0 && !primed) {
+                // (when the exchange area aliases the ring, the previous item's merge wrote it
+                // with ordinary stores)
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
 #pragma unroll
                 for (int r = 0; r < C::RING; r++)
-                    if (warp + r * WARPS < n_pages) issue_page(warp + r * WARPS, r);
+                    if (warp + r * WARPS < n_pages) issue_page(warp + r * WARPS, (ring_it + r) % C::RING);
             }
-            int it = 0;
-            for (int pg = warp; pg < n_pages; pg += WARPS, it++) {
-                const int rb = it % C::RING;
+            // stage page pg into registers and re-arm its ring buffer
+            auto fetch = [&](Regs& r, int pg) {
+                const int rb = ring_it % C::RING;
+                ring_it++;
                 if (!stalled && !mbar_wait(my_bars + rb * 8, (phase >> rb) & 1u)) stalled = true;
                 phase ^= 1u << rb;
-                Regs r;
                 read_page(r, rb);
                 __syncwarp();  // every lane has its slices: the buffer may be refilled
                 const int nxt = pg + C::RING * WARPS;
                 if (lane == 0 && nxt < n_pages && !stalled) issue_page(nxt, rb);
-                compute(r, pg);
+            };
+            Regs ra, rb_;
+            uint32_t pba[NH][2][2], pbb[NH][2][2];
+            float c[NH][2][4];
+            int pg = warp;
+            // (two head halves already give the scheduler independent work and the extra live
+            // registers would spill: plain order there)
+            constexpr bool kPipelined = NH == 1 || D == 256;
+            if constexpr (!kPipelined) {
+                for (; pg < n_pages; pg += WARPS) {
+                    fetch(ra, pg);
+                    qk_scores(ra, c);
+                    softmax_update(ra, pg, c, pba);
+                    pv_accum(ra.v, pba);
+                }
+            } else if (pg < n_pages) {
+                fetch(ra, pg);
+                qk_scores(ra, c);
+                softmax_update(ra, pg, c, pba);
+                while (true) {
+                    // ra / pba hold page pg, scores done, P.V pending
+                    if (pg + WARPS >= n_pages) { pv_accum(ra.v, pba); break; }
+                    fetch(rb_, pg + WARPS);
+                    qk_scores(rb_, c);
+                    pv_accum(ra.v, pba);
+                    softmax_update(rb_, pg + WARPS, c, pbb);
+                    pg += WARPS;
+                    if (pg + WARPS >= n_pages) { pv_accum(rb_.v, pbb); break; }
+                    fetch(ra, pg + WARPS);
+                    qk_scores(ra, c);
+                    pv_accum(rb_.v, pbb);
+                    softmax_update(ra, pg + WARPS, c, pba);
+                    pg += WARPS;
+                }
+            }
+        }
+
+        // ---- this warp's ring is drained: request the first pages of the next item now, so that
+        // they arrive while the merge below runs (only when the merge has its own exchange area)
+        const int next = skip_empty(item + gridDim.x);
+        primed = false;
+        if constexpr (C::SEP) {
+            if (next < n_items) {
+                const Item nx = item_info(next);
+                if (lane == 0 && !stalled) {
+#pragma unroll
+                    for (int r = 0; r < C::RING; r++)
+                        if (warp + r * WARPS < nx.n_pages)
+                            issue_page_of(nx, warp + r * WARPS, (ring_it + r) % C::RING);
+                }
+                primed = true;
             }
         }
 
@@ -674,7 +752,6 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             }
         }
         __syncthreads();
-        const int next = skip_empty(item + gridDim.x);
         if (warp < NRED) {
             float* prow = partial_row(cur);
             for (int j = tid; j < NH * NMT * 32; j += NRED * 32) {

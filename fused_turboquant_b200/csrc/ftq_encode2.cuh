@@ -77,6 +77,45 @@ __device__ __forceinline__ float fma_sat(float a, float b, float c) {
     return r;
 }
 
+// Raw (not yet widened) run of 8 consecutive elements, so that the next iteration's loads can
+// be in flight while the current vectors are processed.
+template <typename T> struct Raw8 { uint4 v; };
+template <> struct Raw8<float> { float4 a, b; };
+
+template <typename T>
+__device__ __forceinline__ void load_raw8(const T* p, Raw8<T>& r) {
+    r.v = __ldg(reinterpret_cast<const uint4*>(p));
+}
+template <>
+__device__ __forceinline__ void load_raw8<float>(const float* p, Raw8<float>& r) {
+    r.a = __ldg(reinterpret_cast<const float4*>(p));
+    r.b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+}
+template <typename T>
+__device__ __forceinline__ void widen8(const Raw8<T>& r, float (&o)[8]);
+template <>
+__device__ __forceinline__ void widen8<float>(const Raw8<float>& r, float (&o)[8]) {
+    o[0] = r.a.x; o[1] = r.a.y; o[2] = r.a.z; o[3] = r.a.w;
+    o[4] = r.b.x; o[5] = r.b.y; o[6] = r.b.z; o[7] = r.b.w;
+}
+template <>
+__device__ __forceinline__ void widen8<__nv_bfloat16>(const Raw8<__nv_bfloat16>& r, float (&o)[8]) {
+    o[0] = bf16_lo(r.v.x); o[1] = bf16_hi(r.v.x);
+    o[2] = bf16_lo(r.v.y); o[3] = bf16_hi(r.v.y);
+    o[4] = bf16_lo(r.v.z); o[5] = bf16_hi(r.v.z);
+    o[6] = bf16_lo(r.v.w); o[7] = bf16_hi(r.v.w);
+}
+template <>
+__device__ __forceinline__ void widen8<__half>(const Raw8<__half>& r, float (&o)[8]) {
+    const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        o[2 * j] = f.x;
+        o[2 * j + 1] = f.y;
+    }
+}
+
 // In-lane butterfly stage on register-index bit B of packed pairs.
 template <int E, int B>
 __device__ __forceinline__ void stage2(u64 (&p)[E]) {
@@ -134,28 +173,44 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
     const u64 scale2 = pk2(tab.rsqrt_d, tab.rsqrt_d);
     const u64 cs2 = pk2(kCellScale, kCellScale), cm2 = pk2(kCellMagic, kCellMagic);
 
+    // the two vectors of this lane for the group starting at `base`: issue their loads
+    Raw8<T> rawA[NCH], rawB[NCH];
+    auto issue_loads = [&](int64_t base) {
+        const int64_t vA = base + sub, vB = base + 4 + sub;
+        if (vA < n_vec) {
+            const int64_t o = vA / src.n_inner;
+            const T* row = xbase + o * src.outer_stride + (vA - o * src.n_inner) * src.inner_stride;
+#pragma unroll
+            for (int i = 0; i < NCH; i++) load_raw8<T>(row + 8 * (t + 8 * i), rawA[i]);
+        }
+        if (vB < n_vec) {
+            const int64_t o = vB / src.n_inner;
+            const T* row = xbase + o * src.outer_stride + (vB - o * src.n_inner) * src.inner_stride;
+#pragma unroll
+            for (int i = 0; i < NCH; i++) load_raw8<T>(row + 8 * (t + 8 * i), rawB[i]);
+        }
+    };
+    if (warp * 8 < n_vec) issue_loads(warp * 8);
+
     for (int64_t base = warp * 8; base < n_vec; base += n_warps * 8) {
         const int64_t vA = base + sub, vB = base + 4 + sub;
         const bool okA = vA < n_vec, okB = vB < n_vec;
         u64 p[E];
-        {
-            const int64_t oA = okA ? vA / src.n_inner : 0, oB = okB ? vB / src.n_inner : 0;
-            const T* rowA = xbase + oA * src.outer_stride +
-                            (okA ? vA - oA * src.n_inner : 0) * src.inner_stride;
-            const T* rowB = xbase + oB * src.outer_stride +
-                            (okB ? vB - oB * src.n_inner : 0) * src.inner_stride;
 #pragma unroll
-            for (int i = 0; i < NCH; i++) {
-                float a[8], b[8];
-                if (okA) load8<T>(rowA + 8 * (t + 8 * i), a);
-                if (okB) load8<T>(rowB + 8 * (t + 8 * i), b);
+        for (int i = 0; i < NCH; i++) {
+            float a[8], b[8];
+            widen8<T>(rawA[i], a);
+            widen8<T>(rawB[i], b);
 #pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    const float fa = okA ? __uint_as_float(__float_as_uint(a[c]) ^ sgn[8 * i + c]) : 0.f;
-                    const float fb = okB ? __uint_as_float(__float_as_uint(b[c]) ^ sgn[8 * i + c]) : 0.f;
-                    p[8 * i + c] = pk2(fa, fb);
-                }
+            for (int c = 0; c < 8; c++) {
+                const float fa = okA ? __uint_as_float(__float_as_uint(a[c]) ^ sgn[8 * i + c]) : 0.f;
+                const float fb = okB ? __uint_as_float(__float_as_uint(b[c]) ^ sgn[8 * i + c]) : 0.f;
+                p[8 * i + c] = pk2(fa, fb);
             }
+        }
+        // next group's loads fly while this one is processed (16-bit inputs: 4 registers per run)
+        if constexpr (sizeof(T) == 2) {
+            if (base + n_warps * 8 < n_vec) issue_loads(base + n_warps * 8);
         }
         // stages h = 1, 2, 4 on the coordinates inside a run
         stage2<E, 0>(p);
@@ -262,6 +317,9 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
         }
         emit_vector<D, BITS>(wA, normA, okA, vA, sink, sink_layer, lane);
         emit_vector<D, BITS>(wB, normB, okB, vB, sink, sink_layer, lane);
+        if constexpr (sizeof(T) != 2) {
+            if (base + n_warps * 8 < n_vec) issue_loads(base + n_warps * 8);
+        }
     }
 }
 
