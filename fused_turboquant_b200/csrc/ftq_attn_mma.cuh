@@ -77,64 +77,6 @@ __device__ __forceinline__ uint32_t lut32(uint32_t addr) {
     return v;
 }
 
-__device__ __forceinline__ uint32_t ldg_nc32(const void* p) {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];\n" : "=r"(v) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint2 ldg_nc64(const void* p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];\n"
-                 : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint4 ldg_nc128(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
-// Load slice `idx` (SB bytes each, slices back to back starting at `row`, which
-// is 4-byte aligned) into ceil(SB/4) words.  Slices whose size is not a
-// multiple of 4 are cut out of the enclosing aligned chunk with funnel shifts.
-template <int SB>
-__device__ __forceinline__ void load_slice(const uint8_t* row, int idx, uint32_t (&w)[(SB + 3) / 4]) {
-    if constexpr (SB % 16 == 0) {
-#pragma unroll
-        for (int i = 0; i < SB / 16; i++) {
-            const uint4 v = ldg_nc128(row + idx * SB + 16 * i);
-            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-        }
-    } else if constexpr (SB % 8 == 0) {
-#pragma unroll
-        for (int i = 0; i < SB / 8; i++) {
-            const uint2 v = ldg_nc64(row + idx * SB + 8 * i);
-            w[2 * i] = v.x; w[2 * i + 1] = v.y;
-        }
-    } else if constexpr (SB % 4 == 0) {
-#pragma unroll
-        for (int i = 0; i < SB / 4; i++) w[i] = ldg_nc32(row + idx * SB + 4 * i);
-    } else if constexpr (SB == 6) {  // two slices per aligned 12-byte chunk
-        const uint8_t* c = row + (idx >> 1) * 12;
-        const uint32_t x0 = ldg_nc32(c), x1 = ldg_nc32(c + 4), x2 = ldg_nc32(c + 8);
-        const bool odd = idx & 1;
-        w[0] = odd ? __funnelshift_r(x1, x2, 16) : x0;
-        w[1] = odd ? (x2 >> 16) : (x1 & 0xffffu);
-    } else if constexpr (SB == 3) {  // four slices per aligned 12-byte chunk
-        const uint8_t* c = row + (idx >> 2) * 12;
-        const uint32_t x0 = ldg_nc32(c), x1 = ldg_nc32(c + 4), x2 = ldg_nc32(c + 8);
-        const int q = idx & 3;
-        const uint32_t lo = q == 0 ? x0 : (q == 1 ? __funnelshift_r(x0, x1, 24)
-                                                  : (q == 2 ? __funnelshift_r(x1, x2, 16) : (x2 >> 8)));
-        w[0] = lo & 0xffffffu;
-    } else {
-        static_assert(SB == 2, "unsupported slice size");
-        const uint32_t x = ldg_nc32(row + (idx >> 1) * 4);
-        w[0] = (idx & 1) ? (x >> 16) : (x & 0xffffu);
-    }
-}
-
 // ---- mbarrier + bulk-copy (TMA, 1-D, no multicast) helpers; all addresses are shared-window
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
@@ -178,7 +120,9 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return v;
 }
 
-// load_slice for a page staged in shared memory (`row` is a shared-window address).
+// Load slice `idx` (SB bytes each, slices back to back starting at the 4-byte aligned shared
+// address `row`) of a staged page into ceil(SB/4) words.  Slices whose size is not a multiple
+// of 4 are cut out of the enclosing aligned chunk with funnel shifts.
 template <int SB>
 __device__ __forceinline__ void lds_slice(uint32_t row, int idx, uint32_t (&w)[(SB + 3) / 4]) {
     if constexpr (SB % 16 == 0) {
