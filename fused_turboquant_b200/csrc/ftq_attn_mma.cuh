@@ -46,10 +46,13 @@
 //   code exactly once per KV head.
 #pragma once
 
+#include <type_traits>
+
 #include "ftq_attn.cuh"
 
 namespace ftq {
 
+constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 constexpr int kMmaMaxChunkPages = 1024;  // block ids of one chunk are staged in shared memory
 
 // (not volatile: a pure function of its operands, so the compiler may interleave the MMAs
@@ -195,7 +198,10 @@ struct MmaCfg {
     static constexpr int IWK = 2 * BK, IWV = 2 * BV;    // table index width (two codes)
     static constexpr bool BYTE = BK == 4 || BV == 4;    // a 64 KB byte-indexed window is used
     // head_dim 256 needs > 128 registers per thread: 8 warps, one CTA per SM
-    static constexpr int WARPS = (BYTE && D != 256) ? 16 : 8;
+#ifndef FTQ_W16
+#define FTQ_W16 16
+#endif
+    static constexpr int WARPS = (BYTE && D != 256) ? FTQ_W16 : 8;
     static constexpr int THREADS = 32 * WARPS;
     static constexpr int CTAS_PER_SM = (BYTE || D == 256) ? 1 : 2;
     static constexpr int OFF_KN = kPageTokens * PDK;
@@ -244,6 +250,13 @@ struct PageRegs {
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h16)));
+}
+
+// 2^x, one MUFU (flushes denormal results to zero; exp2(-inf) = 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
@@ -306,6 +319,11 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     const int g = lane >> 2, tg = lane & 3;
     const bool odd = g & 1;
     const int group = p.Hq / p.Hkv;  // <= 4 * NH
+    // byte selectors (source 4 = a zero byte): a lane's own fp16 of a packed pair, and the
+    // placement of a weight in the low (even g) or high (odd g) half of a B register
+    const uint32_t sel_own = odd ? 0x4432u : 0x4410u;
+    const uint32_t sel_plo = odd ? 0x1044u : 0x4410u;
+    const uint32_t sel_phi = odd ? 0x3244u : 0x4432u;
 
     // ---- once per CTA: dequantisation tables
     if constexpr (C::BYTE) {
@@ -422,7 +440,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             octet_fwht<E>(a, lane);
 #pragma unroll
             for (int k = 0; k < E; k++)
-                qs[qs_index(hh, t8 + 8 * k)] = hv ? a[k] * p.rsqrt_d * p.scale : 0.f;
+                qs[qs_index(hh, t8 + 8 * k)] = hv ? a[k] * p.rsqrt_d * (p.scale * kLog2e) : 0.f;
         }
     };
     // warps that fold the per-warp states into the partial rows; when at least two warps are
@@ -452,9 +470,10 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 qb[hh][kb][1] = *reinterpret_cast<const uint32_t*>(&hi);
             }
 
-        const uint8_t* pool = p.pool + layer * p.pool_layer_stride;
-        const int64_t head_off = static_cast<int64_t>(hkv) * C::PAGE_BYTES;
-        const int64_t blk_stride = static_cast<int64_t>(p.Hkv) * C::PAGE_BYTES;
+        // page address = head_base + block id * blk_stride (one 32 x 32 -> 64 bit multiply-add)
+        const uint8_t* head_base =
+            p.pool + layer * p.pool_layer_stride + static_cast<int64_t>(hkv) * C::PAGE_BYTES;
+        const uint32_t blk_stride = static_cast<uint32_t>(p.Hkv) * C::PAGE_BYTES;
 
         // per lane: softmax state of head 4*hh + tg, O[head][(D/8)*g .. + D/8)
         float m_run[NH], l_run[NH], oacc[NH][NMT][4];
@@ -472,7 +491,8 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         const uint32_t my_ring = ring + warp * C::RING * C::PAGE_BYTES;
         // lane 0 starts the bulk copy of page pg into ring buffer rb (contiguous PAGE_BYTES)
         auto issue_page = [&](int pg, int rb) {
-            const uint8_t* page = pool + sblk[pg] * blk_stride + head_off;
+            const uint8_t* page =
+                head_base + static_cast<uint64_t>(static_cast<uint32_t>(sblk[pg])) * blk_stride;
             mbar_expect_tx(my_bars + rb * 8, C::PAGE_BYTES);
             bulk_g2s(my_ring + rb * C::PAGE_BYTES, page, C::PAGE_BYTES, my_bars + rb * 8);
         };
@@ -480,7 +500,8 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         auto issue_page_of = [&](const Item& it2, int pg, int rb) {
             const int32_t blk = p.block_table[static_cast<int64_t>(it2.b) * p.max_blocks +
                                               it2.t0 / kPageTokens + pg];
-            const uint8_t* page = p.pool + it2.layer * p.pool_layer_stride + blk * blk_stride +
+            const uint8_t* page = p.pool + it2.layer * p.pool_layer_stride +
+                                  static_cast<uint64_t>(static_cast<uint32_t>(blk)) * blk_stride +
                                   static_cast<int64_t>(it2.hkv) * C::PAGE_BYTES;
             mbar_expect_tx(my_bars + rb * 8, C::PAGE_BYTES);
             bulk_g2s(my_ring + rb * C::PAGE_BYTES, page, C::PAGE_BYTES, my_bars + rb * 8);
@@ -526,30 +547,44 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             }
         };
 
-        // online softmax per head (4*hh + tg) over the page's scores; the weights p * vnorm are
-        // rounded to fp16 and transposed into the B operand of P.V
-        auto softmax_update = [&](const Regs& r, int pg, const float (&c)[NH][2][4],
+        // online softmax per head (4*hh + tg) over the page's scores (base-2 exponent domain:
+        // the queries carry log2(e)); the weights p * vnorm are rounded to fp16 and transposed
+        // into the B operand of P.V.  FULL = all 16 tokens of the page are valid.
+        auto softmax_update = [&](auto full_tag, const Regs& r, int pg, const float (&c)[NH][2][4],
                                   uint32_t (&pb)[NH][2][2]) {
-            const int ntok = min(kPageTokens, t1 - t0 - pg * kPageTokens);
-            const int tokA = 4 * (g >> 1) + (g & 1), tokB = tokA + 2;  // rows g, g+8 of S
-            const bool okA = tokA < ntok, okB = tokB < ntok;
-            const float kna = half_bits_to_float(odd ? r.kn.x >> 16 : r.kn.x & 0xffffu);
-            const float knb = half_bits_to_float(odd ? r.kn.y >> 16 : r.kn.y & 0xffffu);
-            const float vna =
-                okA ? half_bits_to_float(odd ? r.vn.x >> 16 : r.vn.x & 0xffffu) * p.inv_v_scale : 0.f;
-            const float vnb =
-                okB ? half_bits_to_float(odd ? r.vn.y >> 16 : r.vn.y & 0xffffu) * p.inv_v_scale : 0.f;
+            constexpr bool FULL = decltype(full_tag)::value;
+            bool okA = true, okB = true;
+            if constexpr (!FULL) {
+                const int ntok = t1 - t0 - pg * kPageTokens;
+                const int tokA = 4 * (g >> 1) + (g & 1);  // rows g, g+8 of S: tokens tokA, tokA + 2
+                okA = tokA < ntok;
+                okB = tokA + 2 < ntok;
+            }
+            const float kna = half_bits_to_float(__byte_perm(r.kn.x, 0u, sel_own));
+            const float knb = half_bits_to_float(__byte_perm(r.kn.y, 0u, sel_own));
+            float vna = half_bits_to_float(__byte_perm(r.vn.x, 0u, sel_own)) * p.inv_v_scale;
+            float vnb = half_bits_to_float(__byte_perm(r.vn.y, 0u, sel_own)) * p.inv_v_scale;
+            if constexpr (!FULL) {
+                vna = okA ? vna : 0.f;
+                vnb = okB ? vnb : 0.f;
+            }
 #pragma unroll
             for (int hh = 0; hh < NH; hh++) {
-                const float sa = okA ? (c[hh][0][0] + c[hh][1][0]) * kna : -INFINITY;
-                const float sb = okB ? (c[hh][0][2] + c[hh][1][2]) * knb : -INFINITY;
+                float sa = (c[hh][0][0] + c[hh][1][0]) * kna;
+                float sb = (c[hh][0][2] + c[hh][1][2]) * knb;
+                if constexpr (!FULL) {
+                    sa = okA ? sa : -INFINITY;
+                    sb = okB ? sb : -INFINITY;
+                }
                 float mx = fmaxf(sa, sb);
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                const float m_new = fmaxf(m_run[hh], mx);  // finite: page token 0 is valid
-                if (m_new != m_run[hh]) {                  // same decision in all lanes of a head
-                    const float corr = m_run[hh] == -INFINITY ? 0.f : __expf(m_run[hh] - m_new);
+                // mx is finite (page token 0 is valid).  The rescale is skipped by the whole warp
+                // when no head of this half saw a new maximum.
+                if (__any_sync(0xffffffffu, mx > m_run[hh])) {
+                    const float m_new = fmaxf(m_run[hh], mx);
+                    const float corr = fast_exp2(m_run[hh] - m_new);  // 1 if unchanged, 0 from -inf
                     l_run[hh] *= corr;
 #pragma unroll
                     for (int mt = 0; mt < NMT; mt++)
@@ -557,15 +592,15 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                         for (int i = 0; i < 4; i++) oacc[hh][mt][i] *= corr;
                     m_run[hh] = m_new;
                 }
-                const float pa = okA ? __expf(sa - m_new) : 0.f;
-                const float pbv = okB ? __expf(sb - m_new) : 0.f;
+                const float pa = fast_exp2(sa - m_run[hh]);  // exp2(-inf) = 0 for masked tokens
+                const float pbv = fast_exp2(sb - m_run[hh]);
                 l_run[hh] += pa + pbv;
                 const uint32_t ha = __half_as_ushort(__float2half_rn(pa * vna));
                 const uint32_t hb = __half_as_ushort(__float2half_rn(pbv * vnb));
                 // M[token row][column n], both columns of a head equal; transposed, lane (g, tg)
                 // receives head g>>1, page tokens 4tg, 4tg+1 (first) and 4tg+2, 4tg+3 (second)
-                uint32_t t0w = movmatrix_trans(ha | (ha << 16));
-                uint32_t t1w = movmatrix_trans(hb | (hb << 16));
+                uint32_t t0w = movmatrix_trans(__byte_perm(ha, 0u, 0x1010u));
+                uint32_t t1w = movmatrix_trans(__byte_perm(hb, 0u, 0x1010u));
                 // rotate the four 16-bit weights by tg positions to match the V register order
                 if (tg & 2) { const uint32_t x = t0w; t0w = t1w; t1w = x; }
                 {
@@ -575,10 +610,12 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                     t0w = lo;
                     t1w = hi;
                 }
-                pb[hh][0][0] = odd ? (t0w << 16) : (t0w & 0xffffu);
-                pb[hh][0][1] = odd ? (t0w & 0xffff0000u) : (t0w >> 16);
-                pb[hh][1][0] = odd ? (t1w << 16) : (t1w & 0xffffu);
-                pb[hh][1][1] = odd ? (t1w & 0xffff0000u) : (t1w >> 16);
+                // column n = (head, parity): an even g keeps the weight in the low half (parity 0
+                // rows of the k index), an odd g in the high half; the other half is zero
+                pb[hh][0][0] = __byte_perm(t0w, 0u, sel_plo);
+                pb[hh][0][1] = __byte_perm(t0w, 0u, sel_phi);
+                pb[hh][1][0] = __byte_perm(t1w, 0u, sel_plo);
+                pb[hh][1][1] = __byte_perm(t1w, 0u, sel_phi);
             }
         };
 
@@ -621,37 +658,43 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 const int nxt = pg + C::RING * WARPS;
                 if (lane == 0 && nxt < n_pages && !stalled) issue_page(nxt, rb);
             };
+            // all pages but possibly the last one of the chunk are full (warp-uniform branch)
+            auto softmax_page = [&](const Regs& r, int pg2, const float (&c2)[NH][2][4],
+                                    uint32_t (&pb2)[NH][2][2]) {
+                if ((pg2 + 1) * kPageTokens <= t1 - t0) softmax_update(std::true_type{}, r, pg2, c2, pb2);
+                else softmax_update(std::false_type{}, r, pg2, c2, pb2);
+            };
             Regs ra, rb_;
             uint32_t pba[NH][2][2], pbb[NH][2][2];
             float c[NH][2][4];
             int pg = warp;
             // (two head halves already give the scheduler independent work and the extra live
             // registers would spill: plain order there)
-            constexpr bool kPipelined = NH == 1 || D == 256;
+            constexpr bool kPipelined = (NH == 1 || D == 256) && WARPS <= 16;
             if constexpr (!kPipelined) {
                 for (; pg < n_pages; pg += WARPS) {
                     fetch(ra, pg);
                     qk_scores(ra, c);
-                    softmax_update(ra, pg, c, pba);
+                    softmax_page(ra, pg, c, pba);
                     pv_accum(ra.v, pba);
                 }
             } else if (pg < n_pages) {
                 fetch(ra, pg);
                 qk_scores(ra, c);
-                softmax_update(ra, pg, c, pba);
+                softmax_page(ra, pg, c, pba);
                 while (true) {
                     // ra / pba hold page pg, scores done, P.V pending
                     if (pg + WARPS >= n_pages) { pv_accum(ra.v, pba); break; }
                     fetch(rb_, pg + WARPS);
                     qk_scores(rb_, c);
                     pv_accum(ra.v, pba);
-                    softmax_update(rb_, pg + WARPS, c, pbb);
+                    softmax_page(rb_, pg + WARPS, c, pbb);
                     pg += WARPS;
                     if (pg + WARPS >= n_pages) { pv_accum(rb_.v, pbb); break; }
                     fetch(ra, pg + WARPS);
                     qk_scores(ra, c);
                     pv_accum(rb_.v, pbb);
-                    softmax_update(ra, pg + WARPS, c, pba);
+                    softmax_page(ra, pg + WARPS, c, pba);
                     pg += WARPS;
                 }
             }
@@ -711,7 +754,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 for (int w2 = 0; w2 < WARPS; w2++) {
                     const float mw = xml[((w2 * NH + hh) * 2 + 0) * 4 + tg_];
                     if (mw != -INFINITY) {  // (NaN compares unequal: poison goes through)
-                        const float f = __expf(mw - M);
+                        const float f = fast_exp2(mw - M);
                         const float4 o = xchg[((w2 * NH + hh) * NMT + mt) * 32 + ln];
                         a.x = fmaf(o.x, f, a.x);
                         a.y = fmaf(o.y, f, a.y);
@@ -725,7 +768,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                     float* dst = prow + h * prow_head_stride;
                     *reinterpret_cast<float4*>(dst + (D / 8) * g_ + 4 * mt) = a;
                     if (g_ == 0 && mt == 0) {
-                        dst[D] = M;
+                        dst[D] = M * kLn2;  // the partial rows carry natural-log maxima
                         dst[D + 1] = l;
                     }
                 }
