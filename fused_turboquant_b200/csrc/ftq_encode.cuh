@@ -56,30 +56,77 @@ struct EncodeSink {
     int64_t layer_stride;   // bytes, blockIdx.y advances by this
 };
 
-// Transpose an 8-lane x (items per word) matrix of BITS-wide items: afterwards
-// lane j holds the items that had in-word position j, ordered by source lane.
+// Transposition of an 8-lane x (items per word) matrix of BITS-wide items: afterwards lane j
+// holds the items that had in-word position j, ordered by source lane.  Three exchange rounds
+// (partner lane ^ 1, ^ 2, ^ 4).  In a round with item distance s the sender rotates its word
+// by s (left if it is the upper lane of the pair, right otherwise), so that the items the
+// partner wants already sit where the partner puts them: the receiver merges with one
+// bit-select.  Rounds whose distance is a whole number of bytes are a single byte-permute of
+// (own word, partner's word) instead.  For 3-bit items bits 24..31 carry junk between the
+// rounds (never selected into the low 24 bits) and are cleared at the end.
 template <int BITS>
-__device__ __forceinline__ uint32_t octet_transpose_items(uint32_t w, int lane) {
-    constexpr uint32_t m0 = BITS == 4 ? 0x0F0F0F0Fu : BITS == 3 ? 0x001C71C7u : 0x33333333u;
-    constexpr uint32_t m1 = BITS == 4 ? 0x00FF00FFu : BITS == 3 ? 0x0003F03Fu : 0x0F0F0F0Fu;
-    constexpr uint32_t m2 = BITS == 4 ? 0x0000FFFFu : BITS == 3 ? 0x00000FFFu : 0x00FF00FFu;
-    constexpr int s0 = BITS, s1 = 2 * BITS, s2 = 4 * BITS;
-    uint32_t p = __shfl_xor_sync(0xffffffffu, w, 1);
-    w = (lane & 1) ? (((p >> s0) & m0) | (w & (m0 << s0))) : ((w & m0) | ((p & m0) << s0));
-    p = __shfl_xor_sync(0xffffffffu, w, 2);
-    w = (lane & 2) ? (((p >> s1) & m1) | (w & (m1 << s1))) : ((w & m1) | ((p & m1) << s1));
-    p = __shfl_xor_sync(0xffffffffu, w, 4);
-    w = (lane & 4) ? (((p >> s2) & m2) | (w & (m2 << s2))) : ((w & m2) | ((p & m2) << s2));
+struct TransposeConsts {
+    uint32_t a[3];  // rotate-left amount of the sender, or the byte-permute selector
+    uint32_t b[3];  // bits the receiver keeps of its own word (unused for byte-permute rounds)
+};
+
+template <int BITS>
+__device__ __forceinline__ TransposeConsts<BITS> transpose_consts(int lane) {
+    constexpr uint32_t m[3] = {BITS == 4 ? 0x0F0F0F0Fu : BITS == 3 ? 0x001C71C7u : 0x33333333u,
+                               BITS == 4 ? 0x00FF00FFu : BITS == 3 ? 0x0003F03Fu : 0x0F0F0F0Fu,
+                               BITS == 4 ? 0x0000FFFFu : BITS == 3 ? 0x00000FFFu : 0x00FF00FFu};
+    TransposeConsts<BITS> c;
+#pragma unroll
+    for (int j = 0; j < 3; j++) {
+        const int s = BITS << j;
+        const bool upper = (lane >> j) & 1;
+        if (s == 8) {
+            c.a[j] = upper ? 0x3715u : 0x6240u;
+            c.b[j] = 0u;
+        } else if (s == 16) {
+            c.a[j] = upper ? 0x3276u : 0x5410u;
+            c.b[j] = 0u;
+        } else {
+            c.a[j] = upper ? s : 32 - s;
+            c.b[j] = upper ? (m[j] << s) : m[j];
+        }
+    }
+    return c;
+}
+
+template <int BITS>
+__device__ __forceinline__ uint32_t octet_transpose_items(uint32_t w, const TransposeConsts<BITS>& c) {
+#pragma unroll
+    for (int j = 0; j < 3; j++) {
+        const int s = BITS << j;
+        if (s == 8 || s == 16) {
+            const uint32_t p = __shfl_xor_sync(0xffffffffu, w, 1 << j);
+            w = __byte_perm(w, p, c.a[j]);
+        } else {
+            const uint32_t p = __shfl_xor_sync(0xffffffffu, __funnelshift_l(w, w, c.a[j]), 1 << j);
+            w = (w & c.b[j]) | (p & ~c.b[j]);
+        }
+    }
+    if constexpr (BITS == 3) w &= 0x00FFFFFFu;
     return w;
+}
+
+// Slot of the token that vector v belongs to (paged pool / v0 layout); loaded ahead of the
+// arithmetic so that the store at the end does not wait for it.
+__device__ __forceinline__ int64_t load_slot(const EncodeSink& sink, int64_t v, bool valid) {
+    if (sink.mode == kSinkFlat || !valid) return -1;
+    return sink.slot_mapping[v / sink.Hkv];
 }
 
 // Store one encoded vector: `w` holds this lane's codes (coordinates l + 8k) packed as
 // octet_transpose_items expects; the octet transposes them so that every lane owns whole
-// output words, then writes codes and norm to the sink.  Must be called by all 32 lanes.
+// output words, then writes codes and norm to the sink.  `slot` is load_slot(sink, v, valid).
+// Must be called by all 32 lanes.
 template <int D, int BITS, int NW>
 __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm, bool valid,
-                                            int64_t v, const EncodeSink& sink, int64_t sink_layer,
-                                            int lane) {
+                                            int64_t v, int64_t slot, const EncodeSink& sink,
+                                            int64_t sink_layer, int lane,
+                                            const TransposeConsts<BITS>& tc) {
     constexpr int PD = packed_dim(D, BITS);
     const int t = lane & 7;
     // destination of this vector
@@ -91,7 +138,6 @@ __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm,
     } else if (valid) {
         const int64_t token = v / sink.Hkv;
         const int head = static_cast<int>(v - token * sink.Hkv);
-        const int64_t slot = sink.slot_mapping[token];
         if (slot < 0) {
             store = false;
         } else if (sink.mode == kSinkPaged) {
@@ -117,7 +163,7 @@ __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm,
     // transpose across the octet so that every lane owns whole output words
 #pragma unroll
     for (int i = 0; i < NW; i++) {
-        const uint32_t o = octet_transpose_items<BITS>(w[i], lane);
+        const uint32_t o = octet_transpose_items<BITS>(w[i], tc);
         if constexpr (BITS == 3) {
             // lane j holds the 24-bit group j of row i; regroup 8 x 3 bytes into 6 words
             const int g0 = (4 * t) / 3;
@@ -163,10 +209,12 @@ encode_kernel(EncodeSource src, EncodeSink sink, EncodeTables tab, int64_t n_vec
     uint32_t sgn[E];
 #pragma unroll
     for (int r = 0; r < E; r++) sgn[r] = sign_mask(tab.signs, load_coord(t, r));
+    const TransposeConsts<BITS> tc = transpose_consts<BITS>(lane);
 
     for (int64_t base = warp * 4; base < n_vec; base += n_warps * 4) {
         const int64_t v = base + sub;
         const bool valid = v < n_vec;
+        const int64_t slot = load_slot(sink, v, valid);
         const int64_t outer = valid ? v / src.n_inner : 0;
         const int inner = valid ? static_cast<int>(v - outer * src.n_inner) : 0;
         const T* row = xbase + outer * src.outer_stride + inner * src.inner_stride;
@@ -219,7 +267,7 @@ encode_kernel(EncodeSource src, EncodeSink sink, EncodeTables tab, int64_t n_vec
             }
         }
 
-        emit_vector<D, BITS>(w, norm, valid, v, sink, sink_layer, lane);
+        emit_vector<D, BITS>(w, norm, valid, v, slot, sink, sink_layer, lane, tc);
     }
 }
 

@@ -116,6 +116,21 @@ __device__ __forceinline__ void widen8<__half>(const Raw8<__half>& r, float (&o)
     }
 }
 
+template <typename T>
+__device__ __forceinline__ void zero_raw8(Raw8<T>& r) { r.v = make_uint4(0u, 0u, 0u, 0u); }
+template <>
+__device__ __forceinline__ void zero_raw8<float>(Raw8<float>& r) {
+    r.a = make_float4(0.f, 0.f, 0.f, 0.f);
+    r.b = r.a;
+}
+// 16-bit inputs: flip the signs on the packed pairs (mask bits 15 / 31), then widen.
+template <typename T>
+__device__ __forceinline__ void widen8_signed(const Raw8<T>& r, const uint32_t* sg, float (&o)[8]) {
+    Raw8<T> f;
+    f.v = make_uint4(r.v.x ^ sg[0], r.v.y ^ sg[1], r.v.z ^ sg[2], r.v.w ^ sg[3]);
+    widen8<T>(f, o);
+}
+
 // In-lane butterfly stage on register-index bit B of packed pairs.
 template <int E, int B>
 __device__ __forceinline__ void stage2(u64 (&p)[E]) {
@@ -129,27 +144,36 @@ __device__ __forceinline__ void stage2(u64 (&p)[E]) {
     }
 }
 
-// Physical float index of logical coordinate (run m, element c) in a transpose slot:
-// the two float4 halves of a run are swapped for runs 4..7 (mod 8) so that the eight
-// 16-byte stores of an octet cover all 32 banks.
-__device__ __forceinline__ constexpr int slot_index(int m, int c) {
-    return 8 * m + (c ^ (4 * ((m >> 2) & 1)));
+// Transpose slot of one pair of vectors (A, B): [run m = coordinate / 8][element c][A, B],
+// runs 20 floats apart, so that the 16-byte stores of an octet (lanes = consecutive runs) and
+// the 8-byte loads of a half warp (lanes = consecutive elements, second octet 16 banks on)
+// cover all 32 banks without conflicts.
+constexpr int kRunStride = 20;
+__host__ __device__ constexpr int encode2_slot_floats(int D) {
+    const int s = (D / 8) * kRunStride;
+    return s % 32 == 16 ? s : s + 16;
+}
+__host__ __device__ constexpr int encode2_smem_bytes(int D, int warps) {
+    return kQuantCells * 128 + warps * 4 * encode2_slot_floats(D) * 4;
 }
 
+__host__ __device__ constexpr int encode2_threads(int D) { return D >= 256 ? 512 : 256; }
+
 template <int D, int BITS, typename T>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(encode2_threads(D), 512 / encode2_threads(D))
 encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64_t n_vec) {
     constexpr int E = D / kOctet;
     constexpr int NCH = E / 8;
-    constexpr int SLOT = D + 8;  // floats per transpose slot (+8: the 4 octets hit distinct banks)
+    constexpr int SLOT = encode2_slot_floats(D);
     constexpr int NW = BITS == 2 ? (E + 15) / 16 : E / 8;  // packed words per lane
     constexpr int IPW = BITS == 2 ? 16 : 8;                 // items per word
     constexpr int CPF = 24 / BITS;                          // codes per fp32 accumulator
     constexpr int FPW = (IPW + CPF - 1) / CPF;              // accumulators per word
+    constexpr bool NARROW = sizeof(T) == 2;                 // bf16 / fp16 input
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float2* lut = reinterpret_cast<float2*>(smem_raw);                 // [257][16]
-    float* tbuf = reinterpret_cast<float*>(smem_raw + kQuantCells * 128);  // [warps][8][SLOT]
+    float* tbuf = reinterpret_cast<float*>(smem_raw + kQuantCells * 128);  // [warps][4][SLOT]
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, wip = tid >> 5;
@@ -159,35 +183,54 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
     __syncthreads();
     const uint32_t lut_lane =
         static_cast<uint32_t>(__cvta_generic_to_shared(lut)) + (lane & 15) * 8;
-    float* slotA = tbuf + (wip * 8 + sub) * SLOT;
-    float* slotB = slotA + 4 * SLOT;
+    float* slot = tbuf + (wip * 4 + sub) * SLOT;
 
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + tid) >> 5;
     const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
     const T* xbase = static_cast<const T*>(src.base) + blockIdx.y * src.layer_stride;
     const int64_t sink_layer = blockIdx.y * sink.layer_stride;
 
-    uint32_t sgn[E];
+    // sign masks in the load layout: per element for fp32 input; for 16-bit input one mask per
+    // packed pair of elements (bits 15 and 31), applied before the values are widened
+    constexpr int NSGN = NARROW ? E / 2 : E;
+    uint32_t sgn[NSGN];
 #pragma unroll
-    for (int r = 0; r < E; r++) sgn[r] = sign_mask(tab.signs, load_coord(t, r));
+    for (int r = 0; r < NSGN; r++) {
+        if constexpr (NARROW)
+            sgn[r] = (sign_mask(tab.signs, load_coord(t, 2 * r)) >> 16) |
+                     sign_mask(tab.signs, load_coord(t, 2 * r + 1));
+        else
+            sgn[r] = sign_mask(tab.signs, load_coord(t, r));
+    }
     const u64 scale2 = pk2(tab.rsqrt_d, tab.rsqrt_d);
     const u64 cs2 = pk2(kCellScale, kCellScale), cm2 = pk2(kCellMagic, kCellMagic);
+    const TransposeConsts<BITS> tc = transpose_consts<BITS>(lane);
 
-    // the two vectors of this lane for the group starting at `base`: issue their loads
+    // the two vectors of this lane for the group starting at `base`: issue their loads (zeros
+    // stand in for vectors past the end) and fetch the slots their codes go to
     Raw8<T> rawA[NCH], rawB[NCH];
+    int64_t slotA = -1, slotB = -1;
     auto issue_loads = [&](int64_t base) {
         const int64_t vA = base + sub, vB = base + 4 + sub;
+        slotA = load_slot(sink, vA, vA < n_vec);
+        slotB = load_slot(sink, vB, vB < n_vec);
         if (vA < n_vec) {
             const int64_t o = vA / src.n_inner;
             const T* row = xbase + o * src.outer_stride + (vA - o * src.n_inner) * src.inner_stride;
 #pragma unroll
             for (int i = 0; i < NCH; i++) load_raw8<T>(row + 8 * (t + 8 * i), rawA[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < NCH; i++) zero_raw8<T>(rawA[i]);
         }
         if (vB < n_vec) {
             const int64_t o = vB / src.n_inner;
             const T* row = xbase + o * src.outer_stride + (vB - o * src.n_inner) * src.inner_stride;
 #pragma unroll
             for (int i = 0; i < NCH; i++) load_raw8<T>(row + 8 * (t + 8 * i), rawB[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < NCH; i++) zero_raw8<T>(rawB[i]);
         }
     };
     if (warp * 8 < n_vec) issue_loads(warp * 8);
@@ -195,21 +238,28 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
     for (int64_t base = warp * 8; base < n_vec; base += n_warps * 8) {
         const int64_t vA = base + sub, vB = base + 4 + sub;
         const bool okA = vA < n_vec, okB = vB < n_vec;
+        const int64_t cur_slotA = slotA, cur_slotB = slotB;
         u64 p[E];
 #pragma unroll
         for (int i = 0; i < NCH; i++) {
             float a[8], b[8];
-            widen8<T>(rawA[i], a);
-            widen8<T>(rawB[i], b);
+            if constexpr (NARROW) {
+                widen8_signed<T>(rawA[i], &sgn[4 * i], a);
+                widen8_signed<T>(rawB[i], &sgn[4 * i], b);
+            } else {
+                widen8<T>(rawA[i], a);
+                widen8<T>(rawB[i], b);
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const float fa = okA ? __uint_as_float(__float_as_uint(a[c]) ^ sgn[8 * i + c]) : 0.f;
-                const float fb = okB ? __uint_as_float(__float_as_uint(b[c]) ^ sgn[8 * i + c]) : 0.f;
-                p[8 * i + c] = pk2(fa, fb);
+                for (int c = 0; c < 8; c++) {
+                    a[c] = __uint_as_float(__float_as_uint(a[c]) ^ sgn[8 * i + c]);
+                    b[c] = __uint_as_float(__float_as_uint(b[c]) ^ sgn[8 * i + c]);
+                }
             }
+#pragma unroll
+            for (int c = 0; c < 8; c++) p[8 * i + c] = pk2(a[c], b[c]);
         }
         // next group's loads fly while this one is processed (16-bit inputs: 4 registers per run)
-        if constexpr (sizeof(T) == 2) {
+        if constexpr (NARROW) {
             if (base + n_warps * 8 < n_vec) issue_loads(base + n_warps * 8);
         }
         // stages h = 1, 2, 4 on the coordinates inside a run
@@ -217,28 +267,24 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
         stage2<E, 1>(p);
         stage2<E, 2>(p);
 
-        // lane <-> register transposition through shared memory:
+        // lane <-> register transposition through shared memory, both vectors at once:
         // (lane t, register c + 8i) = coordinate 8(t + 8i) + c   ->   (lane l, register k) = l + 8k
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < NCH; i++) {
-            const int m = t + 8 * i;
+            float* run = slot + (t + 8 * i) * kRunStride;
 #pragma unroll
-            for (int j = 0; j < 2; j++) {
-                float a[4], b[4];
-#pragma unroll
-                for (int c = 0; c < 4; c++) upk2(p[8 * i + 4 * j + c], a[c], b[c]);
-                const int off = slot_index(m, 4 * j);
-                *reinterpret_cast<float4*>(slotA + off) = make_float4(a[0], a[1], a[2], a[3]);
-                *reinterpret_cast<float4*>(slotB + off) = make_float4(b[0], b[1], b[2], b[3]);
+            for (int c = 0; c < 8; c += 2) {
+                ulonglong2 v2;
+                v2.x = p[8 * i + c];
+                v2.y = p[8 * i + c + 1];
+                *reinterpret_cast<ulonglong2*>(run + 2 * c) = v2;
             }
         }
         __syncwarp();
 #pragma unroll
-        for (int k = 0; k < E; k++) {
-            const int off = 8 * k + (t ^ (4 * ((k >> 2) & 1)));
-            p[k] = pk2(slotA[off], slotB[off]);
-        }
+        for (int k = 0; k < E; k++)
+            p[k] = *reinterpret_cast<const u64*>(slot + k * kRunStride + 2 * t);
 
         // stages h = 8, 16, ... : register bits 0.. of the new layout
         stage2<E, 0>(p);
@@ -315,9 +361,9 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
                 wB[i] |= __float2uint_rn(b1) << (BITS * CPF);
             }
         }
-        emit_vector<D, BITS>(wA, normA, okA, vA, sink, sink_layer, lane);
-        emit_vector<D, BITS>(wB, normB, okB, vB, sink, sink_layer, lane);
-        if constexpr (sizeof(T) != 2) {
+        emit_vector<D, BITS>(wA, normA, okA, vA, cur_slotA, sink, sink_layer, lane, tc);
+        emit_vector<D, BITS>(wB, normB, okB, vB, cur_slotB, sink, sink_layer, lane, tc);
+        if constexpr (!NARROW) {
             if (base + n_warps * 8 < n_vec) issue_loads(base + n_warps * 8);
         }
     }

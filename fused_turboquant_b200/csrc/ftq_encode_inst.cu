@@ -13,13 +13,16 @@ namespace ftq {
 template <int BITS, typename T>
 static cudaError_t run2(const EncodeSource& src, const EncodeSink& sink, const Encode2Tables& tab,
                         int64_t n_vec, int n_layers, cudaStream_t stream) {
-    constexpr int threads = 256;                       // 8 warps, 64 vectors per CTA pass
-    constexpr int smem = kQuantCells * 128 + 8 * 8 * (FTQ_D + 8) * 4;
+    // 16 warps per SM: two CTAs of 8 warps, or one of 16 where two transpose areas would not
+    // fit next to two copies of the quantiser table (head_dim 256); a warp pass = 8 vectors
+    constexpr int threads = encode2_threads(FTQ_D);
+    constexpr int ctas_per_sm = 512 / threads;
+    constexpr int smem = encode2_smem_bytes(FTQ_D, threads / 32);
     auto kern = encode2_kernel<FTQ_D, BITS, T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    const int64_t want = (n_vec + 63) / 64;
-    const int64_t cap = static_cast<int64_t>(sm_count()) * 2;   // persistent: 2 CTAs per SM
+    const int64_t want = (n_vec + threads / 4 - 1) / (threads / 4);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * ctas_per_sm;   // persistent grid
     const unsigned gx = static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
     kern<<<dim3(gx, n_layers), threads, smem, stream>>>(src, sink, tab, n_vec);
     return cudaGetLastError();
