@@ -104,9 +104,16 @@ bool make_encode2_tables(const ftq::EncodeTables& tab, int bits, ftq::Encode2Tab
     return true;
 }
 
-cudaError_t dispatch_encode(int d, int bits, int dtype, const ftq::EncodeSource& src,
-                            const ftq::EncodeSink& sink, const ftq::EncodeTables& tab,
+cudaError_t dispatch_encode(int d, int bits, int dtype, const ftq::EncodeSource& src_in,
+                            const ftq::EncodeSink& sink_in, const ftq::EncodeTables& tab,
                             int64_t n_vec, int n_layers, cudaStream_t st) {
+    // vector indices are split into (token, head) with 31-bit arithmetic in the kernels (the
+    // public entry points reject larger counts, which no resident input can reach)
+    if (n_vec >= (1ll << 31) || src_in.n_inner <= 0 || sink_in.Hkv <= 0) return cudaErrorInvalidValue;
+    ftq::EncodeSource src = src_in;
+    ftq::EncodeSink sink = sink_in;
+    src.div_inner = ftq::make_fastdiv(static_cast<uint32_t>(src.n_inner));
+    sink.div_hkv = ftq::make_fastdiv(static_cast<uint32_t>(sink.Hkv));
     // A handful of vectors (a decode step) is launch-bound either way: the simple kernel
     // skips the table set-up.  Bulk encodes take the throughput kernel when the codebook allows.
     ftq::Encode2Tables tab2;
@@ -374,6 +381,7 @@ int ftq_encode(const void* x, int dtype, int64_t n_vec, int head_dim, int64_t ro
     if (!bits_ok(bits)) return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got %d", bits);
     if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
     if (n_vec < 0) return fail(FTQ_ERR_INVALID, "n_vec < 0");
+    if (n_vec >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "n_vec must be below 2^31 per call");
     if (n_vec == 0) return FTQ_OK;
     if (!x || !packed || !norms_f16) return fail(FTQ_ERR_INVALID, "NULL tensor pointer");
     if (row_stride < head_dim) return fail(FTQ_ERR_INVALID, "row_stride < head_dim");
@@ -606,6 +614,8 @@ int ftq_paged_store(const void* key, const void* value, int dtype, int64_t n_tok
     if (!bits_ok(bits_k) || !bits_ok(bits_v))
         return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got K=%d V=%d", bits_k, bits_v);
     if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
+    if (n_tokens * Hkv >= (1ll << 31))
+        return fail(FTQ_ERR_INVALID, "n_tokens * Hkv must be below 2^31 per call");
     if (n_tokens < 0 || Hkv <= 0 || n_layers <= 0 || num_blocks < 0)
         return fail(FTQ_ERR_INVALID, "bad shape");
     if (n_tokens == 0) return FTQ_OK;
@@ -716,6 +726,8 @@ int ftq_v0_store(const void* key, const void* value, int dtype, int64_t n_tokens
     if (!bits_ok(bits_k) || !bits_ok(bits_v))
         return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got K=%d V=%d", bits_k, bits_v);
     if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
+    if (n_tokens * Hkv >= (1ll << 31))
+        return fail(FTQ_ERR_INVALID, "n_tokens * Hkv must be below 2^31 per call");
     if (n_tokens < 0 || Hkv <= 0 || block_size <= 0 || num_blocks < 0)
         return fail(FTQ_ERR_INVALID, "bad shape");
     const int pdk = ftq::packed_dim(head_dim, bits_k), pdv = ftq::packed_dim(head_dim, bits_v);

@@ -109,6 +109,25 @@ __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
     return __bfloat162float(v);
 }
 
+// ------------------------------------------------------------- division by a launch constant
+// floor(n / d) for 0 <= n < 2^31 as one wide multiply and a shift: mul = ceil(2^sh / d) with
+// sh = 31 + ceil(log2 d) fits in 32 bits, and n * (mul * d - 2^sh) < 2^sh keeps the floor exact.
+struct FastDiv {
+    uint32_t d, mul, sh;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    f.d = d;
+    uint32_t l = 0;
+    while ((1ull << l) < d) l++;
+    f.sh = 31 + l;
+    f.mul = static_cast<uint32_t>(((1ull << f.sh) + d - 1) / d);
+    return f;
+}
+__host__ __device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
+    return static_cast<uint32_t>((static_cast<uint64_t>(n) * f.mul) >> f.sh);
+}
+
 // ------------------------------------------------------------- butterfly
 
 // Sign of coordinate `coord` as a 0 / 0x80000000 mask.

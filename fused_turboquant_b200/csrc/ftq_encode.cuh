@@ -33,6 +33,7 @@ struct EncodeSource {
     int64_t outer_stride;  // elements
     int64_t inner_stride;  // elements
     int64_t layer_stride;  // elements, blockIdx.y advances by this
+    FastDiv div_inner;     // division by n_inner (filled in by the dispatcher)
 };
 
 enum : int { kSinkFlat = 0, kSinkPaged = 1, kSinkV0 = 2 };
@@ -46,6 +47,7 @@ struct EncodeSink {
     // paged pool / v0 layout: token = v / Hkv, head = v % Hkv, slot = slot_mapping[token]
     const int64_t* slot_mapping;
     int Hkv;
+    FastDiv div_hkv;        // division by Hkv (filled in by the dispatcher)
     int64_t page_bytes;     // paged: bytes per (block, head) page
     int codes_off;          // paged: offset of this tensor's codes inside the page
     int norms_off;          // paged: offset of this tensor's fp16 norms inside the page
@@ -115,7 +117,7 @@ __device__ __forceinline__ uint32_t octet_transpose_items(uint32_t w, const Tran
 // arithmetic so that the store at the end does not wait for it.
 __device__ __forceinline__ int64_t load_slot(const EncodeSink& sink, int64_t v, bool valid) {
     if (sink.mode == kSinkFlat || !valid) return -1;
-    return sink.slot_mapping[v / sink.Hkv];
+    return sink.slot_mapping[fast_div(static_cast<uint32_t>(v), sink.div_hkv)];
 }
 
 // Store one encoded vector: `w` holds this lane's codes (coordinates l + 8k) packed as
@@ -136,8 +138,8 @@ __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm,
     if (sink.mode == kSinkFlat) {
         dst = sink.codes + v * PD;
     } else if (valid) {
-        const int64_t token = v / sink.Hkv;
-        const int head = static_cast<int>(v - token * sink.Hkv);
+        const uint32_t token = fast_div(static_cast<uint32_t>(v), sink.div_hkv);
+        const int head = static_cast<int>(static_cast<uint32_t>(v) - token * sink.Hkv);
         if (slot < 0) {
             store = false;
         } else if (sink.mode == kSinkPaged) {
@@ -215,7 +217,7 @@ encode_kernel(EncodeSource src, EncodeSink sink, EncodeTables tab, int64_t n_vec
         const int64_t v = base + sub;
         const bool valid = v < n_vec;
         const int64_t slot = load_slot(sink, v, valid);
-        const int64_t outer = valid ? v / src.n_inner : 0;
+        const int64_t outer = valid ? fast_div(static_cast<uint32_t>(v), src.div_inner) : 0;
         const int inner = valid ? static_cast<int>(v - outer * src.n_inner) : 0;
         const T* row = xbase + outer * src.outer_stride + inner * src.inner_stride;
 

@@ -215,7 +215,7 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
         slotA = load_slot(sink, vA, vA < n_vec);
         slotB = load_slot(sink, vB, vB < n_vec);
         if (vA < n_vec) {
-            const int64_t o = vA / src.n_inner;
+            const int64_t o = fast_div(static_cast<uint32_t>(vA), src.div_inner);
             const T* row = xbase + o * src.outer_stride + (vA - o * src.n_inner) * src.inner_stride;
 #pragma unroll
             for (int i = 0; i < NCH; i++) load_raw8<T>(row + 8 * (t + 8 * i), rawA[i]);
@@ -224,7 +224,7 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
             for (int i = 0; i < NCH; i++) zero_raw8<T>(rawA[i]);
         }
         if (vB < n_vec) {
-            const int64_t o = vB / src.n_inner;
+            const int64_t o = fast_div(static_cast<uint32_t>(vB), src.div_inner);
             const T* row = xbase + o * src.outer_stride + (vB - o * src.n_inner) * src.inner_stride;
 #pragma unroll
             for (int i = 0; i < NCH; i++) load_raw8<T>(row + 8 * (t + 8 * i), rawB[i]);
