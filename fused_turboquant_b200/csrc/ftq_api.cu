@@ -614,8 +614,8 @@ int ftq_paged_store(const void* key, const void* value, int dtype, int64_t n_tok
     if (!bits_ok(bits_k) || !bits_ok(bits_v))
         return fail(FTQ_ERR_INVALID, "bits must be 2, 3, or 4, got K=%d V=%d", bits_k, bits_v);
     if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
-    if (n_tokens * Hkv >= (1ll << 31))
-        return fail(FTQ_ERR_INVALID, "n_tokens * Hkv must be below 2^31 per call");
+    if (n_tokens * Hkv >= (1ll << 31) || num_blocks * Hkv >= (1ll << 31))
+        return fail(FTQ_ERR_INVALID, "n_tokens * Hkv and num_blocks * Hkv must be below 2^31");
     if (n_tokens < 0 || Hkv <= 0 || n_layers <= 0 || num_blocks < 0)
         return fail(FTQ_ERR_INVALID, "bad shape");
     if (n_tokens == 0) return FTQ_OK;

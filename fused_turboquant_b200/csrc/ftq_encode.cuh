@@ -143,9 +143,12 @@ __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm,
         if (slot < 0) {
             store = false;
         } else if (sink.mode == kSinkPaged) {
-            const int64_t blk = slot / kPageTokens;
-            const int off = static_cast<int>(slot - blk * kPageTokens);
-            uint8_t* page = sink.codes + sink_layer + (blk * sink.Hkv + head) * sink.page_bytes;
+            // slot >= 0 here; pages per layer and bytes per page both fit 32 bits
+            const uint32_t blk = static_cast<uint32_t>(static_cast<uint64_t>(slot) / kPageTokens);
+            const int off = static_cast<int>(static_cast<uint64_t>(slot) % kPageTokens);
+            uint8_t* page = sink.codes + sink_layer +
+                            static_cast<uint64_t>(blk * sink.Hkv + head) *
+                                static_cast<uint32_t>(sink.page_bytes);
             dst = page + sink.codes_off + off * PD;
             if (sink.swap_halves && (off & 2)) rot = PD / 8;
             if (t == 0)

@@ -154,7 +154,7 @@ __host__ __device__ constexpr int encode2_slot_floats(int D) {
     return s % 32 == 16 ? s : s + 16;
 }
 __host__ __device__ constexpr int encode2_smem_bytes(int D, int warps) {
-    return kQuantCells * 128 + warps * 4 * encode2_slot_floats(D) * 4;
+    return warps * 4 * encode2_slot_floats(D) * 4;  // dynamic part (the table is static)
 }
 
 __host__ __device__ constexpr int encode2_threads(int D) { return D >= 256 ? 512 : 256; }
@@ -171,9 +171,11 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
     constexpr int FPW = (IPW + CPF - 1) / CPF;              // accumulators per word
     constexpr bool NARROW = sizeof(T) == 2;                 // bf16 / fp16 input
 
+    // the quantiser table is a static array: its shared-memory offset is then an immediate of
+    // the load and the per-element address is one bit-select (cell row | lane column)
+    __shared__ __align__(128) float2 lut[kQuantCells * 16];            // [257][16]
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    float2* lut = reinterpret_cast<float2*>(smem_raw);                 // [257][16]
-    float* tbuf = reinterpret_cast<float*>(smem_raw + kQuantCells * 128);  // [warps][4][SLOT]
+    float* tbuf = reinterpret_cast<float*>(smem_raw);                  // [warps][4][SLOT]
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, wip = tid >> 5;
@@ -181,8 +183,7 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
     for (int i = tid; i < kQuantCells * 16; i += blockDim.x)
         lut[i] = make_float2(tab.cells[i >> 4].neg_thr_scaled, tab.cells[i >> 4].base);
     __syncthreads();
-    const uint32_t lut_lane =
-        static_cast<uint32_t>(__cvta_generic_to_shared(lut)) + (lane & 15) * 8;
+    const uint32_t lut_col = (lane & 15) * 8;
     float* slot = tbuf + (wip * 4 + sub) * SLOT;
 
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + tid) >> 5;
@@ -332,10 +333,10 @@ encode2_kernel(EncodeSource src, EncodeSink sink, const Encode2Tables tab, int64
             upk2(q, qA, qB);
             float2 eA, eB;
             {
-                const uint32_t aA = lut_lane + (__float_as_uint(cA) & 0xFF80u);
-                const uint32_t aB = lut_lane + (__float_as_uint(cB) & 0xFF80u);
-                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(eA.x), "=f"(eA.y) : "r"(aA));
-                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(eB.x), "=f"(eB.y) : "r"(aB));
+                const uint32_t oA = (__float_as_uint(cA) & 0xFF80u) | lut_col;
+                const uint32_t oB = (__float_as_uint(cB) & 0xFF80u) | lut_col;
+                eA = *reinterpret_cast<const float2*>(reinterpret_cast<const uint8_t*>(lut) + oA);
+                eB = *reinterpret_cast<const float2*>(reinterpret_cast<const uint8_t*>(lut) + oB);
             }
             const float stA = fma_sat(qA, kStepScale, eA.x);
             const float stB = fma_sat(qB, kStepScale, eB.x);
