@@ -22,7 +22,10 @@
  * Parity status: PINNED.  The encode/decode/pack functions are checked
  * bit-for-bit against outputs of the reference itself (the .npz files
  * under tests/golden/, produced by tests/golden/make_golden.py which imports
- * the reference).
+ * the reference), and against outputs of the reference's own Triton kernels
+ * executed in interpreter mode (tests/golden/make_golden_kernels.py ->
+ * kernels_interp.npz): fused encode, fused dense decode, RHT, QK scores, flash
+ * decode.
  *
  * Build with:  gcc -O2 -ffp-contract=off -fno-fast-math -fopenmp -shared -fPIC
  * (-ffp-contract=off matters: a fused multiply-add changes rounding and the
