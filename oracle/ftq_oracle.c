@@ -404,3 +404,213 @@ void ftq_oracle_v0_gather(const uint8_t *kv_cache, int64_t num_blocks, int block
             }
         }
 }
+
+/* ============================================================================
+ * vLLM-v1 "TURBOQUANT" slot format: in-kernel-rotation store and split-KV decode.
+ *
+ * Restates the reference's Triton kernels
+ *   _fused_store_rht + _bucketize_pack_norm_v_store
+ *       src/fused_turboquant/vllm_plugin/triton_inkernel_store.py:365-440, 39-330
+ *   _tq_decode_stage1_offset
+ *       src/fused_turboquant/vllm_plugin/triton_decode_offset.py:42-444
+ * and the stock stage-2 merge they are followed by (call site
+ * src/fused_turboquant/vllm_plugin/v1_backend.py:1068-1085).
+ *
+ * Slot of one (token, KV head):  [key codes | key norm f16 | value codes | scale f16 | zero f16]
+ * at kv_cache + block*stride_block + pos*stride_pos + head*stride_head.
+ *
+ * Parity status: PINNED against tests/golden/tq_v1.npz, which holds what those kernels
+ * wrote when executed in Triton's interpreter mode (tests/golden/make_golden_tq_v1.py).
+ * One degree of freedom is not fixed by the reference: the order in which `tl.sum`
+ * adds the squares of the key.  This file (and the CUDA kernel) add them in "octet order":
+ * 8 running sums over the coordinates 8(t+8i)+c (t = sum index, c then i ascending),
+ * combined pairwise (t^1, t^2, t^4).  A different order moves the norm by an ulp at most,
+ * which can flip a code only where the rotated value sits within ~1e-7 of a midpoint.
+ * ==========================================================================*/
+
+static float tq_key_norm_sq(const float *k, int d) {
+    float lane[8];
+    for (int t = 0; t < 8; t++) {
+        float s = 0.0f;
+        for (int i = 0; i < d / 64; i++)
+            for (int c = 0; c < 8; c++) {
+                float v = k[8 * (t + 8 * i) + c];
+                float sq = v * v;
+                s = s + sq;
+            }
+        lane[t] = s;
+    }
+    for (int m = 1; m < 8; m <<= 1) {
+        float nxt[8];
+        for (int t = 0; t < 8; t++) nxt[t] = lane[t] + lane[t ^ m];
+        memcpy(lane, nxt, sizeof(lane));
+    }
+    return lane[0];
+}
+
+static void tq_pack_bits(const int *idx, uint8_t *out, int d, int bits) {
+    if (bits == 8) {
+        for (int i = 0; i < d; i++) out[i] = (uint8_t)idx[i];
+        return;
+    }
+    uint8_t tmp[FTQ_MAX_D];
+    for (int i = 0; i < d; i++) tmp[i] = (uint8_t)idx[i];
+    ftq_oracle_pack(tmp, out, d, bits);
+}
+
+static void put_f16(uint8_t *dst, float v) {
+    uint16_t h = ftq_oracle_f32_to_f16(v);
+    dst[0] = (uint8_t)(h & 0xff);
+    dst[1] = (uint8_t)(h >> 8);
+}
+static float get_f16(const uint8_t *src) {
+    return ftq_oracle_f16_to_f32((uint16_t)(src[0] | (src[1] << 8)));
+}
+
+/* key/value: [n_tokens, Hkv, d] fp32 contiguous.  y_out (nullable): the rotated unit keys. */
+void ftq_oracle_tq_store(const float *key, const float *value, int64_t n_tokens, int Hkv, int d,
+                         int key_bits, int value_bits, const float *midpoints, uint8_t *kv_cache,
+                         int64_t stride_block, int64_t stride_pos, int64_t stride_head,
+                         int block_size, const int64_t *slot_mapping, float *y_out) {
+    const int n_cent = 1 << key_bits;
+    const int mse_bytes = d * key_bits / 8;
+    const int kps = mse_bytes + 2;
+    const int vdb = value_bits == 8 ? d : d * value_bits / 8;
+    const int vmax = (1 << value_bits) - 1;
+    const float rs = 1.0f / sqrtf((float)d);
+    for (int64_t tok = 0; tok < n_tokens; tok++) {
+        const int64_t slot = slot_mapping[tok];
+        if (slot < 0) continue;
+        for (int h = 0; h < Hkv; h++) {
+            const float *k = key + (tok * Hkv + h) * d;
+            const float *v = value + (tok * Hkv + h) * d;
+            uint8_t *dst = kv_cache + (slot / block_size) * stride_block +
+                           (slot % block_size) * stride_pos + (int64_t)h * stride_head;
+            /* keys: norm of the raw vector, normalise, Hadamard (no signs), midpoint search */
+            float norm = sqrtf(tq_key_norm_sq(k, d) + 1e-16f);
+            float y[FTQ_MAX_D];
+            float den = norm + 1e-8f;
+            for (int i = 0; i < d; i++) y[i] = k[i] / den;
+            for (int hh = 1; hh < d; hh <<= 1)
+                for (int base = 0; base < d; base += 2 * hh)
+                    for (int j = 0; j < hh; j++) {
+                        float a = y[base + j], b = y[base + hh + j];
+                        y[base + j] = a + b;
+                        y[base + hh + j] = a - b;
+                    }
+            int idx[FTQ_MAX_D];
+            for (int i = 0; i < d; i++) {
+                y[i] = y[i] * rs;
+                int c = 0;
+                for (int j = 0; j < n_cent - 1; j++) c += (y[i] >= midpoints[j]) ? 1 : 0;
+                idx[i] = c;
+            }
+            if (y_out) memcpy(y_out + (tok * Hkv + h) * d, y, sizeof(float) * d);
+            tq_pack_bits(idx, dst, d, key_bits);
+            put_f16(dst + mse_bytes, norm);
+            /* values: per-vector uniform quantisation */
+            float mn = v[0], mx = v[0];
+            for (int i = 1; i < d; i++) {
+                mn = v[i] < mn ? v[i] : mn;
+                mx = v[i] > mx ? v[i] : mx;
+            }
+            float scale = (mx - mn) / (float)vmax;
+            if (!(scale > 1e-8f)) scale = 1e-8f;
+            for (int i = 0; i < d; i++) {
+                float t = (v[i] - mn) / scale;
+                t = t + 0.5f;
+                int q = (int)t;
+                idx[i] = q < 0 ? 0 : (q > vmax ? vmax : q);
+            }
+            tq_pack_bits(idx, dst + kps, d, value_bits);
+            put_f16(dst + kps + vdb, scale);
+            put_f16(dst + kps + vdb + 2, mn);
+        }
+    }
+}
+
+static int tq_code(const uint8_t *p, int i, int bits) {
+    if (bits == 8) return p[i];
+    int bo = i * bits;
+    uint32_t w = (uint32_t)p[bo >> 3] | ((uint32_t)p[(bo >> 3) + 1] << 8);
+    return (int)((w >> (bo & 7)) & ((1u << bits) - 1u));
+}
+
+/* q: [B, Hq, d] fp32 in the ORIGINAL space (rotated here with the plain Hadamard transform, as
+ * rotation/matrix.py:47-48 does with a matrix product).  mid_o: [B, Hq, splits, d+1], out: [B, Hq, d],
+ * lse: [B, Hq] (each nullable).  rotate_out != 0 applies the Hadamard transform to the merged output
+ * (values stored in the rotated space, v1_backend.py:1088-1092). */
+void ftq_oracle_tq_decode(const float *q, int B, int Hq, int Hkv, int d, const uint8_t *kv_cache,
+                          int64_t stride_block, int64_t stride_pos, int64_t stride_head,
+                          int block_size, const int32_t *block_table, int max_blocks,
+                          const int32_t *seq_lens, const int32_t *kv_start, int key_bits,
+                          int value_bits, int norm_correction, int rotate_out,
+                          const float *centroids, float scale, int splits, float *mid_o,
+                          float *out, float *lse) {
+    const int group = Hq / Hkv;
+    const int mse_bytes = d * key_bits / 8;
+    const int kps = mse_bytes + 2;
+    const int vdb = value_bits == 8 ? d : d * value_bits / 8;
+#pragma omp parallel for collapse(2) schedule(dynamic)
+    for (int b = 0; b < B; b++)
+        for (int hq = 0; hq < Hq; hq++) {
+            const int hk = hq / group;
+            float qr[FTQ_MAX_D];
+            memcpy(qr, q + ((int64_t)b * Hq + hq) * d, sizeof(float) * d);
+            ftq_oracle_fwht(qr, d);
+            const int seq_len = seq_lens[b];
+            const int start = kv_start ? kv_start[b] : 0;
+            const int eff = seq_len - start;
+            const int split_len = (eff + splits - 1) / splits;
+            double M = -INFINITY, L = 0.0, O[FTQ_MAX_D];
+            for (int i = 0; i < d; i++) O[i] = 0.0;
+            for (int s = 0; s < splits; s++) {
+                const int s0 = start + split_len * s;
+                const int s1 = s0 + split_len < seq_len ? s0 + split_len : seq_len;
+                double m = -INFINITY, l = 0.0, acc[FTQ_MAX_D];
+                for (int i = 0; i < d; i++) acc[i] = 0.0;
+                for (int pos = s0; pos < s1; pos++) {
+                    const int64_t blk = block_table[(int64_t)b * max_blocks + pos / block_size];
+                    const uint8_t *slot = kv_cache + blk * stride_block +
+                                          (int64_t)(pos % block_size) * stride_pos +
+                                          (int64_t)hk * stride_head;
+                    double dot = 0.0, cn = 0.0;
+                    for (int i = 0; i < d; i++) {
+                        const double c = centroids[tq_code(slot, i, key_bits)];
+                        dot += (double)qr[i] * c;
+                        cn += c * c;
+                    }
+                    if (norm_correction) dot *= 1.0 / sqrt(cn + 1e-16);
+                    const double sc = (double)get_f16(slot + mse_bytes) * dot * (double)scale;
+                    const double vs = get_f16(slot + kps + vdb), vz = get_f16(slot + kps + vdb + 2);
+                    const double mn = sc > m ? sc : m;
+                    const double corr = exp(m - mn), p = exp(sc - mn);
+                    for (int i = 0; i < d; i++)
+                        acc[i] = acc[i] * corr + p * (tq_code(slot + kps, i, value_bits) * vs + vz);
+                    l = l * corr + p;
+                    m = mn;
+                }
+                const double safe_l = l > 0.0 ? l : 1.0;
+                const double lse_s = s0 < s1 ? m + log(safe_l) : -INFINITY;
+                if (mid_o) {
+                    float *mo = mid_o + (((int64_t)b * Hq + hq) * splits + s) * (d + 1);
+                    for (int i = 0; i < d; i++) mo[i] = (float)(acc[i] / safe_l);
+                    mo[d] = (float)lse_s;
+                }
+                if (s0 < s1) { /* merge as the stage-2 kernel does, on (acc / l, lse) */
+                    const double Mn = lse_s > M ? lse_s : M;
+                    const double old = exp(M - Mn), w = exp(lse_s - Mn);
+                    for (int i = 0; i < d; i++) O[i] = O[i] * old + w * (acc[i] / safe_l);
+                    L = L * old + w;
+                    M = Mn;
+                }
+            }
+            if (out) {
+                float res[FTQ_MAX_D];
+                for (int i = 0; i < d; i++) res[i] = (float)(O[i] / L);
+                if (rotate_out) ftq_oracle_fwht(res, d);
+                memcpy(out + ((int64_t)b * Hq + hq) * d, res, sizeof(float) * d);
+            }
+            if (lse) lse[(int64_t)b * Hq + hq] = (float)(M + log(L));
+        }
+}

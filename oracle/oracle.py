@@ -202,3 +202,54 @@ def v0_gather(kv_cache: np.ndarray, kv_type: int, pd: int, block_tables, seq_len
                                ctypes.c_int(pd), _p(bt), ctypes.c_int(bt.shape[1]), _p(sl),
                                ctypes.c_int(B), ctypes.c_int(max_seq_len), _p(out_p), _p(out_n))
     return out_p, out_n
+
+
+# ---------------------------------------------------------------- vLLM-v1 slot format
+
+def tq_slot_bytes(d: int, key_bits: int, value_bits: int) -> int:
+    """key codes + fp16 norm + value codes + fp16 scale + fp16 zero, rounded up to even."""
+    s = d * key_bits // 8 + 2 + (d if value_bits == 8 else d * value_bits // 8) + 4
+    return s + s % 2
+
+
+def tq_store(key, value, kv_cache: np.ndarray, slot_mapping, midpoints, key_bits: int,
+             value_bits: int, return_rotated: bool = False):
+    """The reference's in-kernel-rotation store into kv_cache [nb, block_size, Hkv, slot] (in place)."""
+    key, value = _c(key, np.float32), _c(value, np.float32)
+    n, hkv, d = key.shape
+    assert kv_cache.dtype == np.uint8 and kv_cache.flags.c_contiguous and kv_cache.ndim == 4
+    sm = _c(slot_mapping, np.int64)
+    mids = _c(midpoints, np.float32)
+    y = np.empty_like(key) if return_rotated else None
+    st = kv_cache.strides
+    lib().ftq_oracle_tq_store(_p(key), _p(value), ctypes.c_int64(n), ctypes.c_int(hkv),
+                              ctypes.c_int(d), ctypes.c_int(key_bits), ctypes.c_int(value_bits),
+                              _p(mids), _p(kv_cache), ctypes.c_int64(st[0]), ctypes.c_int64(st[1]),
+                              ctypes.c_int64(st[2]), ctypes.c_int(kv_cache.shape[1]), _p(sm), _p(y))
+    return y
+
+
+def tq_decode(q, kv_cache: np.ndarray, block_table, seq_lens, centroids, key_bits: int,
+              value_bits: int, scale: float, splits: int, norm_correction: bool = False,
+              kv_start=None, rotate_out: bool = False):
+    """Split-KV decode over the slot format: returns (out [B,Hq,d], mid_o [B,Hq,splits,d+1], lse)."""
+    q = _c(q, np.float32)
+    B, Hq, d = q.shape
+    hkv = kv_cache.shape[2]
+    bt = _c(block_table, np.int32)
+    sl = _c(seq_lens, np.int32)
+    ks = None if kv_start is None else _c(kv_start, np.int32)
+    cent = _c(centroids, np.float32)
+    mid_o = np.empty((B, Hq, splits, d + 1), np.float32)
+    out = np.empty((B, Hq, d), np.float32)
+    lse = np.empty((B, Hq), np.float32)
+    st = kv_cache.strides
+    lib().ftq_oracle_tq_decode(_p(q), ctypes.c_int(B), ctypes.c_int(Hq), ctypes.c_int(hkv),
+                               ctypes.c_int(d), _p(kv_cache), ctypes.c_int64(st[0]),
+                               ctypes.c_int64(st[1]), ctypes.c_int64(st[2]),
+                               ctypes.c_int(kv_cache.shape[1]), _p(bt), ctypes.c_int(bt.shape[1]),
+                               _p(sl), _p(ks), ctypes.c_int(key_bits), ctypes.c_int(value_bits),
+                               ctypes.c_int(int(norm_correction)), ctypes.c_int(int(rotate_out)),
+                               _p(cent), ctypes.c_float(scale), ctypes.c_int(splits), _p(mid_o),
+                               _p(out), _p(lse))
+    return out, mid_o, lse

@@ -82,3 +82,42 @@ def gate(out, ref, rtol=2e-3, atol=1e-3):
     out = np.asarray(out, np.float64)
     ref = np.asarray(ref, np.float64)
     return int((np.abs(out - ref) > atol + rtol * np.abs(ref)).sum())
+
+
+def tq_v1_compare_cache(cache, ref, slot_mapping, y, midpoints, d, key_bits, value_bits, block_size):
+    """Compare two kv caches in the vLLM-v1 slot format ([nb, block_size, Hkv, slot] uint8).
+
+    Returns counts: value-region bytes that differ, bytes that differ outside written slots, key
+    codes that differ although the rotated value `y` ([n_tokens, Hkv, d]) is farther than 1e-6
+    from every midpoint, and the largest key-norm distance in fp16 ulps.
+    """
+    mse = d * key_bits // 8
+    kps = mse + 2
+    vdb = d if value_bits == 8 else d * value_bits // 8
+    used = kps + vdb + 4
+    hkv = cache.shape[2]
+    written = np.zeros(cache.shape[:3], bool)
+    stats = dict(value_bytes_differ=0, other_bytes_differ=0, key_codes_differ_off_midpoint=0,
+                 key_codes_differ=0, key_norm_max_ulp=0)
+    mids = np.asarray(midpoints, np.float32)
+    for tok, slot in enumerate(np.asarray(slot_mapping)):
+        if slot < 0:
+            continue
+        blk, off = int(slot) // block_size, int(slot) % block_size
+        written[blk, off, :] = True
+        for h in range(hkv):
+            a, b = cache[blk, off, h], ref[blk, off, h]
+            stats["value_bytes_differ"] += int((a[kps:used] != b[kps:used]).sum())
+            stats["other_bytes_differ"] += int((a[used:] != b[used:]).sum())
+            na = int(a[mse]) | (int(a[mse + 1]) << 8)
+            nb_ = int(b[mse]) | (int(b[mse + 1]) << 8)
+            stats["key_norm_max_ulp"] = max(stats["key_norm_max_ulp"], abs(na - nb_))
+            if (a[:mse] != b[:mse]).any():
+                bits = np.unpackbits(a[:mse], bitorder="little").reshape(d, key_bits)
+                bits_r = np.unpackbits(b[:mse], bitorder="little").reshape(d, key_bits)
+                diff = (bits != bits_r).any(axis=1)
+                stats["key_codes_differ"] += int(diff.sum())
+                near = np.abs(y[tok, h][:, None] - mids[None, :]).min(axis=1) < 1e-6
+                stats["key_codes_differ_off_midpoint"] += int((diff & ~near).sum())
+    stats["other_bytes_differ"] += int((cache[~written] != ref[~written]).sum())
+    return stats
