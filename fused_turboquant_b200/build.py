@@ -29,6 +29,7 @@ UNITS = [("ftq_api.cu", "api", [])]
 for _d in (64, 128, 256):
     UNITS.append(("ftq_encode_inst.cu", f"encode_d{_d}", [f"-DFTQ_D={_d}"]))
     UNITS.append(("ftq_attn_inst.cu", f"attn_d{_d}", [f"-DFTQ_D={_d}"]))
+    UNITS.append(("ftq_tq_v1_inst.cu", f"tq_v1_d{_d}", [f"-DFTQ_D={_d}"]))
 
 
 def _nvcc() -> str:

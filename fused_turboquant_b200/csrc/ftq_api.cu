@@ -11,6 +11,7 @@
 #include "../../include/ftq_b200.h"
 #include "ftq_dense.cuh"
 #include "ftq_launch.h"
+#include "ftq_tq_v1_launch.h"
 
 namespace {
 
@@ -844,4 +845,137 @@ extern "C" int ftq_paged_decode_attn_static(
                                  n_layers, block_table, max_blocks, seq_lens, max_seq_len, B, Hq,
                                  Hkv, head_dim, bits_k, bits_v, levels_k_host, levels_v_host,
                                  signs_host, scale, scratch, FTQ_STATIC_SCRATCH_BYTES, stream);
+}
+
+// ------------------------------------------------------------------ vLLM-v1 slot format
+
+namespace {
+bool tq_bits_ok(int kb, int vb) { return kb >= 2 && kb <= 4 && (vb == 2 || vb == 3 || vb == 4 || vb == 8); }
+bool even(int64_t v) { return (v & 1) == 0; }
+}  // namespace
+
+extern "C" int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits) {
+    if (!dim_ok(head_dim) || !tq_bits_ok(key_bits, value_bits)) return -1;
+    const int s = head_dim * key_bits / 8 + 2 + ftq::tq_value_bytes(head_dim, value_bits) + 4;
+    return s + (s & 1);
+}
+
+extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64_t n_tokens, int Hkv,
+                            int head_dim, int64_t token_stride, int64_t head_stride, int key_bits,
+                            int value_bits, const float* midpoints_host, uint8_t* kv_cache,
+                            int64_t stride_block, int64_t stride_pos, int64_t stride_head,
+                            int block_size, const int64_t* slot_mapping, void* stream) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!tq_bits_ok(key_bits, value_bits))
+        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 2..4 / 2,3,4,8)", key_bits,
+                    value_bits);
+    if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
+    if (n_tokens < 0 || Hkv <= 0 || block_size <= 0) return fail(FTQ_ERR_INVALID, "bad shape");
+    if (n_tokens * Hkv >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "n_tokens * Hkv must be below 2^31");
+    if (n_tokens == 0) return FTQ_OK;
+    if (!key || !value || !kv_cache || !slot_mapping || !midpoints_host)
+        return fail(FTQ_ERR_INVALID, "NULL pointer argument");
+    const int64_t es = static_cast<int64_t>(dtype_size(dtype));
+    if (!aligned(key, 16) || !aligned(value, 16) || (token_stride * es) % 16 || (head_stride * es) % 16)
+        return fail(FTQ_ERR_INVALID, "key/value rows must be 16-byte aligned");
+    if (!aligned(kv_cache, 2) || !even(stride_block) || !even(stride_pos) || !even(stride_head))
+        return fail(FTQ_ERR_INVALID, "kv_cache base and strides must be even");
+    if (stride_head < ftq_tq_slot_bytes(head_dim, key_bits, value_bits) - 1)
+        return fail(FTQ_ERR_INVALID, "stride_head smaller than the slot");
+    ftq::TqStoreParams p{};
+    p.key = key;
+    p.value = value;
+    p.token_stride = token_stride;
+    p.head_stride = head_stride;
+    p.Hkv = Hkv;
+    p.div_hkv = ftq::make_fastdiv(static_cast<uint32_t>(Hkv));
+    p.kv_cache = kv_cache;
+    p.stride_block = stride_block;
+    p.stride_pos = stride_pos;
+    p.stride_head = stride_head;
+    p.block_size = block_size;
+    p.div_block = ftq::make_fastdiv(static_cast<uint32_t>(block_size));
+    p.slot_mapping = slot_mapping;
+    const int nmid = (1 << key_bits) - 1;
+    for (int i = 0; i < ftq::kTqMaxMid; i++) p.midpoints[i] = i < nmid ? midpoints_host[i] : FLT_MAX;
+    for (int i = 1; i < nmid; i++)
+        if (!(midpoints_host[i] > midpoints_host[i - 1]))
+            return fail(FTQ_ERR_INVALID, "midpoints must be strictly ascending");
+    p.rsqrt_d = 1.0f / sqrtf(static_cast<float>(head_dim));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t n_vec = n_tokens * Hkv;
+    cudaError_t e = cudaErrorInvalidValue;
+    switch (head_dim) {
+        case 64: e = ftq::launch_tq_store_d64(key_bits, value_bits, dtype, p, n_vec, st); break;
+        case 128: e = ftq::launch_tq_store_d128(key_bits, value_bits, dtype, p, n_vec, st); break;
+        case 256: e = ftq::launch_tq_store_d256(key_bits, value_bits, dtype, p, n_vec, st); break;
+    }
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "tq_store launch");
+}
+
+extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv, int head_dim,
+                             const uint8_t* kv_cache, int64_t stride_block, int64_t stride_pos,
+                             int64_t stride_head, int block_size, const int32_t* block_table,
+                             int max_blocks, const int32_t* seq_lens, const int32_t* kv_start_offset,
+                             int key_bits, int value_bits, int norm_correction, int rotate_output,
+                             const float* centroids_host, float scale, int num_kv_splits,
+                             float* mid_o, void* out, int out_dtype, float* lse, void* stream) {
+    if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
+    if (!tq_bits_ok(key_bits, value_bits))
+        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 2..4 / 2,3,4,8)", key_bits,
+                    value_bits);
+    if (!dtype_ok(q_dtype) || !dtype_ok(out_dtype)) return fail(FTQ_ERR_INVALID, "bad dtype");
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || block_size <= 0 || max_blocks <= 0)
+        return fail(FTQ_ERR_INVALID, "bad shape");
+    if (num_kv_splits <= 0 || num_kv_splits > 65535)
+        return fail(FTQ_ERR_INVALID, "num_kv_splits must be in [1, 65535]");
+    if (B == 0) return FTQ_OK;
+    if (B > 65535) return fail(FTQ_ERR_INVALID, "B must be at most 65535 per call");
+    if (!q || !kv_cache || !block_table || !seq_lens || !centroids_host || !mid_o || !out)
+        return fail(FTQ_ERR_INVALID, "NULL pointer argument");
+    if (!aligned(q, 16) || !aligned(out, 4) || !aligned(mid_o, 4))
+        return fail(FTQ_ERR_INVALID, "q must be 16-byte aligned, out and mid_o 4-byte aligned");
+    if (!aligned(kv_cache, 2) || !even(stride_block) || !even(stride_pos) || !even(stride_head))
+        return fail(FTQ_ERR_INVALID, "kv_cache base and strides must be even");
+    ftq::TqDecodeParams p{};
+    p.q = q;
+    p.q_dtype = q_dtype;
+    p.B = B;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.kv_cache = kv_cache;
+    p.stride_block = stride_block;
+    p.stride_pos = stride_pos;
+    p.stride_head = stride_head;
+    p.block_size = block_size;
+    p.div_block = ftq::make_fastdiv(static_cast<uint32_t>(block_size));
+    p.block_table = block_table;
+    p.max_blocks = max_blocks;
+    p.seq_lens = seq_lens;
+    p.kv_start = kv_start_offset;
+    p.norm_correction = norm_correction ? 1 : 0;
+    p.scale = scale;
+    p.splits = num_kv_splits;
+    const int gh = head_dim == 64 ? 8 : (head_dim == 128 ? 4 : 2);
+    p.n_hpass = (Hq / Hkv + gh - 1) / gh;
+    if (static_cast<int64_t>(Hkv) * p.n_hpass > 65535) return fail(FTQ_ERR_INVALID, "too many heads");
+    p.rsqrt_d = 1.0f / sqrtf(static_cast<float>(head_dim));
+    int rc = pack_levels(centroids_host, key_bits, &p.centroids);
+    if (rc) return rc;
+    p.mid_o = mid_o;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaErrorInvalidValue;
+    switch (head_dim) {
+        case 64: e = ftq::launch_tq_split_d64(key_bits, value_bits, p, st); break;
+        case 128: e = ftq::launch_tq_split_d128(key_bits, value_bits, p, st); break;
+        case 256: e = ftq::launch_tq_split_d256(key_bits, value_bits, p, st); break;
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "tq_decode stage 1 launch");
+    const int64_t rows = static_cast<int64_t>(B) * Hq;
+    switch (head_dim) {
+        case 64: e = ftq::launch_tq_merge_d64(out_dtype, mid_o, out, lse, rows, num_kv_splits, rotate_output, p.rsqrt_d, st); break;
+        case 128: e = ftq::launch_tq_merge_d128(out_dtype, mid_o, out, lse, rows, num_kv_splits, rotate_output, p.rsqrt_d, st); break;
+        case 256: e = ftq::launch_tq_merge_d256(out_dtype, mid_o, out, lse, rows, num_kv_splits, rotate_output, p.rsqrt_d, st); break;
+    }
+    return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "tq_decode merge launch");
 }

@@ -1,0 +1,545 @@
+// vLLM-v1 "TURBOQUANT" slot format: fused store and split-KV decode attention.
+//
+// Slot of one (token, KV head), at kv_cache + block*stride_block + pos*stride_pos +
+// head*stride_head (slots are only 2-byte aligned: their size is rounded up to even):
+//     [key codes (D*kb/8) | key norm fp16 | value codes (D*vb/8, or D for 8 bits) |
+//      value scale fp16 | value zero fp16]
+//
+// Store  = the reference's in-kernel-rotation store
+//          (src/fused_turboquant/vllm_plugin/triton_inkernel_store.py:365-440 and 39-330):
+//          norm of the RAW key, normalise, Hadamard butterfly without signs, * 1/sqrt(D),
+//          code = #{midpoints <= y}, pack; values: per-vector min/max uniform quantisation,
+//          q = int((v - min) / scale + 0.5), scale and min stored as fp16.
+// Decode = `_tq_decode_stage1_offset` (vllm_plugin/triton_decode_offset.py:42-444) for all query
+//          heads of a GQA group at once (each slot is read once per KV head, not once per query
+//          head), writing the same [B, Hq, splits, D+1] partials (acc / l, lse), followed by a
+//          merge kernel with the semantics of the stock stage-2 kernel the reference launches
+//          (vllm_plugin/v1_backend.py:1068-1085) and, optionally, the Hadamard transform that
+//          maps an output accumulated over rotated values back (v1_backend.py:1088-1092).
+//
+// The order in which the key's squares are added is not fixed by the reference (a Triton
+// reduction); here: 8 running sums in register order, combined pairwise over the octet.
+#pragma once
+
+#include <type_traits>
+
+#include "ftq_attn.cuh"
+#include "ftq_encode.cuh"
+
+namespace ftq {
+
+constexpr int kTqMaxMid = 15;  // key codes of 2..4 bits
+
+struct TqStoreParams {
+    const void* key;       // [n_tokens, Hkv, D], strides in elements
+    const void* value;
+    int64_t token_stride, head_stride;
+    int Hkv;
+    FastDiv div_hkv;
+    uint8_t* kv_cache;
+    int64_t stride_block, stride_pos, stride_head;  // bytes
+    int block_size;
+    FastDiv div_block;
+    const int64_t* slot_mapping;
+    float midpoints[kTqMaxMid];
+    float rsqrt_d;  // 1.0f / sqrtf(D), as the reference computes it
+};
+
+__host__ __device__ constexpr int tq_value_bytes(int d, int vb) { return vb == 8 ? d : d * vb / 8; }
+
+__device__ __forceinline__ void store_u32_as_halves(uint8_t* dst, uint32_t w) {
+    reinterpret_cast<uint16_t*>(dst)[0] = static_cast<uint16_t>(w);
+    reinterpret_cast<uint16_t*>(dst)[1] = static_cast<uint16_t>(w >> 16);
+}
+
+template <int D, int KB, int VB, typename T>
+__global__ void __launch_bounds__(256)
+tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
+    constexpr int E = D / kOctet;
+    constexpr int NCH = E / 8;
+    constexpr int MSE = D * KB / 8;
+    constexpr int KPS = MSE + 2;
+    constexpr int VDB = tq_value_bytes(D, VB);
+    constexpr int VMAX = (1 << VB) - 1;
+    constexpr int NMID = (1 << KB) - 1;
+    constexpr int NW = KB == 2 ? (E + 15) / 16 : E / 8;
+
+    const int lane = threadIdx.x & 31;
+    const int t = lane & 7, sub = lane >> 3;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    const TransposeConsts<KB> tc = transpose_consts<KB>(lane);
+
+    for (int64_t base = warp * 4; base < n_vec; base += n_warps * 4) {
+        const int64_t v = base + sub;
+        const bool valid = v < n_vec;
+        const uint32_t token = valid ? fast_div(static_cast<uint32_t>(v), p.div_hkv) : 0u;
+        const int head = valid ? static_cast<int>(static_cast<uint32_t>(v) - token * p.Hkv) : 0;
+        const int64_t slot = valid ? p.slot_mapping[token] : -1;
+        const bool store = valid && slot >= 0;
+        const int64_t row_off = static_cast<int64_t>(token) * p.token_stride + head * p.head_stride;
+        uint8_t* dst = nullptr;
+        if (store) {
+            int64_t blk, off;
+            if (slot < (1ll << 31)) {
+                const uint32_t b32 = fast_div(static_cast<uint32_t>(slot), p.div_block);
+                blk = b32;
+                off = static_cast<uint32_t>(slot) - b32 * p.block_size;
+            } else {
+                blk = slot / p.block_size;
+                off = slot - blk * p.block_size;
+            }
+            dst = p.kv_cache + blk * p.stride_block + off * p.stride_pos + head * p.stride_head;
+        }
+
+        // ---- key: raw norm, normalise, butterfly, midpoint search
+        float y[E];
+#pragma unroll
+        for (int i = 0; i < NCH; i++) {
+            float tmp[8];
+            if (valid) {
+                load8<T>(static_cast<const T*>(p.key) + row_off + 8 * (t + 8 * i), tmp);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; c++) tmp[c] = 0.f;
+            }
+#pragma unroll
+            for (int c = 0; c < 8; c++) y[8 * i + c] = tmp[c];
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int r = 0; r < E; r++) s = __fadd_rn(s, __fmul_rn(y[r], y[r]));
+        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
+        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
+        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 4));
+        const float norm = __fsqrt_rn(__fadd_rn(s, 1e-16f));
+        const float den = __fadd_rn(norm, 1e-8f);
+#pragma unroll
+        for (int r = 0; r < E; r++) y[r] = __fdiv_rn(y[r], den);
+        octet_fwht<E>(y, lane);  // -> (lane l, register k) = coordinate l + 8k
+
+        uint32_t w[NW];
+#pragma unroll
+        for (int i = 0; i < NW; i++) w[i] = 0u;
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            const float yv = __fmul_rn(y[k], p.rsqrt_d);
+            uint32_t code = 0;
+#pragma unroll
+            for (int j = 0; j < NMID; j++) code += (yv >= p.midpoints[j]) ? 1u : 0u;
+            if constexpr (KB == 2) {
+                const int pos = ((k >> 1) & 7) | ((k & 1) << 3);
+                w[k >> 4] |= code << (2 * pos);
+            } else {
+                w[k >> 3] |= code << (KB * (k & 7));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NW; i++) {
+            const uint32_t o = octet_transpose_items<KB>(w[i], tc);
+            if constexpr (KB == 3) {
+                const int g0 = (4 * t) / 3;
+                const uint32_t lo = __shfl_sync(0xffffffffu, o, g0, 8);
+                const uint32_t hi = __shfl_sync(0xffffffffu, o, g0 + 1, 8);
+                const uint64_t cat = (static_cast<uint64_t>(hi) << 24) | lo;
+                const uint32_t word = static_cast<uint32_t>(cat >> (8 * ((4 * t) % 3)));
+                if (store && t < 6) store_u32_as_halves(dst + 4 * (6 * i + t), word);
+            } else {
+                const int widx = t + 8 * i;
+                if (store && widx < MSE / 4) store_u32_as_halves(dst + 4 * widx, o);
+            }
+        }
+        if (store && t == 0)
+            *reinterpret_cast<__half*>(dst + MSE) = __float2half_rn(norm);
+
+        // ---- value: per-vector uniform quantisation; a lane owns runs of 8 consecutive coordinates
+        float vv[E];
+        float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < NCH; i++) {
+            float tmp[8];
+            if (valid) {
+                load8<T>(static_cast<const T*>(p.value) + row_off + 8 * (t + 8 * i), tmp);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; c++) tmp[c] = 0.f;
+            }
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                vv[8 * i + c] = tmp[c];
+                mn = fminf(mn, tmp[c]);
+                mx = fmaxf(mx, tmp[c]);
+            }
+        }
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, m));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+        }
+        float scale = __fdiv_rn(__fsub_rn(mx, mn), static_cast<float>(VMAX));
+        scale = scale > 1e-8f ? scale : 1e-8f;
+#pragma unroll
+        for (int i = 0; i < NCH; i++) {
+            uint32_t q[8];
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const float f = __fadd_rn(__fdiv_rn(__fsub_rn(vv[8 * i + c], mn), scale), 0.5f);
+                const int qi = __float2int_rz(f);
+                q[c] = static_cast<uint32_t>(min(max(qi, 0), VMAX));
+            }
+            const int run = t + 8 * i;  // coordinates 8*run .. 8*run + 7
+            if (!store) continue;
+            uint8_t* vd = dst + KPS;
+            if constexpr (VB == 8) {
+#pragma unroll
+                for (int c = 0; c < 8; c += 2)
+                    reinterpret_cast<uint16_t*>(vd + 8 * run)[c >> 1] =
+                        static_cast<uint16_t>(q[c] | (q[c + 1] << 8));
+            } else {
+                uint32_t word = 0;
+#pragma unroll
+                for (int c = 0; c < 8; c++) word |= q[c] << (VB * c);
+                if constexpr (VB == 4) {
+                    store_u32_as_halves(vd + 4 * run, word);
+                } else if constexpr (VB == 2) {
+                    *reinterpret_cast<uint16_t*>(vd + 2 * run) = static_cast<uint16_t>(word);
+                } else {
+                    vd[3 * run] = static_cast<uint8_t>(word);
+                    vd[3 * run + 1] = static_cast<uint8_t>(word >> 8);
+                    vd[3 * run + 2] = static_cast<uint8_t>(word >> 16);
+                }
+            }
+        }
+        if (store && t == 0) {
+            *reinterpret_cast<__half*>(dst + KPS + VDB) = __float2half_rn(scale);
+            *reinterpret_cast<__half*>(dst + KPS + VDB + 2) = __float2half_rn(mn);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ decode
+
+struct TqDecodeParams {
+    const void* q;  // [B, Hq, D], original space
+    int q_dtype;
+    int B, Hq, Hkv;
+    const uint8_t* kv_cache;
+    int64_t stride_block, stride_pos, stride_head;
+    int block_size;
+    FastDiv div_block;
+    const int32_t* block_table;
+    int max_blocks;
+    const int32_t* seq_lens;
+    const int32_t* kv_start;  // nullable
+    int norm_correction;
+    float scale;
+    int splits, n_hpass;
+    float rsqrt_d;
+    Codebook centroids;
+    float* mid_o;  // [B, Hq, splits, D + 1]
+};
+
+constexpr int kTqTileTokens = 64;
+
+template <int D, int KB, int VB>
+__global__ void __launch_bounds__(kAttnThreads)
+tq_split_kernel(const TqDecodeParams p) {
+    constexpr int E = AttnCfg<D>::E;
+    constexpr int GH = AttnCfg<D>::GH;
+    constexpr int MSE = D * KB / 8;
+    constexpr int VDB = tq_value_bytes(D, VB);
+    constexpr int NBK = MSE / kOctet, NBV = VDB / kOctet;
+    constexpr int SLOT_U16 = (MSE + 2 + VDB + 4) / 2;
+
+    // tile buffers; once the loop is over the K/V areas double as the cross-warp merge area
+    constexpr int TILE_BYTES = kTqTileTokens * (MSE + VDB);
+    constexpr int MERGE_BYTES = 4 * GH * (D + 2) * 4;
+    constexpr int BUF_BYTES = ((TILE_BYTES > MERGE_BYTES ? TILE_BYTES : MERGE_BYTES) + 15) / 16 * 16;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    uint8_t* kbuf = smem_raw;                               // [64][MSE]
+    uint8_t* vbuf = smem_raw + kTqTileTokens * MSE;         // [64][VDB]
+    float* meta = reinterpret_cast<float*>(smem_raw + BUF_BYTES);   // [3][64]: key norm, value scale, zero
+    const uint8_t** slots = reinterpret_cast<const uint8_t**>(meta + 3 * kTqTileTokens);  // [64]
+    float* qs = reinterpret_cast<float*>(slots + kTqTileTokens);    // [GH][D]
+    float* lut = qs + GH * D;                                       // [16]
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int t = lane & 7, o = lane >> 3;
+    const int sid = blockIdx.x;
+    const int hkv = blockIdx.y / p.n_hpass;
+    const int hp = blockIdx.y - hkv * p.n_hpass;
+    const int b = blockIdx.z;
+    const int group = p.Hq / p.Hkv;
+    const int h0 = hp * GH;
+    const int nh = min(GH, group - h0);
+
+    const int seq_len = p.seq_lens[b];
+    const int kv_start = p.kv_start ? p.kv_start[b] : 0;
+    const int eff = seq_len - kv_start;
+    const int split_len = (eff + p.splits - 1) / p.splits;
+    const int t0 = kv_start + split_len * sid;
+    const int t1 = min(t0 + split_len, seq_len);
+    float* mo = p.mid_o + ((static_cast<int64_t>(b) * p.Hq + hkv * group + h0) * p.splits + sid) * (D + 1);
+    const int64_t mo_head_stride = static_cast<int64_t>(p.splits) * (D + 1);
+    if (t0 >= t1) {  // neutral partial: zeros and lse = -inf
+        for (int idx = tid; idx < nh * (D + 1); idx += kAttnThreads) {
+            const int h = idx / (D + 1), d = idx - h * (D + 1);
+            mo[h * mo_head_stride + d] = d == D ? -INFINITY : 0.f;
+        }
+        return;
+    }
+
+    // ---- prologue: centroids and the rotated (no signs), pre-scaled queries of this pass
+    if (tid < kMaxLevels) lut[tid] = p.centroids.v[tid];
+    {
+        const int hh = warp * 4 + o;
+        const bool hv = hh < nh;
+        const int64_t qoff = (static_cast<int64_t>(b) * p.Hq + hkv * group + h0 + (hv ? hh : 0)) * D;
+        float a[E];
+#pragma unroll
+        for (int i = 0; i < E / 8; i++) {
+            float tmp[8];
+            const int64_t eo = qoff + 8 * (t + 8 * i);
+            if (p.q_dtype == kF32) load8<float>(static_cast<const float*>(p.q) + eo, tmp);
+            else if (p.q_dtype == kBF16)
+                load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.q) + eo, tmp);
+            else load8<__half>(static_cast<const __half*>(p.q) + eo, tmp);
+#pragma unroll
+            for (int c = 0; c < 8; c++) a[8 * i + c] = tmp[c];
+        }
+        octet_fwht<E>(a, lane);
+        if (hh < GH) {
+#pragma unroll
+            for (int k = 0; k < E; k++)
+                qs[hh * D + t + 8 * k] = hv ? a[k] * p.rsqrt_d * p.scale : 0.f;
+        }
+    }
+    __syncthreads();
+
+    float qr[GH][E];
+#pragma unroll
+    for (int h = 0; h < GH; h++)
+#pragma unroll
+        for (int r = 0; r < E; r++) qr[h][r] = qs[h * D + t * E + r];
+
+    float m_run[GH], l_run[GH], acc[GH][E];
+#pragma unroll
+    for (int h = 0; h < GH; h++) {
+        m_run[h] = -INFINITY;
+        l_run[h] = 0.f;
+#pragma unroll
+        for (int r = 0; r < E; r++) acc[h][r] = 0.f;
+    }
+
+    const int32_t* btab = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+    for (int ts = t0; ts < t1; ts += kTqTileTokens) {
+        const int ntile = min(kTqTileTokens, t1 - ts);
+        // slot addresses of the tile's tokens
+        if (tid < ntile) {
+            const uint32_t pos = static_cast<uint32_t>(ts + tid);
+            const uint32_t pg = fast_div(pos, p.div_block);
+            const uint32_t off = pos - pg * p.block_size;
+            slots[tid] = p.kv_cache + static_cast<int64_t>(btab[pg]) * p.stride_block +
+                         off * p.stride_pos + hkv * p.stride_head;
+        }
+        __syncthreads();
+        // stage the slots (2-byte granules: slots are only 2-byte aligned), sorted into
+        // key codes / value codes / the three scalars
+        for (int idx = tid; idx < ntile * SLOT_U16; idx += kAttnThreads) {
+            const int tk = idx / SLOT_U16, j = idx - tk * SLOT_U16;
+            const uint16_t v = reinterpret_cast<const uint16_t*>(slots[tk])[j];
+            if (j < MSE / 2) {
+                reinterpret_cast<uint16_t*>(kbuf)[tk * (MSE / 2) + j] = v;
+            } else if (j == MSE / 2) {
+                meta[tk] = __half2float(__ushort_as_half(v));
+            } else if (j < MSE / 2 + 1 + VDB / 2) {
+                reinterpret_cast<uint16_t*>(vbuf)[tk * (VDB / 2) + j - MSE / 2 - 1] = v;
+            } else {
+                meta[(j - (MSE / 2 + VDB / 2)) * kTqTileTokens + tk] = __half2float(__ushort_as_half(v));
+            }
+        }
+        __syncthreads();
+
+        const int tw = warp * 16;  // this warp's 16 tokens of the tile
+        if (tw < ntile) {          // warp-uniform
+            float sc[4][GH];
+#pragma unroll
+            for (int step = 0; step < 4; step++) {
+                const int tk = tw + step * 4 + o;
+                uint32_t w[(NBK + 3) / 4];
+                load_code_bytes<NBK>(kbuf + tk * MSE + t * NBK, w);
+                float kv[E];
+                float cn = 0.f;
+#pragma unroll
+                for (int r = 0; r < E; r++) {
+                    kv[r] = lut[extract_code<KB>(w, r)];
+                    cn = fmaf(kv[r], kv[r], cn);
+                }
+                float kn = meta[tk];
+                if (p.norm_correction) {  // re-normalise the centroid vector to unit length
+                    cn += __shfl_xor_sync(0xffffffffu, cn, 1);
+                    cn += __shfl_xor_sync(0xffffffffu, cn, 2);
+                    cn += __shfl_xor_sync(0xffffffffu, cn, 4);
+                    kn *= 1.0f / sqrtf(cn + 1e-16f);
+                }
+#pragma unroll
+                for (int h = 0; h < GH; h++) {
+                    float d = 0.f;
+#pragma unroll
+                    for (int r = 0; r < E; r++) d = fmaf(qr[h][r], kv[r], d);
+                    d += __shfl_xor_sync(0xffffffffu, d, 1);
+                    d += __shfl_xor_sync(0xffffffffu, d, 2);
+                    d += __shfl_xor_sync(0xffffffffu, d, 4);
+                    sc[step][h] = tk < ntile ? d * kn : -INFINITY;
+                }
+            }
+            float wp[4][GH];
+#pragma unroll
+            for (int h = 0; h < GH; h++) {
+                float mx = fmaxf(fmaxf(sc[0][h], sc[1][h]), fmaxf(sc[2][h], sc[3][h]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float m_new = fmaxf(m_run[h], mx);  // finite: the warp's first token is valid
+                const float corr = m_run[h] == -INFINITY ? 0.f : __expf(m_run[h] - m_new);
+                m_run[h] = m_new;
+                float ls = 0.f;
+#pragma unroll
+                for (int step = 0; step < 4; step++) {
+                    const float pe = sc[step][h] == -INFINITY ? 0.f : __expf(sc[step][h] - m_new);
+                    ls += pe;
+                    wp[step][h] = pe;
+                }
+                l_run[h] = l_run[h] * corr + ls;
+#pragma unroll
+                for (int r = 0; r < E; r++) acc[h][r] *= corr;
+            }
+#pragma unroll
+            for (int step = 0; step < 4; step++) {
+                const int tk = tw + step * 4 + o;
+                const bool ok = tk < ntile;
+                uint32_t w[(NBV + 3) / 4];
+                load_code_bytes<NBV>(vbuf + tk * VDB + t * NBV, w);
+                // (slots past the end of the tile hold stale bytes: keep them out of the arithmetic)
+                const float vs = ok ? meta[kTqTileTokens + tk] : 0.f;
+                const float vz = ok ? meta[2 * kTqTileTokens + tk] : 0.f;
+                float vv[E];
+#pragma unroll
+                for (int r = 0; r < E; r++)
+                    vv[r] = fmaf(static_cast<float>(extract_code<VB>(w, r)), vs, vz);
+#pragma unroll
+                for (int h = 0; h < GH; h++) {
+                    const float wgt = ok ? wp[step][h] : 0.f;
+#pragma unroll
+                    for (int r = 0; r < E; r++) acc[h][r] = fmaf(wgt, vv[r], acc[h][r]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- combine the 4 octets of each warp, then the 4 warps through shared memory
+#pragma unroll
+    for (int h = 0; h < GH; h++) {
+        // octets of a warp share m_run (the max was reduced over the warp), so sums just add
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
+#pragma unroll
+        for (int r = 0; r < E; r++) {
+            acc[h][r] += __shfl_xor_sync(0xffffffffu, acc[h][r], 8);
+            acc[h][r] += __shfl_xor_sync(0xffffffffu, acc[h][r], 16);
+        }
+    }
+    float* wacc = reinterpret_cast<float*>(smem_raw);  // [4][GH][D]
+    float* wm = wacc + 4 * GH * D;                     // [4][GH]
+    float* wl = wm + 4 * GH;                           // [4][GH]
+    if (o == 0) {
+#pragma unroll
+        for (int h = 0; h < GH; h++) {
+#pragma unroll
+            for (int r = 0; r < E; r++) wacc[(warp * GH + h) * D + t * E + r] = acc[h][r];
+            if (t == 0) {
+                wm[warp * GH + h] = m_run[h];
+                wl[warp * GH + h] = l_run[h];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nh * D; idx += kAttnThreads) {
+        const int h = idx / D, d = idx - h * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w2 = 0; w2 < 4; w2++) M = fmaxf(M, wm[w2 * GH + h]);
+        float a = 0.f, l = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < 4; w2++) {
+            const float mw = wm[w2 * GH + h];
+            if (mw != -INFINITY) {
+                const float f = __expf(mw - M);
+                a = fmaf(wacc[(w2 * GH + h) * D + d], f, a);
+                l = fmaf(wl[w2 * GH + h], f, l);
+            }
+        }
+        const float safe_l = l > 0.f ? l : 1.f;
+        mo[h * mo_head_stride + d] = a / safe_l;
+        if (d == 0) mo[h * mo_head_stride + D] = M + logf(safe_l);
+    }
+}
+
+template <int D>
+constexpr int tq_split_smem_bytes(int kb, int vb) {
+    const int mse = D * kb / 8, vdb = tq_value_bytes(D, vb);
+    const int tile = kTqTileTokens * (mse + vdb);
+    const int merge = 4 * AttnCfg<D>::GH * (D + 2) * 4;
+    const int buf = ((tile > merge ? tile : merge) + 15) / 16 * 16;
+    return buf + 3 * kTqTileTokens * 4 + kTqTileTokens * 8 + AttnCfg<D>::GH * D * 4 + kMaxLevels * 4;
+}
+
+// Merge the split partials of 4 (sequence, query head) rows per warp: softmax-weighted by lse,
+// optionally Hadamard-transform the result, cast and store.  mid_o rows with lse = -inf are skipped.
+template <int D, typename OT>
+__global__ void __launch_bounds__(128)
+tq_merge_kernel(const float* __restrict__ mid_o, OT* __restrict__ out, float* __restrict__ lse_out,
+                int64_t n_rows, int splits, int rotate, float rsqrt_d) {
+    constexpr int E = D / kOctet;
+    const int lane = threadIdx.x & 31;
+    const int t = lane & 7;
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / 8;
+    const bool valid = row < n_rows;
+    const float* base = mid_o + (valid ? row : 0) * static_cast<int64_t>(splits) * (D + 1);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; s++) M = fmaxf(M, base[static_cast<int64_t>(s) * (D + 1) + D]);
+    float a[E];
+#pragma unroll
+    for (int r = 0; r < E; r++) a[r] = 0.f;
+    float l = 0.f;
+    for (int s = 0; s < splits; s++) {
+        const float* ps = base + static_cast<int64_t>(s) * (D + 1);
+        const float ls = ps[D];
+        if (ls == -INFINITY) continue;
+        const float f = __expf(ls - M);
+        l += f;
+#pragma unroll
+        for (int r = 0; r < E; r++) a[r] = fmaf(ps[load_coord(t, r)], f, a[r]);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int r = 0; r < E; r++) a[r] *= inv;
+    if (rotate) {
+        octet_fwht<E>(a, lane);
+#pragma unroll
+        for (int k = 0; k < E; k++) a[k] *= rsqrt_d;
+    }
+    if (!valid) return;
+    OT* orow = out + row * D;
+#pragma unroll
+    for (int r = 0; r < E; r++) {
+        const int coord = rotate ? t + 8 * r : load_coord(t, r);
+        if constexpr (sizeof(OT) == 4) orow[coord] = a[r];
+        else if constexpr (std::is_same<OT, __half>::value) orow[coord] = __float2half_rn(a[r]);
+        else orow[coord] = __float2bfloat16_rn(a[r]);
+    }
+    if (lse_out && t == 0) lse_out[row] = l > 0.f ? M + logf(l) : -INFINITY;
+}
+
+}  // namespace ftq

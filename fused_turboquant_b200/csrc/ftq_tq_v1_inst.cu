@@ -1,0 +1,106 @@
+// Instantiates the vLLM-v1 slot-format kernels for one head_dim (FTQ_D).
+#include "ftq_launch.h"
+#include "ftq_tq_v1.cuh"
+
+#ifndef FTQ_D
+#error "compile with -DFTQ_D=64, 128 or 256"
+#endif
+#define FTQ_CAT2(a, b) a##b
+#define FTQ_CAT(a, b) FTQ_CAT2(a, b)
+
+namespace ftq {
+
+template <int KB, int VB, typename T>
+static cudaError_t store_run(const TqStoreParams& p, int64_t n_vec, cudaStream_t stream) {
+    const int64_t want = (n_vec + 31) / 32;  // 8 warps x 4 vectors per CTA pass
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    const unsigned gx = static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
+    tq_store_kernel<FTQ_D, KB, VB, T><<<gx, 256, 0, stream>>>(p, n_vec);
+    return cudaGetLastError();
+}
+
+template <int KB, int VB>
+static cudaError_t store_by_dtype(int dtype, const TqStoreParams& p, int64_t n_vec, cudaStream_t s) {
+    switch (dtype) {
+        case kF32: return store_run<KB, VB, float>(p, n_vec, s);
+        case kF16: return store_run<KB, VB, __half>(p, n_vec, s);
+        case kBF16: return store_run<KB, VB, __nv_bfloat16>(p, n_vec, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <int KB>
+static cudaError_t store_by_vb(int vb, int dtype, const TqStoreParams& p, int64_t n_vec, cudaStream_t s) {
+    switch (vb) {
+        case 2: return store_by_dtype<KB, 2>(dtype, p, n_vec, s);
+        case 3: return store_by_dtype<KB, 3>(dtype, p, n_vec, s);
+        case 4: return store_by_dtype<KB, 4>(dtype, p, n_vec, s);
+        case 8: return store_by_dtype<KB, 8>(dtype, p, n_vec, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t FTQ_CAT(launch_tq_store_d, FTQ_D)(int kb, int vb, int dtype, const TqStoreParams& p,
+                                             int64_t n_vec, cudaStream_t stream) {
+    switch (kb) {
+        case 2: return store_by_vb<2>(vb, dtype, p, n_vec, stream);
+        case 3: return store_by_vb<3>(vb, dtype, p, n_vec, stream);
+        case 4: return store_by_vb<4>(vb, dtype, p, n_vec, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <int KB, int VB>
+static cudaError_t split_run(const TqDecodeParams& p, cudaStream_t stream) {
+    constexpr int smem = tq_split_smem_bytes<FTQ_D>(KB, VB);
+    static_assert(smem <= 48 * 1024, "tile does not fit the default shared-memory carve-out");
+    const dim3 grid(p.splits, p.Hkv * p.n_hpass, p.B);
+    tq_split_kernel<FTQ_D, KB, VB><<<grid, kAttnThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int KB>
+static cudaError_t split_by_vb(int vb, const TqDecodeParams& p, cudaStream_t s) {
+    switch (vb) {
+        case 2: return split_run<KB, 2>(p, s);
+        case 3: return split_run<KB, 3>(p, s);
+        case 4: return split_run<KB, 4>(p, s);
+        case 8: return split_run<KB, 8>(p, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t FTQ_CAT(launch_tq_split_d, FTQ_D)(int kb, int vb, const TqDecodeParams& p,
+                                             cudaStream_t stream) {
+    switch (kb) {
+        case 2: return split_by_vb<2>(vb, p, stream);
+        case 3: return split_by_vb<3>(vb, p, stream);
+        case 4: return split_by_vb<4>(vb, p, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t FTQ_CAT(launch_tq_merge_d, FTQ_D)(int out_dtype, const float* mid_o, void* out,
+                                             float* lse, int64_t n_rows, int splits, int rotate,
+                                             float rsqrt_d, cudaStream_t stream) {
+    const unsigned grid = static_cast<unsigned>((n_rows + 15) / 16);  // 128 threads = 16 rows
+    switch (out_dtype) {
+        case kF32:
+            tq_merge_kernel<FTQ_D, float><<<grid, 128, 0, stream>>>(
+                mid_o, static_cast<float*>(out), lse, n_rows, splits, rotate, rsqrt_d);
+            break;
+        case kF16:
+            tq_merge_kernel<FTQ_D, __half><<<grid, 128, 0, stream>>>(
+                mid_o, static_cast<__half*>(out), lse, n_rows, splits, rotate, rsqrt_d);
+            break;
+        case kBF16:
+            tq_merge_kernel<FTQ_D, __nv_bfloat16><<<grid, 128, 0, stream>>>(
+                mid_o, static_cast<__nv_bfloat16*>(out), lse, n_rows, splits, rotate, rsqrt_d);
+            break;
+        default:
+            return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace ftq

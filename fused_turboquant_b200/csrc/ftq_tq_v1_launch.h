@@ -1,0 +1,22 @@
+// Launchers of the vLLM-v1 slot-format kernels (ftq_tq_v1_inst.cu, one object per head_dim).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "ftq_tq_v1.cuh"
+
+namespace ftq {
+
+#define FTQ_DECLARE_TQ_LAUNCHERS(DD)                                                              \
+    cudaError_t launch_tq_store_d##DD(int kb, int vb, int dtype, const TqStoreParams& p,          \
+                                      int64_t n_vec, cudaStream_t stream);                        \
+    cudaError_t launch_tq_split_d##DD(int kb, int vb, const TqDecodeParams& p, cudaStream_t stream); \
+    cudaError_t launch_tq_merge_d##DD(int out_dtype, const float* mid_o, void* out, float* lse,    \
+                                      int64_t n_rows, int splits, int rotate, float rsqrt_d,      \
+                                      cudaStream_t stream);
+
+FTQ_DECLARE_TQ_LAUNCHERS(64)
+FTQ_DECLARE_TQ_LAUNCHERS(128)
+FTQ_DECLARE_TQ_LAUNCHERS(256)
+
+}  // namespace ftq

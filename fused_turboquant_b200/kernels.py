@@ -27,8 +27,9 @@ from . import _lib
 
 _DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 
-_table_cache: "weakref.WeakKeyDictionary[torch.Tensor, tuple[int, np.ndarray]]" = (
-    weakref.WeakKeyDictionary())
+# id(tensor) -> (weak reference, tensor version, host copy).  Keyed by identity: tensors compare
+# element-wise, which rules them out as dictionary keys.
+_table_cache: dict[int, tuple[weakref.ref, int, np.ndarray]] = {}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 
@@ -42,11 +43,12 @@ def _host_table(t) -> np.ndarray | None:
         return None
     if isinstance(t, np.ndarray):
         return np.ascontiguousarray(t, dtype=np.float32)
-    hit = _table_cache.get(t)
-    if hit is not None and hit[0] == t._version:
-        return hit[1]
+    key = id(t)
+    hit = _table_cache.get(key)
+    if hit is not None and hit[0]() is t and hit[1] == t._version:
+        return hit[2]
     arr = np.ascontiguousarray(t.detach().to(torch.float32).cpu().numpy())
-    _table_cache[t] = (t._version, arr)
+    _table_cache[key] = (weakref.ref(t, lambda _r, k=key: _table_cache.pop(k, None)), t._version, arr)
     return arr
 
 

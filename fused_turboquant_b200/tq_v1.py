@@ -1,0 +1,178 @@
+"""vLLM-v1 "TURBOQUANT" slot format: the host side of the reference's in-kernel-rotation
+backend, on libftq_b200.so.
+
+  TurboQuantSlotConfig   <- BoundaryTurboQuantConfig / vLLM's TurboQuantConfig slot properties
+                            (vllm_plugin/boundary_tq_config.py:21-81)
+  midpoints_of           <- MatrixRotationStrategy.setup_layer (vllm_plugin/rotation/matrix.py:34-42)
+  launch_store           <- HadamardStrategy.launch_store / _launch_rht
+                            (vllm_plugin/rotation/hadamard.py:44-58, triton_inkernel_store.py:554-646),
+                            with the optional value pre-rotation of v1_backend.py:727-740
+  decode_attention       <- FusedTurboQuantV1Impl._decode_attention_offset_only
+                            (vllm_plugin/v1_backend.py:975-1093)
+
+The kv cache is the uint8 tensor ``[num_blocks, block_size, num_kv_heads, slot]`` vLLM allocates.
+Tensors must live on a CUDA device; there is no CPU path.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from .kernels import _DT, _host_table, _ptr, _require_cuda, _stream, rht
+
+
+@dataclass(frozen=True)
+class TurboQuantSlotConfig:
+    """Slot layout of one (token, KV head): key codes | key norm f16 | value codes | scale f16 | zero f16."""
+
+    head_dim: int
+    key_quant_bits: int       # 2..4: Lloyd-Max codes
+    value_quant_bits: int     # 2, 3, 4 or 8: per-vector uniform codes
+    norm_correction: bool = True
+
+    def __post_init__(self):
+        if self.head_dim not in (64, 128, 256):
+            raise ValueError(f"head_dim must be 64, 128 or 256, got {self.head_dim}")
+        if self.key_quant_bits not in (2, 3, 4):
+            raise ValueError(f"key_quant_bits must be 2, 3 or 4, got {self.key_quant_bits}")
+        if self.value_quant_bits not in (2, 3, 4, 8):
+            raise ValueError(f"value_quant_bits must be 2, 3, 4 or 8, got {self.value_quant_bits}")
+
+    key_fp8 = False
+
+    @property
+    def key_mse_bits(self) -> int:
+        return self.key_quant_bits
+
+    @property
+    def mse_bits(self) -> int:
+        return self.key_quant_bits
+
+    @property
+    def n_centroids(self) -> int:
+        return 2 ** self.key_quant_bits
+
+    @property
+    def effective_value_quant_bits(self) -> int:
+        return self.value_quant_bits
+
+    @property
+    def key_packed_size(self) -> int:
+        return math.ceil(self.head_dim * self.key_quant_bits / 8) + 2
+
+    @property
+    def value_data_bytes(self) -> int:
+        if self.value_quant_bits == 8:
+            return self.head_dim
+        return math.ceil(self.head_dim * self.value_quant_bits / 8)
+
+    @property
+    def value_packed_size(self) -> int:
+        return self.value_data_bytes + 4
+
+    @property
+    def slot_size(self) -> int:
+        return self.key_packed_size + self.value_packed_size
+
+    @property
+    def slot_size_aligned(self) -> int:
+        return self.slot_size + self.slot_size % 2
+
+
+def midpoints_of(centroids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """(sorted fp32 centroids, their midpoints) as the reference derives them per layer."""
+    c, _ = centroids.to(torch.float32).sort()
+    return c, (c[:-1] + c[1:]) / 2
+
+
+def _cache_strides(kv_cache: torch.Tensor) -> tuple[int, int, int]:
+    if kv_cache.dtype != torch.uint8:
+        kv_cache = kv_cache.view(torch.uint8)
+    if kv_cache.dim() != 4 or kv_cache.stride(3) != 1:
+        raise ValueError("kv_cache must be [num_blocks, block_size, num_kv_heads, slot] with a dense last dim")
+    return kv_cache.stride(0), kv_cache.stride(1), kv_cache.stride(2)
+
+
+def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
+                 slot_mapping: torch.Tensor, midpoints, tq_config: TurboQuantSlotConfig,
+                 head_size: int | None = None, v_rotate: bool = False) -> None:
+    """Quantise ``key``/``value`` ``[N, Hkv, D]`` into the slots ``slot_mapping`` names (< 0: skipped)."""
+    _require_cuda(key, "key")
+    _require_cuda(kv_cache, "kv_cache")
+    n, hkv, d = key.shape
+    if head_size is not None and head_size != d:
+        raise ValueError(f"head_size {head_size} does not match key.shape[-1] {d}")
+    if d != tq_config.head_dim:
+        raise ValueError(f"key head size {d} does not match the config ({tq_config.head_dim})")
+    if value.shape != key.shape:
+        raise ValueError("key and value must have the same shape")
+    if key.dtype not in _DT:
+        key = key.float()
+    if value.dtype != key.dtype:
+        value = value.to(key.dtype)
+    if v_rotate:  # values live in the Hadamard-rotated space (undone on the decode output)
+        value = rht(value.float().contiguous(), None).to(key.dtype)
+    if key.stride(2) != 1 or value.stride() != key.stride():
+        key, value = key.contiguous(), value.contiguous()
+    if kv_cache.dtype != torch.uint8:
+        kv_cache = kv_cache.view(torch.uint8)
+    sb, sp, sh = _cache_strides(kv_cache)
+    if kv_cache.shape[3] < tq_config.slot_size:
+        raise ValueError(f"kv_cache slots of {kv_cache.shape[3]} bytes are smaller than {tq_config.slot_size}")
+    sm = slot_mapping.to(device=key.device, dtype=torch.int64).contiguous()
+    with torch.cuda.device(key.device):
+        rc = _lib.load().ftq_tq_store(
+            _ptr(key), _ptr(value), _DT[key.dtype], n, hkv, d, key.stride(0), key.stride(1),
+            tq_config.key_quant_bits, tq_config.value_quant_bits, _lib.fptr(_host_table(midpoints)),
+            _ptr(kv_cache), sb, sp, sh, kv_cache.shape[1], _ptr(sm), _stream(key.device))
+    _lib.check(rc, "ftq_tq_store")
+
+
+def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor,
+                     seq_lens: torch.Tensor, centroids, tq_config: TurboQuantSlotConfig, scale: float,
+                     num_kv_splits: int = 8, kv_start_offset: torch.Tensor | None = None,
+                     v_rotate: bool = False, mid_o: torch.Tensor | None = None,
+                     output: torch.Tensor | None = None, lse: torch.Tensor | None = None,
+                     out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Decode attention of ``query`` ``[B, Hq, D]`` over the compressed cache; returns ``[B, Hq, D]``.
+
+    ``mid_o`` ``[B, Hq, num_kv_splits, D+1]`` fp32, ``output`` and ``lse`` ``[B, Hq]`` fp32 may be
+    supplied (pre-allocated per layer, as the reference keeps them for CUDA-graph capture).
+    """
+    _require_cuda(query, "query")
+    _require_cuda(kv_cache, "kv_cache")
+    B, hq, d = query.shape
+    if d != tq_config.head_dim:
+        raise ValueError(f"query head size {d} does not match the config ({tq_config.head_dim})")
+    if query.dtype not in _DT:
+        query = query.float()
+    query = query.contiguous()
+    if kv_cache.dtype != torch.uint8:
+        kv_cache = kv_cache.view(torch.uint8)
+    sb, sp, sh = _cache_strides(kv_cache)
+    hkv = kv_cache.shape[2]
+    dev = query.device
+    bt = block_table.to(device=dev, dtype=torch.int32).contiguous()
+    sl = seq_lens.to(device=dev, dtype=torch.int32).contiguous()
+    ks = None if kv_start_offset is None else kv_start_offset.to(device=dev, dtype=torch.int32).contiguous()
+    if mid_o is None:
+        mid_o = torch.empty((B, hq, num_kv_splits, d + 1), dtype=torch.float32, device=dev)
+    elif mid_o.shape != (B, hq, num_kv_splits, d + 1) or mid_o.dtype != torch.float32 or not mid_o.is_contiguous():
+        raise ValueError("mid_o must be a contiguous fp32 [B, Hq, num_kv_splits, D+1] tensor")
+    odt = out_dtype or query.dtype
+    if output is None:
+        output = torch.empty((B, hq, d), dtype=odt, device=dev)
+    elif output.shape != (B, hq, d) or not output.is_contiguous() or output.dtype not in _DT:
+        raise ValueError("output must be a contiguous [B, Hq, D] tensor of a supported dtype")
+    with torch.cuda.device(dev):
+        rc = _lib.load().ftq_tq_decode(
+            _ptr(query), _DT[query.dtype], B, hq, hkv, d, _ptr(kv_cache), sb, sp, sh,
+            kv_cache.shape[1], _ptr(bt), bt.shape[1], _ptr(sl), _ptr(ks),
+            tq_config.key_quant_bits, tq_config.value_quant_bits, int(tq_config.norm_correction),
+            int(v_rotate), _lib.fptr(_host_table(centroids)), float(scale), num_kv_splits,
+            _ptr(mid_o), _ptr(output), _DT[output.dtype], _ptr(lse), _stream(dev))
+    _lib.check(rc, "ftq_tq_decode")
+    return output

@@ -249,6 +249,60 @@ int ftq_v0_gather(const uint8_t *kv_cache, int64_t num_blocks, int block_size, i
                   int max_blocks, const int32_t *seq_lens, int B, int max_seq_len,
                   uint8_t *out_codes, float *out_norms, void *stream);
 
+/* ---------------------------------------------------------------------------
+ * vLLM-v1 "TURBOQUANT" slot format (the reference's in-kernel-rotation backend).
+ *
+ * kv_cache is the uint8 tensor [num_blocks, block_size, Hkv, slot] vLLM allocates
+ * (src/fused_turboquant/vllm_plugin/v1_backend.py:149-261); the three byte strides
+ * are passed explicitly, so any slot padding works.  They and the base address must
+ * be even.  A slot holds
+ *     [key codes D*kb/8 | key norm f16 | value codes D*vb/8 (D for vb = 8) | scale f16 | zero f16]
+ * (vllm_plugin/boundary_tq_config.py:66-81; ftq_tq_slot_bytes returns its size rounded
+ * up to even).  Supported: head_dim 64/128/256, key_bits 2/3/4 (Lloyd-Max codes),
+ * value_bits 2/3/4/8 (per-vector uniform codes).  FP8 keys, 1- and 8-bit key codes and
+ * Lloyd-Max value codes return FTQ_ERR_UNSUPPORTED.
+ */
+int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits);
+
+/*
+ * Replaces RotationStrategy.launch_store -> _launch_rht -> _fused_store_rht
+ * (vllm_plugin/rotation/hadamard.py:44-58, triton_inkernel_store.py:554-646 and 365-440):
+ * per (token, KV head): norm of the raw key, key / (norm + 1e-8), Hadamard butterfly
+ * without signs, * 1/sqrt(D), code = number of midpoints <= y, pack, fp16 norm; value:
+ * min/max, scale = max((max - min) / (2^vb - 1), 1e-8), code = int((v - min) / scale + 0.5),
+ * pack, fp16 scale and min.  Tokens with slot_mapping[token] < 0 are skipped.
+ * key/value: [n_tokens, Hkv, head_dim] of `dtype`, strides in elements, rows 16-byte aligned.
+ * midpoints_host: 2^key_bits - 1 floats, ascending.  Values are stored as given: a caller that
+ * keeps values in the rotated space (TURBOQUANT_V_ROTATE) rotates them first, e.g. with ftq_rht
+ * and no signs.
+ */
+int ftq_tq_store(const void *key, const void *value, int dtype, int64_t n_tokens, int Hkv,
+                 int head_dim, int64_t token_stride, int64_t head_stride, int key_bits,
+                 int value_bits, const float *midpoints_host, uint8_t *kv_cache,
+                 int64_t stride_block, int64_t stride_pos, int64_t stride_head, int block_size,
+                 const int64_t *slot_mapping, void *stream);
+
+/*
+ * Replaces _decode_attention_offset_only (vllm_plugin/v1_backend.py:975-1093): query
+ * rotation q @ H, _tq_decode_stage1_offset (vllm_plugin/triton_decode_offset.py:42-444)
+ * and the stage-2 merge, in two launches.  q: [B, Hq, head_dim] of q_dtype in the original
+ * space.  Attends positions [kv_start_offset[b], seq_lens[b]) (kv_start_offset may be NULL = 0),
+ * split into num_kv_splits ranges exactly as the reference splits them.  mid_o
+ * (caller-provided, [B, Hq, num_kv_splits, head_dim + 1] fp32) receives the same partials
+ * the reference's stage 1 writes (acc / l and lse; zeros and -inf for an empty range).
+ * out: [B, Hq, head_dim] of out_dtype; lse (nullable): [B, Hq] fp32.  norm_correction:
+ * re-normalise each key's centroid vector to unit length.  rotate_output: apply the
+ * Hadamard transform to the merged output (values were stored in the rotated space).
+ * centroids_host: 2^key_bits floats, ascending.  No allocation, no host synchronisation.
+ */
+int ftq_tq_decode(const void *q, int q_dtype, int B, int Hq, int Hkv, int head_dim,
+                  const uint8_t *kv_cache, int64_t stride_block, int64_t stride_pos,
+                  int64_t stride_head, int block_size, const int32_t *block_table,
+                  int max_blocks, const int32_t *seq_lens, const int32_t *kv_start_offset,
+                  int key_bits, int value_bits, int norm_correction, int rotate_output,
+                  const float *centroids_host, float scale, int num_kv_splits, float *mid_o,
+                  void *out, int out_dtype, float *lse, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

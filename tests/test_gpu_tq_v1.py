@@ -1,0 +1,132 @@
+"""GPU parity of the vLLM-v1 slot-format path (fused store, split-KV decode) against the
+reference's own kernels (tests/golden/tq_v1.npz: their outputs in Triton's interpreter mode)
+and against the oracle's restatement.
+
+Bars: value codes, scale/zero and untouched bytes identical; key codes identical except where
+the rotated value sits within 1e-6 of a midpoint; key norm within one fp16 ulp of the reference
+kernel and identical to the oracle (same summation order); decode partials and outputs within
+2e-4 relative + 2e-5 absolute in fp32, the 2e-3 / 1e-3 gate for 16-bit outputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import gate, tq_v1_compare_cache
+
+pytestmark = pytest.mark.gpu
+
+CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8"]
+cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _meta(g, name):
+    return (int(v) for v in g[f"{name}_meta"])
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_store_vs_reference_kernel_and_oracle(oracle, golden, name):
+    from fused_turboquant_b200 import tq_v1
+    g = golden("tq_v1.npz")
+    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = _meta(g, name)
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
+    assert cfg.slot_size_aligned == slot
+    cache = torch.zeros((nb, bs, Hkv, slot), dtype=torch.uint8, device="cuda")
+    tq_v1.launch_store(cu(g[f"{name}_K"]), cu(g[f"{name}_V"]), cache, cu(g[f"{name}_slot_mapping"]),
+                       g[f"{name}_midpoints"], cfg, D)
+    got = cache.cpu().numpy()
+    st = tq_v1_compare_cache(got, g[f"{name}_cache"], g[f"{name}_slot_mapping"], g[f"{name}_y"],
+                             g[f"{name}_midpoints"], D, kb, vb, bs)
+    assert st["value_bytes_differ"] == 0 and st["other_bytes_differ"] == 0, st
+    assert st["key_codes_differ_off_midpoint"] == 0 and st["key_norm_max_ulp"] <= 1, st
+    ref = np.zeros_like(got)
+    oracle.tq_store(g[f"{name}_K"], g[f"{name}_V"], ref, g[f"{name}_slot_mapping"],
+                    g[f"{name}_midpoints"], kb, vb)
+    np.testing.assert_array_equal(got, ref)
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_decode_vs_reference_kernels(oracle, golden, name):
+    from fused_turboquant_b200 import tq_v1
+    g = golden("tq_v1.npz")
+    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = _meta(g, name)
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
+    B, Hq = g[f"{name}_q"].shape[:2]
+    mid_o = torch.empty((B, Hq, splits, D + 1), dtype=torch.float32, device="cuda")
+    lse = torch.empty((B, Hq), dtype=torch.float32, device="cuda")
+    out = tq_v1.decode_attention(cu(g[f"{name}_q"]), cu(g[f"{name}_cache"]), cu(g[f"{name}_block_table"]),
+                                 cu(g[f"{name}_seq_lens"]), g[f"{name}_centroids"], cfg, D ** -0.5,
+                                 num_kv_splits=splits, kv_start_offset=cu(g[f"{name}_kv_start"]),
+                                 mid_o=mid_o, lse=lse)
+    ref = g[f"{name}_mid_o"]
+    m = mid_o.cpu().numpy()
+    live = np.isfinite(ref[..., D])
+    np.testing.assert_array_equal(np.isfinite(m[..., D]), live)
+    np.testing.assert_allclose(m[..., D][live], ref[..., D][live], rtol=1e-5, atol=2e-5)
+    np.testing.assert_allclose(m[..., :D][live], ref[..., :D][live], rtol=2e-4, atol=2e-5)
+    assert np.all(m[..., :D][~live] == 0)
+    o_ref, _, lse_ref = oracle.tq_decode(g[f"{name}_q"], g[f"{name}_cache"], g[f"{name}_block_table"],
+                                         g[f"{name}_seq_lens"], g[f"{name}_centroids"], kb, vb, D ** -0.5,
+                                         splits, norm_correction=bool(nc), kv_start=g[f"{name}_kv_start"])
+    if f"{name}_out" in g.files:
+        o_ref, lse_ref = g[f"{name}_out"], g[f"{name}_lse"]
+    np.testing.assert_allclose(out.cpu().numpy(), o_ref, rtol=2e-4, atol=2e-5)
+    np.testing.assert_allclose(lse.cpu().numpy(), lse_ref, rtol=1e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,kb,vb,G,nc", [(128, 4, 4, 4, True), (64, 2, 3, 7, False), (256, 3, 8, 2, True),
+                                          (128, 3, 2, 8, False)])
+def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, dtype):
+    """Ragged batch, 16-bit inputs, values kept in the rotated space, several splits."""
+    from fused_turboquant_b200 import tq_v1
+    rng = np.random.default_rng(D + kb + vb)
+    Hkv, bs, splits = 2, 16, 5
+    seq = [1, 37, 300, 129]
+    B, Hq = len(seq), Hkv * G
+    max_blocks = max((s + bs - 1) // bs for s in seq)
+    nb = B * max_blocks + 3
+    bt = rng.permutation(nb)[:B * max_blocks].astype(np.int32).reshape(B, max_blocks)
+    slots = np.concatenate([[bt[b, t // bs] * bs + t % bs for t in range(s)] for b, s in enumerate(seq)])
+    n = len(slots)
+    K = torch.from_numpy(rng.standard_normal((n, Hkv, D)).astype(np.float32)).to(dtype)
+    V = torch.from_numpy((rng.standard_normal((n, Hkv, D)) * 2 + 0.5).astype(np.float32)).to(dtype)
+    q = torch.from_numpy(rng.standard_normal((B, Hq, D)).astype(np.float32)).to(dtype)
+    cent = np.sort(rng.standard_normal(1 << kb).astype(np.float32)) / np.sqrt(D)
+    cent_t, mids_t = tq_v1.midpoints_of(torch.from_numpy(cent))
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, nc)
+    slot = cfg.slot_size_aligned
+    cache = torch.zeros((nb, bs, Hkv, slot), dtype=torch.uint8, device="cuda")
+    tq_v1.launch_store(K.cuda(), V.cuda(), cache, torch.from_numpy(slots).cuda(), mids_t, cfg, v_rotate=True)
+    # oracle: values rotated first (plain Hadamard transform of the 16-bit inputs, kept in fp32 ->
+    # the library rounds the rotated values back to the input dtype before quantising them)
+    v_rot = torch.from_numpy(oracle.rht(V.float().numpy().reshape(-1, D), None)).to(dtype).float().numpy()
+    ref = np.zeros((nb, bs, Hkv, slot), np.uint8)
+    oracle.tq_store(K.float().numpy(), v_rot.reshape(n, Hkv, D), ref, slots, mids_t.numpy(), kb, vb)
+    np.testing.assert_array_equal(cache.cpu().numpy(), ref)
+    out = tq_v1.decode_attention(q.cuda(), cache, torch.from_numpy(bt).cuda(),
+                                 torch.tensor(seq, dtype=torch.int32).cuda(), cent_t, cfg, D ** -0.5,
+                                 num_kv_splits=splits, v_rotate=True, out_dtype=torch.float32)
+    o_ref, _, _ = oracle.tq_decode(q.float().numpy(), ref, bt, np.array(seq, np.int32), cent_t.numpy(), kb, vb,
+                                   D ** -0.5, splits, norm_correction=nc, rotate_out=True)
+    assert gate(out.cpu().numpy(), o_ref, 2e-4, 1e-4) == 0
+    out16 = tq_v1.decode_attention(q.cuda(), cache, torch.from_numpy(bt).cuda(),
+                                   torch.tensor(seq, dtype=torch.int32).cuda(), cent_t, cfg, D ** -0.5,
+                                   num_kv_splits=splits, v_rotate=True)
+    assert out16.dtype == dtype
+    assert torch.equal(out16, out.to(dtype)) or gate(out16.float().cpu().numpy(), o_ref) <= out16.numel() // 500
+
+
+def test_errors(golden):
+    from fused_turboquant_b200 import tq_v1
+    with pytest.raises(ValueError):
+        tq_v1.TurboQuantSlotConfig(96, 4, 4)
+    with pytest.raises(ValueError):
+        tq_v1.TurboQuantSlotConfig(128, 8, 4)
+    cfg = tq_v1.TurboQuantSlotConfig(128, 4, 4)
+    assert (cfg.key_packed_size, cfg.value_packed_size, cfg.slot_size_aligned) == (66, 68, 134)
+    k = torch.zeros((4, 2, 128), device="cuda")
+    cache = torch.zeros((2, 16, 2, 100), dtype=torch.uint8, device="cuda")
+    with pytest.raises(ValueError):
+        tq_v1.launch_store(k, k, cache, torch.zeros(4, dtype=torch.int64), torch.linspace(-1, 1, 15), cfg)
+    with pytest.raises(RuntimeError):
+        tq_v1.launch_store(k.cpu(), k.cpu(), cache, torch.zeros(4, dtype=torch.int64), torch.linspace(-1, 1, 15), cfg)
