@@ -333,33 +333,101 @@ tq_split_kernel(const TqDecodeParams p) {
     }
 
     const int32_t* btab = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
-    for (int ts = t0; ts < t1; ts += kTqTileTokens) {
-        const int ntile = min(kTqTileTokens, t1 - ts);
-        // slot addresses of the tile's tokens
-        if (tid < ntile) {
-            const uint32_t pos = static_cast<uint32_t>(ts + tid);
-            const uint32_t pg = fast_div(pos, p.div_block);
-            const uint32_t off = pos - pg * p.block_size;
-            slots[tid] = p.kv_cache + static_cast<int64_t>(btab[pg]) * p.stride_block +
-                         off * p.stride_pos + hkv * p.stride_head;
+    // address of the slot of position `pos` (this CTA's KV head)
+    auto slot_ptr = [&](int pos) {
+        const uint32_t pg = fast_div(static_cast<uint32_t>(pos), p.div_block);
+        const uint32_t off = static_cast<uint32_t>(pos) - pg * p.block_size;
+        return p.kv_cache + static_cast<int64_t>(btab[pg]) * p.stride_block + off * p.stride_pos +
+               hkv * p.stride_head;
+    };
+    // put 16-bit unit j of a slot where the math reads it: key codes / value codes / scalars
+    auto place_u16 = [&](int tk, int j, uint32_t v) {
+        if (j < MSE / 2) {
+            reinterpret_cast<uint16_t*>(kbuf)[tk * (MSE / 2) + j] = static_cast<uint16_t>(v);
+        } else if (j == MSE / 2) {
+            meta[tk] = __half2float(__ushort_as_half(static_cast<uint16_t>(v)));
+        } else if (j < MSE / 2 + 1 + VDB / 2) {
+            reinterpret_cast<uint16_t*>(vbuf)[tk * (VDB / 2) + j - MSE / 2 - 1] = static_cast<uint16_t>(v);
+        } else if (j < SLOT_U16) {
+            meta[(j - (MSE / 2 + VDB / 2)) * kTqTileTokens + tk] =
+                __half2float(__ushort_as_half(static_cast<uint16_t>(v)));
         }
-        __syncthreads();
-        // stage the slots (2-byte granules: slots are only 2-byte aligned), sorted into
-        // key codes / value codes / the three scalars
-        for (int idx = tid; idx < ntile * SLOT_U16; idx += kAttnThreads) {
-            const int tk = idx / SLOT_U16, j = idx - tk * SLOT_U16;
-            const uint16_t v = reinterpret_cast<const uint16_t*>(slots[tk])[j];
-            if (j < MSE / 2) {
-                reinterpret_cast<uint16_t*>(kbuf)[tk * (MSE / 2) + j] = v;
-            } else if (j == MSE / 2) {
-                meta[tk] = __half2float(__ushort_as_half(v));
-            } else if (j < MSE / 2 + 1 + VDB / 2) {
-                reinterpret_cast<uint16_t*>(vbuf)[tk * (VDB / 2) + j - MSE / 2 - 1] = v;
-            } else {
-                meta[(j - (MSE / 2 + VDB / 2)) * kTqTileTokens + tk] = __half2float(__ushort_as_half(v));
+    };
+
+    // Staging with a register prefetch: two threads per token (warps 0-1 the first half of the
+    // slot, warps 2-3 the second) load the slot as ALIGNED 32-bit words -- a slot starts on a
+    // 2-byte boundary, so the words are shifted by 16 bits for every other slot and the first /
+    // last unit is fetched on its own rather than touching bytes outside the slot.  The loads of
+    // tile i+1 are issued before the math of tile i and consumed after it.
+    constexpr int NWORDS = (MSE + VDB + 6 + 2) / 4;  // words covering the used bytes (last one half used)
+    constexpr int HW = (NWORDS + 1) / 2;             // words per thread
+    constexpr bool PREFETCH = HW <= 34;
+    uint32_t raw[PREFETCH ? HW + 1 : 1];
+    int raw_mis = 0;
+    const int ld_tk = tid & (kTqTileTokens - 1), ld_m0 = (tid >> 6) * HW;
+    auto prefetch = [&](int ts) {
+        if constexpr (PREFETCH) {
+            const bool live = ts + ld_tk < t1;
+            const uint8_t* sp = live ? slot_ptr(ts + ld_tk) : p.kv_cache;
+            raw_mis = static_cast<int>(reinterpret_cast<uintptr_t>(sp) >> 1) & 1;
+            const uint8_t* al = sp - 2 * raw_mis;
+#pragma unroll
+            for (int i = 0; i <= HW; i++) {
+                const int m = ld_m0 + i;
+                uint32_t v = 0u;
+                if (live && m < NWORDS) {
+                    if (m == 0 && raw_mis)
+                        v = static_cast<uint32_t>(__ldg(reinterpret_cast<const uint16_t*>(sp))) << 16;
+                    else if (m == NWORDS - 1 && !raw_mis)
+                        v = __ldg(reinterpret_cast<const uint16_t*>(sp + 4 * m));
+                    else
+                        v = __ldg(reinterpret_cast<const uint32_t*>(al + 4 * m));
+                }
+                raw[i] = v;
             }
         }
-        __syncthreads();
+    };
+    if constexpr (PREFETCH) prefetch(t0);
+
+    for (int ts = t0; ts < t1; ts += kTqTileTokens) {
+        const int ntile = min(kTqTileTokens, t1 - ts);
+        if constexpr (PREFETCH) {
+#pragma unroll
+            for (int i = 0; i < HW; i++) {
+                const int m = ld_m0 + i;  // word m of the slot = 16-bit units 2m, 2m + 1
+                const uint32_t w = raw_mis ? __funnelshift_r(raw[i], raw[i + 1], 16) : raw[i];
+                if (m < MSE / 4) {
+                    reinterpret_cast<uint32_t*>(kbuf)[ld_tk * (MSE / 4) + m] = w;
+                } else if (m < NWORDS) {
+                    place_u16(ld_tk, 2 * m, w & 0xffffu);
+                    place_u16(ld_tk, 2 * m + 1, w >> 16);
+                }
+            }
+            __syncthreads();
+            if (ts + kTqTileTokens < t1) prefetch(ts + kTqTileTokens);
+        } else {
+            // wide slots: plain staging, 8 loads per thread in flight
+            if (tid < ntile) slots[tid] = slot_ptr(ts + tid);
+            __syncthreads();
+            for (int base = tid; base < ntile * SLOT_U16; base += kAttnThreads * 8) {
+                uint16_t v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int idx = base + u * kAttnThreads;
+                    const int tk = idx / SLOT_U16, j = idx - tk * SLOT_U16;
+                    v[u] = idx < ntile * SLOT_U16
+                               ? __ldg(reinterpret_cast<const uint16_t*>(slots[tk]) + j) : uint16_t(0);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int idx = base + u * kAttnThreads;
+                    if (idx >= ntile * SLOT_U16) break;
+                    const int tk = idx / SLOT_U16;
+                    place_u16(tk, idx - tk * SLOT_U16, v[u]);
+                }
+            }
+            __syncthreads();
+        }
 
         const int tw = warp * 16;  // this warp's 16 tokens of the tile
         if (tw < ntile) {          // warp-uniform

@@ -127,6 +127,31 @@ class PagedKVPool:
         return out
 
 
+    def continuation_attention(self, q: torch.Tensor, block_table: torch.Tensor,
+                               seq_lens: torch.Tensor, max_seq_len: int, scale: float | None = None,
+                               layer: int = 0) -> torch.Tensor:
+        """Causal attention of ``q_len`` new tokens per sequence whose keys/values are already stored.
+
+        q: [B, q_len, Hq, D]; seq_lens: [B] totals INCLUDING the new tokens.  Query i of a sequence
+        attends positions < seq_len - q_len + i + 1.  Same device-side formulation as the reference's
+        continuation chunk (vllm_plugin/v1_backend.py:1359-1384): the decode kernel run on one
+        synthetic sequence per query with its own length; no host synchronisation.
+        """
+        B, q_len, Hq, D = q.shape
+        synth_bt, synth_sl = synthetic_decode_batch(block_table, seq_lens, q_len)
+        out = self.decode_attention(q.reshape(B * q_len, Hq, D), synth_bt, synth_sl, max_seq_len,
+                                    scale, layer=layer)
+        return out.view(B, q_len, Hq, D)
+
+
+def synthetic_decode_batch(block_table: torch.Tensor, seq_lens: torch.Tensor, q_len: int):
+    """Per-query block tables and lengths that turn a causal multi-query step into decode steps."""
+    bt = block_table.repeat_interleave(q_len, dim=0)
+    ar = torch.arange(q_len, device=seq_lens.device, dtype=seq_lens.dtype)
+    sl = (seq_lens[:, None] - (q_len - 1) + ar[None, :]).reshape(-1)
+    return bt, sl
+
+
 def v0_store(kv_cache: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
              slot_mapping: torch.Tensor, key_bits: int, value_bits: int, signs, bounds_k,
              bounds_v) -> None:

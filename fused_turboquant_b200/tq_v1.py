@@ -176,3 +176,20 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
             _ptr(mid_o), _ptr(output), _DT[output.dtype], _ptr(lse), _stream(dev))
     _lib.check(rc, "ftq_tq_decode")
     return output
+
+
+def continuation_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor,
+                           seq_lens: torch.Tensor, centroids, tq_config: TurboQuantSlotConfig,
+                           scale: float, num_kv_splits: int = 8, v_rotate: bool = False) -> torch.Tensor:
+    """Causal attention of ``q_len`` new tokens per sequence that are already in the cache.
+
+    query: [B, q_len, Hq, D]; seq_lens: [B] totals including the new tokens.  The reference's
+    continuation chunk (vllm_plugin/v1_backend.py:1359-1384): one synthetic decode sequence per
+    query with length ``cached_len + i + 1`` and the sequence's block table.
+    """
+    from .paged import synthetic_decode_batch
+    B, q_len, hq, d = query.shape
+    bt, sl = synthetic_decode_batch(block_table, seq_lens, q_len)
+    out = decode_attention(query.reshape(B * q_len, hq, d), kv_cache, bt, sl, centroids, tq_config,
+                           scale, num_kv_splits=num_kv_splits, v_rotate=v_rotate)
+    return out.view(B, q_len, hq, d)

@@ -296,3 +296,27 @@ def test_store_and_decode_are_graph_capturable(tables):
         step()                               # same step, eagerly (the store rewrites the same slot)
         torch.cuda.synchronize()
         assert torch.equal(got, out), pos
+
+
+def test_continuation_attention_is_causal_multi_query(oracle, tables):
+    """q_len new tokens per sequence, each attending only up to its own position."""
+    from fused_turboquant_b200 import PagedKVPool
+    d, Hkv, G, bk, bv, q_len = 128, 2, 4, 4, 4, 5
+    seq = np.array([40, 23], np.int32)
+    B, S = len(seq), int(seq.max())
+    max_blocks, num_blocks = (S + 15) // 16, 8
+    rng = np.random.default_rng(5)
+    _, k_idx, k_n, v_idx, v_n, signs = _rand_case(oracle, tables, B, Hkv, G, S, d, bk, bv, 21)
+    qm = rng.standard_normal((B, q_len, Hkv * G, d)).astype(np.float32)
+    bt = shuffled_block_table(rng, B, max_blocks, num_blocks)
+    kv = PagedKVPool(num_blocks, Hkv, d, bk, bv, n_layers=1)
+    kv.pool[0].copy_(torch.from_numpy(pool_from_contiguous(k_idx, k_n, v_idx, v_n, bt, num_blocks, d,
+                                                           bk, bv, seq)))
+    out = kv.continuation_attention(torch.from_numpy(qm).cuda(), torch.from_numpy(bt).cuda(),
+                                    torch.from_numpy(seq).cuda(), S)
+    assert out.shape == (B, q_len, Hkv * G, d)
+    for i in range(q_len):
+        lens = (seq - q_len + i + 1).astype(np.int32)
+        ref = oracle.decode_attn(qm[:, i], k_idx, k_n, v_idx, v_n, _lv(tables, d, bk), _lv(tables, d, bv),
+                                 signs, d ** -0.5, bk, bv, seq_lens=lens)
+        assert gate(out[:, i].cpu().numpy(), ref, 2e-4, 1e-4) == 0
