@@ -241,6 +241,15 @@ struct TqDecodeParams {
 
 constexpr int kTqTileTokens = 64;
 
+// Row stride (bytes) of a staged tile whose rows hold `bytes` of codes read in lane slices of `nb`
+// bytes: one alignment unit of padding when that lowers the bank-conflict degree of the
+// token-per-thread stores that fill the tile (degree = gcd(stride in words, 32)).
+__host__ __device__ constexpr int tq_gcd(int a, int b) { return b == 0 ? a : tq_gcd(b, a % b); }
+__host__ __device__ constexpr int tq_row_stride(int bytes, int nb) {
+    const int unit = nb % 16 == 0 ? 16 : (nb % 8 == 0 ? 8 : 4);
+    return tq_gcd((bytes + unit) / 4, 32) < tq_gcd(bytes / 4, 32) ? bytes + unit : bytes;
+}
+
 template <int D, int KB, int VB>
 __global__ void __launch_bounds__(kAttnThreads)
 tq_split_kernel(const TqDecodeParams p) {
@@ -252,12 +261,13 @@ tq_split_kernel(const TqDecodeParams p) {
     constexpr int SLOT_U16 = (MSE + 2 + VDB + 4) / 2;
 
     // tile buffers; once the loop is over the K/V areas double as the cross-warp merge area
-    constexpr int TILE_BYTES = kTqTileTokens * (MSE + VDB);
+    constexpr int KROW = tq_row_stride(MSE, NBK), VROW = tq_row_stride(VDB, NBV);
+    constexpr int TILE_BYTES = kTqTileTokens * (KROW + VROW);
     constexpr int MERGE_BYTES = 4 * GH * (D + 2) * 4;
     constexpr int BUF_BYTES = ((TILE_BYTES > MERGE_BYTES ? TILE_BYTES : MERGE_BYTES) + 15) / 16 * 16;
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    uint8_t* kbuf = smem_raw;                               // [64][MSE]
-    uint8_t* vbuf = smem_raw + kTqTileTokens * MSE;         // [64][VDB]
+    uint8_t* kbuf = smem_raw;                               // [64][KROW]
+    uint8_t* vbuf = smem_raw + kTqTileTokens * KROW;        // [64][VROW]
     float* meta = reinterpret_cast<float*>(smem_raw + BUF_BYTES);   // [3][64]: key norm, value scale, zero
     const uint8_t** slots = reinterpret_cast<const uint8_t**>(meta + 3 * kTqTileTokens);  // [64]
     float* qs = reinterpret_cast<float*>(slots + kTqTileTokens);    // [GH][D]
@@ -343,11 +353,11 @@ tq_split_kernel(const TqDecodeParams p) {
     // put 16-bit unit j of a slot where the math reads it: key codes / value codes / scalars
     auto place_u16 = [&](int tk, int j, uint32_t v) {
         if (j < MSE / 2) {
-            reinterpret_cast<uint16_t*>(kbuf)[tk * (MSE / 2) + j] = static_cast<uint16_t>(v);
+            reinterpret_cast<uint16_t*>(kbuf)[tk * (KROW / 2) + j] = static_cast<uint16_t>(v);
         } else if (j == MSE / 2) {
             meta[tk] = __half2float(__ushort_as_half(static_cast<uint16_t>(v)));
         } else if (j < MSE / 2 + 1 + VDB / 2) {
-            reinterpret_cast<uint16_t*>(vbuf)[tk * (VDB / 2) + j - MSE / 2 - 1] = static_cast<uint16_t>(v);
+            reinterpret_cast<uint16_t*>(vbuf)[tk * (VROW / 2) + j - MSE / 2 - 1] = static_cast<uint16_t>(v);
         } else if (j < SLOT_U16) {
             meta[(j - (MSE / 2 + VDB / 2)) * kTqTileTokens + tk] =
                 __half2float(__ushort_as_half(static_cast<uint16_t>(v)));
@@ -397,7 +407,7 @@ tq_split_kernel(const TqDecodeParams p) {
                 const int m = ld_m0 + i;  // word m of the slot = 16-bit units 2m, 2m + 1
                 const uint32_t w = raw_mis ? __funnelshift_r(raw[i], raw[i + 1], 16) : raw[i];
                 if (m < MSE / 4) {
-                    reinterpret_cast<uint32_t*>(kbuf)[ld_tk * (MSE / 4) + m] = w;
+                    reinterpret_cast<uint32_t*>(kbuf)[ld_tk * (KROW / 4) + m] = w;
                 } else if (m < NWORDS) {
                     place_u16(ld_tk, 2 * m, w & 0xffffu);
                     place_u16(ld_tk, 2 * m + 1, w >> 16);
@@ -436,7 +446,7 @@ tq_split_kernel(const TqDecodeParams p) {
             for (int step = 0; step < 4; step++) {
                 const int tk = tw + step * 4 + o;
                 uint32_t w[(NBK + 3) / 4];
-                load_code_bytes<NBK>(kbuf + tk * MSE + t * NBK, w);
+                load_code_bytes<NBK>(kbuf + tk * KROW + t * NBK, w);
                 float kv[E];
                 float cn = 0.f;
 #pragma unroll
@@ -487,7 +497,7 @@ tq_split_kernel(const TqDecodeParams p) {
                 const int tk = tw + step * 4 + o;
                 const bool ok = tk < ntile;
                 uint32_t w[(NBV + 3) / 4];
-                load_code_bytes<NBV>(vbuf + tk * VDB + t * NBV, w);
+                load_code_bytes<NBV>(vbuf + tk * VROW + t * NBV, w);
                 // (slots past the end of the tile hold stale bytes: keep them out of the arithmetic)
                 const float vs = ok ? meta[kTqTileTokens + tk] : 0.f;
                 const float vz = ok ? meta[2 * kTqTileTokens + tk] : 0.f;
@@ -557,7 +567,7 @@ tq_split_kernel(const TqDecodeParams p) {
 template <int D>
 constexpr int tq_split_smem_bytes(int kb, int vb) {
     const int mse = D * kb / 8, vdb = tq_value_bytes(D, vb);
-    const int tile = kTqTileTokens * (mse + vdb);
+    const int tile = kTqTileTokens * (tq_row_stride(mse, mse / kOctet) + tq_row_stride(vdb, vdb / kOctet));
     const int merge = 4 * AttnCfg<D>::GH * (D + 2) * 4;
     const int buf = ((tile > merge ? tile : merge) + 15) / 16 * 16;
     return buf + 3 * kTqTileTokens * 4 + kTqTileTokens * 8 + AttnCfg<D>::GH * D * 4 + kMaxLevels * 4;
