@@ -676,8 +676,8 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     // 16-bit queries with a GQA group of at most 8 take the tensor-core kernel; fp32 queries
     // (and larger groups) take the fp32 kernel.
     const bool mma = use_mma_path(Hq, Hkv, q_dtype);
-    // one CTA per SM when a 4-bit byte table is in use (or head_dim 256), else two
-    const int mma_ctas = (bits_k == 4 || bits_v == 4 || head_dim == 256) ? 1 : 2;
+    // one CTA per SM (16 warps) when a 4-bit byte table is in use, else two (8 warps each)
+    const int mma_ctas = (bits_k == 4 || bits_v == 4) ? 1 : 2;
     const ChunkPlan pl = mma ? plan_chunks_mma(B, Hkv, max_seq_len, n_layers, mma_ctas)
                              : plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     const size_t need = ftq_decode_workspace_bytes(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
@@ -862,7 +862,8 @@ extern "C" int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits) {
 
 extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64_t n_tokens, int Hkv,
                             int head_dim, int64_t token_stride, int64_t head_stride, int key_bits,
-                            int value_bits, const float* midpoints_host, uint8_t* kv_cache,
+                            int value_bits, int rotate_values, const float* midpoints_host,
+                            uint8_t* kv_cache,
                             int64_t stride_block, int64_t stride_pos, int64_t stride_head,
                             int block_size, const int64_t* slot_mapping, void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
@@ -870,6 +871,8 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
         return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 2..4 / 2,3,4,8)", key_bits,
                     value_bits);
     if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
+    if (rotate_values && value_bits == 8)
+        return fail(FTQ_ERR_UNSUPPORTED, "rotate_values with 8-bit values: rotate them before the call");
     if (n_tokens < 0 || Hkv <= 0 || block_size <= 0) return fail(FTQ_ERR_INVALID, "bad shape");
     if (n_tokens * Hkv >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "n_tokens * Hkv must be below 2^31");
     if (n_tokens == 0) return FTQ_OK;
@@ -906,9 +909,9 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
     const int64_t n_vec = n_tokens * Hkv;
     cudaError_t e = cudaErrorInvalidValue;
     switch (head_dim) {
-        case 64: e = ftq::launch_tq_store_d64(key_bits, value_bits, dtype, p, n_vec, st); break;
-        case 128: e = ftq::launch_tq_store_d128(key_bits, value_bits, dtype, p, n_vec, st); break;
-        case 256: e = ftq::launch_tq_store_d256(key_bits, value_bits, dtype, p, n_vec, st); break;
+        case 64: e = ftq::launch_tq_store_d64(key_bits, value_bits, dtype, p, rotate_values != 0, n_vec, st); break;
+        case 128: e = ftq::launch_tq_store_d128(key_bits, value_bits, dtype, p, rotate_values != 0, n_vec, st); break;
+        case 256: e = ftq::launch_tq_store_d256(key_bits, value_bits, dtype, p, rotate_values != 0, n_vec, st); break;
     }
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "tq_store launch");
 }

@@ -197,13 +197,6 @@ struct MmaCfg {
     static constexpr int KSB = PDK / 4, VSB = PDV / 8;  // slice bytes per lane
     static constexpr int IWK = 2 * BK, IWV = 2 * BV;    // table index width (two codes)
     static constexpr bool BYTE = BK == 4 || BV == 4;    // a 64 KB byte-indexed window is used
-    // head_dim 256 needs > 128 registers per thread: 8 warps, one CTA per SM
-#ifndef FTQ_W16
-#define FTQ_W16 16
-#endif
-    static constexpr int WARPS = (BYTE && D != 256) ? FTQ_W16 : 8;
-    static constexpr int THREADS = 32 * WARPS;
-    static constexpr int CTAS_PER_SM = (BYTE || D == 256) ? 1 : 2;
     static constexpr int OFF_KN = kPageTokens * PDK;
     static constexpr int OFF_VC = OFF_KN + 2 * kPageTokens;
     static constexpr int OFF_VN = OFF_VC + kPageTokens * PDV;
@@ -213,27 +206,43 @@ struct MmaCfg {
     static constexpr int TVS = BV == 4 ? 0 : (1 << IWV) * 128;
     static constexpr int SMALL_ALIGN = TKS > TVS ? TKS : TVS;
     static constexpr int SMALL_BYTES = TKS + TVS + SMALL_ALIGN;  // incl. alignment slack
-    // exchange area of the end-of-item merge: every warp's (O, m, l)
     static constexpr int STATE_F4 = NH * NMT;                    // float4 items per lane
-    static constexpr int XCHG_BYTES = WARPS * (32 * STATE_F4 * 16 + NH * 2 * 4 * 4);
     // per-warp ring of pages staged by bulk copies (TMA), one mbarrier per buffer
     static constexpr int RING = 2;
-    // two groups of shared-memory objects, placed first-fit around the 64 KB table window
-    // With one head half the merge exchange area gets its own space when it fits, so that the
-    // first pages of the NEXT item can already be copied into the ring while the merge runs;
-    // otherwise it aliases the ring (idle during the merge).
-    static constexpr int RING_BYTES = WARPS * RING * PAGE_BYTES;
     static constexpr int BASE_A = SMALL_BYTES + 8 * (D + 16) * 4 + kMmaMaxChunkPages * 4 + 64;
-    static constexpr int BARS = WARPS * RING * 8 + 256;
-    __host__ __device__ static constexpr int total(bool sep) {
-        const int a = BASE_A + (sep ? XCHG_BYTES + 16 : 0);
-        const int b = ((sep || RING_BYTES > XCHG_BYTES) ? RING_BYTES : XCHG_BYTES) + BARS;
+    // Shared memory needed with `w` warps.  Two groups of objects are placed first-fit around the
+    // 64 KB table window.  With one head half the merge exchange area (every warp's (O, m, l))
+    // gets its own space when it fits (`sep`), so that the first pages of the NEXT item can
+    // already be copied into the ring while the merge runs; otherwise it aliases the ring
+    // (idle during the merge).
+    __host__ __device__ static constexpr int xchg_bytes(int w) {
+        return w * (32 * STATE_F4 * 16 + NH * 2 * 4 * 4);
+    }
+    __host__ __device__ static constexpr int total_w(int w, bool sep) {
+        const int xchg = xchg_bytes(w), ring = w * RING * PAGE_BYTES, bars = w * RING * 8 + 256;
+        const int a = BASE_A + (sep ? xchg + 16 : 0);
+        const int b = ((sep || ring > xchg) ? ring : xchg) + bars;
         if (!BYTE) return a + b;
         // objects are placed first-fit before / after the 64 KB-aligned table window
         const int mn = a < b ? a : b;
         const int worst = (65536 + b > mn + a + b) ? 65536 + b : mn + a + b;
         return 65536 + worst;
     }
+    // head_dim 256 keeps the query fragments in shared memory (one 8-byte load per k-block and
+    // page) instead of 32 registers, which lets it run 16 warps per SM like head_dim 128
+    // wherever 16 page rings fit next to the byte table
+#ifndef FTQ_W16
+#define FTQ_W16 16
+#endif
+    static constexpr int WARPS = (BYTE && total_w(FTQ_W16, false) <= 227 * 1024) ? FTQ_W16 : 8;
+    // (an 8-warp CTA that owns its SM has 255 registers per thread and keeps them in registers)
+    static constexpr bool QSMEM = D == 256 && !(BYTE && WARPS == 8);
+    static constexpr int THREADS = 32 * WARPS;
+    static constexpr int CTAS_PER_SM = BYTE ? 1 : 2;
+    static constexpr int XCHG_BYTES = xchg_bytes(WARPS);
+    static constexpr int RING_BYTES = WARPS * RING * PAGE_BYTES;
+    static constexpr int BARS = WARPS * RING * 8 + 256;
+    __host__ __device__ static constexpr int total(bool sep) { return total_w(WARPS, sep); }
     static constexpr bool SEP = NH == 1 && total(true) <= 227 * 1024;
     static constexpr int GROUP_A = BASE_A + (SEP ? XCHG_BYTES + 16 : 0);
     static constexpr int GROUP_B = ((SEP || RING_BYTES > XCHG_BYTES) ? RING_BYTES : XCHG_BYTES) + BARS;
@@ -457,18 +466,46 @@ attn_mma_kernel(const AttnParams p, int n_items) {
 
         // Q^T fragments: column n = g is head 4*hh + (g >> 1); k-block kb covers coordinates
         // (D/4)*tg + 4*kb + {0,1} (b0) and + {2,3} (b1)
-        uint32_t qb[NH][NKB][2];
+        uint32_t qb[C::QSMEM ? 1 : NH][C::QSMEM ? 1 : NKB][2];
+        // shared-memory copy of the fragments (QSMEM): [hh][kb][lane] x 8 bytes, in place of the
+        // fp32 queries, which nobody reads again before the next item's prologue rewrites them
+        const uint32_t qfrag = static_cast<uint32_t>(__cvta_generic_to_shared(qs));
+        if constexpr (!C::QSMEM) {
 #pragma unroll
-        for (int hh = 0; hh < NH; hh++)
+            for (int hh = 0; hh < NH; hh++)
 #pragma unroll
-            for (int kb = 0; kb < NKB; kb++) {
-                const float4 q4 = *reinterpret_cast<const float4*>(
-                    qs + qs_index(4 * hh + (g >> 1), (D / 4) * tg + 4 * kb));
-                const __half2 lo = __floats2half2_rn(q4.x, q4.y);
-                const __half2 hi = __floats2half2_rn(q4.z, q4.w);
-                qb[hh][kb][0] = *reinterpret_cast<const uint32_t*>(&lo);
-                qb[hh][kb][1] = *reinterpret_cast<const uint32_t*>(&hi);
+                for (int kb = 0; kb < NKB; kb++) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(
+                        qs + qs_index(4 * hh + (g >> 1), (D / 4) * tg + 4 * kb));
+                    const __half2 lo = __floats2half2_rn(q4.x, q4.y);
+                    const __half2 hi = __floats2half2_rn(q4.z, q4.w);
+                    qb[hh][kb][0] = *reinterpret_cast<const uint32_t*>(&lo);
+                    qb[hh][kb][1] = *reinterpret_cast<const uint32_t*>(&hi);
+                }
+        } else {
+            constexpr int NE = NH * NKB * 32, PER = (NE + THREADS - 1) / THREADS;
+            uint2 frag[PER];
+#pragma unroll
+            for (int i = 0; i < PER; i++) {
+                const int e = tid + i * THREADS;
+                const int ln = e & 31, kb = (e >> 5) % NKB, hh = (e >> 5) / NKB;
+                if (e < NE) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(
+                        qs + qs_index(4 * hh + (ln >> 3), (D / 4) * (ln & 3) + 4 * kb));
+                    const __half2 lo = __floats2half2_rn(q4.x, q4.y);
+                    const __half2 hi = __floats2half2_rn(q4.z, q4.w);
+                    frag[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
+                                         *reinterpret_cast<const uint32_t*>(&hi));
+                }
             }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < PER; i++) {
+                const int e = tid + i * THREADS;
+                if (e < NE) reinterpret_cast<uint2*>(qs)[e] = frag[i];
+            }
+            __syncthreads();
+        }
 
         // page address = head_base + block id * blk_stride (one 32 x 32 -> 64 bit multiply-add)
         const uint8_t* head_base =
@@ -542,8 +579,14 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 const uint32_t a2 = lut32(entry_addr<C::IWK>(r.k[0], 2 * kb + 1, lk_lane));
                 const uint32_t a3 = lut32(entry_addr<C::IWK>(r.k[1], 2 * kb + 1, lk_lane));
 #pragma unroll
-                for (int hh = 0; hh < NH; hh++)
-                    mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qb[hh][kb][0], qb[hh][kb][1]);
+                for (int hh = 0; hh < NH; hh++) {
+                    if constexpr (C::QSMEM) {
+                        const uint2 qv = lds64(qfrag + ((hh * NKB + kb) * 32 + lane) * 8);
+                        mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qv.x, qv.y);
+                    } else {
+                        mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qb[hh][kb][0], qb[hh][kb][1]);
+                    }
+                }
             }
         };
 
@@ -670,7 +713,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             int pg = warp;
             // (two head halves already give the scheduler independent work and the extra live
             // registers would spill: plain order there)
-            constexpr bool kPipelined = (NH == 1 || D == 256) && WARPS <= 16;
+            constexpr bool kPipelined = (NH == 1 || (D == 256 && !C::QSMEM)) && !C::QSMEM && WARPS <= 16;
             if constexpr (!kPipelined) {
                 for (; pg < n_pages; pg += WARPS) {
                     fetch(ra, pg);

@@ -24,7 +24,7 @@
 #include <type_traits>
 
 #include "ftq_attn.cuh"
-#include "ftq_encode.cuh"
+#include "ftq_encode2.cuh"
 
 namespace ftq {
 
@@ -52,9 +52,24 @@ __device__ __forceinline__ void store_u32_as_halves(uint8_t* dst, uint32_t w) {
     reinterpret_cast<uint16_t*>(dst)[1] = static_cast<uint16_t>(w >> 16);
 }
 
-template <int D, int KB, int VB, typename T>
+// Round a value the way a tensor of the input dtype would hold it.
+template <typename T>
+__device__ __forceinline__ float round_as(float v);
+template <> __device__ __forceinline__ float round_as<float>(float v) { return v; }
+template <> __device__ __forceinline__ float round_as<__half>(float v) {
+    return __half2float(__float2half_rn(v));
+}
+template <> __device__ __forceinline__ float round_as<__nv_bfloat16>(float v) {
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// ROTV: the values are Hadamard-transformed (no signs, * 1/sqrt(D), rounded to the input dtype)
+// before they are quantised, i.e. the cache keeps them in the rotated space
+// (src/fused_turboquant/vllm_plugin/v1_backend.py:727-740 does this with a matrix product).
+template <int D, int KB, int VB, typename T, bool ROTV>
 __global__ void __launch_bounds__(256)
 tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
+    static_assert(!ROTV || VB != 8, "rotated 8-bit values are rotated by the caller");
     constexpr int E = D / kOctet;
     constexpr int NCH = E / 8;
     constexpr int MSE = D * KB / 8;
@@ -69,6 +84,8 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
     const TransposeConsts<KB> tc = transpose_consts<KB>(lane);
+    const TransposeConsts<(ROTV ? VB : 4)> tcv = transpose_consts<(ROTV ? VB : 4)>(lane);
+    (void)tcv;
 
     for (int64_t base = warp * 4; base < n_vec; base += n_warps * 4) {
         const int64_t v = base + sub;
@@ -154,7 +171,6 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
 
         // ---- value: per-vector uniform quantisation; a lane owns runs of 8 consecutive coordinates
         float vv[E];
-        float mn = INFINITY, mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < NCH; i++) {
             float tmp[8];
@@ -165,11 +181,18 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
                 for (int c = 0; c < 8; c++) tmp[c] = 0.f;
             }
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                vv[8 * i + c] = tmp[c];
-                mn = fminf(mn, tmp[c]);
-                mx = fmaxf(mx, tmp[c]);
-            }
+            for (int c = 0; c < 8; c++) vv[8 * i + c] = tmp[c];
+        }
+        if constexpr (ROTV) {
+            octet_fwht<E>(vv, lane);
+#pragma unroll
+            for (int k = 0; k < E; k++) vv[k] = round_as<T>(__fmul_rn(vv[k], p.rsqrt_d));
+        }
+        float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < E; k++) {
+            mn = fminf(mn, vv[k]);
+            mx = fmaxf(mx, vv[k]);
         }
 #pragma unroll
         for (int m = 1; m < 8; m <<= 1) {
@@ -178,35 +201,71 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
         }
         float scale = __fdiv_rn(__fsub_rn(mx, mn), static_cast<float>(VMAX));
         scale = scale > 1e-8f ? scale : 1e-8f;
+        if constexpr (!ROTV) {
 #pragma unroll
-        for (int i = 0; i < NCH; i++) {
-            uint32_t q[8];
+            for (int i = 0; i < NCH; i++) {
+                uint32_t q[8];
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const float f = __fadd_rn(__fdiv_rn(__fsub_rn(vv[8 * i + c], mn), scale), 0.5f);
-                const int qi = __float2int_rz(f);
-                q[c] = static_cast<uint32_t>(min(max(qi, 0), VMAX));
-            }
-            const int run = t + 8 * i;  // coordinates 8*run .. 8*run + 7
-            if (!store) continue;
-            uint8_t* vd = dst + KPS;
-            if constexpr (VB == 8) {
+                for (int c = 0; c < 8; c++) {
+                    const float f = __fadd_rn(__fdiv_rn(__fsub_rn(vv[8 * i + c], mn), scale), 0.5f);
+                    const int qi = __float2int_rz(f);
+                    q[c] = static_cast<uint32_t>(min(max(qi, 0), VMAX));
+                }
+                const int run = t + 8 * i;  // coordinates 8*run .. 8*run + 7
+                if (!store) continue;
+                uint8_t* vd = dst + KPS;
+                if constexpr (VB == 8) {
 #pragma unroll
-                for (int c = 0; c < 8; c += 2)
-                    reinterpret_cast<uint16_t*>(vd + 8 * run)[c >> 1] =
-                        static_cast<uint16_t>(q[c] | (q[c + 1] << 8));
-            } else {
-                uint32_t word = 0;
-#pragma unroll
-                for (int c = 0; c < 8; c++) word |= q[c] << (VB * c);
-                if constexpr (VB == 4) {
-                    store_u32_as_halves(vd + 4 * run, word);
-                } else if constexpr (VB == 2) {
-                    *reinterpret_cast<uint16_t*>(vd + 2 * run) = static_cast<uint16_t>(word);
+                    for (int c = 0; c < 8; c += 2)
+                        reinterpret_cast<uint16_t*>(vd + 8 * run)[c >> 1] =
+                            static_cast<uint16_t>(q[c] | (q[c + 1] << 8));
                 } else {
-                    vd[3 * run] = static_cast<uint8_t>(word);
-                    vd[3 * run + 1] = static_cast<uint8_t>(word >> 8);
-                    vd[3 * run + 2] = static_cast<uint8_t>(word >> 16);
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int c = 0; c < 8; c++) word |= q[c] << (VB * c);
+                    if constexpr (VB == 4) {
+                        store_u32_as_halves(vd + 4 * run, word);
+                    } else if constexpr (VB == 2) {
+                        *reinterpret_cast<uint16_t*>(vd + 2 * run) = static_cast<uint16_t>(word);
+                    } else {
+                        vd[3 * run] = static_cast<uint8_t>(word);
+                        vd[3 * run + 1] = static_cast<uint8_t>(word >> 8);
+                        vd[3 * run + 2] = static_cast<uint8_t>(word >> 16);
+                    }
+                }
+            }
+        } else {
+            // rotated values sit in the butterfly's output layout (lane l, register k = coordinate
+            // l + 8k): pack and transpose them exactly like the key codes
+            constexpr int NWV = VB == 2 ? (E + 15) / 16 : E / 8;
+            uint32_t wv[NWV];
+#pragma unroll
+            for (int i = 0; i < NWV; i++) wv[i] = 0u;
+#pragma unroll
+            for (int k = 0; k < E; k++) {
+                const float f = __fadd_rn(__fdiv_rn(__fsub_rn(vv[k], mn), scale), 0.5f);
+                const uint32_t code = static_cast<uint32_t>(min(max(__float2int_rz(f), 0), VMAX));
+                if constexpr (VB == 2) {
+                    const int pos = ((k >> 1) & 7) | ((k & 1) << 3);
+                    wv[k >> 4] |= code << (2 * pos);
+                } else {
+                    wv[k >> 3] |= code << (VB * (k & 7));
+                }
+            }
+            uint8_t* vd = dst + KPS;
+#pragma unroll
+            for (int i = 0; i < NWV; i++) {
+                const uint32_t o = octet_transpose_items<VB>(wv[i], tcv);
+                if constexpr (VB == 3) {
+                    const int g0 = (4 * t) / 3;
+                    const uint32_t lo = __shfl_sync(0xffffffffu, o, g0, 8);
+                    const uint32_t hi = __shfl_sync(0xffffffffu, o, g0 + 1, 8);
+                    const uint64_t cat = (static_cast<uint64_t>(hi) << 24) | lo;
+                    const uint32_t word = static_cast<uint32_t>(cat >> (8 * ((4 * t) % 3)));
+                    if (store && t < 6) store_u32_as_halves(vd + 4 * (6 * i + t), word);
+                } else {
+                    const int widx = t + 8 * i;
+                    if (store && widx < VDB / 4) store_u32_as_halves(vd + 4 * widx, o);
                 }
             }
         }
@@ -327,19 +386,24 @@ tq_split_kernel(const TqDecodeParams p) {
     }
     __syncthreads();
 
-    float qr[GH][E];
+    // queries and accumulators as pairs of adjacent coordinates: the dot products and the value
+    // accumulation run on Blackwell's packed fp32 FMA (two independent IEEE FMAs per instruction)
+    constexpr int EP = E / 2;
+    u64 qr[GH][EP];
 #pragma unroll
     for (int h = 0; h < GH; h++)
 #pragma unroll
-        for (int r = 0; r < E; r++) qr[h][r] = qs[h * D + t * E + r];
+        for (int i = 0; i < EP; i++)
+            qr[h][i] = pk2(qs[h * D + t * E + 2 * i], qs[h * D + t * E + 2 * i + 1]);
 
-    float m_run[GH], l_run[GH], acc[GH][E];
+    float m_run[GH], l_run[GH];
+    u64 acc[GH][EP];
 #pragma unroll
     for (int h = 0; h < GH; h++) {
         m_run[h] = -INFINITY;
         l_run[h] = 0.f;
 #pragma unroll
-        for (int r = 0; r < E; r++) acc[h][r] = 0.f;
+        for (int i = 0; i < EP; i++) acc[h][i] = pk2(0.f, 0.f);
     }
 
     const int32_t* btab = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
@@ -447,15 +511,18 @@ tq_split_kernel(const TqDecodeParams p) {
                 const int tk = tw + step * 4 + o;
                 uint32_t w[(NBK + 3) / 4];
                 load_code_bytes<NBK>(kbuf + tk * KROW + t * NBK, w);
-                float kv[E];
-                float cn = 0.f;
+                u64 kv[EP];
+                u64 cn2 = pk2(0.f, 0.f);
 #pragma unroll
-                for (int r = 0; r < E; r++) {
-                    kv[r] = lut[extract_code<KB>(w, r)];
-                    cn = fmaf(kv[r], kv[r], cn);
+                for (int i = 0; i < EP; i++) {
+                    kv[i] = pk2(lut[extract_code<KB>(w, 2 * i)], lut[extract_code<KB>(w, 2 * i + 1)]);
+                    cn2 = fma2(kv[i], kv[i], cn2);
                 }
                 float kn = meta[tk];
                 if (p.norm_correction) {  // re-normalise the centroid vector to unit length
+                    float c0, c1;
+                    upk2(cn2, c0, c1);
+                    float cn = c0 + c1;
                     cn += __shfl_xor_sync(0xffffffffu, cn, 1);
                     cn += __shfl_xor_sync(0xffffffffu, cn, 2);
                     cn += __shfl_xor_sync(0xffffffffu, cn, 4);
@@ -463,9 +530,12 @@ tq_split_kernel(const TqDecodeParams p) {
                 }
 #pragma unroll
                 for (int h = 0; h < GH; h++) {
-                    float d = 0.f;
+                    u64 d2 = pk2(0.f, 0.f);
 #pragma unroll
-                    for (int r = 0; r < E; r++) d = fmaf(qr[h][r], kv[r], d);
+                    for (int i = 0; i < EP; i++) d2 = fma2(qr[h][i], kv[i], d2);
+                    float d0, d1;
+                    upk2(d2, d0, d1);
+                    float d = d0 + d1;
                     d += __shfl_xor_sync(0xffffffffu, d, 1);
                     d += __shfl_xor_sync(0xffffffffu, d, 2);
                     d += __shfl_xor_sync(0xffffffffu, d, 4);
@@ -489,8 +559,9 @@ tq_split_kernel(const TqDecodeParams p) {
                     wp[step][h] = pe;
                 }
                 l_run[h] = l_run[h] * corr + ls;
+                const u64 corr2 = pk2(corr, corr);
 #pragma unroll
-                for (int r = 0; r < E; r++) acc[h][r] *= corr;
+                for (int i = 0; i < EP; i++) acc[h][i] = mul2(acc[h][i], corr2);
             }
 #pragma unroll
             for (int step = 0; step < 4; step++) {
@@ -501,15 +572,18 @@ tq_split_kernel(const TqDecodeParams p) {
                 // (slots past the end of the tile hold stale bytes: keep them out of the arithmetic)
                 const float vs = ok ? meta[kTqTileTokens + tk] : 0.f;
                 const float vz = ok ? meta[2 * kTqTileTokens + tk] : 0.f;
-                float vv[E];
+                const u64 vs2 = pk2(vs, vs), vz2 = pk2(vz, vz);
+                u64 vv[EP];
 #pragma unroll
-                for (int r = 0; r < E; r++)
-                    vv[r] = fmaf(static_cast<float>(extract_code<VB>(w, r)), vs, vz);
+                for (int i = 0; i < EP; i++)
+                    vv[i] = fma2(pk2(static_cast<float>(extract_code<VB>(w, 2 * i)),
+                                     static_cast<float>(extract_code<VB>(w, 2 * i + 1))), vs2, vz2);
 #pragma unroll
                 for (int h = 0; h < GH; h++) {
                     const float wgt = ok ? wp[step][h] : 0.f;
+                    const u64 wgt2 = pk2(wgt, wgt);
 #pragma unroll
-                    for (int r = 0; r < E; r++) acc[h][r] = fmaf(wgt, vv[r], acc[h][r]);
+                    for (int i = 0; i < EP; i++) acc[h][i] = fma2(wgt2, vv[i], acc[h][i]);
                 }
             }
         }
@@ -523,9 +597,9 @@ tq_split_kernel(const TqDecodeParams p) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
 #pragma unroll
-        for (int r = 0; r < E; r++) {
-            acc[h][r] += __shfl_xor_sync(0xffffffffu, acc[h][r], 8);
-            acc[h][r] += __shfl_xor_sync(0xffffffffu, acc[h][r], 16);
+        for (int i = 0; i < EP; i++) {
+            acc[h][i] = add2(acc[h][i], __shfl_xor_sync(0xffffffffu, acc[h][i], 8));
+            acc[h][i] = add2(acc[h][i], __shfl_xor_sync(0xffffffffu, acc[h][i], 16));
         }
     }
     float* wacc = reinterpret_cast<float*>(smem_raw);  // [4][GH][D]
@@ -535,7 +609,8 @@ tq_split_kernel(const TqDecodeParams p) {
 #pragma unroll
         for (int h = 0; h < GH; h++) {
 #pragma unroll
-            for (int r = 0; r < E; r++) wacc[(warp * GH + h) * D + t * E + r] = acc[h][r];
+            for (int i = 0; i < EP; i++)
+                *reinterpret_cast<u64*>(wacc + (warp * GH + h) * D + t * E + 2 * i) = acc[h][i];
             if (t == 0) {
                 wm[warp * GH + h] = m_run[h];
                 wl[warp * GH + h] = l_run[h];

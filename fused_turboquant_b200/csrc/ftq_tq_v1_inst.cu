@@ -11,41 +11,51 @@
 namespace ftq {
 
 template <int KB, int VB, typename T>
-static cudaError_t store_run(const TqStoreParams& p, int64_t n_vec, cudaStream_t stream) {
+static cudaError_t store_run(const TqStoreParams& p, bool rotate_v, int64_t n_vec, cudaStream_t stream) {
     const int64_t want = (n_vec + 31) / 32;  // 8 warps x 4 vectors per CTA pass
     const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     const unsigned gx = static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
-    tq_store_kernel<FTQ_D, KB, VB, T><<<gx, 256, 0, stream>>>(p, n_vec);
+    if constexpr (VB != 8) {
+        if (rotate_v) {
+            tq_store_kernel<FTQ_D, KB, VB, T, true><<<gx, 256, 0, stream>>>(p, n_vec);
+            return cudaGetLastError();
+        }
+    } else if (rotate_v) {
+        return cudaErrorInvalidValue;  // 8-bit values are rotated by the caller
+    }
+    tq_store_kernel<FTQ_D, KB, VB, T, false><<<gx, 256, 0, stream>>>(p, n_vec);
     return cudaGetLastError();
 }
 
 template <int KB, int VB>
-static cudaError_t store_by_dtype(int dtype, const TqStoreParams& p, int64_t n_vec, cudaStream_t s) {
+static cudaError_t store_by_dtype(int dtype, const TqStoreParams& p, bool rot, int64_t n_vec,
+                                  cudaStream_t s) {
     switch (dtype) {
-        case kF32: return store_run<KB, VB, float>(p, n_vec, s);
-        case kF16: return store_run<KB, VB, __half>(p, n_vec, s);
-        case kBF16: return store_run<KB, VB, __nv_bfloat16>(p, n_vec, s);
+        case kF32: return store_run<KB, VB, float>(p, rot, n_vec, s);
+        case kF16: return store_run<KB, VB, __half>(p, rot, n_vec, s);
+        case kBF16: return store_run<KB, VB, __nv_bfloat16>(p, rot, n_vec, s);
     }
     return cudaErrorInvalidValue;
 }
 
 template <int KB>
-static cudaError_t store_by_vb(int vb, int dtype, const TqStoreParams& p, int64_t n_vec, cudaStream_t s) {
+static cudaError_t store_by_vb(int vb, int dtype, const TqStoreParams& p, bool rot, int64_t n_vec,
+                               cudaStream_t s) {
     switch (vb) {
-        case 2: return store_by_dtype<KB, 2>(dtype, p, n_vec, s);
-        case 3: return store_by_dtype<KB, 3>(dtype, p, n_vec, s);
-        case 4: return store_by_dtype<KB, 4>(dtype, p, n_vec, s);
-        case 8: return store_by_dtype<KB, 8>(dtype, p, n_vec, s);
+        case 2: return store_by_dtype<KB, 2>(dtype, p, rot, n_vec, s);
+        case 3: return store_by_dtype<KB, 3>(dtype, p, rot, n_vec, s);
+        case 4: return store_by_dtype<KB, 4>(dtype, p, rot, n_vec, s);
+        case 8: return store_by_dtype<KB, 8>(dtype, p, rot, n_vec, s);
     }
     return cudaErrorInvalidValue;
 }
 
 cudaError_t FTQ_CAT(launch_tq_store_d, FTQ_D)(int kb, int vb, int dtype, const TqStoreParams& p,
-                                             int64_t n_vec, cudaStream_t stream) {
+                                             bool rotate_v, int64_t n_vec, cudaStream_t stream) {
     switch (kb) {
-        case 2: return store_by_vb<2>(vb, dtype, p, n_vec, stream);
-        case 3: return store_by_vb<3>(vb, dtype, p, n_vec, stream);
-        case 4: return store_by_vb<4>(vb, dtype, p, n_vec, stream);
+        case 2: return store_by_vb<2>(vb, dtype, p, rotate_v, n_vec, stream);
+        case 3: return store_by_vb<3>(vb, dtype, p, rotate_v, n_vec, stream);
+        case 4: return store_by_vb<4>(vb, dtype, p, rotate_v, n_vec, stream);
     }
     return cudaErrorInvalidValue;
 }

@@ -9,7 +9,7 @@ namespace ftq {
 
 #define FTQ_DECLARE_TQ_LAUNCHERS(DD)                                                              \
     cudaError_t launch_tq_store_d##DD(int kb, int vb, int dtype, const TqStoreParams& p,          \
-                                      int64_t n_vec, cudaStream_t stream);                        \
+                                      bool rotate_v, int64_t n_vec, cudaStream_t stream);         \
     cudaError_t launch_tq_split_d##DD(int kb, int vb, const TqDecodeParams& p, cudaStream_t stream); \
     cudaError_t launch_tq_merge_d##DD(int out_dtype, const float* mid_o, void* out, float* lse,    \
                                       int64_t n_rows, int splits, int rotate, float rsqrt_d,      \

@@ -113,7 +113,9 @@ def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
         key = key.float()
     if value.dtype != key.dtype:
         value = value.to(key.dtype)
-    if v_rotate:  # values live in the Hadamard-rotated space (undone on the decode output)
+    rotate_in_kernel = bool(v_rotate) and tq_config.value_quant_bits != 8
+    if v_rotate and not rotate_in_kernel:
+        # 8-bit values: rotate here (the kernel fuses the rotation for 2/3/4-bit values only)
         value = rht(value.float().contiguous(), None).to(key.dtype)
     if key.stride(2) != 1 or value.stride() != key.stride():
         key, value = key.contiguous(), value.contiguous()
@@ -126,8 +128,9 @@ def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
     with torch.cuda.device(key.device):
         rc = _lib.load().ftq_tq_store(
             _ptr(key), _ptr(value), _DT[key.dtype], n, hkv, d, key.stride(0), key.stride(1),
-            tq_config.key_quant_bits, tq_config.value_quant_bits, _lib.fptr(_host_table(midpoints)),
-            _ptr(kv_cache), sb, sp, sh, kv_cache.shape[1], _ptr(sm), _stream(key.device))
+            tq_config.key_quant_bits, tq_config.value_quant_bits, int(rotate_in_kernel),
+            _lib.fptr(_host_table(midpoints)), _ptr(kv_cache), sb, sp, sh, kv_cache.shape[1],
+            _ptr(sm), _stream(key.device))
     _lib.check(rc, "ftq_tq_store")
 
 

@@ -272,13 +272,15 @@ int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits);
  * min/max, scale = max((max - min) / (2^vb - 1), 1e-8), code = int((v - min) / scale + 0.5),
  * pack, fp16 scale and min.  Tokens with slot_mapping[token] < 0 are skipped.
  * key/value: [n_tokens, Hkv, head_dim] of `dtype`, strides in elements, rows 16-byte aligned.
- * midpoints_host: 2^key_bits - 1 floats, ascending.  Values are stored as given: a caller that
- * keeps values in the rotated space (TURBOQUANT_V_ROTATE) rotates them first, e.g. with ftq_rht
- * and no signs.
+ * midpoints_host: 2^key_bits - 1 floats, ascending.  rotate_values != 0 keeps the values in the
+ * rotated space (TURBOQUANT_V_ROTATE, v1_backend.py:727-740): they are Hadamard-transformed in
+ * the kernel (no signs, * 1/sqrt(D), rounded to `dtype` as the reference's tensor would be) before
+ * they are quantised; not available for value_bits = 8 (FTQ_ERR_UNSUPPORTED: rotate them first,
+ * e.g. with ftq_rht and no signs).
  */
 int ftq_tq_store(const void *key, const void *value, int dtype, int64_t n_tokens, int Hkv,
                  int head_dim, int64_t token_stride, int64_t head_stride, int key_bits,
-                 int value_bits, const float *midpoints_host, uint8_t *kv_cache,
+                 int value_bits, int rotate_values, const float *midpoints_host, uint8_t *kv_cache,
                  int64_t stride_block, int64_t stride_pos, int64_t stride_head, int block_size,
                  const int64_t *slot_mapping, void *stream);
 
