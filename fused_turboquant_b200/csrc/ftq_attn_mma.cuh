@@ -80,6 +80,12 @@ __device__ __forceinline__ uint32_t lut32(uint32_t addr) {
     return v;
 }
 
+__device__ __forceinline__ uint2 lut64(uint32_t addr) {
+    uint2 v;
+    asm("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
 // ---- mbarrier + bulk-copy (TMA, 1-D, no multicast) helpers; all addresses are shared-window
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
@@ -203,7 +209,11 @@ struct MmaCfg {
     static constexpr int PAGE_BYTES = OFF_VN + 2 * kPageTokens;
     // small (non-byte) tables, each aligned to its own size
     static constexpr int TKS = BK == 4 ? 0 : (1 << IWK) * 128;
-    static constexpr int TVS = BV == 4 ? 0 : (1 << IWV) * 128;
+    // 2-bit values next to 4-bit keys: the upper half of every row of the key's byte window holds,
+    // 16 times, the FOUR centroids of a value byte (8 bytes), so one byte-permute + one 8-byte
+    // load dequantise four codes (instead of shift/and + two 4-byte loads)
+    static constexpr bool V2BYTE = BK == 4 && BV == 2;
+    static constexpr int TVS = (BV == 4 || V2BYTE) ? 0 : (1 << IWV) * 128;
     static constexpr int SMALL_ALIGN = TKS > TVS ? TKS : TVS;
     static constexpr int SMALL_BYTES = TKS + TVS + SMALL_ALIGN;  // incl. alignment slack
     static constexpr int STATE_F4 = NH * NMT;                    // float4 items per lane
@@ -347,6 +357,11 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             } else if constexpr (BV == 4 && !SHARED_LUT) {
                 const __half2 h = __floats2half2_rn(p.lv_scaled.v[e & 15], p.lv_scaled.v[e >> 4]);
                 tb[i] = *reinterpret_cast<const uint32_t*>(&h);
+            } else if constexpr (C::V2BYTE) {
+                const int sh = 4 * (col & 1);  // word 0: codes 0, 1 of the byte; word 1: codes 2, 3
+                const __half2 h = __floats2half2_rn(p.lv_scaled.v[(e >> sh) & 3],
+                                                    p.lv_scaled.v[(e >> (sh + 2)) & 3]);
+                tb[i] = *reinterpret_cast<const uint32_t*>(&h);
             }
         }
     }
@@ -358,7 +373,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             t[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
     }
-    if constexpr (BV != 4 && !SHARED_LUT) {
+    if constexpr (BV != 4 && !SHARED_LUT && !C::V2BYTE) {
         uint32_t* t = reinterpret_cast<uint32_t*>(gptr(tv_small));
         for (int i = tid; i < (1 << C::IWV) * 32; i += THREADS) {
             const int e = i >> 5;
@@ -367,7 +382,9 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         }
     }
     const uint32_t lk_lane = (BK == 4 ? window : tk_small) | (lane * 4);
-    const uint32_t lv_lane = (BV == 4 ? (window | (SHARED_LUT ? 0u : 128u)) : tv_small) | (lane * 4);
+    const uint32_t lv_lane =
+        C::V2BYTE ? (window | 128u | ((lane & 15) * 8))
+                  : ((BV == 4 ? (window | (SHARED_LUT ? 0u : 128u)) : tv_small) | (lane * 4));
 
     // ---- once per CTA: one mbarrier per ring buffer (a single arrival + the copy's bytes)
     if (lane == 0) {
@@ -668,10 +685,18 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             for (int ks = 0; ks < 2; ks++)
 #pragma unroll
                 for (int mt = 0; mt < NMT; mt++) {
-                    const uint32_t a0 = lut32(entry_addr<C::IWV>(v[2 * ks], 2 * mt, lv_lane));
-                    const uint32_t a1 = lut32(entry_addr<C::IWV>(v[2 * ks], 2 * mt + 1, lv_lane));
-                    const uint32_t a2 = lut32(entry_addr<C::IWV>(v[2 * ks + 1], 2 * mt, lv_lane));
-                    const uint32_t a3 = lut32(entry_addr<C::IWV>(v[2 * ks + 1], 2 * mt + 1, lv_lane));
+                    uint32_t a0, a1, a2, a3;
+                    if constexpr (C::V2BYTE) {
+                        // byte mt of a token's slice = its d-pairs 2mt and 2mt + 1
+                        const uint2 lo = lut64(entry_addr<8>(v[2 * ks], mt, lv_lane));
+                        const uint2 hi = lut64(entry_addr<8>(v[2 * ks + 1], mt, lv_lane));
+                        a0 = lo.x; a1 = lo.y; a2 = hi.x; a3 = hi.y;
+                    } else {
+                        a0 = lut32(entry_addr<C::IWV>(v[2 * ks], 2 * mt, lv_lane));
+                        a1 = lut32(entry_addr<C::IWV>(v[2 * ks], 2 * mt + 1, lv_lane));
+                        a2 = lut32(entry_addr<C::IWV>(v[2 * ks + 1], 2 * mt, lv_lane));
+                        a3 = lut32(entry_addr<C::IWV>(v[2 * ks + 1], 2 * mt + 1, lv_lane));
+                    }
 #pragma unroll
                     for (int hh = 0; hh < NH; hh++)
                         mma_16816(oacc[hh][mt], a0, a1, a2, a3, pb[hh][ks][0], pb[hh][ks][1]);
