@@ -13,8 +13,9 @@
 // by it): a common rounding bias of the centroids would otherwise add up over
 // all coordinates into one output element through the inverse rotation.
 //
-// Work split: persistent CTAs (one per SM with 16 warps when a 4-bit byte table
-// is in use, else two per SM with 8 warps) loop over work items
+// Work split: persistent CTAs (one per SM when a 4-bit byte table is in use --
+// 16 warps, or 8 where 16 page rings do not fit beside the table -- else two per
+// SM with 8 warps) loop over work items
 // (KV chunk, KV head, sequence x layer); the dequantisation tables are built once
 // per CTA.  Within an item each warp walks pages warp, warp+W, ... with its own
 // online-softmax state; the states are merged pairwise (registers + a small
