@@ -968,10 +968,24 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
     p.mid_o = mid_o;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaErrorInvalidValue;
-    switch (head_dim) {
-        case 64: e = ftq::launch_tq_split_d64(key_bits, value_bits, p, st); break;
-        case 128: e = ftq::launch_tq_split_d128(key_bits, value_bits, p, st); break;
-        case 256: e = ftq::launch_tq_split_d256(key_bits, value_bits, p, st); break;
+    // 16-bit queries with a GQA group of at most 8 take the tensor-core kernel (head_dim 64 / 128,
+    // value codes of 2..4 bits); everything else the fp32 kernel
+    const int group = Hq / Hkv;
+    const bool mma = q_dtype != FTQ_F32 && group <= 8 && value_bits != 8 && head_dim != 256;
+    if (mma) {
+        const int64_t items = static_cast<int64_t>(B) * Hkv * num_kv_splits;
+        if (items >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "too many (sequence, head, split) items");
+        const int nh = group <= 4 ? 1 : 2;
+        if (head_dim == 64)
+            e = ftq::launch_tq_mma_d64(key_bits, value_bits, nh, p, static_cast<int>(items), st);
+        else
+            e = ftq::launch_tq_mma_d128(key_bits, value_bits, nh, p, static_cast<int>(items), st);
+    } else {
+        switch (head_dim) {
+            case 64: e = ftq::launch_tq_split_d64(key_bits, value_bits, p, st); break;
+            case 128: e = ftq::launch_tq_split_d128(key_bits, value_bits, p, st); break;
+            case 256: e = ftq::launch_tq_split_d256(key_bits, value_bits, p, st); break;
+        }
     }
     if (e != cudaSuccess) return cuda_fail(e, "tq_decode stage 1 launch");
     const int64_t rows = static_cast<int64_t>(B) * Hq;

@@ -1,6 +1,9 @@
 // Instantiates the vLLM-v1 slot-format kernels for one head_dim (FTQ_D).
 #include "ftq_launch.h"
 #include "ftq_tq_v1.cuh"
+#if FTQ_D != 256
+#include "ftq_tq_v1_mma.cuh"
+#endif
 
 #ifndef FTQ_D
 #error "compile with -DFTQ_D=64, 128 or 256"
@@ -87,6 +90,49 @@ cudaError_t FTQ_CAT(launch_tq_split_d, FTQ_D)(int kb, int vb, const TqDecodePara
         case 3: return split_by_vb<3>(vb, p, stream);
         case 4: return split_by_vb<4>(vb, p, stream);
     }
+    return cudaErrorInvalidValue;
+}
+
+#if FTQ_D != 256
+template <int KB, int VB, int NH>
+static cudaError_t mma_run(const TqDecodeParams& p, int n_items, cudaStream_t stream) {
+    using C = TqMmaCfg<FTQ_D, KB, VB, NH>;
+    static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory budget");
+    auto kern = tq_mma_kernel<FTQ_D, KB, VB, NH>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    const int64_t slots = static_cast<int64_t>(sm_count()) * C::CTAS_PER_SM;
+    const unsigned gx = static_cast<unsigned>(n_items < slots ? n_items : slots);
+    kern<<<gx, C::THREADS, C::SMEM_BYTES, stream>>>(p, n_items);
+    return cudaGetLastError();
+}
+
+template <int KB, int VB>
+static cudaError_t mma_by_nh(int nh, const TqDecodeParams& p, int n_items, cudaStream_t s) {
+    return nh == 1 ? mma_run<KB, VB, 1>(p, n_items, s) : mma_run<KB, VB, 2>(p, n_items, s);
+}
+
+template <int KB>
+static cudaError_t mma_by_vb(int vb, int nh, const TqDecodeParams& p, int n_items, cudaStream_t s) {
+    switch (vb) {
+        case 2: return mma_by_nh<KB, 2>(nh, p, n_items, s);
+        case 3: return mma_by_nh<KB, 3>(nh, p, n_items, s);
+        case 4: return mma_by_nh<KB, 4>(nh, p, n_items, s);
+    }
+    return cudaErrorInvalidValue;
+}
+#endif
+
+// Tensor-core stage 1 (16-bit queries, GQA group <= 8, value_bits != 8, head_dim 64 / 128).
+cudaError_t FTQ_CAT(launch_tq_mma_d, FTQ_D)(int kb, int vb, int nh, const TqDecodeParams& p,
+                                           int n_items, cudaStream_t stream) {
+#if FTQ_D != 256
+    switch (kb) {
+        case 2: return mma_by_vb<2>(vb, nh, p, n_items, stream);
+        case 3: return mma_by_vb<3>(vb, nh, p, n_items, stream);
+        case 4: return mma_by_vb<4>(vb, nh, p, n_items, stream);
+    }
+#endif
     return cudaErrorInvalidValue;
 }
 

@@ -108,12 +108,50 @@ def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, dtype):
                                  num_kv_splits=splits, v_rotate=True, out_dtype=torch.float32)
     o_ref, _, _ = oracle.tq_decode(q.float().numpy(), ref, bt, np.array(seq, np.int32), cent_t.numpy(), kb, vb,
                                    D ** -0.5, splits, norm_correction=nc, rotate_out=True)
-    assert gate(out.cpu().numpy(), o_ref, 2e-4, 1e-4) == 0
+    # 16-bit queries take the tensor-core kernel where it exists (fp16 centroids / weights, fp32
+    # accumulation): the north-star gate; 8-bit values and head_dim 256 stay on the fp32 kernel
+    if vb == 8 or D == 256:
+        assert gate(out.cpu().numpy(), o_ref, 2e-4, 1e-4) == 0
+    else:
+        assert gate(out.cpu().numpy(), o_ref) == 0, np.abs(out.cpu().numpy() - o_ref).max()
     out16 = tq_v1.decode_attention(q.cuda(), cache, torch.from_numpy(bt).cuda(),
                                    torch.tensor(seq, dtype=torch.int32).cuda(), cent_t, cfg, D ** -0.5,
                                    num_kv_splits=splits, v_rotate=True)
     assert out16.dtype == dtype
     assert torch.equal(out16, out.to(dtype)) or gate(out16.float().cpu().numpy(), o_ref) <= out16.numel() // 500
+
+
+@pytest.mark.parametrize("qdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7"])
+def test_tensor_core_decode_vs_reference_fixture(oracle, golden, name, qdtype):
+    """16-bit queries: the tensor-core stage 1 on the reference kernel's own cache bytes."""
+    from fused_turboquant_b200 import tq_v1
+    g = golden("tq_v1.npz")
+    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = _meta(g, name)
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
+    q = cu(g[f"{name}_q"]).to(qdtype)
+    B, Hq = q.shape[:2]
+    mid_o = torch.empty((B, Hq, splits, D + 1), dtype=torch.float32, device="cuda")
+    out = tq_v1.decode_attention(q, cu(g[f"{name}_cache"]), cu(g[f"{name}_block_table"]),
+                                 cu(g[f"{name}_seq_lens"]), g[f"{name}_centroids"], cfg, D ** -0.5,
+                                 num_kv_splits=splits, kv_start_offset=cu(g[f"{name}_kv_start"]),
+                                 mid_o=mid_o, out_dtype=torch.float32)
+    o_ref, m_ref, _ = oracle.tq_decode(q.float().cpu().numpy(), g[f"{name}_cache"], g[f"{name}_block_table"],
+                                       g[f"{name}_seq_lens"], g[f"{name}_centroids"], kb, vb, D ** -0.5,
+                                       splits, norm_correction=bool(nc), kv_start=g[f"{name}_kv_start"])
+    m = mid_o.cpu().numpy()
+    live = np.isfinite(m_ref[..., D])
+    np.testing.assert_array_equal(np.isfinite(m[..., D]), live)
+    assert np.all(m[..., :D][~live] == 0)
+    np.testing.assert_allclose(m[..., D][live], m_ref[..., D][live], rtol=2e-3, atol=5e-3)
+    # fp16 centroids / weights on keys with x12 outlier channels: a few elements in a thousand sit
+    # just outside the 2e-3 / 1e-3 gate in fp32 (all far inside one bf16 ulp of the output)
+    part, ref_part = m[..., :D][live], m_ref[..., :D][live]
+    assert gate(part, ref_part) <= part.size // 150, gate(part, ref_part)
+    assert np.abs(part - ref_part).max() < 8e-3
+    o = out.cpu().numpy()
+    assert gate(o, o_ref) <= o.size // 300, gate(o, o_ref)
+    assert np.abs(o - o_ref).max() < 5e-3
 
 
 def test_errors(golden):
