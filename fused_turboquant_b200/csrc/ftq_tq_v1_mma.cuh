@@ -10,11 +10,10 @@
 //
 // What differs from the page-layout kernel:
 //  * Pages do not exist in this cache: the 16 slots of a page are token-major, 134-byte-ish
-//    records that start on 2-byte boundaries, so no bulk copy can fetch them.  Two lanes per
-//    token (one for the key part, one for the value part) load it as aligned 32-bit words into
-//    registers one page ahead; at the top of an iteration the words are realigned (funnel shift
-//    by 16 bits where needed) and written into the warp's page buffer in the layout the
-//    fragment loads expect.
+//    records that start on 2-byte boundaries, so no bulk copy can fetch them.  A warp copies
+//    the 16 slots of its next page as they are -- aligned 32-bit words, consecutive lanes on
+//    consecutive words of a slot -- into registers one page ahead and from there into 16 rows of
+//    its page buffer; the fragment loads shift by a row's start offset (0 or 2 bytes).
 //  * Values are uniform codes: value = code * scale + zero.  The value table returns the (centred)
 //    fp16 integers of a byte's (or index's) two codes, the per-token scale is folded into the softmax
 //    weight and sum(p * zero) is one more scalar accumulator per head (added to every
@@ -42,17 +41,16 @@ struct TqMmaCfg {
     static constexpr int WARPS = BYTE ? 16 : 8;
     static constexpr int THREADS = 32 * WARPS;
     static constexpr int CTAS_PER_SM = BYTE ? 1 : 2;
-    // page buffer of a warp: key rows, value rows (halves exchanged for tokens with bit 1 set,
-    // as in the page-layout pool), then fp16 key norms / value scales / value zeros.  Rows whose
-    // size is a multiple of 32 bytes are padded by 16: the token-per-lane stores that fill the
-    // buffer would otherwise hit only two or four banks.
-    static constexpr int KROW = PDK % 32 == 0 ? PDK + 16 : PDK;
-    static constexpr int VROW = PDV % 32 == 0 ? PDV + 16 : PDV;
-    static constexpr int OFF_VC = kPageTokens * KROW;
-    static constexpr int OFF_KN = OFF_VC + kPageTokens * VROW;
-    static constexpr int OFF_VS = OFF_KN + 2 * kPageTokens;
-    static constexpr int OFF_VZ = OFF_VS + 2 * kPageTokens;
-    static constexpr int PAGE_BYTES = OFF_VZ + 2 * kPageTokens;
+    // Page buffer of a warp: 16 rows, row t = the aligned 32-bit words that cover token t's slot
+    // (the slot itself starts at byte 0 or 2 of the row), then the 16 alignment bits and the 16
+    // slot addresses the copy loop reads.
+    static constexpr int USED = PDK + 2 + PDV + 4;             // bytes of a slot that carry data
+    static constexpr int NWR = (USED + 2) / 4;                 // words per row (USED = 2 mod 4)
+    static constexpr int ROWB = (4 * NWR + 15) / 16 * 16;
+    static constexpr int OFF_MIS = kPageTokens * ROWB;         // u32: bit t = slot t starts 2 bytes in
+    static constexpr int OFF_AL = OFF_MIS + 16;                // u64[16]: aligned slot addresses | mis
+    static constexpr int PAGE_BYTES = OFF_AL + kPageTokens * 8 + 16;
+    static constexpr int NCOPY = (kPageTokens * NWR + 31) / 32;  // words per lane and page
     static constexpr int TKS = KB == 4 ? 0 : (1 << IWK) * 128;
     static constexpr int TVS = VB == 4 ? 0 : (1 << IWV) * 128;
     static constexpr int SMALL_ALIGN = TKS > TVS ? TKS : TVS;
@@ -102,7 +100,6 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
     const int g = lane >> 2, tg = lane & 3;
     const bool odd = g & 1;
     const int group = p.Hq / p.Hkv;  // <= 4 * NH
-    const uint32_t sel_own = odd ? 0x4432u : 0x4410u;
     const uint32_t sel_plo = odd ? 0x1044u : 0x4410u;
     const uint32_t sel_phi = odd ? 0x3244u : 0x4432u;
 
@@ -173,7 +170,6 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
     constexpr int NRED = (NH * NMT <= WARPS) ? NH * NMT : WARPS;
 
     const uint32_t my_page = bufs + warp * C::PAGE_BYTES;
-    const int ld_tk = lane & 15;
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
         const Item cur_it = item_info(item);
@@ -237,72 +233,100 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
         }
 
         const int32_t* btab = p.block_table + static_cast<int64_t>(cur_it.b) * p.max_blocks;
-        // ---- staging, one page ahead, in registers.  Lanes 0..15 fetch the KEY part of their
-        // token's slot (codes + norm, PDK + 2 bytes), lanes 16..31 the VALUE part (codes + scale +
-        // zero, PDV + 4 bytes, starting PDK + 2 bytes into the slot).  A part is a run of whole
-        // 32-bit words plus 16-bit pieces: when it starts on a 4-byte boundary the words ARE the
-        // codes and the piece after them is the norm / scale; when it starts 2 bytes off, one
-        // 16-bit piece comes first, the words are taken from 2 bytes further on and every code word
-        // straddles two of them (funnel shift by 16), the norm / scale being the upper half of the
-        // last one.  Either way every load is aligned and stays inside the slot, and both kinds of
-        // lane run the same instructions on different addresses.
-        constexpr int NWK = PDK / 4, NWV = PDV / 4, NWMAX = NWK > NWV ? NWK : NWV;
-        const bool vpart = lane >= 16;
-        const int nw = vpart ? NWV : NWK;
-        uint32_t raw[NWMAX], e1 = 0u, e2 = 0u;
-        int raw_m = 0;
+        // ---- staging, one page ahead, in registers.  The 16 slots of a page are copied word by
+        // word: lane l takes the words l, l + 32, ... of the list (token 0 words 0..NWR-1, token 1
+        // ...), so that a load instruction reads consecutive words of one or two slots.  Slots
+        // start on 2-byte boundaries; the words are taken from the 4-byte boundary at or 2 bytes
+        // before the start (both inside the cache: slots are even-sized and the cache is 4-byte
+        // aligned), except that the last, half-used word of a slot that starts ON a boundary is
+        // fetched as 16 bits (nothing past the slot is read).  Nothing is realigned here: the
+        // fragment loads below shift by the row's start offset.
+        constexpr int NWR = C::NWR, NCOPY = C::NCOPY;
+        uint32_t raw[NCOPY];
+        uint32_t mis_next = 0u;
         auto prefetch = [&](int pg) {
             if (pg >= n_pages) return;  // warp-uniform
             // tokens past the end of the range re-read the last valid slot (their weight is zero)
-            const int pos = min(t0 + pg * kPageTokens + ld_tk, t1 - 1);
+            const int pos = min(t0 + pg * kPageTokens + (lane & 15), t1 - 1);
             const uint32_t blk = fast_div(static_cast<uint32_t>(pos), p.div_block);
             const uint32_t off = static_cast<uint32_t>(pos) - blk * p.block_size;
-            const uint8_t* ps = p.kv_cache + static_cast<int64_t>(btab[blk]) * p.stride_block +
-                                off * p.stride_pos + hkv * p.stride_head + (vpart ? PDK + 2 : 0);
-            raw_m = static_cast<int>(reinterpret_cast<uintptr_t>(ps) >> 1) & 1;
-            const uint32_t* b0 = reinterpret_cast<const uint32_t*>(ps + 2 * raw_m);
-#pragma unroll
-            for (int j = 0; j < NWMAX; j++)
-                raw[j] = (NWK == NWV || j < nw) ? __ldg(b0 + j) : 0u;
-            e1 = __ldg(reinterpret_cast<const uint16_t*>(raw_m ? ps : ps + 4 * nw));
-            e2 = __ldg(reinterpret_cast<const uint16_t*>(ps + 4 * nw + (vpart ? 2 : 0)));
-        };
-        // write the prefetched part into the warp's page buffer (see TqMmaCfg for its layout)
-        auto scatter = [&]() {
-            const uint32_t row = my_page + (vpart ? C::OFF_VC + ld_tk * C::VROW : ld_tk * C::KROW);
-            // value rows: halves exchanged for tokens with bit 1 set
-            const int rot = (vpart && (ld_tk & 2)) ? NWV / 2 : 0;
-            uint32_t prev = e1 << 16;
-#pragma unroll
-            for (int j = 0; j < NWMAX; j++) {
-                const uint32_t val = raw_m ? __funnelshift_r(prev, raw[j], 16) : raw[j];
-                prev = (NWK == NWV || j < nw) ? raw[j] : prev;
-                int widx = j + rot;
-                widx = widx >= nw ? widx - nw : widx;
-                if (NWK == NWV || j < nw)
-                    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(row + 4 * widx), "r"(val));
+            const uint8_t* sp = p.kv_cache + static_cast<int64_t>(btab[blk]) * p.stride_block +
+                                off * p.stride_pos + hkv * p.stride_head;
+            const uint32_t m = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(sp) >> 1) & 1u;
+            mis_next = __ballot_sync(0xffffffffu, m != 0u) & 0xffffu;
+            __syncwarp();  // the address list of the previous prefetch has been read by every lane
+            if (lane < 16) {
+                const unsigned long long entry = (reinterpret_cast<uintptr_t>(sp) - 2 * m) | m;
+                asm volatile("st.shared.b64 [%0], %1;\n" ::"r"(my_page + C::OFF_AL + 8 * lane), "l"(entry));
             }
-            const uint32_t tail = raw_m ? prev >> 16 : e1;  // key norm / value scale
-            asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(my_page + (vpart ? C::OFF_VS : C::OFF_KN) + 2 * ld_tk),
-                         "h"(static_cast<unsigned short>(tail)));
-            if (vpart)
-                asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(my_page + C::OFF_VZ + 2 * ld_tk),
-                             "h"(static_cast<unsigned short>(e2)));
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < NCOPY; i++) {
+                const int f = 32 * i + lane;
+                const int tok = f / NWR, w = f - tok * NWR;
+                uint32_t v = 0u;
+                if (kPageTokens * NWR % 32 == 0 || f < kPageTokens * NWR) {
+                    unsigned long long entry;
+                    asm volatile("ld.shared.b64 %0, [%1];\n" : "=l"(entry) : "r"(my_page + C::OFF_AL + 8 * tok));
+                    const uint8_t* al = reinterpret_cast<const uint8_t*>(entry & ~3ull);
+                    if (w == NWR - 1 && !(entry & 1ull))
+                        v = __ldg(reinterpret_cast<const uint16_t*>(al + 4 * w));
+                    else
+                        v = __ldg(reinterpret_cast<const uint32_t*>(al + 4 * w));
+                }
+                raw[i] = v;
+            }
+        };
+        // write the prefetched words into the warp's page buffer (rows of ROWB bytes)
+        auto scatter = [&]() {
+#pragma unroll
+            for (int i = 0; i < NCOPY; i++) {
+                const int f = 32 * i + lane;
+                const int tok = f / NWR, w = f - tok * NWR;
+                if (kPageTokens * NWR % 32 == 0 || f < kPageTokens * NWR)
+                    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(my_page + tok * C::ROWB + 4 * w), "r"(raw[i]));
+            }
+            if (lane == 0) asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(my_page + C::OFF_MIS), "r"(mis_next));
+        };
+        // SB bytes at byte address `addr` (any alignment) of the page buffer -> ceil(SB/4) words
+        auto lds_bytes = [&](uint32_t addr, auto sb_tag, uint32_t* out) {
+            constexpr int SB = decltype(sb_tag)::value;
+            constexpr int NW = (SB + 3) / 4;
+            const uint32_t base = addr & ~3u, sh = 8u * (addr & 3u);
+            uint32_t wds[NW + 1];
+#pragma unroll
+            for (int j = 0; j <= NW; j++) wds[j] = lds32(base + 4 * j);
+#pragma unroll
+            for (int j = 0; j < NW; j++) out[j] = __funnelshift_r(wds[j], wds[j + 1], sh);
+        };
+        auto lds_half = [&](uint32_t addr) {
+            unsigned short h;
+            asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(h) : "r"(addr));
+            return __half2float(__ushort_as_half(h));
         };
         // every lane copies its slices of the staged page into registers (same fragment maps as
         // the page-layout kernel: K slice tg of tokens rho(g), rho(g)+2; V slice g of tokens
-        // 4tg .. 4tg+3 in lane-rotated order)
+        // 4tg .. 4tg+3 in lane-rotated order) together with the scalars of its two score rows
+        float kn_a, kn_b, vs_a, vs_b, vz_a, vz_b;
         auto read_page = [&](Regs& r) {
+            const uint32_t mis = lds32(my_page + C::OFF_MIS);
             const int ktok = 4 * (g >> 1) + (g & 1);
-            lds_slice<C::KSB>(my_page + ktok * C::KROW, tg, r.k[0]);
-            lds_slice<C::KSB>(my_page + (ktok + 2) * C::KROW, tg, r.k[1]);
+            const uint32_t rowa = my_page + ktok * C::ROWB + 2u * ((mis >> ktok) & 1u);
+            const uint32_t rowb = my_page + (ktok + 2) * C::ROWB + 2u * ((mis >> (ktok + 2)) & 1u);
+            lds_bytes(rowa + C::KSB * tg, std::integral_constant<int, C::KSB>{}, r.k[0]);
+            lds_bytes(rowb + C::KSB * tg, std::integral_constant<int, C::KSB>{}, r.k[1]);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const int u = (j + tg) & 3;
-                lds_slice<C::VSB>(my_page + C::OFF_VC + (4 * tg + u) * C::VROW, g ^ ((u & 2) << 1), r.v[j]);
+                const int tk = 4 * tg + ((j + tg) & 3);
+                const uint32_t row = my_page + tk * C::ROWB + 2u * ((mis >> tk) & 1u);
+                lds_bytes(row + PDK + 2 + C::VSB * g, std::integral_constant<int, C::VSB>{}, r.v[j]);
             }
-            r.kn = lds64(my_page + C::OFF_KN + 8 * (g >> 1));
-            r.vn = lds64(my_page + C::OFF_VS + 8 * (g >> 1));
+            kn_a = lds_half(rowa + PDK);
+            kn_b = lds_half(rowb + PDK);
+            vs_a = lds_half(rowa + PDK + 2 + PDV);
+            vs_b = lds_half(rowb + PDK + 2 + PDV);
+            vz_a = lds_half(rowa + PDK + 4 + PDV);
+            vz_b = lds_half(rowb + PDK + 4 + PDV);
         };
 
         prefetch(warp);
@@ -313,7 +337,6 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
             prefetch(pg + WARPS);
             Regs r;
             read_page(r);
-            const uint2 vzw = lds64(my_page + C::OFF_VZ + 8 * (g >> 1));
 
             // ---- S = K.Q^T (two accumulator chains per head half) and, for the norm correction,
             // the key tile times itself: its diagonal is sum_d c^2 per token
@@ -345,8 +368,7 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
             const int ntok = min(kPageTokens, t1 - t0 - pg * kPageTokens);
             const int tokA = 4 * (g >> 1) + (g & 1);
             const bool okA = tokA < ntok, okB = tokA + 2 < ntok;
-            float kna = half_bits_to_float(__byte_perm(r.kn.x, 0u, sel_own));
-            float knb = half_bits_to_float(__byte_perm(r.kn.y, 0u, sel_own));
+            float kna = kn_a, knb = kn_b;
             if (p.norm_correction) {
                 // (row g, column g) of the first product is held by lane (g, g >> 1), element g & 1;
                 // (row g + 8, column g) of the second one by the same lane, element 2 + (g & 1)
@@ -356,10 +378,10 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
                 kna *= rsqrtf(__shfl_sync(0xffffffffu, da, src) + 1e-16f);
                 knb *= rsqrtf(__shfl_sync(0xffffffffu, db, src) + 1e-16f);
             }
-            const float vsa = okA ? half_bits_to_float(__byte_perm(r.vn.x, 0u, sel_own)) : 0.f;
-            const float vsb = okB ? half_bits_to_float(__byte_perm(r.vn.y, 0u, sel_own)) : 0.f;
-            const float vza = okA ? fmaf(kCtr, vsa, half_bits_to_float(__byte_perm(vzw.x, 0u, sel_own))) : 0.f;
-            const float vzb = okB ? fmaf(kCtr, vsb, half_bits_to_float(__byte_perm(vzw.y, 0u, sel_own))) : 0.f;
+            const float vsa = okA ? vs_a : 0.f;
+            const float vsb = okB ? vs_b : 0.f;
+            const float vza = okA ? fmaf(kCtr, vsa, vz_a) : 0.f;
+            const float vzb = okB ? fmaf(kCtr, vsb, vz_b) : 0.f;
             uint32_t pb[NH][2][2];
 #pragma unroll
             for (int hh = 0; hh < NH; hh++) {
