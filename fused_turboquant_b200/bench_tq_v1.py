@@ -62,8 +62,20 @@ def main() -> None:
         del k, v
     seq_lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
     q = torch.randn((L, B, Hq, D), generator=gen, device=dev).bfloat16()
-    # enough (sequence, KV head, split) CTAs for a few waves of 148 SMs
-    splits = args.splits or max(1, min(64, (148 * 8 + B * Hkv - 1) // (B * Hkv)))
+    # smallest split count whose (sequence, KV head, split) items fill whole waves of the
+    # persistent CTAs to >= 95 % (one CTA per SM with a 4-bit table, else two)
+    slots = torch.cuda.get_device_properties(dev).multi_processor_count * (1 if 4 in (kb, vb) else 2)
+    splits = args.splits
+    if not splits:
+        best = (0.0, 1)
+        for s in range(1, 33):
+            items = B * Hkv * s
+            eff = items / (-(-items // slots) * slots)
+            if eff > best[0] + 1e-9:
+                best = (eff, s)
+            if eff >= 0.95:
+                break
+        splits = best[1]
     mid_o = torch.empty((B, Hq, splits, D + 1), dtype=torch.float32, device=dev)
     out = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=dev)
 

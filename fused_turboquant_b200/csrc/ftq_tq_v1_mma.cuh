@@ -241,9 +241,31 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
         // aligned), except that the last, half-used word of a slot that starts ON a boundary is
         // fetched as 16 bits (nothing past the slot is read).  Nothing is realigned here: the
         // fragment loads below shift by the row's start offset.
-        constexpr int NWR = C::NWR, NCOPY = C::NCOPY;
+        // Slots of 24+ words are copied one token per load instruction (lane = word; words 32, 33
+        // of all 16 tokens in one more instruction), shorter ones as a flat list of words.
+        constexpr int NWR = C::NWR;
+        constexpr bool ROWMODE = NWR >= 24;
+        constexpr int REM = ROWMODE && NWR > 32 ? NWR - 32 : 0;
+        static_assert(REM * kPageTokens <= 32, "slot too long for the copy loop");
+        constexpr int NCOPY = ROWMODE ? kPageTokens + (REM ? 1 : 0) : C::NCOPY;
         uint32_t raw[NCOPY];
         uint32_t mis_next = 0u;
+        // (token, word) that copy step i handles in this lane; word < 0: nothing
+        auto copy_slot = [&](int i, int& tok, int& w) {
+            if constexpr (ROWMODE) {
+                if (i < kPageTokens) {
+                    tok = i;
+                    w = lane < (NWR < 32 ? NWR : 32) ? lane : -1;
+                } else {
+                    tok = lane / (REM ? REM : 1);
+                    w = tok < kPageTokens ? 32 + lane % (REM ? REM : 1) : -1;
+                }
+            } else {
+                const int f = 32 * i + lane;
+                tok = f / NWR;
+                w = f < kPageTokens * NWR ? f - tok * NWR : -1;
+            }
+        };
         auto prefetch = [&](int pg) {
             if (pg >= n_pages) return;  // warp-uniform
             // tokens past the end of the range re-read the last valid slot (their weight is zero)
@@ -262,10 +284,10 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
             __syncwarp();
 #pragma unroll
             for (int i = 0; i < NCOPY; i++) {
-                const int f = 32 * i + lane;
-                const int tok = f / NWR, w = f - tok * NWR;
+                int tok, w;
+                copy_slot(i, tok, w);
                 uint32_t v = 0u;
-                if (kPageTokens * NWR % 32 == 0 || f < kPageTokens * NWR) {
+                if (w >= 0) {
                     unsigned long long entry;
                     asm volatile("ld.shared.b64 %0, [%1];\n" : "=l"(entry) : "r"(my_page + C::OFF_AL + 8 * tok));
                     const uint8_t* al = reinterpret_cast<const uint8_t*>(entry & ~3ull);
@@ -281,9 +303,9 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
         auto scatter = [&]() {
 #pragma unroll
             for (int i = 0; i < NCOPY; i++) {
-                const int f = 32 * i + lane;
-                const int tok = f / NWR, w = f - tok * NWR;
-                if (kPageTokens * NWR % 32 == 0 || f < kPageTokens * NWR)
+                int tok, w;
+                copy_slot(i, tok, w);
+                if (w >= 0)
                     asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(my_page + tok * C::ROWB + 4 * w), "r"(raw[i]));
             }
             if (lane == 0) asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(my_page + C::OFF_MIS), "r"(mis_next));
@@ -294,8 +316,14 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
             constexpr int NW = (SB + 3) / 4;
             const uint32_t base = addr & ~3u, sh = 8u * (addr & 3u);
             uint32_t wds[NW + 1];
+            if constexpr (SB == 16) {  // rows and 16-byte slices keep `base` 16-byte aligned
+                const uint4 q4 = lds128(base);
+                wds[0] = q4.x; wds[1] = q4.y; wds[2] = q4.z; wds[3] = q4.w;
+                wds[4] = lds32(base + 16);
+            } else {
 #pragma unroll
-            for (int j = 0; j <= NW; j++) wds[j] = lds32(base + 4 * j);
+                for (int j = 0; j <= NW; j++) wds[j] = lds32(base + 4 * j);
+            }
 #pragma unroll
             for (int j = 0; j < NW; j++) out[j] = __funnelshift_r(wds[j], wds[j + 1], sh);
         };
