@@ -971,7 +971,10 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
     // 16-bit queries with a GQA group of at most 8 take the tensor-core kernel (head_dim 64 / 128,
     // value codes of 2..4 bits); everything else the fp32 kernel
     const int group = Hq / Hkv;
-    const bool mma = q_dtype != FTQ_F32 && group <= 8 && value_bits != 8 && head_dim != 256;
+    // (its copy loop reads whole aligned words: a cache that starts on an odd 2-byte boundary -- a
+    // view at an offset -- stays on the fp32 kernel, which reads 2-byte pieces)
+    const bool mma = q_dtype != FTQ_F32 && group <= 8 && value_bits != 8 && head_dim != 256 &&
+                     aligned(kv_cache, 4);
     if (mma) {
         const int64_t items = static_cast<int64_t>(B) * Hkv * num_kv_splits;
         if (items >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "too many (sequence, head, split) items");

@@ -154,6 +154,30 @@ def test_tensor_core_decode_vs_reference_fixture(oracle, golden, name, qdtype):
     assert np.abs(o - o_ref).max() < 5e-3
 
 
+def test_cache_view_at_an_odd_halfword_offset(oracle, golden):
+    """A cache that starts 2 bytes past a 4-byte boundary (a view into a larger buffer)."""
+    from fused_turboquant_b200 import tq_v1
+    g = golden("tq_v1.npz")
+    name = "d128_k4v4"
+    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = _meta(g, name)
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
+    n = nb * bs * Hkv * slot
+    buf = torch.zeros(n + 4, dtype=torch.uint8, device="cuda")
+    cache = buf[2:2 + n].view(nb, bs, Hkv, slot)
+    assert cache.data_ptr() % 4 == 2
+    tq_v1.launch_store(cu(g[f"{name}_K"]), cu(g[f"{name}_V"]), cache, cu(g[f"{name}_slot_mapping"]),
+                       g[f"{name}_midpoints"], cfg, D)
+    np.testing.assert_array_equal(cache.cpu().numpy(), g[f"{name}_cache"])
+    assert int(buf[:2].sum()) == 0 and int(buf[2 + n:].sum()) == 0
+    q = cu(g[f"{name}_q"]).bfloat16()
+    args = (cu(g[f"{name}_block_table"]), cu(g[f"{name}_seq_lens"]), g[f"{name}_centroids"], cfg, D ** -0.5)
+    out = tq_v1.decode_attention(q, cache, *args, num_kv_splits=splits, out_dtype=torch.float32)
+    ref = tq_v1.decode_attention(q, cu(g[f"{name}_cache"]), *args, num_kv_splits=splits,
+                                 out_dtype=torch.float32)
+    # (the aligned copy runs the tensor-core kernel, the view the fp32 one)
+    assert gate(out.cpu().numpy(), ref.cpu().numpy()) <= out.numel() // 300
+
+
 def test_errors(golden):
     from fused_turboquant_b200 import tq_v1
     with pytest.raises(ValueError):
