@@ -154,6 +154,46 @@ def test_tensor_core_decode_vs_reference_fixture(oracle, golden, name, qdtype):
     assert np.abs(o - o_ref).max() < 5e-3
 
 
+def test_llama_shape_sampled(oracle):
+    """32 query / 8 KV heads, head_dim 128, 4-bit keys and values, 16 sequences x 8192 tokens through
+    shuffled block tables: the stored slots of sampled tokens and the decode output of sampled
+    sequences against the oracle (both decode kernels)."""
+    from fused_turboquant_b200 import tq_v1
+    D, Hkv, G, kb, vb, bs, B, ctx = 128, 8, 4, 4, 4, 16, 16, 8192
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, norm_correction=True)
+    slot = cfg.slot_size_aligned
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    nblk = B * ctx // bs
+    bt = torch.randperm(nblk, generator=gen, device="cuda").view(B, ctx // bs).to(torch.int32)
+    pos = torch.arange(ctx, device="cuda")
+    slots = (bt.long()[:, pos // bs] * bs + pos % bs).reshape(-1)
+    K = torch.randn((B * ctx, Hkv, D), generator=gen, device="cuda").bfloat16()
+    V = (torch.randn((B * ctx, Hkv, D), generator=gen, device="cuda") * 1.5 + 0.3).bfloat16()
+    cent, mids = tq_v1.midpoints_of(torch.sort(torch.randn(16, generator=gen, device="cuda")).values / D ** 0.5)
+    cache = torch.zeros((nblk, bs, Hkv, slot), dtype=torch.uint8, device="cuda")
+    tq_v1.launch_store(K, V, cache, slots, mids, cfg)
+    cache_np = cache.cpu().numpy()
+    # stored bytes of 300 sampled tokens
+    pick = torch.randperm(B * ctx, generator=gen, device="cuda")[:300].cpu().numpy()
+    ref = np.zeros_like(cache_np)
+    oracle.tq_store(K[pick].float().cpu().numpy(), V[pick].float().cpu().numpy(), ref, slots[pick].cpu().numpy(),
+                    mids.cpu().numpy(), kb, vb)
+    sl = slots[pick].cpu().numpy()
+    np.testing.assert_array_equal(cache_np[sl // bs, sl % bs], ref[sl // bs, sl % bs])
+    # decode of three sampled sequences, one of them cut short
+    q = torch.randn((B, Hkv * G, D), generator=gen, device="cuda").bfloat16()
+    seq = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    seq[5] = 4099
+    sample = [0, 5, B - 1]
+    o_ref, _, _ = oracle.tq_decode(q[sample].float().cpu().numpy(), cache_np, bt[sample].cpu().numpy(),
+                                   seq[sample].cpu().numpy(), cent.cpu().numpy(), kb, vb, D ** -0.5, 4,
+                                   norm_correction=True)
+    for qq, tol in ((q, (2e-3, 1e-3)), (q.float(), (2e-4, 1e-4))):   # tensor-core / fp32 kernel
+        out = tq_v1.decode_attention(qq, cache, bt, seq, cent, cfg, D ** -0.5, num_kv_splits=9,
+                                     out_dtype=torch.float32)
+        assert gate(out[sample].cpu().numpy(), o_ref, *tol) == 0
+
+
 def test_cache_view_at_an_odd_halfword_offset(oracle, golden):
     """A cache that starts 2 bytes past a 4-byte boundary (a view into a larger buffer)."""
     from fused_turboquant_b200 import tq_v1
