@@ -35,7 +35,7 @@ import torch  # noqa: E402
 METRIC = "tq_paged_decode_attn_hbm_gbs"
 UNIT = "GB/s"
 
-# BASELINE configs 2..5 (config 1 is the CPU-runnable parity case, not a bench line).
+# Benchmark configurations 2..5 (configuration 1 is the CPU-runnable parity case, not a bench line).
 WORKLOADS = {
     # name: layers, B, ctx, Hq, Hkv, D, bits_k, bits_v, ragged
     "cfg2": dict(desc="qwen2.5-0.5b-shaped decode, K3V3", layers=24, B=32, ctx=4096, Hq=14, Hkv=2,

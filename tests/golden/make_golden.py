@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this directory by running the REFERENCE itself.
 
-    python tests/golden/make_golden.py [--reference /path/to/reference]
+    python tests/golden/make_golden.py --reference /path/to/reference
 
 Needs the reference checkout (imported from <reference>/src, CPU only); the
 fixtures it writes are what travels: tests never import the reference.  Every
@@ -44,7 +44,7 @@ def edge_rows(d: int, gen: torch.Generator) -> torch.Tensor:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from fused_turboquant.core.hadamard import fwht, generate_rht_signs, randomized_hadamard
@@ -96,7 +96,7 @@ def main() -> None:
     np.savez_compressed(os.path.join(HERE, "encode.npz"), **enc)
     np.savez_compressed(os.path.join(HERE, "decode_dense.npz"), **dec)
 
-    # ---- composed decode attention (a reduced BASELINE config 1 and two mixed-bit cases)
+    # ---- composed decode attention (a reduced round-trip configuration and two mixed-bit cases)
     att = {}
     cases = [  # name, B, Hkv, group, S, D, bits_k, bits_v, outliers
         ("cfg1small", 1, 2, 4, 96, 128, 4, 4, True),

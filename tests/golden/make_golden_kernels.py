@@ -1,6 +1,6 @@
 """Generates kernels_interp.npz by running the REFERENCE's own GPU kernels on the CPU.
 
-    python tests/golden/make_golden_kernels.py [--reference /path/to/reference]
+    python tests/golden/make_golden_kernels.py --reference /path/to/reference
 
 The reference's device code is written in Triton; Triton's interpreter mode
 (TRITON_INTERPRET=1) executes those kernels on CPU tensors, program by program, so that the
@@ -39,7 +39,7 @@ DEC_CASES = ((64, 2), (128, 4), (256, 3))
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     import fused_turboquant.kernels.triton_attention as ta

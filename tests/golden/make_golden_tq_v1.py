@@ -1,7 +1,7 @@
 """Generates tq_v1.npz: the reference's vLLM-v1 ("TURBOQUANT" slot format) store and decode
 kernels, executed on the CPU in Triton's interpreter mode.
 
-    python tests/golden/make_golden_tq_v1.py [--reference /path/to/reference]
+    python tests/golden/make_golden_tq_v1.py --reference /path/to/reference
 
 Per case (head_dim, key bits, value bits, norm correction, kv_start) the file holds the inputs
 (K, V, q, slot mapping, block table, seq_lens, centroids, midpoints) and what the reference's
@@ -42,7 +42,7 @@ CASES = [
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from vllm.model_executor.layers.quantization.turboquant.centroids import get_centroids

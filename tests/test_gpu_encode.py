@@ -81,7 +81,7 @@ def test_encode_ragged_counts_and_shapes(oracle, tables, n):
 
 
 def test_encode_config1_full_size(oracle, tables):
-    """BASELINE config 1: K and V fp32 [1, 8, 1024, 128], 4 outlier channels per head x20, 4-bit."""
+    """Benchmark configuration 1: K and V fp32 [1, 8, 1024, 128], 4 outlier channels per head x20, 4-bit."""
     d, bits = 128, 4
     signs, bounds, _ = _tables(tables, d, bits)
     g = torch.Generator("cpu").manual_seed(20251)

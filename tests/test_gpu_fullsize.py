@@ -1,4 +1,4 @@
-"""Parity at BASELINE full sizes, through sampled oracle comparisons and size-independent
+"""Parity at the full sizes of the benchmark configurations, through sampled oracle comparisons and size-independent
 properties (determinism, independence of the physical page placement, independence of the
 split-KV chunking)."""
 import numpy as np
@@ -40,7 +40,7 @@ def test_encode_config3_layer_sampled_against_oracle(oracle, tables):
 
 @pytest.mark.parametrize("cfg", ["cfg3", "cfg2", "cfg5"])
 def test_decode_full_config_sampled_and_invariants(oracle, tables, cfg):
-    """One layer at the full batch/context of a BASELINE config: sampled sequences against the
+    """One layer at the full batch/context of a benchmark configuration: sampled sequences against the
     oracle (2e-3 / 1e-3 gate on the fp32 result), bit-identical output under a different
     physical page placement, and agreement under a different split-KV chunking."""
     from fused_turboquant_b200 import PagedKVPool
