@@ -235,21 +235,22 @@ ChunkPlan plan_chunks(int B, int Hq, int Hkv, int d, int max_seq_len, int n_laye
 
 // Chunking of the tensor-core path (persistent CTAs): few, large chunks keep the per-item
 // prologue and merge small; the chunk count is the smallest one whose item count fills the
-// CTA slots in whole waves to >= 95 % (else the best found).  Chunks hold at most 16384 tokens
-// (the block ids of a chunk are staged in shared memory) and at least 1024.
+// CTA slots in whole waves to >= 95 % (else the best found).  Chunks hold at most 8192 tokens (short
+// enough for the dynamic hand-out of items to even out ragged batches; their block ids are staged
+// in shared memory) and at least 1024.
 ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers, int ctas_per_sm) {
     ChunkPlan pl;
     pl.n_hpass = 1;
     const int64_t units = static_cast<int64_t>(B) * Hkv * n_layers;
     const int64_t slots = static_cast<int64_t>(ftq::sm_count()) * ctas_per_sm;
     const int seq = max_seq_len > 0 ? max_seq_len : 1;
-    const int c_min = (seq + 16383) / 16384;
+    const int c_min = (seq + 8191) / 8192;
     const int c_max = (seq + 1023) / 1024 > c_min ? (seq + 1023) / 1024 : c_min;
     int best_nc = c_min, best_ct = 0;
     double best_eff = -1.0;
     for (int nc = c_min; nc <= c_max && nc < c_min + 64; nc++) {
         int ct = ((seq + nc - 1) / nc + 63) / 64 * 64;
-        if (ct > 16384) ct = 16384;
+        if (ct > 8192) ct = 8192;
         const int real_nc = (seq + ct - 1) / ct;
         const int64_t items = units * real_nc;
         const int64_t waves = (items + slots - 1) / slots;
@@ -532,6 +533,9 @@ int ftq_qk_scores(const float* q_rot, const uint8_t* k_codes, const void* k_norm
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_qk_scores launch");
 }
 
+// the last bytes of a decode workspace hold the work-item counter of the tensor-core kernel
+static constexpr size_t kCounterBytes = 256;
+
 size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_seq_len,
                                   int n_layers) {
     if (!dim_ok(head_dim) || B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || n_layers <= 0) return 0;
@@ -544,7 +548,7 @@ size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_
     const size_t n2 = partial_bytes(m2, B, Hq, head_dim, n_layers);
     if (n1 > n) n = n1;
     if (n2 > n) n = n2;
-    return n;
+    return n + kCounterBytes;  // + the work-item counter of the persistent kernel
 }
 
 static int check_attn_common(int B, int Hq, int Hkv, int head_dim, int bits_k, int bits_v,
@@ -708,6 +712,9 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
         // K and V can share one table only when the scaled V levels equal the K levels
         const bool shared_lut = bits_k == bits_v &&
             memcmp(p.lk.v, p.lv_scaled.v, sizeof(float) << bits_k) == 0;
+        p.work_counter = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + need - kCounterBytes);
+        e = cudaMemsetAsync(p.work_counter, 0, sizeof(int), st);
+        if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn counter reset");
         e = dispatch_mma(head_dim, bits_k, bits_v, shared_lut, p, n_layers * B, st);
     } else {
         e = dispatch_split(head_dim, bits_k, bits_v, true, p, n_layers * B, st);

@@ -45,6 +45,7 @@ struct AttnParams {
     int cp16;                   // contiguous source: every span 16-byte aligned
     int chunk_tokens, n_chunks, n_hpass;
     float* partials;            // [L*B*Hq][n_chunks][D + 4]
+    int* work_counter;          // tensor-core path: next work item (zeroed before the launch)
     Codebook lk, lv;
     SignBits signs;
     float rsqrt_d;

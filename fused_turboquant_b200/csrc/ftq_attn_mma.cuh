@@ -424,19 +424,23 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         return p.partials +
                ((static_cast<int64_t>(it.lb) * p.Hq + it.hkv * group) * p.n_chunks + it.chunk) * ROW;
     };
-    // first non-empty item at or after `item` (CTA-uniform); empty ones get (-inf, 0) rows
-    auto skip_empty = [&](int item) {
-        while (item < n_items) {
-            const Item it = item_info(item);
-            if (it.t0 < it.t1) break;
-            if (tid < group) {
-                float* prow = partial_row(it);
-                prow[tid * prow_head_stride + D] = -INFINITY;
-                prow[tid * prow_head_stride + D + 1] = 0.f;
+    // Work items are handed out by a global counter (zeroed by the host before the launch), one
+    // at a time and in index order, so that CTAs that drew short items come back for more: with
+    // ragged batches a fixed item-to-CTA assignment leaves most SMs idle while a few finish long
+    // sequences.  Thread 0 draws; items without tokens get their (-inf, 0) rows on the spot.
+    __shared__ int s_next;
+    auto fetch_item = [&]() {  // thread 0 only
+        while (true) {
+            const int it_idx = atomicAdd(p.work_counter, 1);
+            if (it_idx >= n_items) return n_items;
+            const Item it = item_info(it_idx);
+            if (it.t0 < it.t1) return it_idx;
+            float* prow = partial_row(it);
+            for (int h = 0; h < group; h++) {
+                prow[h * prow_head_stride + D] = -INFINITY;
+                prow[h * prow_head_stride + D + 1] = 0.f;
             }
-            item += gridDim.x;
         }
-        return item;
     };
     // item prologue, run by warps [w0, w0 + nw): block ids of the chunk and the rotated,
     // pre-scaled queries (8 octets of the first two warps rotate the at most 8 heads)
@@ -474,7 +478,9 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     // left over they run the next item's prologue at the same time
     constexpr int NRED = (NH * NMT <= WARPS - 2) ? NH * NMT : WARPS;
 
-    int item = skip_empty(blockIdx.x);
+    if (tid == 0) s_next = fetch_item();
+    __syncthreads();
+    int item = s_next;
     if (item < n_items) prologue(item_info(item), 0, WARPS);
     while (item < n_items) {
         const Item cur = item_info(item);
@@ -769,9 +775,23 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             }
         }
 
-        // ---- this warp's ring is drained: request the first pages of the next item now, so that
-        // they arrive while the merge below runs (only when the merge has its own exchange area)
-        const int next = skip_empty(item + gridDim.x);
+        // ---- this CTA's next item: drawn by thread 0 once its own pages are done, known to
+        // everybody after the barrier below
+        if (tid == 0) s_next = fetch_item();
+
+        // ---- fold the warps' states: every warp publishes (m, l, O), NRED warps reduce
+#pragma unroll
+        for (int hh = 0; hh < NH; hh++) {
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
+        }
+        // a warp whose copy never arrived poisons its state (NaN propagates to the output)
+        if (stalled) m_run[0] = __int_as_float(0x7fc00000);
+        __syncthreads();  // every warp is done with the ring: it becomes the exchange area
+        const int next = s_next;
+        // request the first pages of the next item now, so that they arrive while the merge
+        // below runs (only when the merge has its own exchange area)
         primed = false;
         if constexpr (C::SEP) {
             if (next < n_items) {
@@ -785,17 +805,6 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 primed = true;
             }
         }
-
-        // ---- fold the warps' states: every warp publishes (m, l, O), NRED warps reduce
-#pragma unroll
-        for (int hh = 0; hh < NH; hh++) {
-            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
-            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
-            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
-        }
-        // a warp whose copy never arrived poisons its state (NaN propagates to the output)
-        if (stalled) m_run[0] = __int_as_float(0x7fc00000);
-        __syncthreads();  // every warp is done with the ring: it becomes the exchange area
 #pragma unroll
         for (int hh = 0; hh < NH; hh++) {
 #pragma unroll
