@@ -427,19 +427,26 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     // Work items are handed out by a global counter (zeroed by the host before the launch), one
     // at a time and in index order, so that CTAs that drew short items come back for more: with
     // ragged batches a fixed item-to-CTA assignment leaves most SMs idle while a few finish long
-    // sequences.  Thread 0 draws; items without tokens get their (-inf, 0) rows on the spot.
-    __shared__ int s_next;
-    auto fetch_item = [&]() {  // thread 0 only
+    // sequences.  Thread 0 draws a CTA's NEXT item at the start of the current one (everybody
+    // learns it at the item's first barrier, early enough to request its first pages before the
+    // merge); items without tokens get their (-inf, 0) rows on the spot.
+    __shared__ int s_next[2];  // written in alternation: a slot is read before its next write's barrier
+    int ticket = n_items;  // thread 0: counter value drawn for the next item
+    auto draw_ticket = [&]() {
+        if (tid == 0) ticket = atomicAdd(p.work_counter, 1);
+    };
+    // thread 0 only: first item with tokens at or after ticket t (further tickets drawn on demand)
+    auto resolve_ticket = [&](int t) {
         while (true) {
-            const int it_idx = atomicAdd(p.work_counter, 1);
-            if (it_idx >= n_items) return n_items;
-            const Item it = item_info(it_idx);
-            if (it.t0 < it.t1) return it_idx;
+            if (t >= n_items) return n_items;
+            const Item it = item_info(t);
+            if (it.t0 < it.t1) return t;
             float* prow = partial_row(it);
             for (int h = 0; h < group; h++) {
                 prow[h * prow_head_stride + D] = -INFINITY;
                 prow[h * prow_head_stride + D + 1] = 0.f;
             }
+            t = atomicAdd(p.work_counter, 1);
         }
     };
     // item prologue, run by warps [w0, w0 + nw): block ids of the chunk and the rotated,
@@ -478,15 +485,22 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     // left over they run the next item's prologue at the same time
     constexpr int NRED = (NH * NMT <= WARPS - 2) ? NH * NMT : WARPS;
 
-    if (tid == 0) s_next = fetch_item();
+    draw_ticket();
+    if (tid == 0) s_next[1] = resolve_ticket(ticket);
     __syncthreads();
-    int item = s_next;
+    int item = s_next[1];
+    int slot = 0;
     if (item < n_items) prologue(item_info(item), 0, WARPS);
     while (item < n_items) {
         const Item cur = item_info(item);
         const int hkv = cur.hkv, layer = cur.layer;
         const int t0 = cur.t0, t1 = cur.t1, n_pages = cur.n_pages;
+        // reserve this CTA's next item now: everybody knows it after the barrier, in time for the
+        // early page requests at the end of the main loop
+        if (tid == 0) { draw_ticket(); s_next[slot] = resolve_ticket(ticket); }
         __syncthreads();  // prologue of this item visible; ring and exchange area free
+        const int next = s_next[slot];
+        slot ^= 1;
 
         // Q^T fragments: column n = g is head 4*hh + (g >> 1); k-block kb covers coordinates
         // (D/4)*tg + 4*kb + {0,1} (b0) and + {2,3} (b1)
@@ -775,23 +789,8 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             }
         }
 
-        // ---- this CTA's next item: drawn by thread 0 once its own pages are done, known to
-        // everybody after the barrier below
-        if (tid == 0) s_next = fetch_item();
-
-        // ---- fold the warps' states: every warp publishes (m, l, O), NRED warps reduce
-#pragma unroll
-        for (int hh = 0; hh < NH; hh++) {
-            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
-            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
-            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
-        }
-        // a warp whose copy never arrived poisons its state (NaN propagates to the output)
-        if (stalled) m_run[0] = __int_as_float(0x7fc00000);
-        __syncthreads();  // every warp is done with the ring: it becomes the exchange area
-        const int next = s_next;
-        // request the first pages of the next item now, so that they arrive while the merge
-        // below runs (only when the merge has its own exchange area)
+        // ---- this warp's ring is drained: request the first pages of the next item now, so that
+        // they arrive while the merge below runs (only when the merge has its own exchange area)
         primed = false;
         if constexpr (C::SEP) {
             if (next < n_items) {
@@ -805,6 +804,17 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 primed = true;
             }
         }
+
+        // ---- fold the warps' states: every warp publishes (m, l, O), NRED warps reduce
+#pragma unroll
+        for (int hh = 0; hh < NH; hh++) {
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
+            l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
+        }
+        // a warp whose copy never arrived poisons its state (NaN propagates to the output)
+        if (stalled) m_run[0] = __int_as_float(0x7fc00000);
+        __syncthreads();  // every warp is done with the ring: it becomes the exchange area
 #pragma unroll
         for (int hh = 0; hh < NH; hh++) {
 #pragma unroll
