@@ -194,6 +194,63 @@ def test_llama_shape_sampled(oracle):
         assert gate(out[sample].cpu().numpy(), o_ref, *tol) == 0
 
 
+@pytest.mark.parametrize("qdtype", [torch.bfloat16, torch.float32])
+def test_store_and_decode_are_graph_capturable(qdtype):
+    """A decode step (store of the new token, attention with pre-allocated partials and output)
+    replays from a CUDA graph with fresh inputs: no allocation and no host synchronisation
+    inside the two calls -- what the reference needs from its per-layer buffers
+    (vllm_plugin/v1_backend.py:1852-1866)."""
+    from fused_turboquant_b200 import tq_v1
+    dev = torch.device("cuda")
+    B, Hkv, G, D, bs, splits = 4, 2, 4, 128, 16, 3
+    cfg = tq_v1.TurboQuantSlotConfig(D, 4, 4, norm_correction=True)
+    max_blocks = 20
+    g = torch.Generator("cpu").manual_seed(9)
+    bt = torch.randperm(B * max_blocks, generator=g).view(B, max_blocks).to(torch.int32).to(dev)
+    cache = torch.zeros((B * max_blocks, bs, Hkv, cfg.slot_size_aligned), dtype=torch.uint8, device=dev)
+    cent, mids = tq_v1.midpoints_of(torch.sort(torch.randn(16, generator=g)).values / D ** 0.5)
+    ctx = 200
+    kf = torch.randn(B * ctx, Hkv, D, generator=g).bfloat16().to(dev)
+    slots = torch.cat([bt[b, torch.arange(ctx, device=dev) // bs].long() * bs +
+                       torch.arange(ctx, device=dev) % bs for b in range(B)])
+    tq_v1.launch_store(kf, kf, cache, slots, mids, cfg, v_rotate=True)
+    k_new = torch.zeros(B, Hkv, D, dtype=torch.bfloat16, device=dev)
+    v_new = torch.zeros_like(k_new)
+    q = torch.zeros(B, Hkv * G, D, dtype=qdtype, device=dev)
+    out = torch.zeros_like(q)
+    mid_o = torch.zeros(B, Hkv * G, splits, D + 1, dtype=torch.float32, device=dev)
+    lse = torch.zeros(B, Hkv * G, dtype=torch.float32, device=dev)
+    slot_new = torch.zeros(B, dtype=torch.int64, device=dev)
+    seq_lens = torch.zeros(B, dtype=torch.int32, device=dev)
+
+    def step():
+        tq_v1.launch_store(k_new, v_new, cache, slot_new, mids, cfg, v_rotate=True)
+        tq_v1.decode_attention(q, cache, bt, seq_lens, cent, cfg, D ** -0.5, num_kv_splits=splits,
+                               v_rotate=True, mid_o=mid_o, output=out, lse=lse)
+
+    def set_inputs(pos, seed):
+        gg = torch.Generator("cpu").manual_seed(seed)
+        k_new.copy_(torch.randn(B, Hkv, D, generator=gg).bfloat16())
+        v_new.copy_(torch.randn(B, Hkv, D, generator=gg).bfloat16())
+        q.copy_(torch.randn(B, Hkv * G, D, generator=gg).to(qdtype))
+        slot_new.copy_(bt[:, pos // bs].long() * bs + pos % bs)
+        seq_lens.fill_(pos + 1)
+
+    set_inputs(ctx, 1)
+    step()                                   # warm-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for i, pos in enumerate((ctx, ctx + 1, ctx + 2)):
+        set_inputs(pos, 100 + i)
+        graph.replay()
+        got = out.clone()
+        step()                               # same step, eagerly (the store rewrites the same slot)
+        torch.cuda.synchronize()
+        assert torch.equal(got, out), pos
+
+
 def test_cache_view_at_an_odd_halfword_offset(oracle, golden):
     """A cache that starts 2 bytes past a 4-byte boundary (a view into a larger buffer)."""
     from fused_turboquant_b200 import tq_v1
