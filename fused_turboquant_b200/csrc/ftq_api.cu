@@ -857,7 +857,7 @@ extern "C" int ftq_paged_decode_attn_static(
 // ------------------------------------------------------------------ vLLM-v1 slot format
 
 namespace {
-bool tq_bits_ok(int kb, int vb) { return kb >= 2 && kb <= 4 && (vb == 2 || vb == 3 || vb == 4 || vb == 8); }
+bool tq_bits_ok(int kb, int vb) { return kb >= 1 && kb <= 4 && ((vb >= 1 && vb <= 4) || vb == 8); }
 bool even(int64_t v) { return (v & 1) == 0; }
 }  // namespace
 
@@ -875,7 +875,7 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
                             int block_size, const int64_t* slot_mapping, void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
-        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 2..4 / 2,3,4,8)", key_bits,
+        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 / 1,2,3,4,8)", key_bits,
                     value_bits);
     if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
     if (rotate_values && value_bits == 8)
@@ -932,7 +932,7 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
                              float* mid_o, void* out, int out_dtype, float* lse, void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
-        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 2..4 / 2,3,4,8)", key_bits,
+        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 / 1,2,3,4,8)", key_bits,
                     value_bits);
     if (!dtype_ok(q_dtype) || !dtype_ok(out_dtype)) return fail(FTQ_ERR_INVALID, "bad dtype");
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || block_size <= 0 || max_blocks <= 0)
@@ -976,12 +976,12 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaErrorInvalidValue;
     // 16-bit queries with a GQA group of at most 8 take the tensor-core kernel (head_dim 64 / 128,
-    // value codes of 2..4 bits); everything else the fp32 kernel
+    // key and value codes of 2..4 bits); everything else the fp32 kernel
     const int group = Hq / Hkv;
     // (its copy loop reads whole aligned words: a cache that starts on an odd 2-byte boundary -- a
     // view at an offset -- stays on the fp32 kernel, which reads 2-byte pieces)
-    const bool mma = q_dtype != FTQ_F32 && group <= 8 && value_bits != 8 && head_dim != 256 &&
-                     aligned(kv_cache, 4);
+    const bool mma = q_dtype != FTQ_F32 && group <= 8 && key_bits >= 2 && value_bits >= 2 &&
+                     value_bits != 8 && head_dim != 256 && aligned(kv_cache, 4);
     if (mma) {
         const int64_t items = static_cast<int64_t>(B) * Hkv * num_kv_splits;
         if (items >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "too many (sequence, head, split) items");

@@ -104,9 +104,11 @@ __device__ __forceinline__ void load_code_bytes(const uint8_t* p, uint32_t (&w)[
     } else if constexpr (NB == 3) {
         w[0] = static_cast<uint32_t>(p[0]) | (static_cast<uint32_t>(p[1]) << 8) |
                (static_cast<uint32_t>(p[2]) << 16);
-    } else {
-        static_assert(NB == 2, "unsupported slice size");
+    } else if constexpr (NB == 2) {
         w[0] = *reinterpret_cast<const uint16_t*>(p);
+    } else {
+        static_assert(NB == 1, "unsupported slice size");
+        w[0] = p[0];
     }
 }
 

@@ -28,7 +28,7 @@
 
 namespace ftq {
 
-constexpr int kTqMaxMid = 15;  // key codes of 2..4 bits
+constexpr int kTqMaxMid = 15;  // key codes of 1..4 bits
 
 struct TqStoreParams {
     const void* key;       // [n_tokens, Hkv, D], strides in elements
@@ -50,6 +50,26 @@ __host__ __device__ constexpr int tq_value_bytes(int d, int vb) { return vb == 8
 __device__ __forceinline__ void store_u32_as_halves(uint8_t* dst, uint32_t w) {
     reinterpret_cast<uint16_t*>(dst)[0] = static_cast<uint16_t>(w);
     reinterpret_cast<uint16_t*>(dst)[1] = static_cast<uint16_t>(w >> 16);
+}
+
+// 1-bit codes of a vector in the butterfly's output layout (lane l of the octet, register k =
+// coordinate l + 8k; bit k of `mine` is this lane's code of register k): byte k of the packed
+// codes is the octet's ballot of register k (coordinate 8k + j in bit j, as
+// triton_inkernel_store.py:138-146 packs them).  Called by all 32 lanes.
+template <int E>
+__device__ __forceinline__ void emit_bits1(uint32_t mine, uint8_t* dst, bool store, int lane) {
+    const int t = lane & 7, sub = lane >> 3;
+    uint32_t wd[E / 4];
+#pragma unroll
+    for (int i = 0; i < E / 4; i++) wd[i] = 0u;
+#pragma unroll
+    for (int k = 0; k < E; k++) {
+        const uint32_t b = (__ballot_sync(0xffffffffu, (mine >> k) & 1u) >> (8 * sub)) & 0xffu;
+        wd[k >> 2] |= b << (8 * (k & 3));
+    }
+#pragma unroll
+    for (int j = 0; j < E / 4; j++)
+        if (store && t == j) store_u32_as_halves(dst + 4 * j, wd[j]);
 }
 
 // Round a value the way a tensor of the input dtype would hold it.
@@ -77,14 +97,17 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
     constexpr int VDB = tq_value_bytes(D, VB);
     constexpr int VMAX = (1 << VB) - 1;
     constexpr int NMID = (1 << KB) - 1;
-    constexpr int NW = KB == 2 ? (E + 15) / 16 : E / 8;
+    constexpr int NW = KB == 2 ? (E + 15) / 16 : E / 8;  // (unused for 1-bit codes)
+    constexpr int KT = KB == 1 ? 2 : KB;                 // transposition constants: 2..4 bits only
+    constexpr int VT = (ROTV && VB != 1) ? VB : 4;
 
     const int lane = threadIdx.x & 31;
     const int t = lane & 7, sub = lane >> 3;
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-    const TransposeConsts<KB> tc = transpose_consts<KB>(lane);
-    const TransposeConsts<(ROTV ? VB : 4)> tcv = transpose_consts<(ROTV ? VB : 4)>(lane);
+    const TransposeConsts<KT> tc = transpose_consts<KT>(lane);
+    const TransposeConsts<VT> tcv = transpose_consts<VT>(lane);
+    (void)tc;
     (void)tcv;
 
     for (int64_t base = warp * 4; base < n_vec; base += n_warps * 4) {
@@ -144,16 +167,19 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
             uint32_t code = 0;
 #pragma unroll
             for (int j = 0; j < NMID; j++) code += (yv >= p.midpoints[j]) ? 1u : 0u;
-            if constexpr (KB == 2) {
+            if constexpr (KB == 1) {
+                w[0] |= code << k;
+            } else if constexpr (KB == 2) {
                 const int pos = ((k >> 1) & 7) | ((k & 1) << 3);
                 w[k >> 4] |= code << (2 * pos);
             } else {
                 w[k >> 3] |= code << (KB * (k & 7));
             }
         }
+        if constexpr (KB == 1) emit_bits1<E>(w[0], dst, store, lane);
 #pragma unroll
-        for (int i = 0; i < NW; i++) {
-            const uint32_t o = octet_transpose_items<KB>(w[i], tc);
+        for (int i = 0; i < (KB == 1 ? 0 : NW); i++) {
+            const uint32_t o = octet_transpose_items<KT>(w[i], tc);
             if constexpr (KB == 3) {
                 const int g0 = (4 * t) / 3;
                 const uint32_t lo = __shfl_sync(0xffffffffu, o, g0, 8);
@@ -225,6 +251,8 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
                     for (int c = 0; c < 8; c++) word |= q[c] << (VB * c);
                     if constexpr (VB == 4) {
                         store_u32_as_halves(vd + 4 * run, word);
+                    } else if constexpr (VB == 1) {
+                        vd[run] = static_cast<uint8_t>(word);
                     } else if constexpr (VB == 2) {
                         *reinterpret_cast<uint16_t*>(vd + 2 * run) = static_cast<uint16_t>(word);
                     } else {
@@ -245,7 +273,9 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
             for (int k = 0; k < E; k++) {
                 const float f = __fadd_rn(__fdiv_rn(__fsub_rn(vv[k], mn), scale), 0.5f);
                 const uint32_t code = static_cast<uint32_t>(min(max(__float2int_rz(f), 0), VMAX));
-                if constexpr (VB == 2) {
+                if constexpr (VB == 1) {
+                    wv[0] |= code << k;
+                } else if constexpr (VB == 2) {
                     const int pos = ((k >> 1) & 7) | ((k & 1) << 3);
                     wv[k >> 4] |= code << (2 * pos);
                 } else {
@@ -253,9 +283,10 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
                 }
             }
             uint8_t* vd = dst + KPS;
+            if constexpr (VB == 1) emit_bits1<E>(wv[0], vd, store, lane);
 #pragma unroll
-            for (int i = 0; i < NWV; i++) {
-                const uint32_t o = octet_transpose_items<VB>(wv[i], tcv);
+            for (int i = 0; i < (VB == 1 ? 0 : NWV); i++) {
+                const uint32_t o = octet_transpose_items<VT>(wv[i], tcv);
                 if constexpr (VB == 3) {
                     const int g0 = (4 * t) / 3;
                     const uint32_t lo = __shfl_sync(0xffffffffu, o, g0, 8);

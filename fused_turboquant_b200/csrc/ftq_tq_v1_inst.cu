@@ -45,6 +45,7 @@ template <int KB>
 static cudaError_t store_by_vb(int vb, int dtype, const TqStoreParams& p, bool rot, int64_t n_vec,
                                cudaStream_t s) {
     switch (vb) {
+        case 1: return store_by_dtype<KB, 1>(dtype, p, rot, n_vec, s);
         case 2: return store_by_dtype<KB, 2>(dtype, p, rot, n_vec, s);
         case 3: return store_by_dtype<KB, 3>(dtype, p, rot, n_vec, s);
         case 4: return store_by_dtype<KB, 4>(dtype, p, rot, n_vec, s);
@@ -56,6 +57,7 @@ static cudaError_t store_by_vb(int vb, int dtype, const TqStoreParams& p, bool r
 cudaError_t FTQ_CAT(launch_tq_store_d, FTQ_D)(int kb, int vb, int dtype, const TqStoreParams& p,
                                              bool rotate_v, int64_t n_vec, cudaStream_t stream) {
     switch (kb) {
+        case 1: return store_by_vb<1>(vb, dtype, p, rotate_v, n_vec, stream);
         case 2: return store_by_vb<2>(vb, dtype, p, rotate_v, n_vec, stream);
         case 3: return store_by_vb<3>(vb, dtype, p, rotate_v, n_vec, stream);
         case 4: return store_by_vb<4>(vb, dtype, p, rotate_v, n_vec, stream);
@@ -75,6 +77,7 @@ static cudaError_t split_run(const TqDecodeParams& p, cudaStream_t stream) {
 template <int KB>
 static cudaError_t split_by_vb(int vb, const TqDecodeParams& p, cudaStream_t s) {
     switch (vb) {
+        case 1: return split_run<KB, 1>(p, s);
         case 2: return split_run<KB, 2>(p, s);
         case 3: return split_run<KB, 3>(p, s);
         case 4: return split_run<KB, 4>(p, s);
@@ -86,6 +89,7 @@ static cudaError_t split_by_vb(int vb, const TqDecodeParams& p, cudaStream_t s) 
 cudaError_t FTQ_CAT(launch_tq_split_d, FTQ_D)(int kb, int vb, const TqDecodeParams& p,
                                              cudaStream_t stream) {
     switch (kb) {
+        case 1: return split_by_vb<1>(vb, p, stream);
         case 2: return split_by_vb<2>(vb, p, stream);
         case 3: return split_by_vb<3>(vb, p, stream);
         case 4: return split_by_vb<4>(vb, p, stream);

@@ -29,17 +29,17 @@ class TurboQuantSlotConfig:
     """Slot layout of one (token, KV head): key codes | key norm f16 | value codes | scale f16 | zero f16."""
 
     head_dim: int
-    key_quant_bits: int       # 2..4: Lloyd-Max codes
-    value_quant_bits: int     # 2, 3, 4 or 8: per-vector uniform codes
+    key_quant_bits: int       # 1..4: Lloyd-Max codes
+    value_quant_bits: int     # 1, 2, 3, 4 or 8: per-vector uniform codes
     norm_correction: bool = True
 
     def __post_init__(self):
         if self.head_dim not in (64, 128, 256):
             raise ValueError(f"head_dim must be 64, 128 or 256, got {self.head_dim}")
-        if self.key_quant_bits not in (2, 3, 4):
-            raise ValueError(f"key_quant_bits must be 2, 3 or 4, got {self.key_quant_bits}")
-        if self.value_quant_bits not in (2, 3, 4, 8):
-            raise ValueError(f"value_quant_bits must be 2, 3, 4 or 8, got {self.value_quant_bits}")
+        if self.key_quant_bits not in (1, 2, 3, 4):
+            raise ValueError(f"key_quant_bits must be 1, 2, 3 or 4, got {self.key_quant_bits}")
+        if self.value_quant_bits not in (1, 2, 3, 4, 8):
+            raise ValueError(f"value_quant_bits must be 1, 2, 3, 4 or 8, got {self.value_quant_bits}")
 
     key_fp8 = False
 
@@ -115,7 +115,7 @@ def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
         value = value.to(key.dtype)
     rotate_in_kernel = bool(v_rotate) and tq_config.value_quant_bits != 8
     if v_rotate and not rotate_in_kernel:
-        # 8-bit values: rotate here (the kernel fuses the rotation for 2/3/4-bit values only)
+        # 8-bit values: rotate here (the kernel fuses the rotation for 1..4-bit values only)
         value = rht(value.float().contiguous(), None).to(key.dtype)
     if key.stride(2) != 1 or value.stride() != key.stride():
         key, value = key.contiguous(), value.contiguous()

@@ -258,8 +258,8 @@ int ftq_v0_gather(const uint8_t *kv_cache, int64_t num_blocks, int block_size, i
  * be even.  A slot holds
  *     [key codes D*kb/8 | key norm f16 | value codes D*vb/8 (D for vb = 8) | scale f16 | zero f16]
  * (vllm_plugin/boundary_tq_config.py:66-81; ftq_tq_slot_bytes returns its size rounded
- * up to even).  Supported: head_dim 64/128/256, key_bits 2/3/4 (Lloyd-Max codes),
- * value_bits 2/3/4/8 (per-vector uniform codes).  FP8 keys, 1- and 8-bit key codes and
+ * up to even).  Supported: head_dim 64/128/256, key_bits 1/2/3/4 (Lloyd-Max codes),
+ * value_bits 1/2/3/4/8 (per-vector uniform codes).  FP8 keys, 8-bit key codes and
  * Lloyd-Max value codes return FTQ_ERR_UNSUPPORTED.
  */
 int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits);

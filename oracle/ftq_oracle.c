@@ -453,6 +453,14 @@ static void tq_pack_bits(const int *idx, uint8_t *out, int d, int bits) {
         for (int i = 0; i < d; i++) out[i] = (uint8_t)idx[i];
         return;
     }
+    if (bits == 1) { /* coordinate 8k + j in bit j of byte k (triton_inkernel_store.py:138-146) */
+        for (int k = 0; k < d / 8; k++) {
+            unsigned b = 0;
+            for (int j = 0; j < 8; j++) b |= (unsigned)(idx[8 * k + j] & 1) << j;
+            out[k] = (uint8_t)b;
+        }
+        return;
+    }
     uint8_t tmp[FTQ_MAX_D];
     for (int i = 0; i < d; i++) tmp[i] = (uint8_t)idx[i];
     ftq_oracle_pack(tmp, out, d, bits);

@@ -37,6 +37,10 @@ CASES = [
     ("d64_k3v3_g7", 64, 2, 7, 3, 3, 1, (45, 17), (0, 5), 4, 16),
     ("d256_k4v2", 256, 1, 2, 4, 2, 0, (37, 40), (0, 0), 2, 16),
     ("d128_k2v8", 128, 1, 4, 2, 8, 0, (21, 1), (3, 0), 2, 8),
+    # 1-bit codes (reachable through the reference's bit-width overrides, v1_backend.py:466-491)
+    ("d128_k1v1_nc", 128, 2, 4, 1, 1, 1, (40, 19), (0, 0), 3, 16),
+    ("d64_k1v3", 64, 2, 2, 1, 3, 0, (30, 9), (0, 2), 2, 16),
+    ("d256_k3v1_nc", 256, 1, 2, 3, 1, 1, (21, 18), (0, 0), 2, 8),
 ]
 
 

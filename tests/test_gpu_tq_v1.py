@@ -15,7 +15,8 @@ from helpers import gate, tq_v1_compare_cache
 
 pytestmark = pytest.mark.gpu
 
-CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8"]
+CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8",
+         "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc"]
 cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
@@ -75,7 +76,8 @@ def test_decode_vs_reference_kernels(oracle, golden, name):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("D,kb,vb,G,nc", [(128, 4, 4, 4, True), (64, 2, 3, 7, False), (256, 3, 8, 2, True),
-                                          (128, 3, 2, 8, False)])
+                                          (128, 3, 2, 8, False), (64, 1, 1, 4, True), (128, 1, 4, 2, False),
+                                          (256, 4, 1, 2, True)])
 def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, dtype):
     """Ragged batch, 16-bit inputs, values kept in the rotated space, several splits."""
     from fused_turboquant_b200 import tq_v1
@@ -109,8 +111,9 @@ def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, dtype):
     o_ref, _, _ = oracle.tq_decode(q.float().numpy(), ref, bt, np.array(seq, np.int32), cent_t.numpy(), kb, vb,
                                    D ** -0.5, splits, norm_correction=nc, rotate_out=True)
     # 16-bit queries take the tensor-core kernel where it exists (fp16 centroids / weights, fp32
-    # accumulation): the north-star gate; 8-bit values and head_dim 256 stay on the fp32 kernel
-    if vb == 8 or D == 256:
+    # accumulation): the north-star gate; 8-bit values, 1-bit codes and head_dim 256 stay on the
+    # fp32 kernel
+    if vb == 8 or D == 256 or 1 in (kb, vb):
         assert gate(out.cpu().numpy(), o_ref, 2e-4, 1e-4) == 0
     else:
         assert gate(out.cpu().numpy(), o_ref) == 0, np.abs(out.cpu().numpy() - o_ref).max()

@@ -6,7 +6,8 @@ import pytest
 
 from helpers import tq_v1_compare_cache
 
-CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8"]
+CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8",
+         "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc"]
 
 
 @pytest.mark.parametrize("name", CASES)
