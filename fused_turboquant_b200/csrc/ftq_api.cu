@@ -869,8 +869,8 @@ extern "C" int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits) {
 
 extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64_t n_tokens, int Hkv,
                             int head_dim, int64_t token_stride, int64_t head_stride, int key_bits,
-                            int value_bits, int rotate_values, const float* midpoints_host,
-                            uint8_t* kv_cache,
+                            int value_bits, int rotate_values, int value_lloyd_max,
+                            const float* midpoints_host, uint8_t* kv_cache,
                             int64_t stride_block, int64_t stride_pos, int64_t stride_head,
                             int block_size, const int64_t* slot_mapping, void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
@@ -914,11 +914,14 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
     p.rsqrt_d = 1.0f / sqrtf(static_cast<float>(head_dim));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t n_vec = n_tokens * Hkv;
+    // (as in the reference, the Lloyd-Max flag only changes 4-bit values)
+    const int vmode = (rotate_values ? ftq::kTqRotateValues : 0) |
+                      (value_lloyd_max && value_bits == 4 ? ftq::kTqLloydMaxValues : 0);
     cudaError_t e = cudaErrorInvalidValue;
     switch (head_dim) {
-        case 64: e = ftq::launch_tq_store_d64(key_bits, value_bits, dtype, p, rotate_values != 0, n_vec, st); break;
-        case 128: e = ftq::launch_tq_store_d128(key_bits, value_bits, dtype, p, rotate_values != 0, n_vec, st); break;
-        case 256: e = ftq::launch_tq_store_d256(key_bits, value_bits, dtype, p, rotate_values != 0, n_vec, st); break;
+        case 64: e = ftq::launch_tq_store_d64(key_bits, value_bits, dtype, p, vmode, n_vec, st); break;
+        case 128: e = ftq::launch_tq_store_d128(key_bits, value_bits, dtype, p, vmode, n_vec, st); break;
+        case 256: e = ftq::launch_tq_store_d256(key_bits, value_bits, dtype, p, vmode, n_vec, st); break;
     }
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "tq_store launch");
 }
@@ -928,7 +931,8 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
                              int64_t stride_head, int block_size, const int32_t* block_table,
                              int max_blocks, const int32_t* seq_lens, const int32_t* kv_start_offset,
                              int key_bits, int value_bits, int norm_correction, int rotate_output,
-                             const float* centroids_host, float scale, int num_kv_splits,
+                             int value_lloyd_max, const float* centroids_host, float scale,
+                             int num_kv_splits,
                              float* mid_o, void* out, int out_dtype, float* lse, void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
@@ -964,6 +968,7 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
     p.seq_lens = seq_lens;
     p.kv_start = kv_start_offset;
     p.norm_correction = norm_correction ? 1 : 0;
+    p.value_lloyd_max = (value_lloyd_max && value_bits == 4) ? 1 : 0;  // other widths: ignored, as in the reference
     p.scale = scale;
     p.splits = num_kv_splits;
     const int gh = head_dim == 64 ? 8 : (head_dim == 128 ? 4 : 2);
@@ -976,12 +981,13 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaErrorInvalidValue;
     // 16-bit queries with a GQA group of at most 8 take the tensor-core kernel (head_dim 64 / 128,
-    // key and value codes of 2..4 bits); everything else the fp32 kernel
+    // key and uniform value codes of 2..4 bits); everything else the fp32 kernel
     const int group = Hq / Hkv;
     // (its copy loop reads whole aligned words: a cache that starts on an odd 2-byte boundary -- a
     // view at an offset -- stays on the fp32 kernel, which reads 2-byte pieces)
     const bool mma = q_dtype != FTQ_F32 && group <= 8 && key_bits >= 2 && value_bits >= 2 &&
-                     value_bits != 8 && head_dim != 256 && aligned(kv_cache, 4);
+                     value_bits != 8 && head_dim != 256 && aligned(kv_cache, 4) &&
+                     !p.value_lloyd_max;
     if (mma) {
         const int64_t items = static_cast<int64_t>(B) * Hkv * num_kv_splits;
         if (items >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "too many (sequence, head, split) items");

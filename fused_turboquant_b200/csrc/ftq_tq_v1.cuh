@@ -86,10 +86,17 @@ template <> __device__ __forceinline__ float round_as<__nv_bfloat16>(float v) {
 // ROTV: the values are Hadamard-transformed (no signs, * 1/sqrt(D), rounded to the input dtype)
 // before they are quantised, i.e. the cache keeps them in the rotated space
 // (src/fused_turboquant/vllm_plugin/v1_backend.py:727-740 does this with a matrix product).
-template <int D, int KB, int VB, typename T, bool ROTV>
+// LMV (4-bit values only): Lloyd-Max value codes (TURBOQUANT_V_LLOYD_MAX,
+// triton_inkernel_store.py:159-203): the value is normalised like the key (norm = sqrt(sum + 1e-16),
+// v / (norm + 1e-8)), bucketised against the KEY midpoints, packed as 4-bit codes; the norm goes
+// where the scale would and the zero point is 0.  The squares are added in register order per
+// lane, then pairwise over the octet -- in whichever layout the values sit (after the fused
+// rotation: lane l holds the coordinates l + 8k).
+template <int D, int KB, int VB, typename T, bool ROTV, bool LMV = false>
 __global__ void __launch_bounds__(256)
 tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
     static_assert(!ROTV || VB != 8, "rotated 8-bit values are rotated by the caller");
+    static_assert(!LMV || VB == 4, "Lloyd-Max value codes are 4-bit");
     constexpr int E = D / kOctet;
     constexpr int NCH = E / 8;
     constexpr int MSE = D * KB / 8;
@@ -227,16 +234,36 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
         }
         float scale = __fdiv_rn(__fsub_rn(mx, mn), static_cast<float>(VMAX));
         scale = scale > 1e-8f ? scale : 1e-8f;
+        float vden = 1.f;
+        if constexpr (LMV) {
+            float s2 = 0.f;
+#pragma unroll
+            for (int r = 0; r < E; r++) s2 = __fadd_rn(s2, __fmul_rn(vv[r], vv[r]));
+            s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, 1));
+            s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, 2));
+            s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, 4));
+            scale = __fsqrt_rn(__fadd_rn(s2, 1e-16f));  // the norm takes the scale's place
+            vden = __fadd_rn(scale, 1e-8f);
+            mn = 0.f;                                    // ... and the zero point is 0
+        }
+        auto vcode = [&](float x) -> uint32_t {
+            if constexpr (LMV) {
+                const float u = __fdiv_rn(x, vden);
+                uint32_t c = 0;
+#pragma unroll
+                for (int j = 0; j < NMID; j++) c += (u >= p.midpoints[j]) ? 1u : 0u;
+                return c;
+            } else {
+                const float f = __fadd_rn(__fdiv_rn(__fsub_rn(x, mn), scale), 0.5f);
+                return static_cast<uint32_t>(min(max(__float2int_rz(f), 0), VMAX));
+            }
+        };
         if constexpr (!ROTV) {
 #pragma unroll
             for (int i = 0; i < NCH; i++) {
                 uint32_t q[8];
 #pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    const float f = __fadd_rn(__fdiv_rn(__fsub_rn(vv[8 * i + c], mn), scale), 0.5f);
-                    const int qi = __float2int_rz(f);
-                    q[c] = static_cast<uint32_t>(min(max(qi, 0), VMAX));
-                }
+                for (int c = 0; c < 8; c++) q[c] = vcode(vv[8 * i + c]);
                 const int run = t + 8 * i;  // coordinates 8*run .. 8*run + 7
                 if (!store) continue;
                 uint8_t* vd = dst + KPS;
@@ -271,8 +298,7 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
             for (int i = 0; i < NWV; i++) wv[i] = 0u;
 #pragma unroll
             for (int k = 0; k < E; k++) {
-                const float f = __fadd_rn(__fdiv_rn(__fsub_rn(vv[k], mn), scale), 0.5f);
-                const uint32_t code = static_cast<uint32_t>(min(max(__float2int_rz(f), 0), VMAX));
+                const uint32_t code = vcode(vv[k]);
                 if constexpr (VB == 1) {
                     wv[0] |= code << k;
                 } else if constexpr (VB == 2) {
@@ -322,6 +348,7 @@ struct TqDecodeParams {
     const int32_t* seq_lens;
     const int32_t* kv_start;  // nullable
     int norm_correction;
+    int value_lloyd_max;  // 4-bit values are Lloyd-Max codes of the key table, scale slot = norm
     float scale;
     int splits, n_hpass;
     float rsqrt_d;
@@ -603,12 +630,38 @@ tq_split_kernel(const TqDecodeParams p) {
                 // (slots past the end of the tile hold stale bytes: keep them out of the arithmetic)
                 const float vs = ok ? meta[kTqTileTokens + tk] : 0.f;
                 const float vz = ok ? meta[2 * kTqTileTokens + tk] : 0.f;
-                const u64 vs2 = pk2(vs, vs), vz2 = pk2(vz, vz);
                 u64 vv[EP];
+                bool lm = false;
+                if constexpr (VB == 4) lm = p.value_lloyd_max != 0;
+                if (lm) {
+                    // values[d] = centroid[code] * norm, the centroid vector re-normalised to unit
+                    // length under norm correction (triton_decode_offset.py:399-423)
+                    u64 cn2 = pk2(0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < EP; i++)
-                    vv[i] = fma2(pk2(static_cast<float>(extract_code<VB>(w, 2 * i)),
-                                     static_cast<float>(extract_code<VB>(w, 2 * i + 1))), vs2, vz2);
+                    for (int i = 0; i < EP; i++) {
+                        vv[i] = pk2(lut[extract_code<VB>(w, 2 * i)], lut[extract_code<VB>(w, 2 * i + 1)]);
+                        cn2 = fma2(vv[i], vv[i], cn2);
+                    }
+                    float vn = vs;
+                    if (p.norm_correction) {
+                        float c0, c1;
+                        upk2(cn2, c0, c1);
+                        float cn = c0 + c1;
+                        cn += __shfl_xor_sync(0xffffffffu, cn, 1);
+                        cn += __shfl_xor_sync(0xffffffffu, cn, 2);
+                        cn += __shfl_xor_sync(0xffffffffu, cn, 4);
+                        vn *= 1.0f / sqrtf(cn + 1e-16f);
+                    }
+                    const u64 vn2 = pk2(vn, vn);
+#pragma unroll
+                    for (int i = 0; i < EP; i++) vv[i] = mul2(vv[i], vn2);
+                } else {
+                    const u64 vs2 = pk2(vs, vs), vz2 = pk2(vz, vz);
+#pragma unroll
+                    for (int i = 0; i < EP; i++)
+                        vv[i] = fma2(pk2(static_cast<float>(extract_code<VB>(w, 2 * i)),
+                                         static_cast<float>(extract_code<VB>(w, 2 * i + 1))), vs2, vz2);
+                }
 #pragma unroll
                 for (int h = 0; h < GH; h++) {
                     const float wgt = ok ? wp[step][h] : 0.f;

@@ -1,6 +1,7 @@
 // Instantiates the vLLM-v1 slot-format kernels for one head_dim (FTQ_D).
 #include "ftq_launch.h"
 #include "ftq_tq_v1.cuh"
+#include "ftq_tq_v1_launch.h"
 #if FTQ_D != 256
 #include "ftq_tq_v1_mma.cuh"
 #endif
@@ -14,10 +15,18 @@
 namespace ftq {
 
 template <int KB, int VB, typename T>
-static cudaError_t store_run(const TqStoreParams& p, bool rotate_v, int64_t n_vec, cudaStream_t stream) {
+static cudaError_t store_run(const TqStoreParams& p, int value_mode, int64_t n_vec, cudaStream_t stream) {
     const int64_t want = (n_vec + 31) / 32;  // 8 warps x 4 vectors per CTA pass
     const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     const unsigned gx = static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
+    const bool rotate_v = (value_mode & kTqRotateValues) != 0;
+    if constexpr (VB == 4) {
+        if (value_mode & kTqLloydMaxValues) {
+            if (rotate_v) tq_store_kernel<FTQ_D, KB, VB, T, true, true><<<gx, 256, 0, stream>>>(p, n_vec);
+            else tq_store_kernel<FTQ_D, KB, VB, T, false, true><<<gx, 256, 0, stream>>>(p, n_vec);
+            return cudaGetLastError();
+        }
+    }
     if constexpr (VB != 8) {
         if (rotate_v) {
             tq_store_kernel<FTQ_D, KB, VB, T, true><<<gx, 256, 0, stream>>>(p, n_vec);
@@ -31,36 +40,36 @@ static cudaError_t store_run(const TqStoreParams& p, bool rotate_v, int64_t n_ve
 }
 
 template <int KB, int VB>
-static cudaError_t store_by_dtype(int dtype, const TqStoreParams& p, bool rot, int64_t n_vec,
+static cudaError_t store_by_dtype(int dtype, const TqStoreParams& p, int vmode, int64_t n_vec,
                                   cudaStream_t s) {
     switch (dtype) {
-        case kF32: return store_run<KB, VB, float>(p, rot, n_vec, s);
-        case kF16: return store_run<KB, VB, __half>(p, rot, n_vec, s);
-        case kBF16: return store_run<KB, VB, __nv_bfloat16>(p, rot, n_vec, s);
+        case kF32: return store_run<KB, VB, float>(p, vmode, n_vec, s);
+        case kF16: return store_run<KB, VB, __half>(p, vmode, n_vec, s);
+        case kBF16: return store_run<KB, VB, __nv_bfloat16>(p, vmode, n_vec, s);
     }
     return cudaErrorInvalidValue;
 }
 
 template <int KB>
-static cudaError_t store_by_vb(int vb, int dtype, const TqStoreParams& p, bool rot, int64_t n_vec,
+static cudaError_t store_by_vb(int vb, int dtype, const TqStoreParams& p, int vmode, int64_t n_vec,
                                cudaStream_t s) {
     switch (vb) {
-        case 1: return store_by_dtype<KB, 1>(dtype, p, rot, n_vec, s);
-        case 2: return store_by_dtype<KB, 2>(dtype, p, rot, n_vec, s);
-        case 3: return store_by_dtype<KB, 3>(dtype, p, rot, n_vec, s);
-        case 4: return store_by_dtype<KB, 4>(dtype, p, rot, n_vec, s);
-        case 8: return store_by_dtype<KB, 8>(dtype, p, rot, n_vec, s);
+        case 1: return store_by_dtype<KB, 1>(dtype, p, vmode, n_vec, s);
+        case 2: return store_by_dtype<KB, 2>(dtype, p, vmode, n_vec, s);
+        case 3: return store_by_dtype<KB, 3>(dtype, p, vmode, n_vec, s);
+        case 4: return store_by_dtype<KB, 4>(dtype, p, vmode, n_vec, s);
+        case 8: return store_by_dtype<KB, 8>(dtype, p, vmode, n_vec, s);
     }
     return cudaErrorInvalidValue;
 }
 
 cudaError_t FTQ_CAT(launch_tq_store_d, FTQ_D)(int kb, int vb, int dtype, const TqStoreParams& p,
-                                             bool rotate_v, int64_t n_vec, cudaStream_t stream) {
+                                             int value_mode, int64_t n_vec, cudaStream_t stream) {
     switch (kb) {
-        case 1: return store_by_vb<1>(vb, dtype, p, rotate_v, n_vec, stream);
-        case 2: return store_by_vb<2>(vb, dtype, p, rotate_v, n_vec, stream);
-        case 3: return store_by_vb<3>(vb, dtype, p, rotate_v, n_vec, stream);
-        case 4: return store_by_vb<4>(vb, dtype, p, rotate_v, n_vec, stream);
+        case 1: return store_by_vb<1>(vb, dtype, p, value_mode, n_vec, stream);
+        case 2: return store_by_vb<2>(vb, dtype, p, value_mode, n_vec, stream);
+        case 3: return store_by_vb<3>(vb, dtype, p, value_mode, n_vec, stream);
+        case 4: return store_by_vb<4>(vb, dtype, p, value_mode, n_vec, stream);
     }
     return cudaErrorInvalidValue;
 }

@@ -98,8 +98,15 @@ def _cache_strides(kv_cache: torch.Tensor) -> tuple[int, int, int]:
 
 def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
                  slot_mapping: torch.Tensor, midpoints, tq_config: TurboQuantSlotConfig,
-                 head_size: int | None = None, v_rotate: bool = False) -> None:
-    """Quantise ``key``/``value`` ``[N, Hkv, D]`` into the slots ``slot_mapping`` names (< 0: skipped)."""
+                 head_size: int | None = None, v_rotate: bool = False,
+                 v_lloyd_max: bool = False) -> None:
+    """Quantise ``key``/``value`` ``[N, Hkv, D]`` into the slots ``slot_mapping`` names (< 0: skipped).
+
+    ``v_lloyd_max`` (the reference's TURBOQUANT_V_LLOYD_MAX switch; 4-bit values only, ignored
+    otherwise as in the reference): values become Lloyd-Max codes against the key midpoints, their
+    norm goes into the scale field.  The reference rotates the values whenever that switch is on
+    (vllm_plugin/v1_backend.py:736-740): pass ``v_rotate=True`` with it unless they already are.
+    """
     _require_cuda(key, "key")
     _require_cuda(kv_cache, "kv_cache")
     n, hkv, d = key.shape
@@ -129,7 +136,7 @@ def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
         rc = _lib.load().ftq_tq_store(
             _ptr(key), _ptr(value), _DT[key.dtype], n, hkv, d, key.stride(0), key.stride(1),
             tq_config.key_quant_bits, tq_config.value_quant_bits, int(rotate_in_kernel),
-            _lib.fptr(_host_table(midpoints)), _ptr(kv_cache), sb, sp, sh, kv_cache.shape[1],
+            int(bool(v_lloyd_max)), _lib.fptr(_host_table(midpoints)), _ptr(kv_cache), sb, sp, sh, kv_cache.shape[1],
             _ptr(sm), _stream(key.device))
     _lib.check(rc, "ftq_tq_store")
 
@@ -139,8 +146,11 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
                      num_kv_splits: int = 8, kv_start_offset: torch.Tensor | None = None,
                      v_rotate: bool = False, mid_o: torch.Tensor | None = None,
                      output: torch.Tensor | None = None, lse: torch.Tensor | None = None,
-                     out_dtype: torch.dtype | None = None) -> torch.Tensor:
+                     out_dtype: torch.dtype | None = None, v_lloyd_max: bool = False) -> torch.Tensor:
     """Decode attention of ``query`` ``[B, Hq, D]`` over the compressed cache; returns ``[B, Hq, D]``.
+
+    ``v_rotate``: the cache holds rotated values, the merged output is transformed back.
+    ``v_lloyd_max``: 4-bit values are Lloyd-Max codes (see ``launch_store``).
 
     ``mid_o`` ``[B, Hq, num_kv_splits, D+1]`` fp32, ``output`` and ``lse`` ``[B, Hq]`` fp32 may be
     supplied (pre-allocated per layer, as the reference keeps them for CUDA-graph capture).
@@ -175,7 +185,8 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
             _ptr(query), _DT[query.dtype], B, hq, hkv, d, _ptr(kv_cache), sb, sp, sh,
             kv_cache.shape[1], _ptr(bt), bt.shape[1], _ptr(sl), _ptr(ks),
             tq_config.key_quant_bits, tq_config.value_quant_bits, int(tq_config.norm_correction),
-            int(v_rotate), _lib.fptr(_host_table(centroids)), float(scale), num_kv_splits,
+            int(v_rotate), int(bool(v_lloyd_max)), _lib.fptr(_host_table(centroids)), float(scale),
+            num_kv_splits,
             _ptr(mid_o), _ptr(output), _DT[output.dtype], _ptr(lse), _stream(dev))
     _lib.check(rc, "ftq_tq_decode")
     return output
@@ -183,7 +194,8 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
 
 def continuation_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor,
                            seq_lens: torch.Tensor, centroids, tq_config: TurboQuantSlotConfig,
-                           scale: float, num_kv_splits: int = 8, v_rotate: bool = False) -> torch.Tensor:
+                           scale: float, num_kv_splits: int = 8, v_rotate: bool = False,
+                           v_lloyd_max: bool = False) -> torch.Tensor:
     """Causal attention of ``q_len`` new tokens per sequence that are already in the cache.
 
     query: [B, q_len, Hq, D]; seq_lens: [B] totals including the new tokens.  The reference's
@@ -194,5 +206,6 @@ def continuation_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_ta
     B, q_len, hq, d = query.shape
     bt, sl = synthetic_decode_batch(block_table, seq_lens, q_len)
     out = decode_attention(query.reshape(B * q_len, hq, d), kv_cache, bt, sl, centroids, tq_config,
-                           scale, num_kv_splits=num_kv_splits, v_rotate=v_rotate)
+                           scale, num_kv_splits=num_kv_splits, v_rotate=v_rotate,
+                           v_lloyd_max=v_lloyd_max)
     return out.view(B, q_len, hq, d)

@@ -259,8 +259,8 @@ int ftq_v0_gather(const uint8_t *kv_cache, int64_t num_blocks, int block_size, i
  *     [key codes D*kb/8 | key norm f16 | value codes D*vb/8 (D for vb = 8) | scale f16 | zero f16]
  * (vllm_plugin/boundary_tq_config.py:66-81; ftq_tq_slot_bytes returns its size rounded
  * up to even).  Supported: head_dim 64/128/256, key_bits 1/2/3/4 (Lloyd-Max codes),
- * value_bits 1/2/3/4/8 (per-vector uniform codes).  FP8 keys, 8-bit key codes and
- * Lloyd-Max value codes return FTQ_ERR_UNSUPPORTED.
+ * value_bits 1/2/3/4/8 (per-vector uniform codes; 4-bit values optionally Lloyd-Max codes).
+ * FP8 keys and 8-bit key codes return FTQ_ERR_UNSUPPORTED.
  */
 int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits);
 
@@ -276,12 +276,17 @@ int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits);
  * rotated space (TURBOQUANT_V_ROTATE, v1_backend.py:727-740): they are Hadamard-transformed in
  * the kernel (no signs, * 1/sqrt(D), rounded to `dtype` as the reference's tensor would be) before
  * they are quantised; not available for value_bits = 8 (FTQ_ERR_UNSUPPORTED: rotate them first,
- * e.g. with ftq_rht and no signs).
+ * e.g. with ftq_rht and no signs).  value_lloyd_max != 0 (TURBOQUANT_V_LLOYD_MAX,
+ * triton_inkernel_store.py:159-203; 4-bit values only, ignored for other widths as in the
+ * reference): the (rotated) value is normalised like the key, bucketised against the KEY
+ * midpoints and packed as 4-bit codes; its norm is stored where the scale would be, the zero
+ * point is 0.
  */
 int ftq_tq_store(const void *key, const void *value, int dtype, int64_t n_tokens, int Hkv,
                  int head_dim, int64_t token_stride, int64_t head_stride, int key_bits,
-                 int value_bits, int rotate_values, const float *midpoints_host, uint8_t *kv_cache,
-                 int64_t stride_block, int64_t stride_pos, int64_t stride_head, int block_size,
+                 int value_bits, int rotate_values, int value_lloyd_max,
+                 const float *midpoints_host, uint8_t *kv_cache, int64_t stride_block,
+                 int64_t stride_pos, int64_t stride_head, int block_size,
                  const int64_t *slot_mapping, void *stream);
 
 /*
@@ -295,6 +300,8 @@ int ftq_tq_store(const void *key, const void *value, int dtype, int64_t n_tokens
  * out: [B, Hq, head_dim] of out_dtype; lse (nullable): [B, Hq] fp32.  norm_correction:
  * re-normalise each key's centroid vector to unit length.  rotate_output: apply the
  * Hadamard transform to the merged output (values were stored in the rotated space).
+ * value_lloyd_max: 4-bit values are Lloyd-Max codes of the key table scaled by the stored norm
+ * (triton_decode_offset.py:399-423; re-normalised under norm_correction); ignored for other widths.
  * centroids_host: 2^key_bits floats, ascending.  No allocation, no host synchronisation.
  */
 int ftq_tq_decode(const void *q, int q_dtype, int B, int Hq, int Hkv, int head_dim,
@@ -302,8 +309,9 @@ int ftq_tq_decode(const void *q, int q_dtype, int B, int Hq, int Hkv, int head_d
                   int64_t stride_head, int block_size, const int32_t *block_table,
                   int max_blocks, const int32_t *seq_lens, const int32_t *kv_start_offset,
                   int key_bits, int value_bits, int norm_correction, int rotate_output,
-                  const float *centroids_host, float scale, int num_kv_splits, float *mid_o,
-                  void *out, int out_dtype, float *lse, void *stream);
+                  int value_lloyd_max, const float *centroids_host, float scale,
+                  int num_kv_splits, float *mid_o, void *out, int out_dtype, float *lse,
+                  void *stream);
 
 #ifdef __cplusplus
 }

@@ -448,6 +448,27 @@ static float tq_key_norm_sq(const float *k, int d) {
     return lane[0];
 }
 
+/* Sum of squares in the order the CUDA store adds them when the vector sits in the butterfly's
+ * output layout (after the fused value rotation): lane l of the octet owns the coordinates
+ * l + 8k, k ascending, then the lanes are combined pairwise. */
+static float tq_norm_sq_rotated_layout(const float *v, int d) {
+    float lane[8];
+    for (int l = 0; l < 8; l++) {
+        float s = 0.0f;
+        for (int k = 0; k < d / 8; k++) {
+            float sq = v[l + 8 * k] * v[l + 8 * k];
+            s = s + sq;
+        }
+        lane[l] = s;
+    }
+    for (int m = 1; m < 8; m <<= 1) {
+        float nxt[8];
+        for (int t = 0; t < 8; t++) nxt[t] = lane[t] + lane[t ^ m];
+        memcpy(lane, nxt, sizeof(lane));
+    }
+    return lane[0];
+}
+
 static void tq_pack_bits(const int *idx, uint8_t *out, int d, int bits) {
     if (bits == 8) {
         for (int i = 0; i < d; i++) out[i] = (uint8_t)idx[i];
@@ -475,11 +496,16 @@ static float get_f16(const uint8_t *src) {
     return ftq_oracle_f16_to_f32((uint16_t)(src[0] | (src[1] << 8)));
 }
 
-/* key/value: [n_tokens, Hkv, d] fp32 contiguous.  y_out (nullable): the rotated unit keys. */
+/* key/value: [n_tokens, Hkv, d] fp32 contiguous.  y_out (nullable): the rotated unit keys.
+ * value_lloyd_max (4-bit values only, otherwise ignored: triton_inkernel_store.py:159-203): the
+ * value is normalised like the key, bucketised against the key midpoints, its norm stored in the
+ * scale field, zero point 0.  value_sum_order: 0 = squares added in the key's order, 1 = in the
+ * order of the CUDA store's fused value rotation (the reference leaves the order open). */
 void ftq_oracle_tq_store(const float *key, const float *value, int64_t n_tokens, int Hkv, int d,
                          int key_bits, int value_bits, const float *midpoints, uint8_t *kv_cache,
                          int64_t stride_block, int64_t stride_pos, int64_t stride_head,
-                         int block_size, const int64_t *slot_mapping, float *y_out) {
+                         int block_size, const int64_t *slot_mapping, float *y_out,
+                         int value_lloyd_max, int value_sum_order) {
     const int n_cent = 1 << key_bits;
     const int mse_bytes = d * key_bits / 8;
     const int kps = mse_bytes + 2;
@@ -516,6 +542,21 @@ void ftq_oracle_tq_store(const float *key, const float *value, int64_t n_tokens,
             if (y_out) memcpy(y_out + (tok * Hkv + h) * d, y, sizeof(float) * d);
             tq_pack_bits(idx, dst, d, key_bits);
             put_f16(dst + mse_bytes, norm);
+            if (value_lloyd_max && value_bits == 4) {
+                float vn = sqrtf((value_sum_order ? tq_norm_sq_rotated_layout(v, d)
+                                                  : tq_key_norm_sq(v, d)) + 1e-16f);
+                float vden = vn + 1e-8f;
+                for (int i = 0; i < d; i++) {
+                    float u = v[i] / vden;
+                    int c = 0;
+                    for (int j = 0; j < n_cent - 1; j++) c += (u >= midpoints[j]) ? 1 : 0;
+                    idx[i] = c;
+                }
+                tq_pack_bits(idx, dst + kps, d, 4);
+                put_f16(dst + kps + vdb, vn);
+                put_f16(dst + kps + vdb + 2, 0.0f);
+                continue;
+            }
             /* values: per-vector uniform quantisation */
             float mn = v[0], mx = v[0];
             for (int i = 1; i < d; i++) {
@@ -554,7 +595,8 @@ void ftq_oracle_tq_decode(const float *q, int B, int Hq, int Hkv, int d, const u
                           const int32_t *seq_lens, const int32_t *kv_start, int key_bits,
                           int value_bits, int norm_correction, int rotate_out,
                           const float *centroids, float scale, int splits, float *mid_o,
-                          float *out, float *lse) {
+                          float *out, float *lse, int value_lloyd_max) {
+    const int v_lm = value_lloyd_max && value_bits == 4; /* triton_decode_offset.py:399-423 */
     const int group = Hq / Hkv;
     const int mse_bytes = d * key_bits / 8;
     const int kps = mse_bytes + 2;
@@ -590,11 +632,22 @@ void ftq_oracle_tq_decode(const float *q, int B, int Hq, int Hkv, int d, const u
                     }
                     if (norm_correction) dot *= 1.0 / sqrt(cn + 1e-16);
                     const double sc = (double)get_f16(slot + mse_bytes) * dot * (double)scale;
-                    const double vs = get_f16(slot + kps + vdb), vz = get_f16(slot + kps + vdb + 2);
+                    double vs = get_f16(slot + kps + vdb), vz = get_f16(slot + kps + vdb + 2);
+                    if (v_lm) { /* value = centroid[code] * norm, re-normalised under norm correction */
+                        double vcn = 0.0;
+                        for (int i = 0; i < d; i++) {
+                            const double c = centroids[tq_code(slot + kps, i, 4)];
+                            vcn += c * c;
+                        }
+                        if (norm_correction) vs *= 1.0 / sqrt(vcn + 1e-16);
+                        vz = 0.0;
+                    }
                     const double mn = sc > m ? sc : m;
                     const double corr = exp(m - mn), p = exp(sc - mn);
                     for (int i = 0; i < d; i++)
-                        acc[i] = acc[i] * corr + p * (tq_code(slot + kps, i, value_bits) * vs + vz);
+                        acc[i] = acc[i] * corr +
+                                 p * ((v_lm ? (double)centroids[tq_code(slot + kps, i, 4)]
+                                            : (double)tq_code(slot + kps, i, value_bits)) * vs + vz);
                     l = l * corr + p;
                     m = mn;
                 }

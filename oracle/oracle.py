@@ -213,8 +213,12 @@ def tq_slot_bytes(d: int, key_bits: int, value_bits: int) -> int:
 
 
 def tq_store(key, value, kv_cache: np.ndarray, slot_mapping, midpoints, key_bits: int,
-             value_bits: int, return_rotated: bool = False):
-    """The reference's in-kernel-rotation store into kv_cache [nb, block_size, Hkv, slot] (in place)."""
+             value_bits: int, return_rotated: bool = False, value_lloyd_max: bool = False,
+             value_sum_order: int = 0):
+    """The reference's in-kernel-rotation store into kv_cache [nb, block_size, Hkv, slot] (in place).
+
+    value_lloyd_max: 4-bit values as Lloyd-Max codes of the key table (ignored for other widths);
+    value_sum_order 1 adds the value's squares in the order of the CUDA store's fused rotation."""
     key, value = _c(key, np.float32), _c(value, np.float32)
     n, hkv, d = key.shape
     assert kv_cache.dtype == np.uint8 and kv_cache.flags.c_contiguous and kv_cache.ndim == 4
@@ -225,13 +229,14 @@ def tq_store(key, value, kv_cache: np.ndarray, slot_mapping, midpoints, key_bits
     lib().ftq_oracle_tq_store(_p(key), _p(value), ctypes.c_int64(n), ctypes.c_int(hkv),
                               ctypes.c_int(d), ctypes.c_int(key_bits), ctypes.c_int(value_bits),
                               _p(mids), _p(kv_cache), ctypes.c_int64(st[0]), ctypes.c_int64(st[1]),
-                              ctypes.c_int64(st[2]), ctypes.c_int(kv_cache.shape[1]), _p(sm), _p(y))
+                              ctypes.c_int64(st[2]), ctypes.c_int(kv_cache.shape[1]), _p(sm), _p(y),
+                              ctypes.c_int(int(value_lloyd_max)), ctypes.c_int(int(value_sum_order)))
     return y
 
 
 def tq_decode(q, kv_cache: np.ndarray, block_table, seq_lens, centroids, key_bits: int,
               value_bits: int, scale: float, splits: int, norm_correction: bool = False,
-              kv_start=None, rotate_out: bool = False):
+              kv_start=None, rotate_out: bool = False, value_lloyd_max: bool = False):
     """Split-KV decode over the slot format: returns (out [B,Hq,d], mid_o [B,Hq,splits,d+1], lse)."""
     q = _c(q, np.float32)
     B, Hq, d = q.shape
@@ -251,5 +256,5 @@ def tq_decode(q, kv_cache: np.ndarray, block_table, seq_lens, centroids, key_bit
                                _p(sl), _p(ks), ctypes.c_int(key_bits), ctypes.c_int(value_bits),
                                ctypes.c_int(int(norm_correction)), ctypes.c_int(int(rotate_out)),
                                _p(cent), ctypes.c_float(scale), ctypes.c_int(splits), _p(mid_o),
-                               _p(out), _p(lse))
+                               _p(out), _p(lse), ctypes.c_int(int(value_lloyd_max)))
     return out, mid_o, lse

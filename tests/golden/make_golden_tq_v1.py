@@ -12,6 +12,8 @@ kernels wrote for them:
   {case}_out       output of the stock stage-2 merge over them      (call as in vllm_plugin/v1_backend.py:1068-1085)
   {case}_y         the rotated unit key the store kernel bucketises, recomputed with torch ops
                    (used by the tests to tell a genuine code mismatch from a value sitting on a midpoint)
+  {case}_vy        ("_vlm" cases) the unit value the store kernel bucketises, likewise; {case}_V then
+                   holds the pre-rotated values the store kernel was given
 
 The centroid tables come from the installed vLLM (`get_centroids`), as the reference obtains them;
 the query rotation `q @ H` follows rotation/matrix.py:47-48.  Needs make_golden.py's environment.
@@ -41,6 +43,11 @@ CASES = [
     ("d128_k1v1_nc", 128, 2, 4, 1, 1, 1, (40, 19), (0, 0), 3, 16),
     ("d64_k1v3", 64, 2, 2, 1, 3, 0, (30, 9), (0, 2), 2, 16),
     ("d256_k3v1_nc", 256, 1, 2, 3, 1, 1, (21, 18), (0, 0), 2, 8),
+    # "_vlm": TURBOQUANT_V_LLOYD_MAX=1 -- values pre-rotated as v1_backend.py:736-740 does, stored
+    # as 4-bit Lloyd-Max codes of the key table (3-bit keys: only 8 of the 16 codes occur)
+    ("d128_k4v4_nc_vlm", 128, 2, 4, 4, 4, 1, (50, 23), (0, 0), 3, 16),
+    ("d64_k4v4_vlm", 64, 2, 2, 4, 4, 0, (33, 12), (0, 4), 2, 16),
+    ("d128_k3v4_nc_vlm", 128, 1, 2, 3, 4, 1, (20, 9), (0, 0), 2, 8),
 ]
 
 
@@ -88,6 +95,13 @@ def main() -> None:
         # rows 7 and the last one are the padding tokens: move K/V rows accordingly
         order = list(range(7)) + [len(slots)] + list(range(7, len(slots))) + [len(slots) + 1]
         K, V = K[order].contiguous(), V[order].contiguous()
+        vlm = name.endswith("_vlm")
+        if vlm:
+            V = torch.einsum("nhd,de->nhe", V.float(), H).to(V.dtype).contiguous()
+            vf = V.reshape(-1, D)
+            vnorm = torch.sqrt((vf * vf).sum(-1, keepdim=True) + 1e-16)
+            out[f"{name}_vy"] = (vf / (vnorm + 1e-8)).reshape(V.shape).numpy()
+        os.environ["TURBOQUANT_V_LLOYD_MAX"] = "1" if vlm else "0"
 
         cache = torch.zeros(nb, bs, Hkv, slot, dtype=torch.uint8)
         _launch_rht(K, V, cache, slot_mapping, mids, cfg, D)
@@ -106,7 +120,7 @@ def main() -> None:
             NUM_KV_HEADS=Hkv, HEAD_DIM=D, BLOCK_SIZE=bs, NUM_KV_SPLITS=splits, KV_GROUP_SIZE=G,
             MSE_BITS=kb, MSE_BYTES=cfg.key_packed_size - 2, KPS=cfg.key_packed_size, VQB=vb,
             VAL_DATA_BYTES=cfg.value_data_bytes, ATTN_SCALE=scale, BLOCK_D=BLOCK_D, BLOCK_KV=4,
-            KEY_FP8=0, NORM_CORRECTION=nc, FP8_E4B15=0, V_LLOYD_MAX=0, num_warps=1, num_stages=1)
+            KEY_FP8=0, NORM_CORRECTION=nc, FP8_E4B15=0, V_LLOYD_MAX=int(vlm), num_warps=1, num_stages=1)
         o = torch.zeros(B, Hq, D)
         lse = torch.zeros(B, Hq)
         # the stock merge decides which splits exist from seq_lens alone; the reference only

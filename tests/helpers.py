@@ -84,12 +84,16 @@ def gate(out, ref, rtol=2e-3, atol=1e-3):
     return int((np.abs(out - ref) > atol + rtol * np.abs(ref)).sum())
 
 
-def tq_v1_compare_cache(cache, ref, slot_mapping, y, midpoints, d, key_bits, value_bits, block_size):
+def tq_v1_compare_cache(cache, ref, slot_mapping, y, midpoints, d, key_bits, value_bits, block_size,
+                        vy=None):
     """Compare two kv caches in the vLLM-v1 slot format ([nb, block_size, Hkv, slot] uint8).
 
     Returns counts: value-region bytes that differ, bytes that differ outside written slots, key
     codes that differ although the rotated value `y` ([n_tokens, Hkv, d]) is farther than 1e-6
-    from every midpoint, and the largest key-norm distance in fp16 ulps.
+    from every midpoint, and the largest key-norm distance in fp16 ulps.  With `vy` (the unit
+    values of a Lloyd-Max value cache, 4-bit codes) the value codes and the value norm are compared
+    the same way (`value_codes_differ_off_midpoint`, `value_norm_max_ulp`) and `value_bytes_differ`
+    counts the zero-point field only.
     """
     mse = d * key_bits // 8
     kps = mse + 2
@@ -98,7 +102,8 @@ def tq_v1_compare_cache(cache, ref, slot_mapping, y, midpoints, d, key_bits, val
     hkv = cache.shape[2]
     written = np.zeros(cache.shape[:3], bool)
     stats = dict(value_bytes_differ=0, other_bytes_differ=0, key_codes_differ_off_midpoint=0,
-                 key_codes_differ=0, key_norm_max_ulp=0)
+                 key_codes_differ=0, key_norm_max_ulp=0, value_codes_differ_off_midpoint=0,
+                 value_norm_max_ulp=0)
     mids = np.asarray(midpoints, np.float32)
     for tok, slot in enumerate(np.asarray(slot_mapping)):
         if slot < 0:
@@ -107,7 +112,18 @@ def tq_v1_compare_cache(cache, ref, slot_mapping, y, midpoints, d, key_bits, val
         written[blk, off, :] = True
         for h in range(hkv):
             a, b = cache[blk, off, h], ref[blk, off, h]
-            stats["value_bytes_differ"] += int((a[kps:used] != b[kps:used]).sum())
+            if vy is None:
+                stats["value_bytes_differ"] += int((a[kps:used] != b[kps:used]).sum())
+            else:
+                stats["value_bytes_differ"] += int((a[used - 2:used] != b[used - 2:used]).sum())
+                va = int(a[kps + vdb]) | (int(a[kps + vdb + 1]) << 8)
+                vb_ = int(b[kps + vdb]) | (int(b[kps + vdb + 1]) << 8)
+                stats["value_norm_max_ulp"] = max(stats["value_norm_max_ulp"], abs(va - vb_))
+                ca = np.unpackbits(a[kps:kps + vdb], bitorder="little").reshape(d, 4)
+                cb = np.unpackbits(b[kps:kps + vdb], bitorder="little").reshape(d, 4)
+                vdiff = (ca != cb).any(axis=1)
+                vnear = np.abs(vy[tok, h][:, None] - mids[None, :]).min(axis=1) < 1e-6
+                stats["value_codes_differ_off_midpoint"] += int((vdiff & ~vnear).sum())
             stats["other_bytes_differ"] += int((a[used:] != b[used:]).sum())
             na = int(a[mse]) | (int(a[mse + 1]) << 8)
             nb_ = int(b[mse]) | (int(b[mse + 1]) << 8)

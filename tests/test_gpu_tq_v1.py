@@ -16,7 +16,8 @@ from helpers import gate, tq_v1_compare_cache
 pytestmark = pytest.mark.gpu
 
 CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8",
-         "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc"]
+         "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc",
+         "d128_k4v4_nc_vlm", "d64_k4v4_vlm", "d128_k3v4_nc_vlm"]   # _vlm: Lloyd-Max value codes
 cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
@@ -32,16 +33,18 @@ def test_store_vs_reference_kernel_and_oracle(oracle, golden, name):
     cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
     assert cfg.slot_size_aligned == slot
     cache = torch.zeros((nb, bs, Hkv, slot), dtype=torch.uint8, device="cuda")
+    vlm = name.endswith("_vlm")    # (the fixture's V is already rotated for these cases)
     tq_v1.launch_store(cu(g[f"{name}_K"]), cu(g[f"{name}_V"]), cache, cu(g[f"{name}_slot_mapping"]),
-                       g[f"{name}_midpoints"], cfg, D)
+                       g[f"{name}_midpoints"], cfg, D, v_lloyd_max=vlm)
     got = cache.cpu().numpy()
     st = tq_v1_compare_cache(got, g[f"{name}_cache"], g[f"{name}_slot_mapping"], g[f"{name}_y"],
-                             g[f"{name}_midpoints"], D, kb, vb, bs)
+                             g[f"{name}_midpoints"], D, kb, vb, bs, vy=g[f"{name}_vy"] if vlm else None)
     assert st["value_bytes_differ"] == 0 and st["other_bytes_differ"] == 0, st
     assert st["key_codes_differ_off_midpoint"] == 0 and st["key_norm_max_ulp"] <= 1, st
+    assert st["value_codes_differ_off_midpoint"] == 0 and st["value_norm_max_ulp"] <= 1, st
     ref = np.zeros_like(got)
     oracle.tq_store(g[f"{name}_K"], g[f"{name}_V"], ref, g[f"{name}_slot_mapping"],
-                    g[f"{name}_midpoints"], kb, vb)
+                    g[f"{name}_midpoints"], kb, vb, value_lloyd_max=vlm)
     np.testing.assert_array_equal(got, ref)
 
 
@@ -57,7 +60,7 @@ def test_decode_vs_reference_kernels(oracle, golden, name):
     out = tq_v1.decode_attention(cu(g[f"{name}_q"]), cu(g[f"{name}_cache"]), cu(g[f"{name}_block_table"]),
                                  cu(g[f"{name}_seq_lens"]), g[f"{name}_centroids"], cfg, D ** -0.5,
                                  num_kv_splits=splits, kv_start_offset=cu(g[f"{name}_kv_start"]),
-                                 mid_o=mid_o, lse=lse)
+                                 mid_o=mid_o, lse=lse, v_lloyd_max=name.endswith("_vlm"))
     ref = g[f"{name}_mid_o"]
     m = mid_o.cpu().numpy()
     live = np.isfinite(ref[..., D])
@@ -67,7 +70,8 @@ def test_decode_vs_reference_kernels(oracle, golden, name):
     assert np.all(m[..., :D][~live] == 0)
     o_ref, _, lse_ref = oracle.tq_decode(g[f"{name}_q"], g[f"{name}_cache"], g[f"{name}_block_table"],
                                          g[f"{name}_seq_lens"], g[f"{name}_centroids"], kb, vb, D ** -0.5,
-                                         splits, norm_correction=bool(nc), kv_start=g[f"{name}_kv_start"])
+                                         splits, norm_correction=bool(nc), kv_start=g[f"{name}_kv_start"],
+                                         value_lloyd_max=name.endswith("_vlm"))
     if f"{name}_out" in g.files:
         o_ref, lse_ref = g[f"{name}_out"], g[f"{name}_lse"]
     np.testing.assert_allclose(out.cpu().numpy(), o_ref, rtol=2e-4, atol=2e-5)
@@ -75,10 +79,13 @@ def test_decode_vs_reference_kernels(oracle, golden, name):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("D,kb,vb,G,nc", [(128, 4, 4, 4, True), (64, 2, 3, 7, False), (256, 3, 8, 2, True),
-                                          (128, 3, 2, 8, False), (64, 1, 1, 4, True), (128, 1, 4, 2, False),
-                                          (256, 4, 1, 2, True)])
-def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, dtype):
+@pytest.mark.parametrize("D,kb,vb,G,nc,lm", [
+    (128, 4, 4, 4, True, False), (64, 2, 3, 7, False, False), (256, 3, 8, 2, True, False),
+    (128, 3, 2, 8, False, False), (64, 1, 1, 4, True, False), (128, 1, 4, 2, False, False),
+    (256, 4, 1, 2, True, False),
+    # Lloyd-Max value codes (with the fused value rotation, as the reference always pairs them)
+    (128, 4, 4, 4, True, True), (64, 4, 4, 7, False, True), (256, 3, 4, 2, True, True)])
+def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, lm, dtype):
     """Ragged batch, 16-bit inputs, values kept in the rotated space, several splits."""
     from fused_turboquant_b200 import tq_v1
     rng = np.random.default_rng(D + kb + vb)
@@ -98,28 +105,30 @@ def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, dtype):
     cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, nc)
     slot = cfg.slot_size_aligned
     cache = torch.zeros((nb, bs, Hkv, slot), dtype=torch.uint8, device="cuda")
-    tq_v1.launch_store(K.cuda(), V.cuda(), cache, torch.from_numpy(slots).cuda(), mids_t, cfg, v_rotate=True)
+    tq_v1.launch_store(K.cuda(), V.cuda(), cache, torch.from_numpy(slots).cuda(), mids_t, cfg, v_rotate=True,
+                       v_lloyd_max=lm)
     # oracle: values rotated first (plain Hadamard transform of the 16-bit inputs, kept in fp32 ->
     # the library rounds the rotated values back to the input dtype before quantising them)
     v_rot = torch.from_numpy(oracle.rht(V.float().numpy().reshape(-1, D), None)).to(dtype).float().numpy()
     ref = np.zeros((nb, bs, Hkv, slot), np.uint8)
-    oracle.tq_store(K.float().numpy(), v_rot.reshape(n, Hkv, D), ref, slots, mids_t.numpy(), kb, vb)
+    oracle.tq_store(K.float().numpy(), v_rot.reshape(n, Hkv, D), ref, slots, mids_t.numpy(), kb, vb,
+                    value_lloyd_max=lm, value_sum_order=1)
     np.testing.assert_array_equal(cache.cpu().numpy(), ref)
     out = tq_v1.decode_attention(q.cuda(), cache, torch.from_numpy(bt).cuda(),
                                  torch.tensor(seq, dtype=torch.int32).cuda(), cent_t, cfg, D ** -0.5,
-                                 num_kv_splits=splits, v_rotate=True, out_dtype=torch.float32)
+                                 num_kv_splits=splits, v_rotate=True, out_dtype=torch.float32, v_lloyd_max=lm)
     o_ref, _, _ = oracle.tq_decode(q.float().numpy(), ref, bt, np.array(seq, np.int32), cent_t.numpy(), kb, vb,
-                                   D ** -0.5, splits, norm_correction=nc, rotate_out=True)
+                                   D ** -0.5, splits, norm_correction=nc, rotate_out=True, value_lloyd_max=lm)
     # 16-bit queries take the tensor-core kernel where it exists (fp16 centroids / weights, fp32
     # accumulation): the north-star gate; 8-bit values, 1-bit codes and head_dim 256 stay on the
     # fp32 kernel
-    if vb == 8 or D == 256 or 1 in (kb, vb):
+    if vb == 8 or D == 256 or 1 in (kb, vb) or lm:
         assert gate(out.cpu().numpy(), o_ref, 2e-4, 1e-4) == 0
     else:
         assert gate(out.cpu().numpy(), o_ref) == 0, np.abs(out.cpu().numpy() - o_ref).max()
     out16 = tq_v1.decode_attention(q.cuda(), cache, torch.from_numpy(bt).cuda(),
                                    torch.tensor(seq, dtype=torch.int32).cuda(), cent_t, cfg, D ** -0.5,
-                                   num_kv_splits=splits, v_rotate=True)
+                                   num_kv_splits=splits, v_rotate=True, v_lloyd_max=lm)
     assert out16.dtype == dtype
     assert torch.equal(out16, out.to(dtype)) or gate(out16.float().cpu().numpy(), o_ref) <= out16.numel() // 500
 

@@ -7,7 +7,8 @@ import pytest
 from helpers import tq_v1_compare_cache
 
 CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8",
-         "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc"]
+         "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc",
+         "d128_k4v4_nc_vlm", "d64_k4v4_vlm", "d128_k3v4_nc_vlm"]   # _vlm: Lloyd-Max value codes
 
 
 @pytest.mark.parametrize("name", CASES)
@@ -16,10 +17,14 @@ def test_store_matches_reference_store_kernel(oracle, golden, name):
     D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = (int(v) for v in g[f"{name}_meta"])
     assert slot == oracle.tq_slot_bytes(D, kb, vb)
     cache = np.zeros((nb, bs, Hkv, slot), np.uint8)
+    vlm = name.endswith("_vlm")
     y = oracle.tq_store(g[f"{name}_K"], g[f"{name}_V"], cache, g[f"{name}_slot_mapping"],
-                        g[f"{name}_midpoints"], kb, vb, return_rotated=True)
+                        g[f"{name}_midpoints"], kb, vb, return_rotated=True, value_lloyd_max=vlm)
     stats = tq_v1_compare_cache(cache, g[f"{name}_cache"], g[f"{name}_slot_mapping"], y,
-                                g[f"{name}_midpoints"], D, kb, vb, bs)
+                                g[f"{name}_midpoints"], D, kb, vb, bs,
+                                vy=g[f"{name}_vy"] if vlm else None)
+    # (Lloyd-Max values: codes and norm are held to the same bar as the key's)
+    assert stats["value_codes_differ_off_midpoint"] == 0 and stats["value_norm_max_ulp"] <= 1
     # value codes / scale / zero and every untouched byte: identical.  Key codes: identical except
     # where the rotated value sits on a midpoint (none expected in these fixtures); key norms:
     # at most one fp16 ulp (summation order of the squares is not fixed by the reference)
@@ -38,7 +43,8 @@ def test_decode_matches_reference_decode_kernels(oracle, golden, name):
     out, mid_o, lse = oracle.tq_decode(g[f"{name}_q"], g[f"{name}_cache"], g[f"{name}_block_table"],
                                        g[f"{name}_seq_lens"], g[f"{name}_centroids"], kb, vb,
                                        D ** -0.5, splits, norm_correction=bool(nc),
-                                       kv_start=g[f"{name}_kv_start"])
+                                       kv_start=g[f"{name}_kv_start"],
+                                       value_lloyd_max=name.endswith("_vlm"))
     ref = g[f"{name}_mid_o"]
     live = np.isfinite(ref[..., D])
     np.testing.assert_array_equal(np.isfinite(mid_o[..., D]), live)      # same empty splits
