@@ -25,11 +25,15 @@ NVCC_FLAGS = [
 ]
 
 # (source, object suffix, extra defines)
-UNITS = [("ftq_api.cu", "api", [])]
-for _d in (64, 128, 256):
-    UNITS.append(("ftq_encode_inst.cu", f"encode_d{_d}", [f"-DFTQ_D={_d}"]))
+# (the slowest units first: the pool then finishes them while the short ones fill the gaps)
+UNITS = []
+for _d in (256, 128, 64):
+    UNITS.append(("ftq_tq_v1_inst.cu", f"tq_v1_store_d{_d}", [f"-DFTQ_D={_d}", "-DFTQ_TQ_PART=0"]))
+    UNITS.append(("ftq_tq_v1_inst.cu", f"tq_v1_decode_d{_d}", [f"-DFTQ_D={_d}", "-DFTQ_TQ_PART=1"]))
+for _d in (256, 128, 64):
     UNITS.append(("ftq_attn_inst.cu", f"attn_d{_d}", [f"-DFTQ_D={_d}"]))
-    UNITS.append(("ftq_tq_v1_inst.cu", f"tq_v1_d{_d}", [f"-DFTQ_D={_d}"]))
+    UNITS.append(("ftq_encode_inst.cu", f"encode_d{_d}", [f"-DFTQ_D={_d}"]))
+UNITS.append(("ftq_api.cu", "api", []))
 
 
 def _nvcc() -> str:

@@ -857,13 +857,15 @@ extern "C" int ftq_paged_decode_attn_static(
 // ------------------------------------------------------------------ vLLM-v1 slot format
 
 namespace {
-bool tq_bits_ok(int kb, int vb) { return kb >= 1 && kb <= 4 && ((vb >= 1 && vb <= 4) || vb == 8); }
+// key_bits 8 = FP8 (e4m3) keys, as in vLLM's stock TurboQuantConfig
+bool tq_bits_ok(int kb, int vb) { return ((kb >= 1 && kb <= 4) || kb == 8) && ((vb >= 1 && vb <= 4) || vb == 8); }
+int tq_key_bytes(int d, int kb) { return kb == 8 ? d : d * kb / 8 + 2; }
 bool even(int64_t v) { return (v & 1) == 0; }
 }  // namespace
 
 extern "C" int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits) {
     if (!dim_ok(head_dim) || !tq_bits_ok(key_bits, value_bits)) return -1;
-    const int s = head_dim * key_bits / 8 + 2 + ftq::tq_value_bytes(head_dim, value_bits) + 4;
+    const int s = tq_key_bytes(head_dim, key_bits) + ftq::tq_value_bytes(head_dim, value_bits) + 4;
     return s + (s & 1);
 }
 
@@ -875,7 +877,7 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
                             int block_size, const int64_t* slot_mapping, void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
-        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 / 1,2,3,4,8)", key_bits,
+        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 or 8 = FP8 / 1,2,3,4,8)", key_bits,
                     value_bits);
     if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
     if (rotate_values && value_bits == 8)
@@ -883,7 +885,10 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
     if (n_tokens < 0 || Hkv <= 0 || block_size <= 0) return fail(FTQ_ERR_INVALID, "bad shape");
     if (n_tokens * Hkv >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "n_tokens * Hkv must be below 2^31");
     if (n_tokens == 0) return FTQ_OK;
-    if (!key || !value || !kv_cache || !slot_mapping || !midpoints_host)
+    const bool key_fp8 = key_bits == 8;  // no codebook: midpoints_host may be NULL
+    if (key_fp8 && value_lloyd_max && value_bits == 4)
+        return fail(FTQ_ERR_UNSUPPORTED, "Lloyd-Max value codes need a key codebook (FP8 keys have none)");
+    if (!key || !value || !kv_cache || !slot_mapping || (!key_fp8 && !midpoints_host))
         return fail(FTQ_ERR_INVALID, "NULL pointer argument");
     const int64_t es = static_cast<int64_t>(dtype_size(dtype));
     if (!aligned(key, 16) || !aligned(value, 16) || (token_stride * es) % 16 || (head_stride * es) % 16)
@@ -906,7 +911,7 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
     p.block_size = block_size;
     p.div_block = ftq::make_fastdiv(static_cast<uint32_t>(block_size));
     p.slot_mapping = slot_mapping;
-    const int nmid = (1 << key_bits) - 1;
+    const int nmid = key_fp8 ? 0 : (1 << key_bits) - 1;
     for (int i = 0; i < ftq::kTqMaxMid; i++) p.midpoints[i] = i < nmid ? midpoints_host[i] : FLT_MAX;
     for (int i = 1; i < nmid; i++)
         if (!(midpoints_host[i] > midpoints_host[i - 1]))
@@ -936,7 +941,7 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
                              float* mid_o, void* out, int out_dtype, float* lse, void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
-        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 / 1,2,3,4,8)", key_bits,
+        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 or 8 = FP8 / 1,2,3,4,8)", key_bits,
                     value_bits);
     if (!dtype_ok(q_dtype) || !dtype_ok(out_dtype)) return fail(FTQ_ERR_INVALID, "bad dtype");
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || block_size <= 0 || max_blocks <= 0)
@@ -945,7 +950,10 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
         return fail(FTQ_ERR_INVALID, "num_kv_splits must be in [1, 65535]");
     if (B == 0) return FTQ_OK;
     if (B > 65535) return fail(FTQ_ERR_INVALID, "B must be at most 65535 per call");
-    if (!q || !kv_cache || !block_table || !seq_lens || !centroids_host || !mid_o || !out)
+    const bool key_fp8 = key_bits == 8;  // no codebook: centroids_host may be NULL
+    if (key_fp8 && value_lloyd_max && value_bits == 4)
+        return fail(FTQ_ERR_UNSUPPORTED, "Lloyd-Max value codes need a key codebook (FP8 keys have none)");
+    if (!q || !kv_cache || !block_table || !seq_lens || (!key_fp8 && !centroids_host) || !mid_o || !out)
         return fail(FTQ_ERR_INVALID, "NULL pointer argument");
     if (!aligned(q, 16) || !aligned(out, 4) || !aligned(mid_o, 4))
         return fail(FTQ_ERR_INVALID, "q must be 16-byte aligned, out and mid_o 4-byte aligned");
@@ -975,8 +983,12 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
     p.n_hpass = (Hq / Hkv + gh - 1) / gh;
     if (static_cast<int64_t>(Hkv) * p.n_hpass > 65535) return fail(FTQ_ERR_INVALID, "too many heads");
     p.rsqrt_d = 1.0f / sqrtf(static_cast<float>(head_dim));
-    int rc = pack_levels(centroids_host, key_bits, &p.centroids);
-    if (rc) return rc;
+    if (key_fp8) {
+        memset(&p.centroids, 0, sizeof(p.centroids));
+    } else {
+        const int rc = pack_levels(centroids_host, key_bits, &p.centroids);
+        if (rc) return rc;
+    }
     p.mid_o = mid_o;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaErrorInvalidValue;
@@ -985,7 +997,7 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
     const int group = Hq / Hkv;
     // (its copy loop reads whole aligned words: a cache that starts on an odd 2-byte boundary -- a
     // view at an offset -- stays on the fp32 kernel, which reads 2-byte pieces)
-    const bool mma = q_dtype != FTQ_F32 && group <= 8 && key_bits >= 2 && value_bits >= 2 &&
+    const bool mma = q_dtype != FTQ_F32 && group <= 8 && key_bits >= 2 && key_bits <= 4 && value_bits >= 2 &&
                      value_bits != 8 && head_dim != 256 && aligned(kv_cache, 4) &&
                      !p.value_lloyd_max;
     if (mma) {

@@ -17,9 +17,16 @@
 //          (vllm_plugin/v1_backend.py:1068-1085) and, optionally, the Hadamard transform that
 //          maps an output accumulated over rotated values back (v1_backend.py:1088-1092).
 //
+// Key "bits" = 8 selects FP8 keys (vLLM's stock TurboQuantConfig: key_quant_bits == 8;
+// triton_inkernel_store.py:80-91, triton_decode_offset.py:175-194): the key field is D bytes of
+// e4m3 (rotated key * norm, round to nearest even, saturating, as the cvt instruction the
+// reference's cast compiles to) with no norm behind it; score = sum(q_rot * k) * scale.
+//
 // The order in which the key's squares are added is not fixed by the reference (a Triton
 // reduction); here: 8 running sums in register order, combined pairwise over the octet.
 #pragma once
+
+#include <cuda_fp8.h>
 
 #include <type_traits>
 
@@ -99,13 +106,15 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
     static_assert(!LMV || VB == 4, "Lloyd-Max value codes are 4-bit");
     constexpr int E = D / kOctet;
     constexpr int NCH = E / 8;
-    constexpr int MSE = D * KB / 8;
-    constexpr int KPS = MSE + 2;
+    constexpr bool KFP8 = KB == 8;
+    static_assert(!(KFP8 && LMV), "Lloyd-Max value codes use the key midpoints");
+    constexpr int MSE = D * KB / 8;                      // (FP8 keys: D bytes)
+    constexpr int KPS = MSE + (KFP8 ? 0 : 2);
     constexpr int VDB = tq_value_bytes(D, VB);
     constexpr int VMAX = (1 << VB) - 1;
-    constexpr int NMID = (1 << KB) - 1;
-    constexpr int NW = KB == 2 ? (E + 15) / 16 : E / 8;  // (unused for 1-bit codes)
-    constexpr int KT = KB == 1 ? 2 : KB;                 // transposition constants: 2..4 bits only
+    constexpr int NMID = KFP8 ? 0 : (1 << KB) - 1;
+    constexpr int NW = KB == 2 ? (E + 15) / 16 : E / 8;  // (unused for 1-bit codes and FP8 keys)
+    constexpr int KT = (KB == 1 || KFP8) ? 2 : KB;       // transposition constants: 2..4 bits only
     constexpr int VT = (ROTV && VB != 1) ? VB : 4;
 
     const int lane = threadIdx.x & 31;
@@ -165,11 +174,27 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
         for (int r = 0; r < E; r++) y[r] = __fdiv_rn(y[r], den);
         octet_fwht<E>(y, lane);  // -> (lane l, register k) = coordinate l + 8k
 
+        if constexpr (KFP8) {
+            // lane l holds the coordinates l + 8k: neighbouring lanes trade bytes so that each
+            // stores 16-bit pairs (the even lane those of even k, the odd lane those of odd k)
+            const bool odd = lane & 1;
+#pragma unroll
+            for (int k = 0; k < E; k += 2) {
+                const uint32_t a = __nv_cvt_float_to_fp8(
+                    __fmul_rn(__fmul_rn(y[k], p.rsqrt_d), norm), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t b = __nv_cvt_float_to_fp8(
+                    __fmul_rn(__fmul_rn(y[k + 1], p.rsqrt_d), norm), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t recv = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+                const uint32_t pair = odd ? (recv | (b << 8)) : (a | (recv << 8));
+                const int coord = odd ? t - 1 + 8 * (k + 1) : t + 8 * k;
+                if (store) *reinterpret_cast<uint16_t*>(dst + coord) = static_cast<uint16_t>(pair);
+            }
+        }
         uint32_t w[NW];
 #pragma unroll
         for (int i = 0; i < NW; i++) w[i] = 0u;
 #pragma unroll
-        for (int k = 0; k < E; k++) {
+        for (int k = 0; k < (KFP8 ? 0 : E); k++) {
             const float yv = __fmul_rn(y[k], p.rsqrt_d);
             uint32_t code = 0;
 #pragma unroll
@@ -185,7 +210,7 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
         }
         if constexpr (KB == 1) emit_bits1<E>(w[0], dst, store, lane);
 #pragma unroll
-        for (int i = 0; i < (KB == 1 ? 0 : NW); i++) {
+        for (int i = 0; i < ((KB == 1 || KFP8) ? 0 : NW); i++) {
             const uint32_t o = octet_transpose_items<KT>(w[i], tc);
             if constexpr (KB == 3) {
                 const int g0 = (4 * t) / 3;
@@ -199,7 +224,7 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
                 if (store && widx < MSE / 4) store_u32_as_halves(dst + 4 * widx, o);
             }
         }
-        if (store && t == 0)
+        if (!KFP8 && store && t == 0)
             *reinterpret_cast<__half*>(dst + MSE) = __float2half_rn(norm);
 
         // ---- value: per-vector uniform quantisation; a lane owns runs of 8 consecutive coordinates
@@ -372,10 +397,12 @@ __global__ void __launch_bounds__(kAttnThreads)
 tq_split_kernel(const TqDecodeParams p) {
     constexpr int E = AttnCfg<D>::E;
     constexpr int GH = AttnCfg<D>::GH;
+    constexpr bool KFP8 = KB == 8;   // D bytes of e4m3, no norm field
     constexpr int MSE = D * KB / 8;
+    constexpr int NU = KFP8 ? 0 : 1;  // 16-bit units of the key norm
     constexpr int VDB = tq_value_bytes(D, VB);
     constexpr int NBK = MSE / kOctet, NBV = VDB / kOctet;
-    constexpr int SLOT_U16 = (MSE + 2 + VDB + 4) / 2;
+    constexpr int SLOT_U16 = (MSE + 2 * NU + VDB + 4) / 2;
 
     // tile buffers; once the loop is over the K/V areas double as the cross-warp merge area
     constexpr int KROW = tq_row_stride(MSE, NBK), VROW = tq_row_stride(VDB, NBV);
@@ -476,12 +503,12 @@ tq_split_kernel(const TqDecodeParams p) {
     auto place_u16 = [&](int tk, int j, uint32_t v) {
         if (j < MSE / 2) {
             reinterpret_cast<uint16_t*>(kbuf)[tk * (KROW / 2) + j] = static_cast<uint16_t>(v);
-        } else if (j == MSE / 2) {
+        } else if (NU && j == MSE / 2) {
             meta[tk] = __half2float(__ushort_as_half(static_cast<uint16_t>(v)));
-        } else if (j < MSE / 2 + 1 + VDB / 2) {
-            reinterpret_cast<uint16_t*>(vbuf)[tk * (VROW / 2) + j - MSE / 2 - 1] = static_cast<uint16_t>(v);
+        } else if (j < MSE / 2 + NU + VDB / 2) {
+            reinterpret_cast<uint16_t*>(vbuf)[tk * (VROW / 2) + j - MSE / 2 - NU] = static_cast<uint16_t>(v);
         } else if (j < SLOT_U16) {
-            meta[(j - (MSE / 2 + VDB / 2)) * kTqTileTokens + tk] =
+            meta[(j - (MSE / 2 + NU + VDB / 2) + 1) * kTqTileTokens + tk] =
                 __half2float(__ushort_as_half(static_cast<uint16_t>(v)));
         }
     };
@@ -491,7 +518,8 @@ tq_split_kernel(const TqDecodeParams p) {
     // 2-byte boundary, so the words are shifted by 16 bits for every other slot and the first /
     // last unit is fetched on its own rather than touching bytes outside the slot.  The loads of
     // tile i+1 are issued before the math of tile i and consumed after it.
-    constexpr int NWORDS = (MSE + VDB + 6 + 2) / 4;  // words covering the used bytes (last one half used)
+    constexpr int USED = MSE + 2 * NU + VDB + 4;     // bytes of a slot that are read
+    constexpr int NWORDS = (USED + 2 + 3) / 4;       // aligned words covering them at either alignment
     constexpr int HW = (NWORDS + 1) / 2;             // words per thread
     constexpr bool PREFETCH = HW <= 34;
     uint32_t raw[PREFETCH ? HW + 1 : 1];
@@ -506,14 +534,17 @@ tq_split_kernel(const TqDecodeParams p) {
 #pragma unroll
             for (int i = 0; i <= HW; i++) {
                 const int m = ld_m0 + i;
+                // the slot occupies bytes [lo, hi) of the aligned range: a word that is only half
+                // inside is fetched as that half, one that is outside not at all
+                const int lo = 2 * raw_mis, hi = lo + USED, b0 = 4 * m;
                 uint32_t v = 0u;
-                if (live && m < NWORDS) {
-                    if (m == 0 && raw_mis)
-                        v = static_cast<uint32_t>(__ldg(reinterpret_cast<const uint16_t*>(sp))) << 16;
-                    else if (m == NWORDS - 1 && !raw_mis)
-                        v = __ldg(reinterpret_cast<const uint16_t*>(sp + 4 * m));
+                if (live && b0 < hi) {
+                    if (b0 < lo)
+                        v = static_cast<uint32_t>(__ldg(reinterpret_cast<const uint16_t*>(al + b0 + 2))) << 16;
+                    else if (b0 + 4 > hi)
+                        v = __ldg(reinterpret_cast<const uint16_t*>(al + b0));
                     else
-                        v = __ldg(reinterpret_cast<const uint32_t*>(al + 4 * m));
+                        v = __ldg(reinterpret_cast<const uint32_t*>(al + b0));
                 }
                 raw[i] = v;
             }
@@ -573,11 +604,19 @@ tq_split_kernel(const TqDecodeParams p) {
                 u64 cn2 = pk2(0.f, 0.f);
 #pragma unroll
                 for (int i = 0; i < EP; i++) {
-                    kv[i] = pk2(lut[extract_code<KB>(w, 2 * i)], lut[extract_code<KB>(w, 2 * i + 1)]);
-                    cn2 = fma2(kv[i], kv[i], cn2);
+                    if constexpr (KFP8) {
+                        const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(
+                            static_cast<__nv_fp8x2_storage_t>((w[i >> 1] >> (16 * (i & 1))) & 0xffffu),
+                            __NV_E4M3);
+                        const float2 f2 = __half22float2(__half2(h2));
+                        kv[i] = pk2(f2.x, f2.y);
+                    } else {
+                        kv[i] = pk2(lut[extract_code<KB>(w, 2 * i)], lut[extract_code<KB>(w, 2 * i + 1)]);
+                        cn2 = fma2(kv[i], kv[i], cn2);
+                    }
                 }
-                float kn = meta[tk];
-                if (p.norm_correction) {  // re-normalise the centroid vector to unit length
+                float kn = KFP8 ? 1.f : meta[tk];
+                if (!KFP8 && p.norm_correction) {  // re-normalise the centroid vector to unit length
                     float c0, c1;
                     upk2(cn2, c0, c1);
                     float cn = c0 + c1;

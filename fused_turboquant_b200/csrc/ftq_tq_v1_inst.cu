@@ -1,8 +1,16 @@
-// Instantiates the vLLM-v1 slot-format kernels for one head_dim (FTQ_D).
+// Instantiates the vLLM-v1 slot-format kernels for one head_dim (FTQ_D).  FTQ_TQ_PART selects
+// what this object holds, so that the halves compile in parallel: 0 = the store kernels,
+// 1 = the decode kernels (fp32 split, tensor-core split, merge); undefined = both.
 #include "ftq_launch.h"
 #include "ftq_tq_v1.cuh"
 #include "ftq_tq_v1_launch.h"
-#if FTQ_D != 256
+#if !defined(FTQ_TQ_PART) || FTQ_TQ_PART == 0
+#define FTQ_TQ_STORE 1
+#endif
+#if !defined(FTQ_TQ_PART) || FTQ_TQ_PART == 1
+#define FTQ_TQ_DECODE 1
+#endif
+#if FTQ_D != 256 && defined(FTQ_TQ_DECODE)
 #include "ftq_tq_v1_mma.cuh"
 #endif
 
@@ -14,13 +22,14 @@
 
 namespace ftq {
 
+#ifdef FTQ_TQ_STORE
 template <int KB, int VB, typename T>
 static cudaError_t store_run(const TqStoreParams& p, int value_mode, int64_t n_vec, cudaStream_t stream) {
     const int64_t want = (n_vec + 31) / 32;  // 8 warps x 4 vectors per CTA pass
     const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     const unsigned gx = static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
     const bool rotate_v = (value_mode & kTqRotateValues) != 0;
-    if constexpr (VB == 4) {
+    if constexpr (VB == 4 && KB != 8) {
         if (value_mode & kTqLloydMaxValues) {
             if (rotate_v) tq_store_kernel<FTQ_D, KB, VB, T, true, true><<<gx, 256, 0, stream>>>(p, n_vec);
             else tq_store_kernel<FTQ_D, KB, VB, T, false, true><<<gx, 256, 0, stream>>>(p, n_vec);
@@ -70,10 +79,14 @@ cudaError_t FTQ_CAT(launch_tq_store_d, FTQ_D)(int kb, int vb, int dtype, const T
         case 2: return store_by_vb<2>(vb, dtype, p, value_mode, n_vec, stream);
         case 3: return store_by_vb<3>(vb, dtype, p, value_mode, n_vec, stream);
         case 4: return store_by_vb<4>(vb, dtype, p, value_mode, n_vec, stream);
+        case 8: return store_by_vb<8>(vb, dtype, p, value_mode, n_vec, stream);  // FP8 keys
     }
     return cudaErrorInvalidValue;
 }
 
+#endif  // FTQ_TQ_STORE
+
+#ifdef FTQ_TQ_DECODE
 template <int KB, int VB>
 static cudaError_t split_run(const TqDecodeParams& p, cudaStream_t stream) {
     constexpr int smem = tq_split_smem_bytes<FTQ_D>(KB, VB);
@@ -102,6 +115,7 @@ cudaError_t FTQ_CAT(launch_tq_split_d, FTQ_D)(int kb, int vb, const TqDecodePara
         case 2: return split_by_vb<2>(vb, p, stream);
         case 3: return split_by_vb<3>(vb, p, stream);
         case 4: return split_by_vb<4>(vb, p, stream);
+        case 8: return split_by_vb<8>(vb, p, stream);  // FP8 keys
     }
     return cudaErrorInvalidValue;
 }
@@ -171,5 +185,7 @@ cudaError_t FTQ_CAT(launch_tq_merge_d, FTQ_D)(int out_dtype, const float* mid_o,
     }
     return cudaGetLastError();
 }
+
+#endif  // FTQ_TQ_DECODE
 
 }  // namespace ftq

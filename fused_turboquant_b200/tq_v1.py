@@ -26,34 +26,42 @@ from .kernels import _DT, _host_table, _ptr, _require_cuda, _stream, rht
 
 @dataclass(frozen=True)
 class TurboQuantSlotConfig:
-    """Slot layout of one (token, KV head): key codes | key norm f16 | value codes | scale f16 | zero f16."""
+    """Slot layout of one (token, KV head): key codes | key norm f16 | value codes | scale f16 | zero f16.
+
+    ``key_quant_bits == 8`` selects FP8 (e4m3) keys as vLLM's stock ``TurboQuantConfig`` does: the
+    key field is ``head_dim`` bytes with no norm behind it.  (The reference's 8-bit Lloyd-Max keys,
+    ``BoundaryTurboQuantConfig(key_use_fp8_at_8bit=False)``, are not supported.)
+    """
 
     head_dim: int
-    key_quant_bits: int       # 1..4: Lloyd-Max codes
+    key_quant_bits: int       # 1..4: Lloyd-Max codes; 8: FP8 keys
     value_quant_bits: int     # 1, 2, 3, 4 or 8: per-vector uniform codes
     norm_correction: bool = True
 
     def __post_init__(self):
         if self.head_dim not in (64, 128, 256):
             raise ValueError(f"head_dim must be 64, 128 or 256, got {self.head_dim}")
-        if self.key_quant_bits not in (1, 2, 3, 4):
-            raise ValueError(f"key_quant_bits must be 1, 2, 3 or 4, got {self.key_quant_bits}")
+        if self.key_quant_bits not in (1, 2, 3, 4, 8):
+            raise ValueError(f"key_quant_bits must be 1, 2, 3, 4 or 8 (FP8), got {self.key_quant_bits}")
         if self.value_quant_bits not in (1, 2, 3, 4, 8):
             raise ValueError(f"value_quant_bits must be 1, 2, 3, 4 or 8, got {self.value_quant_bits}")
 
-    key_fp8 = False
+    @property
+    def key_fp8(self) -> bool:
+        return self.key_quant_bits == 8
 
     @property
     def key_mse_bits(self) -> int:
-        return self.key_quant_bits
+        return 0 if self.key_fp8 else self.key_quant_bits
 
     @property
     def mse_bits(self) -> int:
-        return self.key_quant_bits
+        # (as in the reference: with FP8 keys the centroid table is sized for the values)
+        return self.value_quant_bits if self.key_fp8 else self.key_quant_bits
 
     @property
     def n_centroids(self) -> int:
-        return 2 ** self.key_quant_bits
+        return 2 ** self.mse_bits
 
     @property
     def effective_value_quant_bits(self) -> int:
@@ -61,6 +69,8 @@ class TurboQuantSlotConfig:
 
     @property
     def key_packed_size(self) -> int:
+        if self.key_fp8:
+            return self.head_dim
         return math.ceil(self.head_dim * self.key_quant_bits / 8) + 2
 
     @property
@@ -86,6 +96,20 @@ def midpoints_of(centroids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """(sorted fp32 centroids, their midpoints) as the reference derives them per layer."""
     c, _ = centroids.to(torch.float32).sort()
     return c, (c[:-1] + c[1:]) / 2
+
+
+def _key_bits(tq_config) -> int:
+    """key_quant_bits of a (possibly duck-typed) config; 8 must mean FP8 keys."""
+    kb = int(tq_config.key_quant_bits)
+    if kb == 8 and not getattr(tq_config, "key_fp8", True):
+        raise ValueError("8-bit Lloyd-Max key codes are not supported (8 key bits = FP8 keys)")
+    return kb
+
+
+def _table_ptr(table, fp8: bool):
+    # FP8 keys have no key codebook: whatever table the caller holds (the reference sizes it for the
+    # values then) is not read
+    return None if fp8 else _lib.fptr(_host_table(table))
 
 
 def _cache_strides(kv_cache: torch.Tensor) -> tuple[int, int, int]:
@@ -132,11 +156,12 @@ def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
     if kv_cache.shape[3] < tq_config.slot_size:
         raise ValueError(f"kv_cache slots of {kv_cache.shape[3]} bytes are smaller than {tq_config.slot_size}")
     sm = slot_mapping.to(device=key.device, dtype=torch.int64).contiguous()
+    kb = _key_bits(tq_config)
     with torch.cuda.device(key.device):
         rc = _lib.load().ftq_tq_store(
             _ptr(key), _ptr(value), _DT[key.dtype], n, hkv, d, key.stride(0), key.stride(1),
-            tq_config.key_quant_bits, tq_config.value_quant_bits, int(rotate_in_kernel),
-            int(bool(v_lloyd_max)), _lib.fptr(_host_table(midpoints)), _ptr(kv_cache), sb, sp, sh, kv_cache.shape[1],
+            kb, tq_config.value_quant_bits, int(rotate_in_kernel),
+            int(bool(v_lloyd_max)), _table_ptr(midpoints, kb == 8), _ptr(kv_cache), sb, sp, sh, kv_cache.shape[1],
             _ptr(sm), _stream(key.device))
     _lib.check(rc, "ftq_tq_store")
 
@@ -180,12 +205,13 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
         output = torch.empty((B, hq, d), dtype=odt, device=dev)
     elif output.shape != (B, hq, d) or not output.is_contiguous() or output.dtype not in _DT:
         raise ValueError("output must be a contiguous [B, Hq, D] tensor of a supported dtype")
+    kb = _key_bits(tq_config)
     with torch.cuda.device(dev):
         rc = _lib.load().ftq_tq_decode(
             _ptr(query), _DT[query.dtype], B, hq, hkv, d, _ptr(kv_cache), sb, sp, sh,
             kv_cache.shape[1], _ptr(bt), bt.shape[1], _ptr(sl), _ptr(ks),
-            tq_config.key_quant_bits, tq_config.value_quant_bits, int(tq_config.norm_correction),
-            int(v_rotate), int(bool(v_lloyd_max)), _lib.fptr(_host_table(centroids)), float(scale),
+            kb, tq_config.value_quant_bits, int(tq_config.norm_correction),
+            int(v_rotate), int(bool(v_lloyd_max)), _table_ptr(centroids, kb == 8), float(scale),
             num_kv_splits,
             _ptr(mid_o), _ptr(output), _DT[output.dtype], _ptr(lse), _stream(dev))
     _lib.check(rc, "ftq_tq_decode")

@@ -258,9 +258,13 @@ int ftq_v0_gather(const uint8_t *kv_cache, int64_t num_blocks, int block_size, i
  * be even.  A slot holds
  *     [key codes D*kb/8 | key norm f16 | value codes D*vb/8 (D for vb = 8) | scale f16 | zero f16]
  * (vllm_plugin/boundary_tq_config.py:66-81; ftq_tq_slot_bytes returns its size rounded
- * up to even).  Supported: head_dim 64/128/256, key_bits 1/2/3/4 (Lloyd-Max codes),
- * value_bits 1/2/3/4/8 (per-vector uniform codes; 4-bit values optionally Lloyd-Max codes).
- * FP8 keys and 8-bit key codes return FTQ_ERR_UNSUPPORTED.
+ * up to even).  Supported: head_dim 64/128/256, key_bits 1/2/3/4 (Lloyd-Max codes) or 8,
+ * which selects FP8 keys as vLLM's stock TurboQuantConfig does (key_quant_bits == 8;
+ * triton_inkernel_store.py:80-91): the key field is then D bytes of e4m3 (rotated key * norm,
+ * round to nearest even, saturating) with NO norm field, and midpoints_host / centroids_host
+ * may be NULL; value_bits 1/2/3/4/8 (per-vector uniform codes; 4-bit values optionally
+ * Lloyd-Max codes).  The reference's 8-bit Lloyd-Max key codes (256 centroids, boundary
+ * layers only) are not available.
  */
 int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits);
 

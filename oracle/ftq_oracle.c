@@ -487,6 +487,39 @@ static void tq_pack_bits(const int *idx, uint8_t *out, int d, int bits) {
     ftq_oracle_pack(tmp, out, d, bits);
 }
 
+/* fp32 -> FP8 e4m3 (1-4-3, bias 7, no infinities, 0x7f = NaN): round to nearest even, finite
+ * overflow saturates to +-448 -- the semantics of the conversion instruction that the reference's
+ * `.to(tl.float8e4nv)` (triton_inkernel_store.py:84-87) compiles to on a GPU. */
+static uint8_t f32_to_e4m3(float x) {
+    uint8_t sign = signbit(x) ? 0x80 : 0;
+    if (isnan(x)) return (uint8_t)(sign | 0x7f);
+    double a = fabs((double)x);
+    if (a >= 464.0) return (uint8_t)(sign | 0x7e); /* 464 = halfway to the absent 512: saturate */
+    int e;
+    int q; /* value = q * 2^(e-3) with q in [8, 16), or a subnormal multiple of 2^-9 */
+    if (a < 0.015625) { /* below 2^-6: multiples of 2^-9 */
+        double r = nearbyint(a * 512.0); /* default rounding mode: to nearest even */
+        q = (int)r;
+        if (q == 8) return (uint8_t)(sign | 0x08);
+        return (uint8_t)(sign | q);
+    }
+    double m = frexp(a, &e); /* a = m * 2^e, m in [0.5, 1) */
+    q = (int)nearbyint(m * 16.0); /* in [8, 16] */
+    e -= 1;                       /* a ~ (q / 8) * 2^e */
+    if (q == 16) { q = 8; e += 1; }
+    int be = e + 7;
+    if (be > 15 || (be == 15 && q - 8 > 6)) return (uint8_t)(sign | 0x7e);
+    return (uint8_t)(sign | (be << 3) | (q - 8));
+}
+static float e4m3_to_f32(uint8_t b) {
+    int be = (b >> 3) & 0xf, m = b & 7;
+    float v;
+    if (be == 0xf && m == 7) return NAN;
+    if (be == 0) v = ldexpf((float)m, -9);
+    else v = ldexpf((float)(8 + m), be - 7 - 3);
+    return (b & 0x80) ? -v : v;
+}
+
 static void put_f16(uint8_t *dst, float v) {
     uint16_t h = ftq_oracle_f32_to_f16(v);
     dst[0] = (uint8_t)(h & 0xff);
@@ -506,9 +539,10 @@ void ftq_oracle_tq_store(const float *key, const float *value, int64_t n_tokens,
                          int64_t stride_block, int64_t stride_pos, int64_t stride_head,
                          int block_size, const int64_t *slot_mapping, float *y_out,
                          int value_lloyd_max, int value_sum_order) {
-    const int n_cent = 1 << key_bits;
+    const int key_fp8 = key_bits == 8; /* FP8 keys: d bytes of e4m3(y * norm), no norm field */
+    const int n_cent = key_fp8 ? 1 : 1 << key_bits;
     const int mse_bytes = d * key_bits / 8;
-    const int kps = mse_bytes + 2;
+    const int kps = mse_bytes + (key_fp8 ? 0 : 2);
     const int vdb = value_bits == 8 ? d : d * value_bits / 8;
     const int vmax = (1 << value_bits) - 1;
     const float rs = 1.0f / sqrtf((float)d);
@@ -540,8 +574,15 @@ void ftq_oracle_tq_store(const float *key, const float *value, int64_t n_tokens,
                 idx[i] = c;
             }
             if (y_out) memcpy(y_out + (tok * Hkv + h) * d, y, sizeof(float) * d);
-            tq_pack_bits(idx, dst, d, key_bits);
-            put_f16(dst + mse_bytes, norm);
+            if (key_fp8) {
+                for (int i = 0; i < d; i++) {
+                    float un = y[i] * norm;
+                    dst[i] = f32_to_e4m3(un);
+                }
+            } else {
+                tq_pack_bits(idx, dst, d, key_bits);
+                put_f16(dst + mse_bytes, norm);
+            }
             if (value_lloyd_max && value_bits == 4) {
                 float vn = sqrtf((value_sum_order ? tq_norm_sq_rotated_layout(v, d)
                                                   : tq_key_norm_sq(v, d)) + 1e-16f);
@@ -598,8 +639,9 @@ void ftq_oracle_tq_decode(const float *q, int B, int Hq, int Hkv, int d, const u
                           float *out, float *lse, int value_lloyd_max) {
     const int v_lm = value_lloyd_max && value_bits == 4; /* triton_decode_offset.py:399-423 */
     const int group = Hq / Hkv;
+    const int key_fp8 = key_bits == 8; /* triton_decode_offset.py:175-194 */
     const int mse_bytes = d * key_bits / 8;
-    const int kps = mse_bytes + 2;
+    const int kps = mse_bytes + (key_fp8 ? 0 : 2);
     const int vdb = value_bits == 8 ? d : d * value_bits / 8;
 #pragma omp parallel for collapse(2) schedule(dynamic)
     for (int b = 0; b < B; b++)
@@ -624,14 +666,19 @@ void ftq_oracle_tq_decode(const float *q, int B, int Hq, int Hkv, int d, const u
                     const uint8_t *slot = kv_cache + blk * stride_block +
                                           (int64_t)(pos % block_size) * stride_pos +
                                           (int64_t)hk * stride_head;
-                    double dot = 0.0, cn = 0.0;
-                    for (int i = 0; i < d; i++) {
-                        const double c = centroids[tq_code(slot, i, key_bits)];
-                        dot += (double)qr[i] * c;
-                        cn += c * c;
+                    double dot = 0.0, cn = 0.0, sc;
+                    if (key_fp8) {
+                        for (int i = 0; i < d; i++) dot += (double)qr[i] * (double)e4m3_to_f32(slot[i]);
+                        sc = dot * (double)scale;
+                    } else {
+                        for (int i = 0; i < d; i++) {
+                            const double c = centroids[tq_code(slot, i, key_bits)];
+                            dot += (double)qr[i] * c;
+                            cn += c * c;
+                        }
+                        if (norm_correction) dot *= 1.0 / sqrt(cn + 1e-16);
+                        sc = (double)get_f16(slot + mse_bytes) * dot * (double)scale;
                     }
-                    if (norm_correction) dot *= 1.0 / sqrt(cn + 1e-16);
-                    const double sc = (double)get_f16(slot + mse_bytes) * dot * (double)scale;
                     double vs = get_f16(slot + kps + vdb), vz = get_f16(slot + kps + vdb + 2);
                     if (v_lm) { /* value = centroid[code] * norm, re-normalised under norm correction */
                         double vcn = 0.0;

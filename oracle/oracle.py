@@ -207,8 +207,9 @@ def v0_gather(kv_cache: np.ndarray, kv_type: int, pd: int, block_tables, seq_len
 # ---------------------------------------------------------------- vLLM-v1 slot format
 
 def tq_slot_bytes(d: int, key_bits: int, value_bits: int) -> int:
-    """key codes + fp16 norm + value codes + fp16 scale + fp16 zero, rounded up to even."""
-    s = d * key_bits // 8 + 2 + (d if value_bits == 8 else d * value_bits // 8) + 4
+    """key codes + fp16 norm (key_bits 8 = FP8 keys: d bytes, no norm) + value codes + fp16 scale
+    + fp16 zero, rounded up to even."""
+    s = (d if key_bits == 8 else d * key_bits // 8 + 2) + (d if value_bits == 8 else d * value_bits // 8) + 4
     return s + s % 2
 
 
@@ -223,7 +224,7 @@ def tq_store(key, value, kv_cache: np.ndarray, slot_mapping, midpoints, key_bits
     n, hkv, d = key.shape
     assert kv_cache.dtype == np.uint8 and kv_cache.flags.c_contiguous and kv_cache.ndim == 4
     sm = _c(slot_mapping, np.int64)
-    mids = _c(midpoints, np.float32)
+    mids = _c(np.zeros(1) if midpoints is None else midpoints, np.float32)   # (FP8 keys: unused)
     y = np.empty_like(key) if return_rotated else None
     st = kv_cache.strides
     lib().ftq_oracle_tq_store(_p(key), _p(value), ctypes.c_int64(n), ctypes.c_int(hkv),
@@ -244,7 +245,7 @@ def tq_decode(q, kv_cache: np.ndarray, block_table, seq_lens, centroids, key_bit
     bt = _c(block_table, np.int32)
     sl = _c(seq_lens, np.int32)
     ks = None if kv_start is None else _c(kv_start, np.int32)
-    cent = _c(centroids, np.float32)
+    cent = _c(np.zeros(1) if centroids is None else centroids, np.float32)   # (FP8 keys: unused)
     mid_o = np.empty((B, Hq, splits, d + 1), np.float32)
     out = np.empty((B, Hq, d), np.float32)
     lse = np.empty((B, Hq), np.float32)

@@ -12,6 +12,7 @@ kernels wrote for them:
   {case}_out       output of the stock stage-2 merge over them      (call as in vllm_plugin/v1_backend.py:1068-1085)
   {case}_y         the rotated unit key the store kernel bucketises, recomputed with torch ops
                    (used by the tests to tell a genuine code mismatch from a value sitting on a midpoint)
+  {case}_kun       (FP8-key cases) the un-normalised rotated key the store kernel casts to e4m3, likewise
   {case}_vy        ("_vlm" cases) the unit value the store kernel bucketises, likewise; {case}_V then
                    holds the pre-rotated values the store kernel was given
 
@@ -48,6 +49,10 @@ CASES = [
     ("d128_k4v4_nc_vlm", 128, 2, 4, 4, 4, 1, (50, 23), (0, 0), 3, 16),
     ("d64_k4v4_vlm", 64, 2, 2, 4, 4, 0, (33, 12), (0, 4), 2, 16),
     ("d128_k3v4_nc_vlm", 128, 1, 2, 3, 4, 1, (20, 9), (0, 0), 2, 8),
+    # key bits 8 = FP8 (e4m3) keys, vLLM's stock key_quant_bits == 8 (the e4nv variant a B200 takes)
+    ("d128_k8v4", 128, 2, 4, 8, 4, 0, (45, 18), (0, 0), 3, 16),
+    ("d64_k8v2", 64, 2, 2, 8, 2, 0, (27, 11), (0, 3), 2, 16),
+    ("d256_k8v3", 256, 1, 2, 8, 3, 0, (19, 8), (0, 0), 2, 8),
 ]
 
 
@@ -62,14 +67,18 @@ def main() -> None:
     from fused_turboquant.vllm_plugin.boundary_tq_config import BoundaryTurboQuantConfig
     from fused_turboquant.vllm_plugin.rotation.hadamard import _build_hadamard
     from fused_turboquant.vllm_plugin.triton_decode_offset import _tq_decode_stage1_offset
+    import fused_turboquant.vllm_plugin.triton_inkernel_store as store_mod
     from fused_turboquant.vllm_plugin.triton_inkernel_store import _launch_rht
+
+    # the e4b15 / e4nv choice asks the CUDA device for its capability: a B200 takes e4nv
+    store_mod._use_fp8_e4b15 = lambda device: False
 
     torch.set_num_threads(1)
     gen = torch.Generator("cpu").manual_seed(20251)
     out = {}
     for name, D, Hkv, G, kb, vb, nc, seq_lens, kv_start, splits, bs in CASES:
         cfg = BoundaryTurboQuantConfig(head_dim=D, key_quant_bits=kb, value_quant_bits=vb,
-                                       norm_correction=bool(nc))
+                                       norm_correction=bool(nc), key_use_fp8_at_8bit=True)
         slot = cfg.key_packed_size + cfg.value_data_bytes + 4
         slot += slot % 2
         B, Hq = len(seq_lens), Hkv * G
@@ -77,7 +86,7 @@ def main() -> None:
         nb = B * max_blocks + 2
         perm = torch.randperm(nb, generator=gen)
         block_table = perm[:B * max_blocks].to(torch.int32).view(B, max_blocks)
-        cent, _ = get_centroids(D, kb).float().sort()
+        cent, _ = get_centroids(D, cfg.mse_bits).float().sort()   # (FP8 keys: sized for the values, unused)
         mids = (cent[:-1] + cent[1:]) / 2
         H = _build_hadamard(D, "cpu")
 
@@ -118,9 +127,14 @@ def main() -> None:
             q_rot.stride(0), q_rot.stride(1), cache.stride(0), cache.stride(1), cache.stride(2),
             block_table.stride(0), mid_o.stride(0), mid_o.stride(1), mid_o.stride(2),
             NUM_KV_HEADS=Hkv, HEAD_DIM=D, BLOCK_SIZE=bs, NUM_KV_SPLITS=splits, KV_GROUP_SIZE=G,
-            MSE_BITS=kb, MSE_BYTES=cfg.key_packed_size - 2, KPS=cfg.key_packed_size, VQB=vb,
+            # (the reference's call sites pass max(key_mse_bits, 2), v1_backend.py:1052 -- meant for
+            # FP8 keys, whose key_mse_bits is 0, but it also turns 1 into 2, so that with 1-bit keys
+            # its decode would read the store kernel's 1-bit codes as 2-bit ones; the 1-bit fixtures
+            # are made with the kernel's own meaning of MSE_BITS = 1)
+            MSE_BITS=2 if cfg.key_fp8 else kb, MSE_BYTES=0 if cfg.key_fp8 else cfg.key_packed_size - 2,
+            KPS=cfg.key_packed_size, VQB=vb,
             VAL_DATA_BYTES=cfg.value_data_bytes, ATTN_SCALE=scale, BLOCK_D=BLOCK_D, BLOCK_KV=4,
-            KEY_FP8=0, NORM_CORRECTION=nc, FP8_E4B15=0, V_LLOYD_MAX=int(vlm), num_warps=1, num_stages=1)
+            KEY_FP8=int(cfg.key_fp8), NORM_CORRECTION=nc, FP8_E4B15=0, V_LLOYD_MAX=int(vlm), num_warps=1, num_stages=1)
         o = torch.zeros(B, Hq, D)
         lse = torch.zeros(B, Hq)
         # the stock merge decides which splits exist from seq_lens alone; the reference only
@@ -136,6 +150,8 @@ def main() -> None:
         kf = K.float().reshape(-1, D)
         norm = torch.sqrt((kf * kf).sum(-1, keepdim=True) + 1e-16)
         out[f"{name}_y"] = ((kf / (norm + 1e-8)) @ H).reshape(K.shape).numpy()
+        if cfg.key_fp8:   # what the store kernel casts to FP8, recomputed with torch ops
+            out[f"{name}_kun"] = (((kf / (norm + 1e-8)) @ H) * norm).reshape(K.shape).numpy()
         for k_, v_ in (("K", K), ("V", V), ("q", q), ("slot_mapping", slot_mapping),
                        ("block_table", block_table), ("seq_lens", sl), ("kv_start", ks),
                        ("centroids", cent), ("midpoints", mids), ("cache", cache),

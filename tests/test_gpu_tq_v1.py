@@ -17,7 +17,8 @@ pytestmark = pytest.mark.gpu
 
 CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8",
          "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc",
-         "d128_k4v4_nc_vlm", "d64_k4v4_vlm", "d128_k3v4_nc_vlm"]   # _vlm: Lloyd-Max value codes
+         "d128_k4v4_nc_vlm", "d64_k4v4_vlm", "d128_k3v4_nc_vlm",   # _vlm: Lloyd-Max value codes
+         "d128_k8v4", "d64_k8v2", "d256_k8v3"]                     # k8: FP8 (e4m3) keys
 cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
@@ -37,8 +38,10 @@ def test_store_vs_reference_kernel_and_oracle(oracle, golden, name):
     tq_v1.launch_store(cu(g[f"{name}_K"]), cu(g[f"{name}_V"]), cache, cu(g[f"{name}_slot_mapping"]),
                        g[f"{name}_midpoints"], cfg, D, v_lloyd_max=vlm)
     got = cache.cpu().numpy()
-    st = tq_v1_compare_cache(got, g[f"{name}_cache"], g[f"{name}_slot_mapping"], g[f"{name}_y"],
+    st = tq_v1_compare_cache(got, g[f"{name}_cache"], g[f"{name}_slot_mapping"],
+                             g[f"{name}_kun" if kb == 8 else f"{name}_y"],
                              g[f"{name}_midpoints"], D, kb, vb, bs, vy=g[f"{name}_vy"] if vlm else None)
+    assert st["key_fp8_differ_unexplained"] == 0 and st["key_fp8_vs_rne"] == 0, st
     assert st["value_bytes_differ"] == 0 and st["other_bytes_differ"] == 0, st
     assert st["key_codes_differ_off_midpoint"] == 0 and st["key_norm_max_ulp"] <= 1, st
     assert st["value_codes_differ_off_midpoint"] == 0 and st["value_norm_max_ulp"] <= 1, st
@@ -84,7 +87,9 @@ def test_decode_vs_reference_kernels(oracle, golden, name):
     (128, 3, 2, 8, False, False), (64, 1, 1, 4, True, False), (128, 1, 4, 2, False, False),
     (256, 4, 1, 2, True, False),
     # Lloyd-Max value codes (with the fused value rotation, as the reference always pairs them)
-    (128, 4, 4, 4, True, True), (64, 4, 4, 7, False, True), (256, 3, 4, 2, True, True)])
+    (128, 4, 4, 4, True, True), (64, 4, 4, 7, False, True), (256, 3, 4, 2, True, True),
+    # FP8 keys
+    (128, 8, 4, 4, False, False), (64, 8, 8, 7, False, False), (256, 8, 2, 2, False, False)])
 def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, lm, dtype):
     """Ragged batch, 16-bit inputs, values kept in the rotated space, several splits."""
     from fused_turboquant_b200 import tq_v1
@@ -100,7 +105,7 @@ def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, lm, dtype)
     K = torch.from_numpy(rng.standard_normal((n, Hkv, D)).astype(np.float32)).to(dtype)
     V = torch.from_numpy((rng.standard_normal((n, Hkv, D)) * 2 + 0.5).astype(np.float32)).to(dtype)
     q = torch.from_numpy(rng.standard_normal((B, Hq, D)).astype(np.float32)).to(dtype)
-    cent = np.sort(rng.standard_normal(1 << kb).astype(np.float32)) / np.sqrt(D)
+    cent = np.sort(rng.standard_normal(1 << min(kb, 4)).astype(np.float32)) / np.sqrt(D)   # (FP8 keys: unused)
     cent_t, mids_t = tq_v1.midpoints_of(torch.from_numpy(cent))
     cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, nc)
     slot = cfg.slot_size_aligned
@@ -122,7 +127,7 @@ def test_store_then_decode_random_vs_oracle(oracle, D, kb, vb, G, nc, lm, dtype)
     # 16-bit queries take the tensor-core kernel where it exists (fp16 centroids / weights, fp32
     # accumulation): the north-star gate; 8-bit values, 1-bit codes and head_dim 256 stay on the
     # fp32 kernel
-    if vb == 8 or D == 256 or 1 in (kb, vb) or lm:
+    if vb == 8 or D == 256 or 1 in (kb, vb) or lm or kb == 8:
         assert gate(out.cpu().numpy(), o_ref, 2e-4, 1e-4) == 0
     else:
         assert gate(out.cpu().numpy(), o_ref) == 0, np.abs(out.cpu().numpy() - o_ref).max()
@@ -263,11 +268,12 @@ def test_store_and_decode_are_graph_capturable(qdtype):
         assert torch.equal(got, out), pos
 
 
-def test_cache_view_at_an_odd_halfword_offset(oracle, golden):
-    """A cache that starts 2 bytes past a 4-byte boundary (a view into a larger buffer)."""
+@pytest.mark.parametrize("name", ["d128_k4v4", "d128_k8v4", "d64_k1v3"])
+def test_cache_view_at_an_odd_halfword_offset(oracle, golden, name):
+    """A cache that starts 2 bytes past a 4-byte boundary (a view into a larger buffer); the slots
+    of the FP8-key case use a multiple of 4 bytes, the others 2 more."""
     from fused_turboquant_b200 import tq_v1
     g = golden("tq_v1.npz")
-    name = "d128_k4v4"
     D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = _meta(g, name)
     cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
     n = nb * bs * Hkv * slot
@@ -276,13 +282,17 @@ def test_cache_view_at_an_odd_halfword_offset(oracle, golden):
     assert cache.data_ptr() % 4 == 2
     tq_v1.launch_store(cu(g[f"{name}_K"]), cu(g[f"{name}_V"]), cache, cu(g[f"{name}_slot_mapping"]),
                        g[f"{name}_midpoints"], cfg, D)
-    np.testing.assert_array_equal(cache.cpu().numpy(), g[f"{name}_cache"])
+    aligned = torch.zeros((nb, bs, Hkv, slot), dtype=torch.uint8, device="cuda")
+    tq_v1.launch_store(cu(g[f"{name}_K"]), cu(g[f"{name}_V"]), aligned, cu(g[f"{name}_slot_mapping"]),
+                       g[f"{name}_midpoints"], cfg, D)
+    assert torch.equal(cache, aligned)
+    if name == "d128_k4v4":
+        np.testing.assert_array_equal(cache.cpu().numpy(), g[f"{name}_cache"])
     assert int(buf[:2].sum()) == 0 and int(buf[2 + n:].sum()) == 0
     q = cu(g[f"{name}_q"]).bfloat16()
     args = (cu(g[f"{name}_block_table"]), cu(g[f"{name}_seq_lens"]), g[f"{name}_centroids"], cfg, D ** -0.5)
     out = tq_v1.decode_attention(q, cache, *args, num_kv_splits=splits, out_dtype=torch.float32)
-    ref = tq_v1.decode_attention(q, cu(g[f"{name}_cache"]), *args, num_kv_splits=splits,
-                                 out_dtype=torch.float32)
+    ref = tq_v1.decode_attention(q, aligned, *args, num_kv_splits=splits, out_dtype=torch.float32)
     # (the aligned copy runs the tensor-core kernel, the view the fp32 one)
     assert gate(out.cpu().numpy(), ref.cpu().numpy()) <= out.numel() // 300
 
@@ -292,7 +302,7 @@ def test_errors(golden):
     with pytest.raises(ValueError):
         tq_v1.TurboQuantSlotConfig(96, 4, 4)
     with pytest.raises(ValueError):
-        tq_v1.TurboQuantSlotConfig(128, 8, 4)
+        tq_v1.TurboQuantSlotConfig(128, 5, 4)
     cfg = tq_v1.TurboQuantSlotConfig(128, 4, 4)
     assert (cfg.key_packed_size, cfg.value_packed_size, cfg.slot_size_aligned) == (66, 68, 134)
     k = torch.zeros((4, 2, 128), device="cuda")

@@ -8,7 +8,8 @@ from helpers import tq_v1_compare_cache
 
 CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8",
          "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc",
-         "d128_k4v4_nc_vlm", "d64_k4v4_vlm", "d128_k3v4_nc_vlm"]   # _vlm: Lloyd-Max value codes
+         "d128_k4v4_nc_vlm", "d64_k4v4_vlm", "d128_k3v4_nc_vlm",   # _vlm: Lloyd-Max value codes
+         "d128_k8v4", "d64_k8v2", "d256_k8v3"]                     # k8: FP8 (e4m3) keys
 
 
 @pytest.mark.parametrize("name", CASES)
@@ -20,9 +21,12 @@ def test_store_matches_reference_store_kernel(oracle, golden, name):
     vlm = name.endswith("_vlm")
     y = oracle.tq_store(g[f"{name}_K"], g[f"{name}_V"], cache, g[f"{name}_slot_mapping"],
                         g[f"{name}_midpoints"], kb, vb, return_rotated=True, value_lloyd_max=vlm)
-    stats = tq_v1_compare_cache(cache, g[f"{name}_cache"], g[f"{name}_slot_mapping"], y,
+    stats = tq_v1_compare_cache(cache, g[f"{name}_cache"], g[f"{name}_slot_mapping"],
+                                g[f"{name}_kun"] if kb == 8 else y,
                                 g[f"{name}_midpoints"], D, kb, vb, bs,
                                 vy=g[f"{name}_vy"] if vlm else None)
+    # FP8 keys: every byte the interpreter and the oracle disagree on is a subnormal or a tie
+    assert stats["key_fp8_differ_unexplained"] == 0 and stats["key_fp8_vs_rne"] == 0, stats
     # (Lloyd-Max values: codes and norm are held to the same bar as the key's)
     assert stats["value_codes_differ_off_midpoint"] == 0 and stats["value_norm_max_ulp"] <= 1
     # value codes / scale / zero and every untouched byte: identical.  Key codes: identical except

@@ -9,24 +9,39 @@ from fused_turboquant_b200.paged import synthetic_decode_batch
 
 @pytest.mark.parametrize("d,kb,vb,slot", [(128, 4, 4, 134), (128, 3, 4, 118), (64, 3, 3, 54),
                                           (256, 4, 2, 198), (128, 2, 8, 166), (128, 1, 1, 38),
-                                          (64, 1, 3, 38), (256, 3, 1, 134)])
+                                          (64, 1, 3, 38), (256, 3, 1, 134), (128, 8, 4, 196),
+                                          (64, 8, 2, 84), (256, 8, 3, 356)])
 def test_slot_sizes_match_the_reference_kernels_fixture(golden, oracle, d, kb, vb, slot):
     cfg = tq_v1.TurboQuantSlotConfig(d, kb, vb)
     assert cfg.slot_size_aligned == slot == oracle.tq_slot_bytes(d, kb, vb)
-    assert cfg.key_packed_size == d * kb // 8 + 2
     assert cfg.value_packed_size == cfg.value_data_bytes + 4
-    assert cfg.n_centroids == 1 << kb and cfg.key_mse_bits == kb and not cfg.key_fp8
+    if kb == 8:   # FP8 keys: one byte per coordinate, no norm, centroid table sized for the values
+        assert cfg.key_fp8 and cfg.key_packed_size == d and cfg.key_mse_bits == 0
+        assert cfg.n_centroids == 1 << vb
+    else:
+        assert cfg.key_packed_size == d * kb // 8 + 2
+        assert cfg.n_centroids == 1 << kb and cfg.key_mse_bits == kb and not cfg.key_fp8
     g = golden("tq_v1.npz")
     names = {(128, 4, 4): "d128_k4v4", (128, 3, 4): "d128_k3v4_nc", (64, 3, 3): "d64_k3v3_g7",
              (256, 4, 2): "d256_k4v2", (128, 2, 8): "d128_k2v8", (128, 1, 1): "d128_k1v1_nc",
-             (64, 1, 3): "d64_k1v3", (256, 3, 1): "d256_k3v1_nc"}
+             (64, 1, 3): "d64_k1v3", (256, 3, 1): "d256_k3v1_nc", (128, 8, 4): "d128_k8v4",
+             (64, 8, 2): "d64_k8v2", (256, 8, 3): "d256_k8v3"}
     assert int(g[f"{names[(d, kb, vb)]}_meta"][8]) == slot
 
 
 def test_config_rejects_what_the_kernels_do_not_cover():
-    for bad in [(96, 4, 4), (128, 0, 4), (128, 8, 4), (128, 4, 0), (128, 4, 5), (128, 5, 4)]:
+    for bad in [(96, 4, 4), (128, 0, 4), (128, 6, 4), (128, 4, 0), (128, 4, 5), (128, 5, 4)]:
         with pytest.raises(ValueError):
             tq_v1.TurboQuantSlotConfig(*bad)
+
+
+def test_eight_bit_lloyd_max_keys_are_refused():
+    """A duck-typed reference config with 8 key bits that are NOT FP8 must not be taken for FP8."""
+    class Cfg:
+        head_dim, key_quant_bits, value_quant_bits, norm_correction, key_fp8 = 128, 8, 4, True, False
+    with pytest.raises(ValueError):
+        tq_v1._key_bits(Cfg())
+    assert tq_v1._key_bits(tq_v1.TurboQuantSlotConfig(128, 8, 4)) == 8
 
 
 def test_midpoints_follow_the_reference_recipe(golden):
