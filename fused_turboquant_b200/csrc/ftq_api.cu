@@ -938,12 +938,18 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
                              int key_bits, int value_bits, int norm_correction, int rotate_output,
                              int value_lloyd_max, const float* centroids_host, float scale,
                              int num_kv_splits,
-                             float* mid_o, void* out, int out_dtype, float* lse, void* stream) {
+                             float* mid_o, void* out, int out_dtype, float* lse,
+                             const void* prefix_out, int prefix_dtype, const float* prefix_lse,
+                             void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
         return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 or 8 = FP8 / 1,2,3,4,8)", key_bits,
                     value_bits);
     if (!dtype_ok(q_dtype) || !dtype_ok(out_dtype)) return fail(FTQ_ERR_INVALID, "bad dtype");
+    if ((prefix_out != nullptr) != (prefix_lse != nullptr))
+        return fail(FTQ_ERR_INVALID, "prefix_out and prefix_lse go together");
+    if (prefix_out && (!dtype_ok(prefix_dtype) || !aligned(prefix_out, 4) || !aligned(prefix_lse, 4)))
+        return fail(FTQ_ERR_INVALID, "bad prefix dtype or alignment");
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || block_size <= 0 || max_blocks <= 0)
         return fail(FTQ_ERR_INVALID, "bad shape");
     if (num_kv_splits <= 0 || num_kv_splits > 65535)
@@ -1016,11 +1022,21 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
         }
     }
     if (e != cudaSuccess) return cuda_fail(e, "tq_decode stage 1 launch");
-    const int64_t rows = static_cast<int64_t>(B) * Hq;
+    ftq::TqMergeParams mp{};
+    mp.mid_o = mid_o;
+    mp.out = out;
+    mp.lse = lse;
+    mp.n_rows = static_cast<int64_t>(B) * Hq;
+    mp.splits = num_kv_splits;
+    mp.rotate = rotate_output ? 1 : 0;
+    mp.rsqrt_d = p.rsqrt_d;
+    mp.prefix_out = prefix_out;
+    mp.prefix_dtype = prefix_dtype;
+    mp.prefix_lse = prefix_lse;
     switch (head_dim) {
-        case 64: e = ftq::launch_tq_merge_d64(out_dtype, mid_o, out, lse, rows, num_kv_splits, rotate_output, p.rsqrt_d, st); break;
-        case 128: e = ftq::launch_tq_merge_d128(out_dtype, mid_o, out, lse, rows, num_kv_splits, rotate_output, p.rsqrt_d, st); break;
-        case 256: e = ftq::launch_tq_merge_d256(out_dtype, mid_o, out, lse, rows, num_kv_splits, rotate_output, p.rsqrt_d, st); break;
+        case 64: e = ftq::launch_tq_merge_d64(out_dtype, mp, st); break;
+        case 128: e = ftq::launch_tq_merge_d128(out_dtype, mp, st); break;
+        case 256: e = ftq::launch_tq_merge_d256(out_dtype, mp, st); break;
     }
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "tq_decode merge launch");
 }

@@ -771,12 +771,33 @@ constexpr int tq_split_smem_bytes(int kb, int vb) {
     return buf + 3 * kTqTileTokens * 4 + kTqTileTokens * 8 + AttnCfg<D>::GH * D * 4 + kMaxLevels * 4;
 }
 
+struct TqMergeParams {
+    const float* mid_o;  // [n_rows, splits, D + 1]
+    void* out;           // [n_rows, D]
+    float* lse;          // [n_rows], nullable
+    int64_t n_rows;
+    int splits;
+    int rotate;
+    float rsqrt_d;
+    // Attention over an uncompressed prefix of the same rows, computed elsewhere (nullable):
+    // merged in by log-sum-exp as vllm_plugin/v1_backend.py:1267-1277 does.
+    const void* prefix_out;   // [n_rows, D] of prefix_dtype, original space
+    int prefix_dtype;
+    const float* prefix_lse;  // [n_rows]
+};
+
 // Merge the split partials of 4 (sequence, query head) rows per warp: softmax-weighted by lse,
-// optionally Hadamard-transform the result, cast and store.  mid_o rows with lse = -inf are skipped.
+// optionally Hadamard-transform the result, optionally merge a prefix result in, cast and store.
+// mid_o rows with lse = -inf are skipped.
 template <int D, typename OT>
 __global__ void __launch_bounds__(128)
-tq_merge_kernel(const float* __restrict__ mid_o, OT* __restrict__ out, float* __restrict__ lse_out,
-                int64_t n_rows, int splits, int rotate, float rsqrt_d) {
+tq_merge_kernel(const TqMergeParams p) {
+    const float* __restrict__ mid_o = p.mid_o;
+    OT* __restrict__ out = static_cast<OT*>(p.out);
+    float* __restrict__ lse_out = p.lse;
+    const int64_t n_rows = p.n_rows;
+    const int splits = p.splits, rotate = p.rotate;
+    const float rsqrt_d = p.rsqrt_d;
     constexpr int E = D / kOctet;
     const int lane = threadIdx.x & 31;
     const int t = lane & 7;
@@ -807,15 +828,40 @@ tq_merge_kernel(const float* __restrict__ mid_o, OT* __restrict__ out, float* __
         for (int k = 0; k < E; k++) a[k] *= rsqrt_d;
     }
     if (!valid) return;
+    float lse = l > 0.f ? M + logf(l) : -INFINITY;
+    float w_own = 1.f, w_pre = 0.f;
+    const bool prefix = p.prefix_out != nullptr;
+    if (prefix) {
+        const float lp = p.prefix_lse[row];
+        const float lmax = fmaxf(lp, lse);
+        if (lmax == -INFINITY) {  // nothing attended on either side
+            w_own = 0.f;
+        } else {
+            const float ep = __expf(lp - lmax), eq = __expf(lse - lmax);
+            const float total = fmaxf(ep + eq, 1e-20f);
+            w_pre = ep / total;
+            w_own = eq / total;
+            lse = lmax + logf(ep + eq);
+        }
+    }
     OT* orow = out + row * D;
 #pragma unroll
     for (int r = 0; r < E; r++) {
         const int coord = rotate ? t + 8 * r : load_coord(t, r);
-        if constexpr (sizeof(OT) == 4) orow[coord] = a[r];
-        else if constexpr (std::is_same<OT, __half>::value) orow[coord] = __float2half_rn(a[r]);
-        else orow[coord] = __float2bfloat16_rn(a[r]);
+        float v = a[r];
+        if (prefix) {
+            const int64_t at = row * D + coord;
+            const float pv = p.prefix_dtype == kF32 ? static_cast<const float*>(p.prefix_out)[at]
+                             : p.prefix_dtype == kF16
+                                 ? __half2float(static_cast<const __half*>(p.prefix_out)[at])
+                                 : __bfloat162float(static_cast<const __nv_bfloat16*>(p.prefix_out)[at]);
+            v = pv * w_pre + v * w_own;
+        }
+        if constexpr (sizeof(OT) == 4) orow[coord] = v;
+        else if constexpr (std::is_same<OT, __half>::value) orow[coord] = __float2half_rn(v);
+        else orow[coord] = __float2bfloat16_rn(v);
     }
-    if (lse_out && t == 0) lse_out[row] = l > 0.f ? M + logf(l) : -INFINITY;
+    if (lse_out && t == 0) lse_out[row] = lse;
 }
 
 }  // namespace ftq

@@ -163,25 +163,14 @@ cudaError_t FTQ_CAT(launch_tq_mma_d, FTQ_D)(int kb, int vb, int nh, const TqDeco
     return cudaErrorInvalidValue;
 }
 
-cudaError_t FTQ_CAT(launch_tq_merge_d, FTQ_D)(int out_dtype, const float* mid_o, void* out,
-                                             float* lse, int64_t n_rows, int splits, int rotate,
-                                             float rsqrt_d, cudaStream_t stream) {
-    const unsigned grid = static_cast<unsigned>((n_rows + 15) / 16);  // 128 threads = 16 rows
+cudaError_t FTQ_CAT(launch_tq_merge_d, FTQ_D)(int out_dtype, const TqMergeParams& p,
+                                             cudaStream_t stream) {
+    const unsigned grid = static_cast<unsigned>((p.n_rows + 15) / 16);  // 128 threads = 16 rows
     switch (out_dtype) {
-        case kF32:
-            tq_merge_kernel<FTQ_D, float><<<grid, 128, 0, stream>>>(
-                mid_o, static_cast<float*>(out), lse, n_rows, splits, rotate, rsqrt_d);
-            break;
-        case kF16:
-            tq_merge_kernel<FTQ_D, __half><<<grid, 128, 0, stream>>>(
-                mid_o, static_cast<__half*>(out), lse, n_rows, splits, rotate, rsqrt_d);
-            break;
-        case kBF16:
-            tq_merge_kernel<FTQ_D, __nv_bfloat16><<<grid, 128, 0, stream>>>(
-                mid_o, static_cast<__nv_bfloat16*>(out), lse, n_rows, splits, rotate, rsqrt_d);
-            break;
-        default:
-            return cudaErrorInvalidValue;
+        case kF32: tq_merge_kernel<FTQ_D, float><<<grid, 128, 0, stream>>>(p); break;
+        case kF16: tq_merge_kernel<FTQ_D, __half><<<grid, 128, 0, stream>>>(p); break;
+        case kBF16: tq_merge_kernel<FTQ_D, __nv_bfloat16><<<grid, 128, 0, stream>>>(p); break;
+        default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
 }

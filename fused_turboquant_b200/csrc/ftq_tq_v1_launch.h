@@ -17,9 +17,7 @@ constexpr int kTqLloydMaxValues = 2;  // 4-bit values: Lloyd-Max codes against t
     cudaError_t launch_tq_split_d##DD(int kb, int vb, const TqDecodeParams& p, cudaStream_t stream); \
     cudaError_t launch_tq_mma_d##DD(int kb, int vb, int nh, const TqDecodeParams& p, int n_items,   \
                                     cudaStream_t stream);                                         \
-    cudaError_t launch_tq_merge_d##DD(int out_dtype, const float* mid_o, void* out, float* lse,    \
-                                      int64_t n_rows, int splits, int rotate, float rsqrt_d,      \
-                                      cudaStream_t stream);
+    cudaError_t launch_tq_merge_d##DD(int out_dtype, const TqMergeParams& p, cudaStream_t stream);
 
 FTQ_DECLARE_TQ_LAUNCHERS(64)
 FTQ_DECLARE_TQ_LAUNCHERS(128)

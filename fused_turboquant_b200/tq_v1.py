@@ -171,11 +171,16 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
                      num_kv_splits: int = 8, kv_start_offset: torch.Tensor | None = None,
                      v_rotate: bool = False, mid_o: torch.Tensor | None = None,
                      output: torch.Tensor | None = None, lse: torch.Tensor | None = None,
-                     out_dtype: torch.dtype | None = None, v_lloyd_max: bool = False) -> torch.Tensor:
+                     out_dtype: torch.dtype | None = None, v_lloyd_max: bool = False,
+                     prefix_output: torch.Tensor | None = None,
+                     prefix_lse: torch.Tensor | None = None) -> torch.Tensor:
     """Decode attention of ``query`` ``[B, Hq, D]`` over the compressed cache; returns ``[B, Hq, D]``.
 
     ``v_rotate``: the cache holds rotated values, the merged output is transformed back.
     ``v_lloyd_max``: 4-bit values are Lloyd-Max codes (see ``launch_store``).
+    ``prefix_output`` ``[B, Hq, D]`` / ``prefix_lse`` ``[B, Hq]``: attention of the same queries
+    over an uncompressed prefix ``[0, kv_start_offset)`` (the reference's deferred-prefill hybrid,
+    vllm_plugin/v1_backend.py:1096-1277, computes it with SDPA); merged in by log-sum-exp.
 
     ``mid_o`` ``[B, Hq, num_kv_splits, D+1]`` fp32, ``output`` and ``lse`` ``[B, Hq]`` fp32 may be
     supplied (pre-allocated per layer, as the reference keeps them for CUDA-graph capture).
@@ -205,6 +210,16 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
         output = torch.empty((B, hq, d), dtype=odt, device=dev)
     elif output.shape != (B, hq, d) or not output.is_contiguous() or output.dtype not in _DT:
         raise ValueError("output must be a contiguous [B, Hq, D] tensor of a supported dtype")
+    if (prefix_output is None) != (prefix_lse is None):
+        raise ValueError("prefix_output and prefix_lse go together")
+    if prefix_output is not None:
+        _require_cuda(prefix_output, "prefix_output")
+        if prefix_output.shape != (B, hq, d) or prefix_lse.shape != (B, hq):
+            raise ValueError("prefix_output must be [B, Hq, D] and prefix_lse [B, Hq]")
+        if prefix_output.dtype not in _DT:
+            prefix_output = prefix_output.float()
+        prefix_output = prefix_output.contiguous()
+        prefix_lse = prefix_lse.to(device=dev, dtype=torch.float32).contiguous()
     kb = _key_bits(tq_config)
     with torch.cuda.device(dev):
         rc = _lib.load().ftq_tq_decode(
@@ -213,7 +228,8 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
             kb, tq_config.value_quant_bits, int(tq_config.norm_correction),
             int(v_rotate), int(bool(v_lloyd_max)), _table_ptr(centroids, kb == 8), float(scale),
             num_kv_splits,
-            _ptr(mid_o), _ptr(output), _DT[output.dtype], _ptr(lse), _stream(dev))
+            _ptr(mid_o), _ptr(output), _DT[output.dtype], _ptr(lse), _ptr(prefix_output),
+            _DT[prefix_output.dtype] if prefix_output is not None else 0, _ptr(prefix_lse), _stream(dev))
     _lib.check(rc, "ftq_tq_decode")
     return output
 

@@ -306,7 +306,11 @@ int ftq_tq_store(const void *key, const void *value, int dtype, int64_t n_tokens
  * Hadamard transform to the merged output (values were stored in the rotated space).
  * value_lloyd_max: 4-bit values are Lloyd-Max codes of the key table scaled by the stored norm
  * (triton_decode_offset.py:399-423; re-normalised under norm_correction); ignored for other widths.
- * centroids_host: 2^key_bits floats, ascending.  No allocation, no host synchronisation.
+ * centroids_host: 2^key_bits floats, ascending.  prefix_out / prefix_lse (both or neither;
+ * [B, Hq, head_dim] of prefix_dtype in the original space, [B, Hq] fp32): the attention of the same
+ * queries over an uncompressed prefix [0, kv_start_offset[b]) computed by the caller; it is merged
+ * in by log-sum-exp, with the weights of _decode_attention_hybrid (v1_backend.py:1267-1277), after
+ * the output rotation; lse then receives the merged value.  No allocation, no host synchronisation.
  */
 int ftq_tq_decode(const void *q, int q_dtype, int B, int Hq, int Hkv, int head_dim,
                   const uint8_t *kv_cache, int64_t stride_block, int64_t stride_pos,
@@ -315,6 +319,7 @@ int ftq_tq_decode(const void *q, int q_dtype, int B, int Hq, int Hkv, int head_d
                   int key_bits, int value_bits, int norm_correction, int rotate_output,
                   int value_lloyd_max, const float *centroids_host, float scale,
                   int num_kv_splits, float *mid_o, void *out, int out_dtype, float *lse,
+                  const void *prefix_out, int prefix_dtype, const float *prefix_lse,
                   void *stream);
 
 #ifdef __cplusplus

@@ -259,3 +259,18 @@ def tq_decode(q, kv_cache: np.ndarray, block_table, seq_lens, centroids, key_bit
                                _p(cent), ctypes.c_float(scale), ctypes.c_int(splits), _p(mid_o),
                                _p(out), _p(lse), ctypes.c_int(int(value_lloyd_max)))
     return out, mid_o, lse
+
+
+def tq_merge_prefix(out, lse, out_prefix, lse_prefix):
+    """Log-sum-exp merge of two attention results over disjoint key ranges
+    (vllm_plugin/v1_backend.py:1267-1277): returns (out, lse)."""
+    out, out_prefix = np.asarray(out, np.float64), np.asarray(out_prefix, np.float64)
+    lse, lse_prefix = np.asarray(lse, np.float64), np.asarray(lse_prefix, np.float64)
+    lmax = np.maximum(lse, lse_prefix)
+    with np.errstate(invalid="ignore"):
+        ep = np.where(np.isneginf(lmax), 0.0, np.exp(lse_prefix - lmax))
+        eq = np.where(np.isneginf(lmax), 0.0, np.exp(lse - lmax))
+    total = np.maximum(ep + eq, 1e-20)
+    merged = out_prefix * (ep / total)[..., None] + out * (eq / total)[..., None]
+    with np.errstate(divide="ignore"):
+        return merged, lmax + np.log(ep + eq)

@@ -297,6 +297,42 @@ def test_cache_view_at_an_odd_halfword_offset(oracle, golden, name):
     assert gate(out.cpu().numpy(), ref.cpu().numpy()) <= out.numel() // 300
 
 
+@pytest.mark.parametrize("v_rotate", [False, True])
+def test_prefix_hybrid_merge(oracle, golden, v_rotate):
+    """Deferred-prefill hybrid: the first kv_start tokens are attended elsewhere (here: a dense
+    fp32 softmax over random 'prefix' keys), the compressed rest by the decode kernel, and the two
+    are merged by log-sum-exp inside the merge kernel.  One sequence has an empty compressed range,
+    one an empty prefix (lse = -inf)."""
+    from fused_turboquant_b200 import tq_v1
+    g = golden("tq_v1.npz")
+    name = "d128_k3v4_nc"
+    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = _meta(g, name)
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
+    seq = g[f"{name}_seq_lens"]
+    kv_start = np.array([int(seq[0]), 0], np.int32)        # sequence 0: nothing compressed is attended
+    q = g[f"{name}_q"]
+    B, Hq = q.shape[:2]
+    rng = np.random.default_rng(5)
+    out_p = rng.standard_normal((B, Hq, D)).astype(np.float32)
+    lse_p = rng.standard_normal((B, Hq)).astype(np.float32) + 3.0
+    lse_p[1, :3] = -np.inf                                  # no prefix for three heads of sequence 1
+    out_p[1, :3] = 0.0
+    lse = torch.empty((B, Hq), dtype=torch.float32, device="cuda")
+    out = tq_v1.decode_attention(cu(q), cu(g[f"{name}_cache"]), cu(g[f"{name}_block_table"]), cu(seq),
+                                 g[f"{name}_centroids"], cfg, D ** -0.5, num_kv_splits=splits,
+                                 kv_start_offset=cu(kv_start), v_rotate=v_rotate, lse=lse,
+                                 prefix_output=cu(out_p).bfloat16(), prefix_lse=cu(lse_p))
+    o_ref, _, l_ref = oracle.tq_decode(q, g[f"{name}_cache"], g[f"{name}_block_table"], seq,
+                                       g[f"{name}_centroids"], kb, vb, D ** -0.5, splits,
+                                       norm_correction=bool(nc), kv_start=kv_start, rotate_out=v_rotate)
+    o_ref[0], l_ref[0] = 0.0, -np.inf                       # (empty range: the oracle divides 0 / 0)
+    out_p16 = torch.from_numpy(out_p).bfloat16().float().numpy()
+    m_ref, ml_ref = oracle.tq_merge_prefix(o_ref, l_ref, out_p16, lse_p)
+    np.testing.assert_allclose(out.cpu().numpy(), m_ref, rtol=2e-4, atol=2e-5)
+    np.testing.assert_allclose(lse.cpu().numpy(), ml_ref, rtol=1e-5, atol=2e-5)
+    np.testing.assert_allclose(out.cpu().numpy()[0], out_p16[0], rtol=1e-6, atol=1e-6)   # prefix only
+
+
 def test_errors(golden):
     from fused_turboquant_b200 import tq_v1
     with pytest.raises(ValueError):
