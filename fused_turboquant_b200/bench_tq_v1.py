@@ -4,7 +4,8 @@
 
 Synthetic data, one JSON line.  Shapes: ``qwen`` = 14 query / 2 KV heads, head_dim 64, 3-bit keys,
 3-bit values, value rotation on, batch 32 x context 4096, 24 layer caches; ``llama`` = 32 / 8 heads,
-head_dim 128, 4-bit keys and values, batch 64 x context 8192, 4 layer caches (each larger than L2).
+head_dim 128, 4-bit keys and values, batch 64 x context 8192, 4 layer caches (each larger than L2);
+``llama_k8v4`` = the same with FP8 keys.
 Bytes counted: the slot bytes actually used (codes, norm, scale, zero; padding excluded) of every
 attended (token, KV head), once per KV head, plus block ids, queries and outputs.
 """
@@ -20,6 +21,8 @@ from . import tq_v1
 SHAPES = {
     "qwen": dict(Hq=14, Hkv=2, D=64, kb=3, vb=3, B=32, ctx=4096, layers=24, v_rotate=True),
     "llama": dict(Hq=32, Hkv=8, D=128, kb=4, vb=4, B=64, ctx=8192, layers=4, v_rotate=False),
+    # vLLM's stock k8v4 preset: FP8 keys (fp32 kernel)
+    "llama_k8v4": dict(Hq=32, Hkv=8, D=128, kb=8, vb=4, B=64, ctx=8192, layers=4, v_rotate=False),
 }
 
 
@@ -38,7 +41,7 @@ def main() -> None:
     slot, bs = cfg.slot_size_aligned, 16
     blocks_per_seq = ctx // bs
     nb = B * blocks_per_seq
-    cent = torch.sort(torch.randn(1 << kb, generator=gen, device=dev) / D ** 0.5).values
+    cent = torch.sort(torch.randn(1 << min(kb, 4), generator=gen, device=dev) / D ** 0.5).values  # (FP8 keys: unused)
     cent, mids = tq_v1.midpoints_of(cent)
     caches, tables = [], []
     n_tok = B * ctx

@@ -79,6 +79,36 @@ __device__ __forceinline__ void emit_bits1(uint32_t mine, uint8_t* dst, bool sto
         if (store && t == j) store_u32_as_halves(dst + 4 * j, wd[j]);
 }
 
+// code = number of midpoints <= y, found as the reference finds it (binary search on `y >= mid`,
+// triton_inkernel_store.py:92-100; the midpoints are strictly ascending, checked on the host):
+// bit LVL of the code is decided by one comparison against the midpoint that the bits above it
+// select.  tq_pick builds that midpoint with a tree of selects over the known bits (2^k - 1 selects
+// for the k-th bit from the top), so a 4-bit code costs 4 compares + 11 selects instead of 15
+// compares + 15 adds.
+template <int KB, int LVL, int DEPTH, int PREFIX>
+__device__ __forceinline__ float tq_pick(const bool (&bit)[4], const float (&m)[kTqMaxMid]) {
+    if constexpr (DEPTH == KB - 1 - LVL) {
+        return m[(PREFIX << (LVL + 1)) | ((1 << LVL) - 1)];
+    } else {
+        return bit[KB - 1 - DEPTH] ? tq_pick<KB, LVL, DEPTH + 1, PREFIX * 2 + 1>(bit, m)
+                                   : tq_pick<KB, LVL, DEPTH + 1, PREFIX * 2>(bit, m);
+    }
+}
+template <int KB, int LVL>
+__device__ __forceinline__ void tq_search_level(float y, bool (&bit)[4], const float (&m)[kTqMaxMid]) {
+    bit[LVL] = y >= tq_pick<KB, LVL, 0, 0>(bit, m);
+    if constexpr (LVL > 0) tq_search_level<KB, LVL - 1>(y, bit, m);
+}
+// ORs the code of y, shifted left by `shift`, into w (one predicated OR per bit).
+template <int KB>
+__device__ __forceinline__ void tq_or_code(float y, const float (&m)[kTqMaxMid], uint32_t& w, int shift) {
+    bool bit[4] = {false, false, false, false};
+    tq_search_level<KB, KB - 1>(y, bit, m);
+#pragma unroll
+    for (int b = 0; b < KB; b++)
+        if (bit[b]) w |= 1u << (shift + b);
+}
+
 // Round a value the way a tensor of the input dtype would hold it.
 template <typename T>
 __device__ __forceinline__ float round_as(float v);
@@ -196,16 +226,14 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
 #pragma unroll
         for (int k = 0; k < (KFP8 ? 0 : E); k++) {
             const float yv = __fmul_rn(y[k], p.rsqrt_d);
-            uint32_t code = 0;
-#pragma unroll
-            for (int j = 0; j < NMID; j++) code += (yv >= p.midpoints[j]) ? 1u : 0u;
+            constexpr int SB = KFP8 ? 1 : KB;  // (no codes with FP8 keys)
             if constexpr (KB == 1) {
-                w[0] |= code << k;
+                tq_or_code<SB>(yv, p.midpoints, w[0], k);
             } else if constexpr (KB == 2) {
                 const int pos = ((k >> 1) & 7) | ((k & 1) << 3);
-                w[k >> 4] |= code << (2 * pos);
+                tq_or_code<SB>(yv, p.midpoints, w[k >> 4], 2 * pos);
             } else {
-                w[k >> 3] |= code << (KB * (k & 7));
+                tq_or_code<SB>(yv, p.midpoints, w[k >> 3], KB * (k & 7));
             }
         }
         if constexpr (KB == 1) emit_bits1<E>(w[0], dst, store, lane);
@@ -273,10 +301,8 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
         }
         auto vcode = [&](float x) -> uint32_t {
             if constexpr (LMV) {
-                const float u = __fdiv_rn(x, vden);
                 uint32_t c = 0;
-#pragma unroll
-                for (int j = 0; j < NMID; j++) c += (u >= p.midpoints[j]) ? 1u : 0u;
+                tq_or_code<(KFP8 ? 1 : KB)>(__fdiv_rn(x, vden), p.midpoints, c, 0);
                 return c;
             } else {
                 const float f = __fadd_rn(__fdiv_rn(__fsub_rn(x, mn), scale), 0.5f);
