@@ -10,6 +10,7 @@ from __future__ import annotations
 import argparse
 import concurrent.futures as cf
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -50,6 +51,30 @@ def _sources_mtime() -> float:
     return m
 
 
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _deps(path: str, seen=None) -> set:
+    """The file and every project header it includes, transitively."""
+    seen = set() if seen is None else seen
+    path = os.path.normpath(path)
+    if path in seen or not os.path.exists(path):
+        return seen
+    seen.add(path)
+    with open(path) as f:
+        text = f.read()
+    for inc in _INCLUDE.findall(text):
+        _deps(os.path.join(os.path.dirname(path), inc), seen)
+    return seen
+
+
+def _unit_stale(src: str, obj: str) -> bool:
+    if not os.path.exists(obj):
+        return True
+    t = os.path.getmtime(obj)
+    return any(os.path.getmtime(d) > t for d in _deps(os.path.join(CSRC, src)))
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile and link the library if it is missing or older than its sources."""
     if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _sources_mtime():
@@ -61,6 +86,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     def compile_one(unit):
         src, tag, defs = unit
         obj = os.path.join(OBJ_DIR, f"{tag}.o")
+        if not force and not verbose and not _unit_stale(src, obj):
+            return obj      # up to date: only units whose sources changed are recompiled
         cmd = [nvcc, *NVCC_FLAGS, *extra, *defs, "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:

@@ -280,11 +280,11 @@ cudaError_t dispatch_split(int d, int bk, int bv, bool paged, const ftq::AttnPar
 }
 
 cudaError_t dispatch_mma(int d, int bk, int bv, bool shared_lut, const ftq::AttnParams& p, int n_lb,
-                         cudaStream_t st) {
+                         cudaStream_t st, bool* merged) {
     switch (d) {
-        case 64: return ftq::launch_attn_mma_d64(bk, bv, shared_lut, p, n_lb, st);
-        case 128: return ftq::launch_attn_mma_d128(bk, bv, shared_lut, p, n_lb, st);
-        case 256: return ftq::launch_attn_mma_d256(bk, bv, shared_lut, p, n_lb, st);
+        case 64: return ftq::launch_attn_mma_d64(bk, bv, shared_lut, p, n_lb, st, merged);
+        case 128: return ftq::launch_attn_mma_d128(bk, bv, shared_lut, p, n_lb, st, merged);
+        case 256: return ftq::launch_attn_mma_d256(bk, bv, shared_lut, p, n_lb, st, merged);
     }
     return cudaErrorInvalidValue;
 }
@@ -533,8 +533,14 @@ int ftq_qk_scores(const float* q_rot, const uint8_t* k_codes, const void* k_norm
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_qk_scores launch");
 }
 
-// the last bytes of a decode workspace hold the work-item counter of the tensor-core kernel
-static constexpr size_t kCounterBytes = 256;
+// The tail of a decode workspace holds the counters of the tensor-core kernels: the work-item
+// counter (first word) and, from byte 256 on, one counter per (layer, sequence, KV head) unit
+// for the in-kernel split-KV merge.  The host zeroes the whole tail before every launch.
+static size_t counter_bytes(int B, int Hkv, int n_layers) {
+    const size_t units = static_cast<size_t>(n_layers > 0 ? n_layers : 0) * (B > 0 ? B : 0) *
+                         (Hkv > 0 ? Hkv : 0);
+    return (256 + units * sizeof(int) + 255) / 256 * 256;
+}
 
 size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_seq_len,
                                   int n_layers) {
@@ -548,7 +554,7 @@ size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_
     const size_t n2 = partial_bytes(m2, B, Hq, head_dim, n_layers);
     if (n1 > n) n = n1;
     if (n2 > n) n = n2;
-    return n + kCounterBytes;  // + the work-item counter of the persistent kernel
+    return n + counter_bytes(B, Hkv, n_layers);
 }
 
 static int check_attn_common(int B, int Hq, int Hkv, int head_dim, int bits_k, int bits_v,
@@ -712,10 +718,21 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
         // K and V can share one table only when the scaled V levels equal the K levels
         const bool shared_lut = bits_k == bits_v &&
             memcmp(p.lk.v, p.lv_scaled.v, sizeof(float) << bits_k) == 0;
-        p.work_counter = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + need - kCounterBytes);
-        e = cudaMemsetAsync(p.work_counter, 0, sizeof(int), st);
+        const size_t tail = counter_bytes(B, Hkv, n_layers);
+        p.work_counter = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + need - tail);
+        p.unit_counter = p.work_counter + 64;
+        p.out = out;
+        p.out_dtype = out_dtype;
+        p.num_blocks = num_blocks;
+        p.div_chunks = ftq::make_fastdiv(static_cast<uint32_t>(p.n_chunks));
+        p.div_hkv = ftq::make_fastdiv(static_cast<uint32_t>(Hkv));
+        p.div_b = ftq::make_fastdiv(static_cast<uint32_t>(B));
+        e = cudaMemsetAsync(p.work_counter, 0, tail, st);
         if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn counter reset");
-        e = dispatch_mma(head_dim, bits_k, bits_v, shared_lut, p, n_layers * B, st);
+        bool merged = false;
+        e = dispatch_mma(head_dim, bits_k, bits_v, shared_lut, p, n_layers * B, st, &merged);
+        if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn launch");
+        if (merged) return FTQ_OK;  // the streaming kernel finishes the merge itself
     } else {
         e = dispatch_split(head_dim, bits_k, bits_v, true, p, n_layers * B, st);
     }

@@ -46,6 +46,12 @@ struct AttnParams {
     int chunk_tokens, n_chunks, n_hpass;
     float* partials;            // [L*B*Hq][n_chunks][D + 4]
     int* work_counter;          // tensor-core path: next work item (zeroed before the launch)
+    // streaming tensor-core kernel: it finishes the split-KV merge itself
+    int* unit_counter;          // [L*B*Hkv] chunks delivered per unit (zeroed before the launch)
+    void* out;                  // [L*B, Hq, D]
+    int out_dtype;
+    int64_t num_blocks;         // block ids are checked against it
+    FastDiv div_chunks, div_hkv, div_b;  // divisions by n_chunks, Hkv, B
     Codebook lk, lv;
     SignBits signs;
     float rsqrt_d;

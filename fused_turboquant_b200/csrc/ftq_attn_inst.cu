@@ -1,5 +1,5 @@
 // Instantiates the split-KV decode attention kernels for one head_dim (FTQ_D).
-#include "ftq_attn_mma.cuh"
+#include "ftq_attn_stream.cuh"
 #include "ftq_launch.h"
 
 #ifndef FTQ_D
@@ -51,9 +51,38 @@ cudaError_t FTQ_CAT(launch_attn_split_d, FTQ_D)(int bits_k, int bits_v, bool pag
                  : by_bk<false>(bits_k, bits_v, p, n_lb, stream);
 }
 
+// The streaming kernel (no CTA-wide barriers, merge included) serves every configuration in
+// which it can run as many warps per SM as the barrier-synchronised one; the rest (head_dim
+// 256: the per-warp exchange slots do not fit beside 16 page rings) keep attn_mma_kernel and
+// the separate merge launch.
+template <int BK, int BV, int NH>
+constexpr bool use_stream_kernel() {
+    using S = StreamCfg<FTQ_D, BK, BV, NH>;
+    using C = MmaCfg<FTQ_D, BK, BV, NH>;
+#ifdef FTQ_NO_STREAM
+    return false;
+#else
+    return S::FITS && S::WARPS * S::CTAS_PER_SM >= C::WARPS * C::CTAS_PER_SM;
+#endif
+}
+
 template <int BK, int BV, bool SHARED, int NH>
-static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream) {
+static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream, bool* merged) {
     constexpr int D = FTQ_D;
+    if constexpr (use_stream_kernel<BK, BV, NH>()) {
+        using S = StreamCfg<D, BK, BV, NH>;
+        auto kern = attn_stream_kernel<D, BK, BV, SHARED, NH>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             S::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        const int64_t items = static_cast<int64_t>(p.n_chunks) * p.Hkv * n_lb;
+        const int64_t slots = static_cast<int64_t>(sm_count()) * S::CTAS_PER_SM;
+        const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
+        kern<<<grid, S::THREADS, S::SMEM_BYTES, stream>>>(p, static_cast<int>(items));
+        *merged = true;
+        return cudaGetLastError();
+    } else {
+    *merged = false;
     using C = MmaCfg<D, BK, BV, NH>;
     static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory budget");
     auto kern = attn_mma_kernel<D, BK, BV, SHARED, NH>;
@@ -65,32 +94,44 @@ static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream
     const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
     kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, static_cast<int>(items));
     return cudaGetLastError();
+    }
 }
 
 template <int BK, int BV, bool SHARED>
-static cudaError_t run_mma(const AttnParams& p, int n_lb, cudaStream_t stream) {
-    return p.Hq / p.Hkv <= 4 ? run_mma_nh<BK, BV, SHARED, 1>(p, n_lb, stream)
-                             : run_mma_nh<BK, BV, SHARED, 2>(p, n_lb, stream);
+static cudaError_t run_mma(const AttnParams& p, int n_lb, cudaStream_t stream, bool* merged) {
+    return p.Hq / p.Hkv <= 4 ? run_mma_nh<BK, BV, SHARED, 1>(p, n_lb, stream, merged)
+                             : run_mma_nh<BK, BV, SHARED, 2>(p, n_lb, stream, merged);
 }
 
+// FTQ_ONLY_BITS=<b> (a development aid, never set by the build script) instantiates the
+// tensor-core kernels for bits_k = bits_v = b only, which cuts the compile time of an experiment.
 template <int BK>
 static cudaError_t mma_by_bv(int bv, bool shared_lut, const AttnParams& p, int n_lb,
-                             cudaStream_t stream) {
-    if (shared_lut && bv == BK) return run_mma<BK, BK, true>(p, n_lb, stream);
-    switch (bv) {
-        case 2: return run_mma<BK, 2, false>(p, n_lb, stream);
-        case 3: return run_mma<BK, 3, false>(p, n_lb, stream);
-        case 4: return run_mma<BK, 4, false>(p, n_lb, stream);
+                             cudaStream_t stream, bool* merged) {
+#ifdef FTQ_ONLY_BITS
+    if (BK != FTQ_ONLY_BITS || bv != FTQ_ONLY_BITS) return cudaErrorInvalidValue;
+    if constexpr (BK == FTQ_ONLY_BITS) {
+        return shared_lut ? run_mma<BK, BK, true>(p, n_lb, stream, merged)
+                          : run_mma<BK, BK, false>(p, n_lb, stream, merged);
     }
+#else
+    if (shared_lut && bv == BK) return run_mma<BK, BK, true>(p, n_lb, stream, merged);
+    switch (bv) {
+        case 2: return run_mma<BK, 2, false>(p, n_lb, stream, merged);
+        case 3: return run_mma<BK, 3, false>(p, n_lb, stream, merged);
+        case 4: return run_mma<BK, 4, false>(p, n_lb, stream, merged);
+    }
+#endif
     return cudaErrorInvalidValue;
 }
 
 cudaError_t FTQ_CAT(launch_attn_mma_d, FTQ_D)(int bits_k, int bits_v, bool shared_lut,
-                                              const AttnParams& p, int n_lb, cudaStream_t stream) {
+                                              const AttnParams& p, int n_lb, cudaStream_t stream,
+                                              bool* merged) {
     switch (bits_k) {
-        case 2: return mma_by_bv<2>(bits_v, shared_lut, p, n_lb, stream);
-        case 3: return mma_by_bv<3>(bits_v, shared_lut, p, n_lb, stream);
-        case 4: return mma_by_bv<4>(bits_v, shared_lut, p, n_lb, stream);
+        case 2: return mma_by_bv<2>(bits_v, shared_lut, p, n_lb, stream, merged);
+        case 3: return mma_by_bv<3>(bits_v, shared_lut, p, n_lb, stream, merged);
+        case 4: return mma_by_bv<4>(bits_v, shared_lut, p, n_lb, stream, merged);
     }
     return cudaErrorInvalidValue;
 }

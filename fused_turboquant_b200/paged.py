@@ -127,6 +127,40 @@ class PagedKVPool:
         return out
 
 
+    def gather_sequence(self, layer: int, block_row: torch.Tensor, seq_len: int):
+        """Contiguous copy of one sequence's compressed K/V, in the reference's tensor format.
+
+        block_row: [max_blocks] block ids of the sequence.  Returns
+        (k_codes u8 [Hkv, S, pdk], k_norms f16 [Hkv, S], v_codes u8 [Hkv, S, pdv], v_norms f16
+        [Hkv, S]) on the pool's device -- the arguments of the reference's
+        ``flash_decode_compressed`` / ``get_compressed_key`` dict
+        (kernels/triton_flash_decode.py:224-236, hf/fused_cache.py:333-346) for that sequence.
+        Plain tensor indexing (a diagnostic / interop path, not the decode path).
+        """
+        S = int(seq_len)
+        H, D = self.num_kv_heads, self.head_dim
+        pdk, pdv = kernels.packed_dim(D, self.key_bits), kernels.packed_dim(D, self.value_bits)
+        nb = (S + PAGE_TOKENS - 1) // PAGE_TOKENS
+        ids = block_row[:nb].to(device=self.pool.device, dtype=torch.long)
+        pages = self.pool[layer].index_select(0, ids)            # [nb, H, page_bytes]
+        off_kn = PAGE_TOKENS * pdk
+        off_vc = off_kn + 2 * PAGE_TOKENS
+        off_vn = off_vc + PAGE_TOKENS * pdv
+
+        def rows(lo, width):   # [nb, H, 16*width] -> [H, nb*16, width]
+            x = pages[:, :, lo:lo + PAGE_TOKENS * width].reshape(nb, H, PAGE_TOKENS, width)
+            return x.permute(1, 0, 2, 3).reshape(H, nb * PAGE_TOKENS, width)
+
+        k_codes = rows(0, pdk)[:, :S].contiguous()
+        v_raw = rows(off_vc, pdv)
+        # V rows of page tokens with bit 1 set are stored with their halves exchanged
+        swapped = torch.cat([v_raw[..., pdv // 2:], v_raw[..., :pdv // 2]], dim=-1)
+        tok = torch.arange(nb * PAGE_TOKENS, device=pages.device)
+        v_codes = torch.where(((tok & 2) != 0)[None, :, None], swapped, v_raw)[:, :S].contiguous()
+        k_norms = rows(off_kn, 2).contiguous().view(torch.float16).reshape(H, -1)[:, :S].contiguous()
+        v_norms = rows(off_vn, 2).contiguous().view(torch.float16).reshape(H, -1)[:, :S].contiguous()
+        return k_codes, k_norms, v_codes, v_norms
+
     def continuation_attention(self, q: torch.Tensor, block_table: torch.Tensor,
                                seq_lens: torch.Tensor, max_seq_len: int, scale: float | None = None,
                                layer: int = 0) -> torch.Tensor:
