@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cfloat>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/ftq_b200.h"
@@ -234,10 +235,10 @@ ChunkPlan plan_chunks(int B, int Hq, int Hkv, int d, int max_seq_len, int n_laye
 }
 
 // Chunking of the tensor-core path (persistent CTAs): few, large chunks keep the per-item
-// prologue and merge small; the chunk count is the smallest one whose item count fills the
-// CTA slots in whole waves to >= 95 % (else the best found).  Chunks hold at most 8192 tokens (short
-// enough for the dynamic hand-out of items to even out ragged batches; their block ids are staged
-// in shared memory) and at least 1024.
+// fixed costs small, more chunks fill the last wave of CTA slots better; the plan with the
+// lowest modelled cost wins.  Chunks hold at most 8192 tokens (short enough for the dynamic
+// hand-out of items to even out ragged batches; their block ids are staged in shared memory)
+// and at least 1024.
 ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers, int ctas_per_sm) {
     ChunkPlan pl;
     pl.n_hpass = 1;
@@ -246,17 +247,23 @@ ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers, int cta
     const int seq = max_seq_len > 0 ? max_seq_len : 1;
     const int c_min = (seq + 8191) / 8192;
     const int c_max = (seq + 1023) / 1024 > c_min ? (seq + 1023) / 1024 : c_min;
+    // Cost of a plan = waves of items x (pages of an item + the fixed cost of an item, in
+    // pages).  The fixed cost (publish / fold / next item's queries) weighs about 15 pages for
+    // a 16-warp CTA and 30 for an 8-warp one (fitted to measured step times of the uniform
+    // benchmark shapes); the cheapest plan wins, the fewest chunks among equals.
+    const double item_cost = ctas_per_sm == 1 ? 15.0 : 30.0;
     int best_nc = c_min, best_ct = 0;
-    double best_eff = -1.0;
+    double best_cost = -1.0;
     for (int nc = c_min; nc <= c_max && nc < c_min + 64; nc++) {
         int ct = ((seq + nc - 1) / nc + 63) / 64 * 64;
         if (ct > 8192) ct = 8192;
         const int real_nc = (seq + ct - 1) / ct;
         const int64_t items = units * real_nc;
         const int64_t waves = (items + slots - 1) / slots;
-        const double eff = static_cast<double>(items) / static_cast<double>(waves * slots);
-        if (eff > best_eff + 1e-9) { best_eff = eff; best_nc = real_nc; best_ct = ct; }
-        if (eff >= 0.95) { best_nc = real_nc; best_ct = ct; break; }
+        const double cost = static_cast<double>(waves) * (ct / 16.0 + item_cost);
+        if (best_cost < 0.0 || cost < best_cost * (1.0 - 1e-9)) {
+            best_cost = cost; best_nc = real_nc; best_ct = ct;
+        }
     }
     pl.chunk_tokens = best_ct;
     pl.n_chunks = best_nc;
@@ -332,10 +339,15 @@ __global__ void v0_gather_kernel(const uint8_t* __restrict__ kv_cache, int64_t n
         if (pos < seq_lens[b]) {
             const int64_t blk = block_tables[static_cast<int64_t>(b) * max_blocks + pos / block_size];
             const int off = pos % block_size;
-            const uint8_t* slot = kv_cache +
-                ((((static_cast<int64_t>(kv_type) * num_blocks + blk) * block_size + off) * Hkv + h) *
-                 elem_size);
-            val = *reinterpret_cast<const uint32_t*>(slot + 4 * w);
+            if (static_cast<uint64_t>(blk) < static_cast<uint64_t>(num_blocks)) {
+                const uint8_t* slot = kv_cache +
+                    ((((static_cast<int64_t>(kv_type) * num_blocks + blk) * block_size + off) * Hkv + h) *
+                     elem_size);
+                val = *reinterpret_cast<const uint32_t*>(slot + 4 * w);
+            } else {
+                // a block id outside the cache is never dereferenced: the position's norm reads NaN
+                val = w < pd / 4 ? 0u : 0x7fc00000u;
+            }
         }
         if (w < pd / 4) reinterpret_cast<uint32_t*>(out_codes + th * pd)[w] = val;
         else out_norms[th] = __uint_as_float(val);
@@ -652,6 +664,7 @@ int ftq_paged_store(const void* key, const void* value, int dtype, int64_t n_tok
         sink.slot_mapping = slot_mapping;
         sink.Hkv = Hkv;
         sink.page_bytes = page;
+        sink.slot_limit = num_blocks * FTQ_PAGE_TOKENS;
         sink.codes_off = which ? FTQ_PAGE_TOKENS * pdk + 2 * FTQ_PAGE_TOKENS : 0;
         sink.norms_off = which ? FTQ_PAGE_TOKENS * (pdk + pdv) + 2 * FTQ_PAGE_TOKENS
                                : FTQ_PAGE_TOKENS * pdk;
@@ -702,6 +715,7 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     rc = pack_signs(signs_host, head_dim, &p.signs);
     if (rc) return rc;
     p.q = q;
+    p.num_blocks = num_blocks;
     p.pool = pool; p.pool_layer_stride = pool_layer_stride;
     p.block_table = block_table; p.max_blocks = max_blocks;
     p.S = 0; p.seq_lens = seq_lens; p.B = B; p.Hq = Hq; p.Hkv = Hkv;
@@ -777,6 +791,7 @@ int ftq_v0_store(const void* key, const void* value, int dtype, int64_t n_tokens
         sink.slot_mapping = slot_mapping;
         sink.Hkv = Hkv;
         sink.block_size = block_size;
+        sink.slot_limit = num_blocks * block_size;
         sink.elem_size = elem_size;
         sink.plane_off = static_cast<int64_t>(which) * num_blocks * block_size * Hkv * elem_size;
         cudaError_t e = dispatch_encode(head_dim, which ? bits_v : bits_k, dtype, src, sink, tab,
@@ -854,7 +869,9 @@ extern "C" int ftq_paged_decode_attn_static(
     const int32_t* seq_lens, int max_seq_len, int B, int Hq, int Hkv, int head_dim, int bits_k,
     int bits_v, const float* levels_k_host, const float* levels_v_host, const float* signs_host,
     float scale, void* stream) {
-    // Shape errors are reported by the shared path below; only the size limit is checked here.
+    // Argument errors first (the shared path reports the rest), then the size limit.
+    const int bad = check_attn_common(B, Hq, Hkv, head_dim, bits_k, bits_v, q_dtype, out_dtype);
+    if (bad) return bad;
     const size_t need = ftq_decode_workspace_bytes(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     if (need > static_cast<size_t>(FTQ_STATIC_SCRATCH_BYTES))
         return fail(FTQ_ERR_WORKSPACE,

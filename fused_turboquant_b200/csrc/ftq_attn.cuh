@@ -198,6 +198,7 @@ attn_split_kernel(const AttnParams p) {
     const int32_t* btab = PAGED ? p.block_table + static_cast<int64_t>(b) * p.max_blocks : nullptr;
     const int64_t cbase = (static_cast<int64_t>(b) * p.Hkv + hkv) * p.S;
 
+    bool bad_block = false;  // (every thread walks the same block ids)
     auto issue_tile = [&](int ti, int buf) {
         uint8_t* dst = tiles + buf * TILE_BYTES;
 #pragma unroll
@@ -206,7 +207,13 @@ attn_split_kernel(const AttnParams p) {
             if (ts >= t1) break;
             uint8_t* pd = dst + pi * PAGE_BYTES;
             if constexpr (PAGED) {
-                const int64_t blk = btab[ts / kPageTokens];
+                // a block id outside the pool is never dereferenced: block 0 stands in and the
+                // chunk's result is replaced by NaN below
+                int64_t blk = btab[ts / kPageTokens];
+                if (static_cast<uint64_t>(blk) >= static_cast<uint64_t>(p.num_blocks)) {
+                    blk = 0;
+                    bad_block = true;
+                }
                 const uint8_t* src = pool + (blk * p.Hkv + hkv) * PAGE_BYTES;
                 stage_span<16>(pd, src, PAGE_BYTES, PAGE_BYTES, tid, kAttnThreads);
             } else {
@@ -419,6 +426,7 @@ attn_split_kernel(const AttnParams p) {
         }
         prow[h * prow_head_stride + d] = a;
         if (d == 0) {
+            if (bad_block) M = __int_as_float(0x7fc00000);
             prow[h * prow_head_stride + D] = M;
             prow[h * prow_head_stride + D + 1] = l;
         }

@@ -51,18 +51,21 @@ cudaError_t FTQ_CAT(launch_attn_split_d, FTQ_D)(int bits_k, int bits_v, bool pag
                  : by_bk<false>(bits_k, bits_v, p, n_lb, stream);
 }
 
-// The streaming kernel (no CTA-wide barriers, merge included) serves every configuration in
-// which it can run as many warps per SM as the barrier-synchronised one; the rest (head_dim
-// 256: the per-warp exchange slots do not fit beside 16 page rings) keep attn_mma_kernel and
-// the separate merge launch.
+// The streaming kernel (no CTA-wide barriers, merge included) serves the configurations in
+// which it was measured faster than the barrier-synchronised one: a 4-bit byte table (one
+// 16-warp CTA per SM) with one head half (GQA group <= 4).  Measured on B200: +5 % on the
+// Llama-shaped K4V4 batch; the 8-warp configurations (3- and 2-bit codes, where two service
+// warps are a quarter of the CTA) lose 2-6 % and keep attn_mma_kernel + the merge launch, as
+// does head_dim 256 (the per-warp exchange slots do not fit beside 16 page rings).
 template <int BK, int BV, int NH>
 constexpr bool use_stream_kernel() {
     using S = StreamCfg<FTQ_D, BK, BV, NH>;
-    using C = MmaCfg<FTQ_D, BK, BV, NH>;
-#ifdef FTQ_NO_STREAM
+#if defined(FTQ_NO_STREAM)
     return false;
+#elif defined(FTQ_ALL_STREAM)
+    return S::FITS;
 #else
-    return S::FITS && S::WARPS * S::CTAS_PER_SM >= C::WARPS * C::CTAS_PER_SM;
+    return S::FITS && S::WARPS == 16 && NH == 1;
 #endif
 }
 

@@ -431,6 +431,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     // learns it at the item's first barrier, early enough to request its first pages before the
     // merge); items without tokens get their (-inf, 0) rows on the spot.
     __shared__ int s_next[2];  // written in alternation: a slot is read before its next write's barrier
+    __shared__ int s_bad[2];   // item (by parity of its place in this CTA's sequence) saw a bad block id
     int ticket = n_items;  // thread 0: counter value drawn for the next item
     auto draw_ticket = [&]() {
         if (tid == 0) ticket = atomicAdd(p.work_counter, 1);
@@ -451,10 +452,17 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     };
     // item prologue, run by warps [w0, w0 + nw): block ids of the chunk and the rotated,
     // pre-scaled queries (8 octets of the first two warps rotate the at most 8 heads)
-    auto prologue = [&](const Item& it, int w0, int nw) {
+    // (a block id outside [0, num_blocks) is never dereferenced: block 0 stands in for it and
+    // flag `bad_slot` of s_bad makes the item's result NaN)
+    auto prologue = [&](const Item& it, int w0, int nw, int bad_slot) {
         const int32_t* btab =
             p.block_table + static_cast<int64_t>(it.b) * p.max_blocks + it.t0 / kPageTokens;
-        for (int i = tid - w0 * 32; i < it.n_pages; i += nw * 32) sblk[i] = btab[i];
+        for (int i = tid - w0 * 32; i < it.n_pages; i += nw * 32) {
+            const int32_t id = btab[i];
+            const bool ok = static_cast<uint32_t>(id) < static_cast<uint64_t>(p.num_blocks);
+            if (!ok) s_bad[bad_slot] = 1;
+            sblk[i] = ok ? id : 0;
+        }
         if (warp - w0 < 2) {  // warp-uniform
             const int t8 = lane & 7, o = lane >> 3;
             const int hh = (warp - w0) * 4 + o;
@@ -486,11 +494,15 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     constexpr int NRED = (NH * NMT <= WARPS - 2) ? NH * NMT : WARPS;
 
     draw_ticket();
-    if (tid == 0) s_next[1] = resolve_ticket(ticket);
+    if (tid == 0) {
+        s_next[1] = resolve_ticket(ticket);
+        s_bad[0] = 0;
+        s_bad[1] = 0;
+    }
     __syncthreads();
     int item = s_next[1];
     int slot = 0;
-    if (item < n_items) prologue(item_info(item), 0, WARPS);
+    if (item < n_items) prologue(item_info(item), 0, WARPS, 0);
     while (item < n_items) {
         const Item cur = item_info(item);
         const int hkv = cur.hkv, layer = cur.layer;
@@ -499,6 +511,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         // early page requests at the end of the main loop
         if (tid == 0) { draw_ticket(); s_next[slot] = resolve_ticket(ticket); }
         __syncthreads();  // prologue of this item visible; ring and exchange area free
+        const bool bad_item = s_bad[slot] != 0;   // (s_bad[slot ^ 1] collects the next item's)
         const int next = s_next[slot];
         slot ^= 1;
 
@@ -573,8 +586,9 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         };
         // same, for the first pages of a later item, whose block ids are not staged yet
         auto issue_page_of = [&](const Item& it2, int pg, int rb) {
-            const int32_t blk = p.block_table[static_cast<int64_t>(it2.b) * p.max_blocks +
-                                              it2.t0 / kPageTokens + pg];
+            int32_t blk = p.block_table[static_cast<int64_t>(it2.b) * p.max_blocks +
+                                        it2.t0 / kPageTokens + pg];
+            if (static_cast<uint32_t>(blk) >= static_cast<uint64_t>(p.num_blocks)) blk = 0;
             const uint8_t* page = p.pool + it2.layer * p.pool_layer_stride +
                                   static_cast<uint64_t>(static_cast<uint32_t>(blk)) * blk_stride +
                                   static_cast<int64_t>(it2.hkv) * C::PAGE_BYTES;
@@ -813,7 +827,10 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
         }
         // a warp whose copy never arrived poisons its state (NaN propagates to the output)
-        if (stalled) m_run[0] = __int_as_float(0x7fc00000);
+        if (stalled) {
+#pragma unroll
+            for (int hh = 0; hh < NH; hh++) m_run[hh] = __int_as_float(0x7fc00000);
+        }
         __syncthreads();  // every warp is done with the ring: it becomes the exchange area
 #pragma unroll
         for (int hh = 0; hh < NH; hh++) {
@@ -833,9 +850,13 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 const int ln = j & 31, mt = (j >> 5) % NMT, hh = j / (32 * NMT);
                 const int tg_ = ln & 3, g_ = ln >> 2;
                 float M = -INFINITY;
+                bool nan = bad_item;
 #pragma unroll
-                for (int w2 = 0; w2 < WARPS; w2++)
-                    M = fmaxf(M, xml[((w2 * NH + hh) * 2 + 0) * 4 + tg_]);
+                for (int w2 = 0; w2 < WARPS; w2++) {
+                    const float mw = xml[((w2 * NH + hh) * 2 + 0) * 4 + tg_];
+                    nan |= mw != mw;   // (fmaxf drops a NaN operand)
+                    M = fmaxf(M, mw);
+                }
                 float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
                 float l = 0.f;
 #pragma unroll
@@ -856,18 +877,20 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                     float* dst = prow + h * prow_head_stride;
                     *reinterpret_cast<float4*>(dst + (D / 8) * g_ + 4 * mt) = a;
                     if (g_ == 0 && mt == 0) {
-                        dst[D] = M * kLn2;  // the partial rows carry natural-log maxima
+                        // the partial rows carry natural-log maxima; NaN marks a poisoned item
+                        dst[D] = nan ? __int_as_float(0x7fc00000) : M * kLn2;
                         dst[D + 1] = l;
                     }
                 }
             }
         }
         if constexpr (NRED < WARPS) {
-            if (warp >= NRED && next < n_items) prologue(item_info(next), NRED, WARPS - NRED);
+            if (warp >= NRED && next < n_items) prologue(item_info(next), NRED, WARPS - NRED, slot);
         } else {
             __syncthreads();
-            if (next < n_items) prologue(item_info(next), 0, WARPS);
+            if (next < n_items) prologue(item_info(next), 0, WARPS, slot);
         }
+        if (tid == 0) s_bad[slot ^ 1] = 0;  // this item's flag: free for the item after next
         item = next;
     }
 }

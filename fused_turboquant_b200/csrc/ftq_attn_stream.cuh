@@ -90,6 +90,12 @@ struct StreamCfg {
 #else
     static constexpr int SKIP = 8;
 #endif
+    // service warps: 2 = warp 0 folds and finishes units, warp 1 prepares; 1 = warp 0 does both
+#ifdef FTQ_SERVICE_WARPS
+    static constexpr int NSVC = FTQ_SERVICE_WARPS;
+#else
+    static constexpr int NSVC = 2;
+#endif
 
     // First-fit placement (the same walk the kernel does): objects go before or after the
     // 64 KB-aligned table window.  Returns the bytes needed from `base`, or -1.
@@ -502,7 +508,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     // folds the published states and finishes units, warp 1 prepares the item after next, see
     // below) sit out the first S::SKIP rounds.  The map depends on nothing but the page
     // count, so the order of every floating-point sum is fixed.
-    constexpr int NSVC = 2;
+    constexpr int NSVC = S::NSVC;
     auto page_of = [&](int k) {
         if (S::SKIP == 0) return warp + WARPS * k;
         if (warp < NSVC) return (WARPS - NSVC) * S::SKIP + warp + WARPS * k;
@@ -830,7 +836,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         __threadfence_block();
         if (lane == 0) atomicAdd(const_cast<int*>(ctl + kCtlArrived + (seq & 1)), 1);
         if (warp == 0) serve_fold(seq);
-        if (warp == 1) serve_prepare(seq);
+        if (warp == NSVC - 1) serve_prepare(seq);
     };
 
     auto softmax_page = [&](const Regs& r, int pg2, const float (&c2)[NH][2][4],

@@ -46,6 +46,7 @@ struct EncodeSink {
     uint16_t* norms;
     // paged pool / v0 layout: token = v / Hkv, head = v % Hkv, slot = slot_mapping[token]
     const int64_t* slot_mapping;
+    int64_t slot_limit;     // slots at or beyond it (a stale or corrupt mapping) are skipped
     int Hkv;
     FastDiv div_hkv;        // division by Hkv (filled in by the dispatcher)
     int64_t page_bytes;     // paged: bytes per (block, head) page
@@ -117,7 +118,10 @@ __device__ __forceinline__ uint32_t octet_transpose_items(uint32_t w, const Tran
 // arithmetic so that the store at the end does not wait for it.
 __device__ __forceinline__ int64_t load_slot(const EncodeSink& sink, int64_t v, bool valid) {
     if (sink.mode == kSinkFlat || !valid) return -1;
-    return sink.slot_mapping[fast_div(static_cast<uint32_t>(v), sink.div_hkv)];
+    const int64_t slot = sink.slot_mapping[fast_div(static_cast<uint32_t>(v), sink.div_hkv)];
+    // negative = padding (the reference's `slot < 0` skip, triton_inkernel_store.py:398-399);
+    // a slot outside the cache is dropped the same way instead of being written out of bounds
+    return slot < sink.slot_limit ? slot : -1;
 }
 
 // Store one encoded vector: `w` holds this lane's codes (coordinates l + 8k) packed as

@@ -205,9 +205,12 @@ int ftq_paged_decode_attn(const void *q, int q_dtype, void *out, int out_dtype,
  *   - a batch whose partials exceed FTQ_STATIC_SCRATCH_BYTES
  *     (ftq_decode_workspace_bytes tells) is rejected with FTQ_ERR_WORKSPACE;
  *   - all calls on one GPU share the array and it keeps whatever the last call
- *     left (nothing in it has to start at zero: every row that is read is
- *     written first by the same call), so two calls that may run at the same
- *     time on one GPU (different streams) corrupt each other: serialise them;
+ *     left (every partial row that is read is written first by the same call,
+ *     and the counters in its tail are cleared by a memset node at the start
+ *     of every call), so two calls that may run at the same time on one GPU
+ *     (different streams) corrupt each other: serialise them;
+ *   - the device that owns q / out / pool must be the current device of the
+ *     calling thread: the size check and the scratch address are per device;
  *   - the first call on each device looks up the array's device address
  *     (one cudaGetSymbolAddress, no allocation); make that first call outside
  *     any stream capture.

@@ -57,8 +57,12 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         want = torch.full_like(q, float("nan"))
         got = torch.full_like(q, float("nan"))
         assert _call(lib, False, q, want, pool, bt_d, sl_d, max_seq, ws) == 0, lib.ftq_last_error()
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(dev)
         assert _call(lib, True, q, got, pool, bt_d, sl_d, max_seq) == 0, lib.ftq_last_error()
         torch.cuda.synchronize()
+        if call == 1:   # (the first call may load the kernel's module; the second must be clean)
+            assert torch.cuda.mem_get_info(dev)[0] == free_before, "the call changed free device memory"
         a, b = got.float().cpu().numpy(), want.float().cpu().numpy()
         assert np.isfinite(a).all()
         # same gate the other decode tests use for bf16 outputs; in practice the bits agree
