@@ -1,15 +1,30 @@
-"""Compressed KV cache for HF-style attention forwards, stored in a pre-allocated paged pool.
+"""Compressed KV cache for HF-style attention forwards, stored in pre-allocated paged pools.
 
-Mirrors ``CompressedKVCache`` of the reference (src/fused_turboquant/hf/fused_cache.py:140-360):
-``store_compressed_key / store_compressed_value / store_compressed_kv``, ``get_compressed_key /
-get_compressed_value``, ``decode_values``, ``get_seq_length``, ``reset``.  Where the reference
-grows two tensors per layer with ``torch.cat`` on every step (fused_cache.py:194-222) and its
-decode branch materialises dense K scores and dense V (fused_cache.py:576-624), this class writes
-each new token once into a ``PagedKVPool`` and ``decode_attention`` runs the fused paged kernel.
+Drop-in for ``CompressedKVCache`` of the reference
+(src/fused_turboquant/hf/fused_cache.py:140-360): same constructor ``(quantizer,
+compress_v=True)``, same methods (``set_layer_quantizer[_v]``, ``get_layer_quantizer[_v]``,
+``store_compressed_key / _value / _kv``, ``get_compressed_key / _value``, ``decode_values``,
+``reset``) and, when ``transformers`` is importable, the same base class ``DynamicCache`` -- the
+reference's patched forward stores through these methods and then calls ``DynamicCache.update``
+with one-element dummy slices for the length bookkeeping (fused_cache.py:559-574); that keeps
+working unchanged.
 
-Shapes follow HF: keys/values ``[batch, num_kv_heads, q_len, head_dim]``, every sequence of the
-batch has the same length.  Capacity (``max_seq_len``) is fixed at construction; the pool is
-allocated on the first store, when the batch size is known.
+What differs is underneath.  The reference grows two tensors per layer with ``torch.cat`` on
+every step (fused_cache.py:194-222) and its decode branch materialises dense K scores and dense
+V (fused_cache.py:576-624).  Here a layer's K and V codes go, in one fused encode launch, into a
+``PagedKVPool`` (one per layer, so layers may use different bit widths), and
+``decode_attention`` runs the fused paged kernel over it.  ``get_compressed_key/value`` still
+hand out the reference's contiguous dict format (a gather, for callers that want the codes).
+
+Options beyond the reference's constructor are keyword-only: ``max_seq_len`` (capacity per
+sequence, fixed), ``batch_size`` / ``num_kv_heads`` / ``n_layers`` / ``device`` (all four given:
+every pool is allocated at construction, nothing is allocated inside a forward), ``quantizer_v``.
+Sequences of a batch may have different lengths: ``store_compressed_kv(..., new_lens=...)``
+appends only the first ``new_lens[b]`` of the ``q_len`` new tokens of sequence ``b`` (right-padded
+prompts), and every later token of that sequence lands behind its own last one.
+With ``compress_v=False`` (reference: fused_cache.py:559-570, 619-624) only keys are compressed;
+values stay with the caller / ``DynamicCache.update`` and ``decode_attention`` takes them as
+``full_values``.
 """
 from __future__ import annotations
 
@@ -17,137 +32,246 @@ from typing import Optional
 
 import torch
 
-from . import kernels
-from .paged import PagedKVPool, page_bytes
+from . import _trace, kernels
+from .paged import PagedKVPool
 from .quantizer import CompressedTensor, TurboQuantMSE
 
+try:  # the reference's base class, when transformers is installed
+    from transformers import DynamicCache as _Base
+    _HAS_DYNAMIC_CACHE = True
+except Exception:  # pragma: no cover - transformers missing or broken
+    _Base = object
+    _HAS_DYNAMIC_CACHE = False
+
+logger = _trace.get_logger(__name__)
 _PAGE = 16
 
 
-class CompressedKVCache:
-    def __init__(self, quantizer: TurboQuantMSE, compress_v: bool = True, *, n_layers: int,
-                 max_seq_len: int = 4096, quantizer_v: TurboQuantMSE | None = None):
-        if not compress_v:
-            raise ValueError("compress_v=False is not supported: keys and values share one pool")
+class CompressedKVCache(_Base):
+    def __init__(self, quantizer: TurboQuantMSE, compress_v: bool = True, *,
+                 max_seq_len: int = 4096, batch_size: int | None = None,
+                 num_kv_heads: int | None = None, n_layers: int | None = None, device=None,
+                 quantizer_v: TurboQuantMSE | None = None):
+        if _HAS_DYNAMIC_CACHE:
+            super().__init__()
         self.tq = quantizer
-        self.tq_v = quantizer_v or quantizer
-        if self.tq_v.head_dim != self.tq.head_dim:
-            raise ValueError("key and value quantizers must agree on head_dim")
-        self.compress_v = True
-        self.n_layers = n_layers
+        self._tq_v_default = quantizer_v
+        if quantizer_v is not None:
+            self._check_pair(quantizer, quantizer_v)
+        self._layer_tq: dict[int, TurboQuantMSE] = {}
+        self._layer_tq_v: dict[int, TurboQuantMSE] = {}
+        self.compress_v = compress_v
         self.max_blocks = (max_seq_len + _PAGE - 1) // _PAGE
         self.max_seq_len = self.max_blocks * _PAGE
-        self.pool: Optional[PagedKVPool] = None
+        self._pools: dict[int, PagedKVPool] = {}          # layer -> pool (compress_v layers)
+        self._k_only: dict[int, Optional[dict]] = {}      # layer -> reference dict (K-only layers)
         self.block_table: Optional[torch.Tensor] = None
-        self._len = [0] * n_layers          # tokens stored per layer (host-side counters)
+        self._lens: dict[int, torch.Tensor] = {}          # layer -> int32 [B] tokens stored
+        self._max_len: dict[int, int] = {}                # layer -> host-side upper bound
         self._k_pending: dict[int, torch.Tensor] = {}
+        self.batch: Optional[int] = None
+        self._hkv: Optional[int] = None
+        if None not in (batch_size, num_kv_heads, n_layers, device):
+            like = torch.empty((batch_size, num_kv_heads, 0, quantizer.head_dim), device=device)
+            for layer in range(n_layers):
+                self._ensure_layer(layer, like)
+            logger.info("CompressedKVCache: %d layers pre-allocated for batch %d x %d tokens",
+                        n_layers, batch_size, self.max_seq_len)
 
-    # ---- bookkeeping ---------------------------------------------------------------------
-    def get_seq_length(self, layer_idx: int = 0) -> int:
-        return self._len[layer_idx] if layer_idx < self.n_layers else 0
+    # ---- per-layer quantizers (reference: fused_cache.py:167-192) ---------------------------
+    @staticmethod
+    def _check_pair(tq_k: TurboQuantMSE, tq_v: TurboQuantMSE) -> None:
+        if tq_v.head_dim != tq_k.head_dim:
+            raise ValueError("key and value quantizers must agree on head_dim")
+        if getattr(tq_v, "seed", None) != getattr(tq_k, "seed", None):
+            raise ValueError("key and value quantizers must share the rotation seed: one sign table "
+                             "serves the keys and the values of a pool")
+
+    def set_layer_quantizer(self, layer_idx: int, tq: TurboQuantMSE) -> None:
+        """Per-layer quantizer for K (and V, unless V is set separately); set before the layer's first store."""
+        if layer_idx in self._pools or layer_idx in self._k_only:
+            raise RuntimeError(f"layer {layer_idx} already holds tokens: reset() first")
+        self._layer_tq[layer_idx] = tq
+
+    def set_layer_quantizer_v(self, layer_idx: int, tq: TurboQuantMSE) -> None:
+        if layer_idx in self._pools or layer_idx in self._k_only:
+            raise RuntimeError(f"layer {layer_idx} already holds tokens: reset() first")
+        self._check_pair(self.get_layer_quantizer(layer_idx), tq)
+        self._layer_tq_v[layer_idx] = tq
 
     def get_layer_quantizer(self, layer_idx: int) -> TurboQuantMSE:
-        return self.tq
+        return self._layer_tq.get(layer_idx, self.tq)
 
     def get_layer_quantizer_v(self, layer_idx: int) -> TurboQuantMSE:
-        return self.tq_v
+        if layer_idx in self._layer_tq_v:
+            return self._layer_tq_v[layer_idx]
+        if layer_idx in self._layer_tq:
+            return self._layer_tq[layer_idx]
+        return self._tq_v_default or self.tq
 
-    def reset(self) -> None:
-        self._len = [0] * self.n_layers
+    # ---- bookkeeping --------------------------------------------------------------------------
+    def get_seq_length(self, layer_idx: int = 0, *args, **kwargs) -> int:
+        """Tokens stored in the layer (longest sequence).  Falls back to DynamicCache's own count
+        when nothing was stored through the compressed path."""
+        n = self._max_len.get(layer_idx, 0)
+        if n == 0 and _HAS_DYNAMIC_CACHE:
+            try:
+                return int(super().get_seq_length(layer_idx, *args, **kwargs))
+            except Exception:
+                return 0
+        return n
+
+    def seq_lens(self, layer_idx: int) -> Optional[torch.Tensor]:
+        """int32 [B] tokens stored per sequence (device tensor), or None before the first store."""
+        return self._lens.get(layer_idx)
+
+    def reset(self):
+        """Forget every stored token; pools stay allocated and are reused."""
+        for t in self._lens.values():
+            t.zero_()
+        self._max_len.clear()
+        self._k_only = {k: None for k in self._k_only}
         self._k_pending.clear()
+        if _HAS_DYNAMIC_CACHE and hasattr(self, "layers"):
+            self.layers.clear()
 
-    def _ensure_pool(self, like: torch.Tensor) -> None:
+    def _ensure_layer(self, layer_idx: int, like: torch.Tensor) -> None:
         B, hkv, _, d = like.shape
-        if self.pool is None:
-            self.pool = PagedKVPool(B * self.max_blocks, hkv, d, self.tq.bits, self.tq_v.bits,
-                                    self.n_layers, seed=self.tq.seed, device=like.device)
-            # sequence b owns blocks [b * max_blocks, (b + 1) * max_blocks)
+        if self.batch is None:
+            self.batch, self._hkv = B, hkv
+            # sequence b owns blocks [b * max_blocks, (b + 1) * max_blocks) of every layer's pool
             self.block_table = torch.arange(B * self.max_blocks, dtype=torch.int32,
                                             device=like.device).view(B, self.max_blocks)
-            self.batch = B
-        elif B != self.batch or hkv != self.pool.num_kv_heads:
-            raise ValueError("batch size / head count changed: call reset() and build a new cache")
+        elif B != self.batch or hkv != self._hkv:
+            raise ValueError("batch size / head count changed: build a new cache")
+        if layer_idx not in self._lens:
+            self._lens[layer_idx] = torch.zeros(B, dtype=torch.int32, device=like.device)
+        if self.compress_v and layer_idx not in self._pools:
+            tq_k, tq_v = self.get_layer_quantizer(layer_idx), self.get_layer_quantizer_v(layer_idx)
+            self._check_pair(tq_k, tq_v)
+            self._pools[layer_idx] = PagedKVPool(B * self.max_blocks, hkv, d, tq_k.bits, tq_v.bits,
+                                                 n_layers=1, seed=tq_k.seed, device=like.device)
 
-    # ---- stores --------------------------------------------------------------------------
+    # ---- stores -------------------------------------------------------------------------------
+    def _advance(self, layer_idx: int, q_len: int, new_lens, device):
+        """Slots of the q_len new tokens of every sequence (-1 = padding), lengths updated."""
+        start_max = self._max_len.get(layer_idx, 0)
+        if start_max + q_len > self.max_seq_len:
+            raise RuntimeError(f"cache capacity {self.max_seq_len} exceeded")
+        lens = self._lens[layer_idx]
+        t = torch.arange(q_len, device=device, dtype=torch.int32)
+        pos = lens[:, None] + t[None, :]                                   # [B, q_len]
+        blk = torch.gather(self.block_table.long(), 1, (pos // _PAGE).long())
+        slots = blk * _PAGE + (pos % _PAGE).long()
+        if new_lens is not None:
+            nl = new_lens.to(device=device, dtype=torch.int32)
+            slots = torch.where(t[None, :] < nl[:, None], slots, torch.full_like(slots, -1))
+            lens += nl
+        else:
+            lens += q_len
+        self._max_len[layer_idx] = start_max + q_len
+        return slots.reshape(-1)
+
     def store_compressed_kv(self, key_states: torch.Tensor, value_states: torch.Tensor,
-                            layer_idx: int) -> None:
-        """Encode K and V of the new tokens in one launch and append them to the layer."""
+                            layer_idx: int, *, new_lens: torch.Tensor | None = None) -> None:
+        """Encode K and V of the new tokens in one launch and append them to the layer
+        (reference: fused_cache.py:274-331).  ``new_lens`` ([B], optional): valid new tokens per
+        sequence; the rest of the q_len positions is padding and is not stored."""
+        if not self.compress_v:
+            self.store_compressed_key(key_states, layer_idx)
+            return
         if key_states.shape != value_states.shape:
             raise ValueError("key_states and value_states must have the same shape")
-        self._ensure_pool(key_states)
+        self._ensure_layer(layer_idx, key_states)
         B, hkv, q_len, d = key_states.shape
-        start = self._len[layer_idx]
-        if start + q_len > self.max_seq_len:
-            raise RuntimeError(f"cache capacity {self.max_seq_len} exceeded")
-        pos = torch.arange(start, start + q_len, device=key_states.device)
-        slots = (self.block_table.long()[:, pos // _PAGE] * _PAGE + pos % _PAGE).reshape(-1)
+        slots = self._advance(layer_idx, q_len, new_lens, key_states.device)
         k = key_states.permute(0, 2, 1, 3).reshape(B * q_len, hkv, d)
         v = value_states.permute(0, 2, 1, 3).reshape(B * q_len, hkv, d)
-        self.pool.store(k, v, slots, layer=layer_idx)
-        self._len[layer_idx] = start + q_len
+        self._pools[layer_idx].store(k, v, slots, layer=0)
 
-    def store_compressed_key(self, key_states: torch.Tensor, layer_idx: int) -> None:
-        """Keys and values of a step are written together: the keys wait for their values."""
-        self._k_pending[layer_idx] = key_states
+    def store_compressed_key(self, key_states: torch.Tensor, layer_idx: int):
+        """Reference: fused_cache.py:226-243.  With compressed values the keys wait for their
+        values (both go to the pool in one launch); K-only layers append to the contiguous dict."""
+        if self.compress_v:
+            self._k_pending[layer_idx] = key_states
+            return
+        self._ensure_layer(layer_idx, key_states)
+        tq = self.get_layer_quantizer(layer_idx)
+        ct = tq.encode(key_states)
+        entry = {"packed_indices": ct.indices.view(*key_states.shape[:-1], -1),
+                 "norms": ct.norms.view(*key_states.shape[:-1])}
+        prev = self._k_only.get(layer_idx)
+        if prev is not None:
+            entry = {"packed_indices": torch.cat([prev["packed_indices"], entry["packed_indices"]], dim=2),
+                     "norms": torch.cat([prev["norms"], entry["norms"]], dim=2)}
+        self._k_only[layer_idx] = entry
+        self._lens[layer_idx] += key_states.shape[2]
+        self._max_len[layer_idx] = self._max_len.get(layer_idx, 0) + key_states.shape[2]
 
-    def store_compressed_value(self, value_states: torch.Tensor, layer_idx: int) -> None:
+    def store_compressed_value(self, value_states: torch.Tensor, layer_idx: int):
+        """Reference: fused_cache.py:252-265."""
+        if not self.compress_v:
+            raise RuntimeError("this cache was built with compress_v=False: values are not stored here")
         if layer_idx not in self._k_pending:
             raise RuntimeError("store_compressed_key must be called before store_compressed_value")
         self.store_compressed_kv(self._k_pending.pop(layer_idx), value_states, layer_idx)
 
-    # ---- fused decode --------------------------------------------------------------------
+    # ---- fused decode -------------------------------------------------------------------------
     def decode_attention(self, query_states: torch.Tensor, layer_idx: int,
-                         scale: float | None = None) -> torch.Tensor:
-        """Attention of one query token per sequence over everything stored in the layer.
+                         scale: float | None = None, *, full_values: torch.Tensor | None = None
+                         ) -> torch.Tensor:
+        """Attention of one query token per sequence over everything stored in the layer
+        (what the reference's decode branch computes, fused_cache.py:576-624).
 
         query_states: [B, Hq, 1, D] (not rotated); returns [B, Hq, 1, D] in the query's dtype.
+        K-only caches (compress_v=False) need ``full_values`` [B, Hkv, kv_len, D].
         """
         B, hq, q_len, d = query_states.shape
         if q_len != 1:
             raise ValueError("decode_attention takes one query token per sequence")
-        n = self._len[layer_idx]
-        seq_lens = torch.full((B,), n, dtype=torch.int32, device=query_states.device)
-        out = self.pool.decode_attention(query_states[:, :, 0], self.block_table, seq_lens,
-                                         max(n, 1), scale, layer=layer_idx)
-        return out.unsqueeze(2)
+        if self.compress_v:
+            n = self._max_len.get(layer_idx, 0)
+            out = self._pools[layer_idx].decode_attention(
+                query_states[:, :, 0], self.block_table, self._lens[layer_idx], max(n, 1), scale,
+                layer=0)
+            return out.unsqueeze(2)
+        if full_values is None:
+            raise ValueError("compress_v=False: pass the uncompressed values as full_values")
+        tq = self.get_layer_quantizer(layer_idx)
+        entry = self._k_only[layer_idx]
+        scale = (d ** -0.5) if scale is None else scale
+        q_rot = kernels.rht(query_states.float().reshape(-1, d).contiguous(), tq.rotation.signs)
+        scores = kernels.fused_qk_scores_rht(q_rot.view(B, hq, 1, d), entry["packed_indices"],
+                                             entry["norms"], tq.quantizer.levels, scale, bits=tq.bits)
+        w = torch.softmax(scores, dim=-1, dtype=torch.float32).to(query_states.dtype)
+        hkv = full_values.shape[1]
+        v = full_values[:, :, None].expand(B, hkv, hq // hkv, *full_values.shape[2:]) \
+            .reshape(B, hq, *full_values.shape[2:])
+        return torch.matmul(w, v.to(query_states.dtype))
 
-    # ---- contiguous views of the stored codes (the reference's dict format) -----------------
+    # ---- contiguous views of the stored codes (the reference's dict format) ---------------------
     def _gather(self, layer_idx: int, which: int) -> Optional[dict]:
-        if self.pool is None or layer_idx >= self.n_layers or self._len[layer_idx] == 0:
+        n = self._max_len.get(layer_idx, 0)
+        if layer_idx not in self._pools or n == 0:
             return None
-        p = self.pool
-        d, n = p.head_dim, self._len[layer_idx]
-        pdk, pdv = d * p.key_bits // 8, d * p.value_bits // 8
-        off_kn = _PAGE * pdk
-        off_vc = off_kn + 2 * _PAGE
-        off_vn = off_vc + _PAGE * pdv
-        assert off_vn + 2 * _PAGE == page_bytes(d, p.key_bits, p.value_bits)
-        pages = p.pool[layer_idx][self.block_table.long()]          # [B, blocks, Hkv, page]
-        B, nblk, hkv, _ = pages.shape
-        if which == 0:
-            codes = pages[..., :off_kn].reshape(B, nblk, hkv, _PAGE, pdk)
-            norms = pages[..., off_kn:off_vc]
-        else:
-            codes = pages[..., off_vc:off_vn].reshape(B, nblk, hkv, _PAGE, pdv)
-            # value rows of page tokens with bit 1 set are stored with their halves exchanged
-            swapped = torch.cat([codes[..., pdv // 2:], codes[..., :pdv // 2]], dim=-1)
-            bit1 = (torch.arange(_PAGE, device=codes.device) & 2).bool().view(1, 1, 1, _PAGE, 1)
-            codes = torch.where(bit1, swapped, codes)
-            norms = pages[..., off_vn:]
-        norms = norms.contiguous().view(torch.float16).reshape(B, nblk, hkv, _PAGE)
-        codes = codes.permute(0, 2, 1, 3, 4).reshape(B, hkv, nblk * _PAGE, -1)[:, :, :n]
-        norms = norms.permute(0, 2, 1, 3).reshape(B, hkv, nblk * _PAGE)[:, :, :n]
-        return {"packed_indices": codes.contiguous(), "norms": norms.contiguous()}
+        p = self._pools[layer_idx]
+        rows = [p.gather_sequence(0, self.block_table[b], n) for b in range(self.batch)]
+        codes = torch.stack([r[2 * which] for r in rows])
+        norms = torch.stack([r[2 * which + 1] for r in rows])
+        return {"packed_indices": codes, "norms": norms}
 
     def get_compressed_key(self, layer_idx: int) -> Optional[dict]:
+        if not self.compress_v:
+            return self._k_only.get(layer_idx)
         return self._gather(layer_idx, 0)
 
     def get_compressed_value(self, layer_idx: int) -> Optional[dict]:
-        return self._gather(layer_idx, 1)
+        return self._gather(layer_idx, 1) if self.compress_v else None
 
     def decode_values(self, layer_idx: int) -> torch.Tensor:
-        """Dense fp32 values [B, Hkv, kv_len, D] (the reference's unfused V path needs them)."""
+        """Dense fp32 values [B, Hkv, kv_len, D] (reference: fused_cache.py:333-346)."""
+        tq = self.get_layer_quantizer_v(layer_idx)
         entry = self.get_compressed_value(layer_idx)
         ct = CompressedTensor(indices=entry["packed_indices"], norms=entry["norms"],
-                              original_dim=self.tq_v.head_dim, bits=self.tq_v.bits)
-        return self.tq_v.decode(ct)
+                              original_dim=tq.head_dim, bits=tq.bits)
+        return tq.decode(ct)

@@ -12,8 +12,10 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib, codebook, kernels
+from . import _lib, _trace, codebook, kernels
 from .kernels import _DT, _host_table, _ptr, _require_cuda, _stream
+
+logger = _trace.get_logger(__name__)
 
 PAGE_TOKENS = 16
 
@@ -51,6 +53,10 @@ class PagedKVPool:
         self.bounds_v, self.levels_v = codebook.codebook_f32(head_dim, value_bits)
         self.pool = torch.zeros((n_layers, num_blocks, num_kv_heads, self.page_bytes),
                                 dtype=torch.uint8, device=device)
+        logger.info("paged compressed KV pool: %d layers x %d blocks x %d KV heads, head_dim %d, "
+                    "K%d/V%d, %d bytes per 16-token page (%.1f MiB)", n_layers, num_blocks,
+                    num_kv_heads, head_dim, key_bits, value_bits, self.page_bytes,
+                    self.pool.numel() / 2 ** 20)
 
     @property
     def layer_stride(self) -> int:
@@ -76,7 +82,7 @@ class PagedKVPool:
             L, n_tokens = 1, key.shape[0]
             pool = self.pool[layer]
         D, H = self.head_dim, self.num_kv_heads
-        with torch.cuda.device(key.device):
+        with torch.cuda.device(key.device), _trace.nvtx("ftq.store"):
             rc = _lib.load().ftq_paged_store(
                 _ptr(key), _ptr(value), _DT[key.dtype], n_tokens, H, D, H * D, D, self.key_bits,
                 self.value_bits, _lib.fptr(self.signs), _lib.fptr(self.bounds_k),
@@ -116,7 +122,7 @@ class PagedKVPool:
         sl = seq_lens.to(device=q.device, dtype=torch.int32).contiguous()
         need = self.workspace_bytes(B, Hq, max_seq_len, L)
         ws = workspace if workspace is not None else kernels.get_workspace(q.device, need)
-        with torch.cuda.device(q.device):
+        with torch.cuda.device(q.device), _trace.nvtx("ftq.decode"):
             rc = _lib.load().ftq_paged_decode_attn(
                 _ptr(q), _DT[q.dtype], _ptr(out), _DT[out.dtype], _ptr(pool), self.num_blocks,
                 self.layer_stride, L, _ptr(bt), bt.shape[1], _ptr(sl), int(max_seq_len), B, Hq,

@@ -22,6 +22,10 @@ from typing import Sequence
 import torch
 import torch.distributed as dist
 
+from . import _trace
+
+logger = _trace.get_logger(__name__)
+
 
 def shard_sequences_equal(batch: int, world_size: int, rank: int) -> range:
     """Contiguous, near-equal split of `batch` sequences."""
@@ -79,7 +83,8 @@ def all_gather_heads(out_local: torch.Tensor, group=None) -> torch.Tensor:
     local = out_local.contiguous()
     flat = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype,
                        device=local.device)
-    dist.all_gather_into_tensor(flat, local, group=group)
+    with _trace.nvtx("ftq.all_gather"):
+        dist.all_gather_into_tensor(flat, local, group=group)
     gathered = flat.view((world,) + tuple(local.shape))
     # [world, ..., B, Hl, D] -> [..., B, world, Hl, D] -> merge
     nd = local.dim()

@@ -87,3 +87,48 @@ def test_all_gather_heads_gloo_world2():
 def test_all_gather_requires_process_group():
     with pytest.raises(RuntimeError):
         sharding.all_gather_heads(torch.zeros(1, 2, 3))
+
+
+def _absent_rank_worker(rank, world, port, q, done):
+    """Rank 1 joins the group but never enters the collective; rank 0 must get an error, not hang."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=4))
+    if rank == 1:
+        done.wait(60)          # stays alive (a crashed peer is a different failure), skips the call
+        os._exit(0)
+    try:
+        sharding.all_gather_heads(torch.zeros(1, 2, 2, 4))
+        q.put("returned")
+    except Exception as e:     # gloo reports the timeout as a RuntimeError / DistBackendError
+        q.put(f"{type(e).__name__}: {e}"[:300])
+    finally:
+        done.set()
+    os._exit(0)                # (no orderly teardown: the peer never reaches the shutdown barrier)
+
+
+def test_all_gather_with_an_absent_rank_times_out_cleanly():
+    ctx = mp.get_context("spawn")
+    q, done = ctx.Queue(), ctx.Event()
+    port = _free_port()
+    procs = [ctx.Process(target=_absent_rank_worker, args=(r, 2, port, q, done)) for r in range(2)]
+    for p in procs:
+        p.start()
+    msg = q.get(timeout=90)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert msg != "returned", "the collective returned although a rank never joined it"
+    assert "Error" in msg or "Timed out" in msg or "timeout" in msg.lower(), msg
+
+
+def test_mismatched_shard_counts_are_rejected_before_any_collective():
+    # 8 KV heads cannot be split over 3 ranks; the host-side check fires on every rank
+    for rank in range(3):
+        with pytest.raises(ValueError):
+            sharding.shard_kv_heads(8, 64, 3, rank)
+    with pytest.raises(ValueError):
+        sharding.shard_sequences_equal(10, 0, 0)
+    with pytest.raises(ValueError):
+        sharding.shard_sequences_lpt([1, 2, 3], 0)
