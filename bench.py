@@ -585,12 +585,120 @@ def ragged_lpt_record(device, rank, world, steps):
     return rec
 
 
+# vLLM-v1 slot-format shapes (--workload tq_*): single GPU, all layer caches in one allocation
+TQ_SHAPES = {
+    "tq_qwen": dict(desc="slot format, qwen2.5-0.5b shape, K3V3, value rotation", Hq=14, Hkv=2, D=64,
+                    kb=3, vb=3, B=32, ctx=4096, layers=24, v_rotate=True),
+    "tq_llama": dict(desc="slot format, llama-3-8b shape, K4V4", Hq=32, Hkv=8, D=128, kb=4, vb=4,
+                     B=64, ctx=8192, layers=4, v_rotate=False),
+    "tq_llama_k8v4": dict(desc="slot format, llama-3-8b shape, FP8 keys, 4-bit values", Hq=32, Hkv=8,
+                          D=128, kb=8, vb=4, B=64, ctx=8192, layers=4, v_rotate=False),
+}
+
+
+def run_tq_workload(args):
+    """The vLLM-v1 slot-format path (fused store, split-KV decode) on one GPU.  A step decodes
+    every layer; layers smaller than 64 MB go through ONE ftq_tq_decode_layers call, larger
+    ones one call per layer.  Bytes counted: the slot bytes in use (codes, norm, scale, zero;
+    padding excluded) of every attended (token, KV head), block ids, queries and outputs."""
+    from fused_turboquant_b200 import tq_v1
+
+    w = TQ_SHAPES[args.workload]
+    Hq, Hkv, D, kb, vb, B, ctx, L = (w[k] for k in ("Hq", "Hkv", "D", "kb", "vb", "B", "ctx", "layers"))
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(20252)
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, norm_correction=True)
+    slot, bs = cfg.slot_size_aligned, 16
+    blocks_per_seq = ctx // bs
+    nb = B * blocks_per_seq
+    cent = torch.sort(torch.randn(1 << min(kb, 4), generator=gen, device=dev) / D ** 0.5).values
+    cent, mids = tq_v1.midpoints_of(cent)
+    caches = torch.zeros((L, nb, bs, Hkv, slot), dtype=torch.uint8, device=dev)
+    bt = torch.randperm(nb, generator=gen, device=dev).view(B, blocks_per_seq).to(torch.int32)
+    pos = torch.arange(ctx, device=dev)
+    slots = (bt.long()[:, pos // bs] * bs + pos % bs).reshape(-1)
+    n_tok = B * ctx
+    store_ms = []
+    for layer in range(L):
+        k = torch.randn((n_tok, Hkv, D), generator=gen, device=dev).bfloat16()
+        v = torch.randn((n_tok, Hkv, D), generator=gen, device=dev).bfloat16()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        tq_v1.launch_store(k, v, caches[layer], slots, mids, cfg, v_rotate=w["v_rotate"])
+        e1.record()
+        torch.cuda.synchronize()
+        store_ms.append(e0.elapsed_time(e1))
+        del k, v
+    seq_lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+    q = torch.randn((L, B, Hq, D), generator=gen, device=dev).bfloat16()
+    used = cfg.slot_size
+    layer_bytes = B * ctx * Hkv * used + B * blocks_per_seq * 4 + 2 * B * Hq * D * 2
+    batched = layer_bytes < (64 << 20)
+    rows = L if batched else 1
+    # split count with the lowest modelled cost: waves of (row, KV head, split) items over the
+    # persistent CTAs x (pages of an item + the fixed cost of an item, ~15 / 30 pages for a
+    # 16- / 8-warp CTA), as the paged path plans its chunks
+    per_sm = 1 if 4 in (kb, vb) else 2
+    cta_slots = torch.cuda.get_device_properties(dev).multi_processor_count * per_sm
+    best = (float("inf"), 1)
+    for sp in range(1, 33):
+        items = rows * B * Hkv * sp
+        cost = -(-items // cta_slots) * (blocks_per_seq / sp + (15.0 if per_sm == 1 else 30.0))
+        if cost < best[0] * (1 - 1e-9):
+            best = (cost, sp)
+    splits = best[1]
+    mid_o = torch.empty((rows * B, Hq, splits, D + 1), dtype=torch.float32, device=dev)
+    out = torch.empty((L, B, Hq, D), dtype=torch.bfloat16, device=dev)
+
+    def step():
+        if batched:
+            tq_v1.decode_attention(q, caches, bt, seq_lens, cent, cfg, D ** -0.5, num_kv_splits=splits,
+                                   v_rotate=w["v_rotate"], mid_o=mid_o, output=out)
+        else:
+            for layer in range(L):
+                tq_v1.decode_attention(q[layer], caches[layer], bt, seq_lens, cent, cfg, D ** -0.5,
+                                       num_kv_splits=splits, v_rotate=w["v_rotate"], mid_o=mid_o,
+                                       output=out[layer])
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    regs = []
+    for _ in range(max(1, args.regions)):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        regs.append(e0.elapsed_time(e1))
+    ms = float(np.median(regs)) / args.steps
+    peak, peak_src = load_peaks()
+    value = L * layer_bytes / ms / 1e6
+    best_store = min(store_ms[1:]) if L > 1 else store_ms[0]
+    store_bytes = n_tok * Hkv * (2 * D * 2 + used)
+    print(json.dumps({
+        "metric": "tq_v1_decode_attn_hbm_gbs", "value": value, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "timed_regions_ms": regs,
+        "config": {"workload": f"{args.workload}: {w['desc']}", **{k: v for k, v in w.items() if k != "desc"},
+                   "splits": splits, "slot_bytes": slot, "layers_per_call": rows,
+                   "l2": "distinct layer caches, each step reads all of them"},
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s",
+                     "frac": value / peak, "traffic": None, "peak_source": peak_src},
+        "store": {"tokens_per_s": n_tok / best_store * 1e3, "ms": best_store,
+                  "gbs": store_bytes / best_store / 1e6},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + sorted(TQ_SHAPES))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug)")
     ap.add_argument("--regions", type=int, default=5,
@@ -602,6 +710,15 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    if args.workload in TQ_SHAPES:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU arm times the configuration-2..5 "
+                              "workloads only"}), flush=True)
+            return
+        if not torch.cuda.is_available():
+            raise RuntimeError("bench.py needs a CUDA device (no CPU fallback in the product path)")
+        run_tq_workload(args)
+        return
     w = dict(WORKLOADS[args.workload])
     if args.layers:
         w["layers"] = args.layers

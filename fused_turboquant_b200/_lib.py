@@ -46,6 +46,9 @@ SIGNATURES = {
     "ftq_tq_decode": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i64, _i64, _i64, _i, _vp, _i, _vp, _vp,
                            _i, _i, _i, _i, _i, _fp, _c.c_float, _i, _vp, _vp, _i, _vp, _vp, _i, _vp,
                            _vp]),
+    "ftq_tq_decode_layers": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i64, _i64, _i64, _i, _vp, _i, _vp,
+                                  _vp, _i, _i, _i, _i, _i, _fp, _c.c_float, _i, _vp, _vp, _i, _vp,
+                                  _vp, _i, _vp, _i, _i64, _i64, _vp]),
 }
 
 _lib = None

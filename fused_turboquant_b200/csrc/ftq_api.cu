@@ -975,6 +975,30 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
                              float* mid_o, void* out, int out_dtype, float* lse,
                              const void* prefix_out, int prefix_dtype, const float* prefix_lse,
                              void* stream) {
+    return ftq_tq_decode_layers(q, q_dtype, B, Hq, Hkv, head_dim, kv_cache, stride_block, stride_pos,
+                                stride_head, block_size, block_table, max_blocks, seq_lens,
+                                kv_start_offset, key_bits, value_bits, norm_correction, rotate_output,
+                                value_lloyd_max, centroids_host, scale, num_kv_splits, mid_o, out,
+                                out_dtype, lse, prefix_out, prefix_dtype, prefix_lse, 1, 0, 0, stream);
+}
+
+extern "C" int ftq_tq_decode_layers(const void* q, int q_dtype, int B, int Hq, int Hkv, int head_dim,
+                                    const uint8_t* kv_cache, int64_t stride_block, int64_t stride_pos,
+                                    int64_t stride_head, int block_size, const int32_t* block_table,
+                                    int max_blocks, const int32_t* seq_lens,
+                                    const int32_t* kv_start_offset, int key_bits, int value_bits,
+                                    int norm_correction, int rotate_output, int value_lloyd_max,
+                                    const float* centroids_host, float scale, int num_kv_splits,
+                                    float* mid_o, void* out, int out_dtype, float* lse,
+                                    const void* prefix_out, int prefix_dtype, const float* prefix_lse,
+                                    int n_layers, int64_t cache_layer_stride, int64_t num_blocks,
+                                    void* stream) {
+    if (n_layers <= 0 || !even(cache_layer_stride) || num_blocks < 0)
+        return fail(FTQ_ERR_INVALID, "bad n_layers / cache_layer_stride / num_blocks");
+    const int B_seq = B;
+    if (static_cast<int64_t>(B) * n_layers > 65535)
+        return fail(FTQ_ERR_INVALID, "B * n_layers must be at most 65535 per call");
+    B = B * n_layers;   // rows of q / mid_o / out
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
         return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 or 8 = FP8 / 1,2,3,4,8)", key_bits,
@@ -1003,6 +1027,10 @@ extern "C" int ftq_tq_decode(const void* q, int q_dtype, int B, int Hq, int Hkv,
     p.q = q;
     p.q_dtype = q_dtype;
     p.B = B;
+    p.B_seq = B_seq > 0 ? B_seq : 1;
+    p.div_bseq = ftq::make_fastdiv(static_cast<uint32_t>(p.B_seq));
+    p.cache_layer_stride = cache_layer_stride;
+    p.num_blocks = num_blocks;
     p.Hq = Hq;
     p.Hkv = Hkv;
     p.kv_cache = kv_cache;

@@ -389,7 +389,13 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
 struct TqDecodeParams {
     const void* q;  // [B, Hq, D], original space
     int q_dtype;
+    // B counts (layer, sequence) rows: q / mid_o / out are stacked [n_layers * B_seq, ...]; row r
+    // reads the cache of layer r / B_seq and the block table / lengths of sequence r % B_seq
     int B, Hq, Hkv;
+    int B_seq;
+    FastDiv div_bseq;
+    int64_t cache_layer_stride;  // bytes between the caches of consecutive layers
+    int64_t num_blocks;          // block ids are checked against it (<= 0: not checked)
     const uint8_t* kv_cache;
     int64_t stride_block, stride_pos, stride_head;
     int block_size;
@@ -454,8 +460,11 @@ tq_split_kernel(const TqDecodeParams p) {
     const int h0 = hp * GH;
     const int nh = min(GH, group - h0);
 
-    const int seq_len = p.seq_lens[b];
-    const int kv_start = p.kv_start ? p.kv_start[b] : 0;
+    const int layer = static_cast<int>(fast_div(static_cast<uint32_t>(b), p.div_bseq));
+    const int bs = b - layer * p.B_seq;   // sequence (block table / length row)
+    const uint8_t* const kv_layer = p.kv_cache + layer * p.cache_layer_stride;
+    const int seq_len = p.seq_lens[bs];
+    const int kv_start = p.kv_start ? p.kv_start[bs] : 0;
     const int eff = seq_len - kv_start;
     const int split_len = (eff + p.splits - 1) / p.splits;
     const int t0 = kv_start + split_len * sid;
@@ -517,13 +526,19 @@ tq_split_kernel(const TqDecodeParams p) {
         for (int i = 0; i < EP; i++) acc[h][i] = pk2(0.f, 0.f);
     }
 
-    const int32_t* btab = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
-    // address of the slot of position `pos` (this CTA's KV head)
+    const int32_t* btab = p.block_table + static_cast<int64_t>(bs) * p.max_blocks;
+    // address of the slot of position `pos` (this CTA's KV head); a block id outside the cache
+    // is never dereferenced (block 0 stands in, the partial's lse becomes NaN)
+    bool bad_block = false;
     auto slot_ptr = [&](int pos) {
         const uint32_t pg = fast_div(static_cast<uint32_t>(pos), p.div_block);
         const uint32_t off = static_cast<uint32_t>(pos) - pg * p.block_size;
-        return p.kv_cache + static_cast<int64_t>(btab[pg]) * p.stride_block + off * p.stride_pos +
-               hkv * p.stride_head;
+        int64_t id = btab[pg];
+        if (p.num_blocks > 0 && static_cast<uint64_t>(id) >= static_cast<uint64_t>(p.num_blocks)) {
+            id = 0;
+            bad_block = true;
+        }
+        return kv_layer + id * p.stride_block + off * p.stride_pos + hkv * p.stride_head;
     };
     // put 16-bit unit j of a slot where the math reads it: key codes / value codes / scalars
     auto place_u16 = [&](int tk, int j, uint32_t v) {
@@ -554,7 +569,7 @@ tq_split_kernel(const TqDecodeParams p) {
     auto prefetch = [&](int ts) {
         if constexpr (PREFETCH) {
             const bool live = ts + ld_tk < t1;
-            const uint8_t* sp = live ? slot_ptr(ts + ld_tk) : p.kv_cache;
+            const uint8_t* sp = live ? slot_ptr(ts + ld_tk) : kv_layer;
             raw_mis = static_cast<int>(reinterpret_cast<uintptr_t>(sp) >> 1) & 1;
             const uint8_t* al = sp - 2 * raw_mis;
 #pragma unroll
@@ -766,7 +781,7 @@ tq_split_kernel(const TqDecodeParams p) {
             }
         }
     }
-    __syncthreads();
+    const bool any_bad = __syncthreads_or(bad_block) != 0;
     for (int idx = tid; idx < nh * D; idx += kAttnThreads) {
         const int h = idx / D, d = idx - h * D;
         float M = -INFINITY;
@@ -784,7 +799,8 @@ tq_split_kernel(const TqDecodeParams p) {
         }
         const float safe_l = l > 0.f ? l : 1.f;
         mo[h * mo_head_stride + d] = a / safe_l;
-        if (d == 0) mo[h * mo_head_stride + D] = M + logf(safe_l);
+        if (d == 0)
+            mo[h * mo_head_stride + D] = any_bad ? __int_as_float(0x7fc00000) : M + logf(safe_l);
     }
 }
 

@@ -148,15 +148,17 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
     auto qs_index = [](int head, int coord) {
         return head * (D + 16) + (coord / (D / 4)) * (D / 4 + 4) + coord % (D / 4);
     };
-    struct Item { int sid, hkv, b, t0, t1, n_pages; };
+    struct Item { int sid, hkv, b, bs, layer, t0, t1, n_pages; };
     auto item_info = [&](int item) {
         Item it;
         it.sid = item % p.splits;
         const int r = item / p.splits;
         it.hkv = r % p.Hkv;
-        it.b = r / p.Hkv;
-        const int seq_len = p.seq_lens[it.b];
-        const int kv_start = p.kv_start ? p.kv_start[it.b] : 0;
+        it.b = r / p.Hkv;   // (layer, sequence) row
+        it.layer = static_cast<int>(fast_div(static_cast<uint32_t>(it.b), p.div_bseq));
+        it.bs = it.b - it.layer * p.B_seq;
+        const int seq_len = p.seq_lens[it.bs];
+        const int kv_start = p.kv_start ? p.kv_start[it.bs] : 0;
         const int split_len = (seq_len - kv_start + p.splits - 1) / p.splits;
         it.t0 = kv_start + split_len * it.sid;
         it.t1 = min(it.t0 + split_len, seq_len);
@@ -232,7 +234,9 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
                 for (int i = 0; i < 4; i++) oacc[hh][mt][i] = 0.f;
         }
 
-        const int32_t* btab = p.block_table + static_cast<int64_t>(cur_it.b) * p.max_blocks;
+        const int32_t* btab = p.block_table + static_cast<int64_t>(cur_it.bs) * p.max_blocks;
+        const uint8_t* const kv_layer = p.kv_cache + cur_it.layer * p.cache_layer_stride;
+        bool bad_block = false;   // a block id outside the cache: block 0 stands in, lse becomes NaN
         // ---- staging, one page ahead, in registers.  The 16 slots of a page are copied word by
         // word: lane l takes the words l, l + 32, ... of the list (token 0 words 0..NWR-1, token 1
         // ...), so that a load instruction reads consecutive words of one or two slots.  Slots
@@ -272,7 +276,12 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
             const int pos = min(t0 + pg * kPageTokens + (lane & 15), t1 - 1);
             const uint32_t blk = fast_div(static_cast<uint32_t>(pos), p.div_block);
             const uint32_t off = static_cast<uint32_t>(pos) - blk * p.block_size;
-            const uint8_t* sp = p.kv_cache + static_cast<int64_t>(btab[blk]) * p.stride_block +
+            int64_t id = btab[blk];
+            if (p.num_blocks > 0 && static_cast<uint64_t>(id) >= static_cast<uint64_t>(p.num_blocks)) {
+                id = 0;
+                bad_block = true;
+            }
+            const uint8_t* sp = kv_layer + id * p.stride_block +
                                 off * p.stride_pos + hkv * p.stride_head;
             const uint32_t m = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(sp) >> 1) & 1u;
             mis_next = __ballot_sync(0xffffffffu, m != 0u) & 0xffffu;
@@ -476,7 +485,8 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
                 z_run[hh] += __shfl_xor_sync(0xffffffffu, z_run[hh], m);
             }
         }
-        __syncthreads();  // every warp is done with its page buffer: the area becomes the exchange area
+        // every warp is done with its page buffer: the area becomes the exchange area
+        const bool any_bad = __syncthreads_or(bad_block) != 0;
 #pragma unroll
         for (int hh = 0; hh < NH; hh++) {
 #pragma unroll
@@ -524,7 +534,8 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
                     o4[1] = (a.y + z) * inv;
                     o4[2] = (a.z + z) * inv;
                     o4[3] = (a.w + z) * inv;
-                    if (g_ == 0 && mt == 0) dst[D] = M * kLn2 + logf(l);
+                    if (g_ == 0 && mt == 0)
+                        dst[D] = any_bad ? __int_as_float(0x7fc00000) : M * kLn2 + logf(l);
                 }
             }
         }

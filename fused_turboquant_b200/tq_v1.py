@@ -176,6 +176,10 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
                      prefix_lse: torch.Tensor | None = None) -> torch.Tensor:
     """Decode attention of ``query`` ``[B, Hq, D]`` over the compressed cache; returns ``[B, Hq, D]``.
 
+    All layers in one call: ``query`` ``[L, B, Hq, D]`` with ``kv_cache`` ``[L, num_blocks,
+    block_size, Hkv, slot]`` (one allocation, every layer the same block table); ``mid_o``,
+    ``output``, ``lse`` and the prefix tensors then carry the same leading ``L``.
+
     ``v_rotate``: the cache holds rotated values, the merged output is transformed back.
     ``v_lloyd_max``: 4-bit values are Lloyd-Max codes (see ``launch_store``).
     ``prefix_output`` ``[B, Hq, D]`` / ``prefix_lse`` ``[B, Hq]``: attention of the same queries
@@ -187,14 +191,24 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
     """
     _require_cuda(query, "query")
     _require_cuda(kv_cache, "kv_cache")
+    if kv_cache.dtype != torch.uint8:
+        kv_cache = kv_cache.view(torch.uint8)
+    n_layers, layer_stride, lead = 1, 0, ()
+    if query.dim() == 4:
+        if kv_cache.dim() != 5 or kv_cache.shape[0] != query.shape[0]:
+            raise ValueError("a [L, B, Hq, D] query needs a [L, num_blocks, block_size, Hkv, slot] cache")
+        n_layers, lead = query.shape[0], (query.shape[0],)
+        layer_stride = kv_cache.stride(0)
+        query = query.reshape(-1, *query.shape[2:])
+        kv_cache = kv_cache[0]
     B, hq, d = query.shape
+    B //= n_layers
+    rows = B * n_layers
     if d != tq_config.head_dim:
         raise ValueError(f"query head size {d} does not match the config ({tq_config.head_dim})")
     if query.dtype not in _DT:
         query = query.float()
     query = query.contiguous()
-    if kv_cache.dtype != torch.uint8:
-        kv_cache = kv_cache.view(torch.uint8)
     sb, sp, sh = _cache_strides(kv_cache)
     hkv = kv_cache.shape[2]
     dev = query.device
@@ -202,35 +216,40 @@ def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: t
     sl = seq_lens.to(device=dev, dtype=torch.int32).contiguous()
     ks = None if kv_start_offset is None else kv_start_offset.to(device=dev, dtype=torch.int32).contiguous()
     if mid_o is None:
-        mid_o = torch.empty((B, hq, num_kv_splits, d + 1), dtype=torch.float32, device=dev)
-    elif mid_o.shape != (B, hq, num_kv_splits, d + 1) or mid_o.dtype != torch.float32 or not mid_o.is_contiguous():
-        raise ValueError("mid_o must be a contiguous fp32 [B, Hq, num_kv_splits, D+1] tensor")
+        mid_o = torch.empty((rows, hq, num_kv_splits, d + 1), dtype=torch.float32, device=dev)
+    elif mid_o.numel() != rows * hq * num_kv_splits * (d + 1) or mid_o.dtype != torch.float32 or \
+            not mid_o.is_contiguous():
+        raise ValueError("mid_o must be a contiguous fp32 [(L,) B, Hq, num_kv_splits, D+1] tensor")
     odt = out_dtype or query.dtype
     if output is None:
-        output = torch.empty((B, hq, d), dtype=odt, device=dev)
-    elif output.shape != (B, hq, d) or not output.is_contiguous() or output.dtype not in _DT:
-        raise ValueError("output must be a contiguous [B, Hq, D] tensor of a supported dtype")
+        output = torch.empty(lead + (B, hq, d), dtype=odt, device=dev)
+    elif output.shape != lead + (B, hq, d) or not output.is_contiguous() or output.dtype not in _DT:
+        raise ValueError("output must be a contiguous [(L,) B, Hq, D] tensor of a supported dtype")
+    if lse is not None and (lse.dtype != torch.float32 or not lse.is_contiguous() or
+                            lse.numel() != rows * hq or lse.device != dev):
+        raise ValueError("lse must be a contiguous fp32 [(L,) B, Hq] tensor on the query's device")
     if (prefix_output is None) != (prefix_lse is None):
         raise ValueError("prefix_output and prefix_lse go together")
     if prefix_output is not None:
         _require_cuda(prefix_output, "prefix_output")
-        if prefix_output.shape != (B, hq, d) or prefix_lse.shape != (B, hq):
-            raise ValueError("prefix_output must be [B, Hq, D] and prefix_lse [B, Hq]")
+        if prefix_output.shape != lead + (B, hq, d) or prefix_lse.shape != lead + (B, hq):
+            raise ValueError("prefix_output must be [(L,) B, Hq, D] and prefix_lse [(L,) B, Hq]")
         if prefix_output.dtype not in _DT:
             prefix_output = prefix_output.float()
         prefix_output = prefix_output.contiguous()
         prefix_lse = prefix_lse.to(device=dev, dtype=torch.float32).contiguous()
     kb = _key_bits(tq_config)
     with torch.cuda.device(dev):
-        rc = _lib.load().ftq_tq_decode(
+        rc = _lib.load().ftq_tq_decode_layers(
             _ptr(query), _DT[query.dtype], B, hq, hkv, d, _ptr(kv_cache), sb, sp, sh,
             kv_cache.shape[1], _ptr(bt), bt.shape[1], _ptr(sl), _ptr(ks),
             kb, tq_config.value_quant_bits, int(tq_config.norm_correction),
             int(v_rotate), int(bool(v_lloyd_max)), _table_ptr(centroids, kb == 8), float(scale),
             num_kv_splits,
             _ptr(mid_o), _ptr(output), _DT[output.dtype], _ptr(lse), _ptr(prefix_output),
-            _DT[prefix_output.dtype] if prefix_output is not None else 0, _ptr(prefix_lse), _stream(dev))
-    _lib.check(rc, "ftq_tq_decode")
+            _DT[prefix_output.dtype] if prefix_output is not None else 0, _ptr(prefix_lse),
+            n_layers, layer_stride, kv_cache.shape[0], _stream(dev))
+    _lib.check(rc, "ftq_tq_decode_layers")
     return output
 
 

@@ -325,6 +325,29 @@ int ftq_tq_decode(const void *q, int q_dtype, int B, int Hq, int Hkv, int head_d
                   const void *prefix_out, int prefix_dtype, const float *prefix_lse,
                   void *stream);
 
+/*
+ * ftq_tq_decode over the caches of n_layers layers in ONE call (two launches in total): q, mid_o,
+ * out, lse and the prefix tensors are stacked along a leading layer axis ([n_layers * B, ...] rows,
+ * layer-major), layer i's cache starts cache_layer_stride bytes (even) after layer i - 1's, and
+ * every layer uses the same block_table / seq_lens / kv_start_offset rows (vLLM gives all layers
+ * of a request the same block ids).  The reference launches once per layer
+ * (vllm_plugin/v1_backend.py:1030-1085); small layers (a 0.5 B model moves 14 MB per layer) are
+ * launch-bound that way, which is what this entry point removes.  n_layers * B <= 65535.
+ * num_blocks > 0 additionally checks every block id the kernels read against [0, num_blocks): an
+ * id outside is never dereferenced, and the (sequence, head) rows it belongs to come back as NaN.
+ * With n_layers = 1, cache_layer_stride = 0, num_blocks = 0 this is ftq_tq_decode.
+ */
+int ftq_tq_decode_layers(const void *q, int q_dtype, int B, int Hq, int Hkv, int head_dim,
+                         const uint8_t *kv_cache, int64_t stride_block, int64_t stride_pos,
+                         int64_t stride_head, int block_size, const int32_t *block_table,
+                         int max_blocks, const int32_t *seq_lens, const int32_t *kv_start_offset,
+                         int key_bits, int value_bits, int norm_correction, int rotate_output,
+                         int value_lloyd_max, const float *centroids_host, float scale,
+                         int num_kv_splits, float *mid_o, void *out, int out_dtype, float *lse,
+                         const void *prefix_out, int prefix_dtype, const float *prefix_lse,
+                         int n_layers, int64_t cache_layer_stride, int64_t num_blocks,
+                         void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -351,3 +351,48 @@ def test_errors(golden):
         tq_v1.launch_store(k, k, cache, torch.zeros(4, dtype=torch.int64), torch.linspace(-1, 1, 15), cfg)
     with pytest.raises(RuntimeError):
         tq_v1.launch_store(k.cpu(), k.cpu(), cache, torch.zeros(4, dtype=torch.int64), torch.linspace(-1, 1, 15), cfg)
+
+
+@pytest.mark.parametrize("D,kb,vb,G,qdtype", [(128, 4, 4, 4, torch.bfloat16), (64, 3, 3, 7, torch.bfloat16),
+                                               (128, 4, 4, 4, torch.float32), (256, 4, 2, 2, torch.bfloat16)])
+def test_all_layers_in_one_call_equals_per_layer_calls(D, kb, vb, G, qdtype):
+    """ftq_tq_decode_layers: the caches of L layers (one allocation, one block table) decoded in one
+    call give, bit for bit, what L separate calls give; a block id outside the cache makes exactly
+    the rows of its sequence NaN (the cache is a narrower view of its allocation, so nothing out
+    of bounds is touched either way)."""
+    from fused_turboquant_b200 import tq_v1
+    L, B, Hkv, bs, splits = 3, 4, 2, 16, 4
+    seq_lens = torch.tensor([200, 37, 512, 90], dtype=torch.int32, device="cuda")
+    blocks_per_seq = 32
+    nb = B * blocks_per_seq
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, norm_correction=True)
+    g = torch.Generator(device="cuda").manual_seed(D + kb)
+    big = torch.zeros((L, nb + 8, bs, Hkv, cfg.slot_size_aligned), dtype=torch.uint8, device="cuda")
+    caches = big[:, :nb]                               # the kernels see nb blocks per layer
+    bt = torch.randperm(nb, generator=g, device="cuda").view(B, blocks_per_seq).to(torch.int32)
+    cent = torch.sort(torch.randn(1 << kb, generator=g, device="cuda") / D ** 0.5).values
+    cent, mids = tq_v1.midpoints_of(cent)
+    pos = torch.arange(512, device="cuda")
+    slots = (bt.long()[:, pos // bs] * bs + pos % bs)
+    slots = torch.where(pos[None, :] < seq_lens[:, None], slots, torch.full_like(slots, -1)).reshape(-1)
+    for layer in range(L):
+        k = torch.randn((B * 512, Hkv, D), generator=g, device="cuda").bfloat16()
+        v = torch.randn((B * 512, Hkv, D), generator=g, device="cuda").bfloat16()
+        tq_v1.launch_store(k, v, caches[layer], slots, mids, cfg)
+    q = torch.randn((L, B, Hkv * G, D), generator=g, device="cuda").to(qdtype)
+    lse = torch.empty((L, B, Hkv * G), dtype=torch.float32, device="cuda")
+    one = tq_v1.decode_attention(q, caches, bt, seq_lens, cent, cfg, D ** -0.5, num_kv_splits=splits,
+                                 lse=lse, out_dtype=torch.float32)
+    assert one.shape == (L, B, Hkv * G, D) and torch.isfinite(one).all()
+    for layer in range(L):
+        lse1 = torch.empty((B, Hkv * G), dtype=torch.float32, device="cuda")
+        per = tq_v1.decode_attention(q[layer], caches[layer], bt, seq_lens, cent, cfg, D ** -0.5,
+                                     num_kv_splits=splits, lse=lse1, out_dtype=torch.float32)
+        assert torch.equal(per, one[layer]) and torch.equal(lse1, lse[layer])
+    bad = bt.clone()
+    bad[2, 5] = nb + 3                                  # inside the allocation, outside the view
+    got = tq_v1.decode_attention(q, caches, bad, seq_lens, cent, cfg, D ** -0.5, num_kv_splits=splits,
+                                 out_dtype=torch.float32)
+    assert torch.isnan(got[:, 2]).all()
+    keep = [0, 1, 3]
+    assert torch.equal(got[:, keep], one[:, keep])
