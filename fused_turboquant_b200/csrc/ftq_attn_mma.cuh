@@ -341,9 +341,25 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     const int group = p.Hq / p.Hkv;  // <= 4 * NH
     // byte selectors (source 4 = a zero byte): a lane's own fp16 of a packed pair, and the
     // placement of a weight in the low (even g) or high (odd g) half of a B register
-    const uint32_t sel_own = odd ? 0x4432u : 0x4410u;
-    const uint32_t sel_plo = odd ? 0x1044u : 0x4410u;
-    const uint32_t sel_phi = odd ? 0x3244u : 0x4432u;
+    uint32_t sel_own = odd ? 0x4432u : 0x4410u;
+    uint32_t sel_plo = odd ? 0x1044u : 0x4410u;
+    uint32_t sel_phi = odd ? 0x3244u : 0x4432u;
+    // Lane constants of the page reads: byte offset of the key row rho(g) and of the norm quad;
+    // per value register j the row of page token 4tg + ((j + tg) & 3) (plus the slice where
+    // slices are whole words) and the slice index otherwise (slice g, halves exchanged for tokens
+    // with bit 1 set).  (The streaming kernel pins these in registers; here that measured no gain.)
+    uint32_t koff = (4 * (g >> 1) + (g & 1)) * MmaCfg<D, BK, BV, NH>::PDK;
+    uint32_t noff = MmaCfg<D, BK, BV, NH>::OFF_KN + 8 * (g >> 1);
+    uint32_t vrow[4];
+    int vidx[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        using CC = MmaCfg<D, BK, BV, NH>;
+        const int u = (j + tg) & 3;
+        const int slice = g ^ ((u & 2) << 1);
+        vrow[j] = CC::OFF_VC + (4 * tg + u) * CC::PDV + (CC::VSB % 4 == 0 ? slice * CC::VSB : 0);
+        vidx[j] = CC::VSB % 4 == 0 ? 0 : slice;
+    }
 
     // ---- once per CTA: dequantisation tables
     if constexpr (C::BYTE) {
@@ -598,22 +614,21 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         // every lane copies its slices of the staged page into registers
         auto read_page = [&](Regs& r, int rb) {
             const uint32_t page = my_ring + rb * C::PAGE_BYTES;
-            const int ktok = 4 * (g >> 1) + (g & 1);  // rho(g)
-            lds_slice<C::KSB>(page + ktok * C::PDK, tg, r.k[0]);
-            lds_slice<C::KSB>(page + (ktok + 2) * C::PDK, tg, r.k[1]);
+            lds_slice<C::KSB>(page + koff, tg, r.k[0]);
+            lds_slice<C::KSB>(page + koff + 2 * C::PDK, tg, r.k[1]);
             // register j holds page token 4tg + ((j + tg) & 3): the four lanes of a quad then read
             // rows of alternating parity in one instruction (2-way instead of 4-way bank conflict);
             // the P.V k-slots of a lane may hold its tokens in any order as long as the weights
-            // follow (see the rotation of the transposed weights below)
-            // the pool stores a V row with its two halves exchanged for tokens with bit 1 set, so
-            // that the four rows a quad reads in one instruction fall into distinct bank groups
+            // follow (see the rotation of the transposed weights below).  The pool stores a V row
+            // with its two halves exchanged for tokens with bit 1 set, so that the four rows a quad
+            // reads in one instruction fall into distinct bank groups.
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const int u = (j + tg) & 3;
-                lds_slice<C::VSB>(page + C::OFF_VC + (4 * tg + u) * C::PDV, g ^ ((u & 2) << 1), r.v[j]);
+                if constexpr (C::VSB % 4 == 0) lds_slice<C::VSB>(page + vrow[j], 0, r.v[j]);
+                else lds_slice<C::VSB>(page + vrow[j], vidx[j], r.v[j]);
             }
-            r.kn = lds64(page + C::OFF_KN + 8 * (g >> 1));
-            r.vn = lds64(page + C::OFF_VN + 8 * (g >> 1));
+            r.kn = lds64(page + noff);
+            r.vn = lds64(page + noff + (C::OFF_VN - C::OFF_KN));
         };
 
         // S = K.Q^T of one page (two accumulator chains per head half)
