@@ -326,11 +326,11 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             t[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
     }
-    uint32_t lk_lane = (BK == 4 ? window : tk_small) | (lane * 4);
-    uint32_t lv_lane =
+    // (pinning these two as well made the compiler spill in the page loop)
+    const uint32_t lk_lane = (BK == 4 ? window : tk_small) | (lane * 4);
+    const uint32_t lv_lane =
         C::V2BYTE ? (window | 128u | ((lane & 15) * 8))
                   : ((BV == 4 ? (window | (SHARED_LUT ? 0u : 128u)) : tv_small) | (lane * 4));
-    asm volatile("" : "+r"(lk_lane), "+r"(lv_lane));
     __syncthreads();
     if (ctl[kCtlLayout]) return;  // cannot happen for a configuration the launcher accepts
     const uint32_t my_ring = static_cast<uint32_t>(ctl[kCtlRingAddr + warp]);
