@@ -1,6 +1,9 @@
-// Paged split-KV decode attention, fast path: packed codes go straight from
-// HBM to registers, are dequantised through a bank-conflict-free shared-memory
-// table, and feed warp-level m16n8k16 fp16 MMAs (fp32 accumulate).  With a GQA
+// Paged split-KV decode attention on the tensor cores (barrier-synchronised form;
+// ftq_attn_stream.cuh holds the streaming form of the same arithmetic): whole
+// 16-token pages arrive in a per-warp ring by 1-D bulk copies (TMA), every lane
+// copies its slices to registers, the codes are dequantised through a
+// bank-conflict-free shared-memory table and feed warp-level m16n8k16 fp16 MMAs
+// (fp32 accumulate).  With a GQA
 // group of G query heads the products are skinny GEMMs (G x D x tokens), so the
 // per-element work no longer grows with G and every packed byte is dequantised
 // exactly once per KV head.
