@@ -107,3 +107,59 @@ def test_gather_sequence_matches_the_host_restatement_of_the_layout():
         np.testing.assert_array_equal(vc.cpu().numpy(), rv[0])
         np.testing.assert_array_equal(kn.cpu().numpy().view(np.uint16), rkn[0].view(np.uint16))
         np.testing.assert_array_equal(vn.cpu().numpy().view(np.uint16), rvn[0].view(np.uint16))
+
+
+@pytest.mark.parametrize("d,G,bk,bv", [(128, 4, 4, 4), (128, 2, 4, 3), (64, 4, 4, 4)])
+def test_many_short_items_per_cta(oracle, tables, d, G, bk, bv):
+    """Hundreds of one- and two-page sequences (plus empty ones and a few long ones): every CTA of
+    the streaming kernel runs many items in which most warps have no page at all, which is the
+    path where a warp runs ahead of its published state and has to hand page requests back.
+    All outputs against the oracle; two runs bit-identical."""
+    from fused_turboquant_b200 import PagedKVPool
+    rng = np.random.default_rng(d + bk + bv)
+    B, Hkv = 700, 2
+    seq_lens = rng.integers(1, 40, B).astype(np.int32)
+    seq_lens[rng.integers(0, B, 25)] = 0
+    seq_lens[[3, 77, 410]] = [1000, 555, 2049]
+    max_seq = int(seq_lens.max())
+    max_blocks = (max_seq + 15) // 16
+    nblk = int(((seq_lens + 15) // 16).sum())
+    perm = rng.permutation(nblk).astype(np.int32)
+    bt = np.zeros((B, max_blocks), np.int32)
+    pos = 0
+    for b in range(B):
+        nb = (int(seq_lens[b]) + 15) // 16
+        bt[b, :nb] = perm[pos:pos + nb]
+        pos += nb
+    n_tok = int(seq_lens.sum())
+    g = torch.Generator("cpu").manual_seed(1)
+    key = torch.randn(n_tok, Hkv, d, generator=g).bfloat16()
+    val = torch.randn(n_tok, Hkv, d, generator=g).bfloat16()
+    q = torch.randn(B, Hkv * G, d, generator=g).bfloat16()
+    slots = np.concatenate([bt[b, np.arange(seq_lens[b]) // 16].astype(np.int64) * 16 +
+                            np.arange(seq_lens[b]) % 16 for b in range(B)])
+    pool = PagedKVPool(nblk, Hkv, d, bk, bv, n_layers=1, device="cuda")
+    pool.store(key.cuda(), val.cuda(), torch.from_numpy(slots).cuda(), layer=0)
+    bt_d, sl_d = torch.from_numpy(bt).cuda(), torch.from_numpy(seq_lens).cuda()
+    outs = [pool.decode_attention(q.cuda(), bt_d, sl_d, max_seq, layer=0,
+                                  out=torch.empty(q.shape, dtype=torch.float32, device="cuda"))
+            for _ in range(2)]
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+    got = outs[0].cpu().numpy()
+    assert np.isfinite(got).all()
+    assert (got[seq_lens == 0] == 0).all()                      # softmax over nothing
+    ek, enk = oracle.encode(key.float().numpy(), pool.signs, pool.bounds_k, bk)
+    ev, env = oracle.encode(val.float().numpy(), pool.signs, pool.bounds_v, bv)
+    starts = np.concatenate([[0], np.cumsum(seq_lens)])
+    bad = 0
+    for b in list(range(0, B, 9)) + [3, 77, 410]:
+        S = int(seq_lens[b])
+        if S == 0:
+            continue
+        sl = slice(starts[b], starts[b] + S)
+        tr = lambda a: np.ascontiguousarray(np.swapaxes(a[sl], 0, 1))[None]
+        ref = oracle.decode_attn(q[b:b + 1].float().numpy(), tr(ek), tr(enk), tr(ev), tr(env),
+                                 pool.levels_k, pool.levels_v, pool.signs, d ** -0.5, bk, bv)
+        bad += int((np.abs(got[b:b + 1] - ref) > 1e-3 + 2e-3 * np.abs(ref)).sum())
+    assert bad == 0
