@@ -500,39 +500,49 @@ attn_stream_kernel(const AttnParams p, int n_items) {
 
     // ---- per-warp stream state (all warp-uniform)
     uint32_t phase = 0;                 // bit r = parity the next wait on ring buffer r expects
-    int gseq = 0, gk = 0;               // next page to request: k-th page of this warp in item gseq
+    int gseq = 0;                       // item the next page request belongs to
     int cseq = 0;                       // item number the arithmetic state belongs to
-    int g_pages = ctl[kCtlPages + 0];
     bool g_end = ctl[kCtlItem + 0] >= n_items;
     bool deferred = false;              // a request was handed back: later ones must not overtake it
 
-    // k-th page of `warp` in an item: round-robin, except that the two service warps (warp 0
-    // folds the published states and finishes units, warp 1 prepares the item after next, see
-    // below) sit out the first S::SKIP rounds.  The map depends on nothing but the page
-    // count, so the order of every floating-point sum is fixed.
+    // Pages of an item are dealt round-robin, except that the two service warps (warp 0 folds
+    // the published states and finishes units, warp 1 prepares the item after next, see below)
+    // sit out the first SKIP rounds.  Warp w's pages: w - NSVC, then steps of W - NSVC while the
+    // page lies in the first SKIP - 1 rounds, steps of W after that; a service warp starts at
+    // (W - NSVC) * SKIP + w.  The map depends on nothing but the page count, so the order of
+    // every floating-point sum is fixed.
     constexpr int NSVC = S::NSVC;
-    auto page_of = [&](int k) {
-        if (S::SKIP == 0) return warp + WARPS * k;
-        if (warp < NSVC) return (WARPS - NSVC) * S::SKIP + warp + WARPS * k;
-        if (k < S::SKIP) return (WARPS - NSVC) * k + warp - NSVC;
-        return (WARPS - NSVC) * S::SKIP + warp + WARPS * (k - S::SKIP);
-    };
+    constexpr int WC = S::SKIP > 0 ? WARPS - NSVC : WARPS;
+    constexpr int THR = S::SKIP > 0 ? WC * (S::SKIP - 1) : 0;
+    const int g_first = S::SKIP > 0 ? (warp < NSVC ? WC * S::SKIP + warp : warp - NSVC) : warp;
+    int g_next = g_first;                                   // next page of item gseq for this warp
+    int g_lim = g_end ? 0 : ctl[kCtlPages + 0];             // its page count (0: nothing to take)
     // request the next page of the stream into ring buffer rb; returns its index within item
     // gseq, -1 at the end of the stream, -2 when the request is handed back
     auto grab = [&](int rb) {
-        int pg = deferred ? -2 : -1;
-        while (!g_end && !deferred) {
-            const int cand = page_of(gk);
-            if (cand < g_pages) { pg = cand; gk++; break; }
-            // Item gseq + 1 is prepared once every warp has published its state of item
-            // gseq - 1: only wait for it once this warp has done so (cseq >= gseq); otherwise
-            // hand the decision back to the consumer.
-            if (gseq > cseq) { pg = -2; deferred = true; break; }
-            gseq++;
-            gk = 0;
-            if (!stalled && !wait_ge(kCtlReady, gseq)) stalled = true;
-            g_pages = ctl[kCtlPages + (gseq & 1)];
-            g_end = ctl[kCtlItem + (gseq & 1)] >= n_items;
+        int pg = g_next;
+        if (pg < g_lim) {
+            g_next += pg < THR ? WC : WARPS;
+        } else {
+            // this warp's pages of item gseq are used up (or nothing may be taken)
+            pg = deferred ? -2 : -1;
+            while (!g_end && !deferred) {
+                if (g_next < g_lim) {
+                    pg = g_next;
+                    g_next += pg < THR ? WC : WARPS;
+                    break;
+                }
+                // Item gseq + 1 is prepared once every warp has published its state of item
+                // gseq - 1: only wait for it once this warp has done so (cseq >= gseq);
+                // otherwise hand the decision back to the consumer.
+                if (gseq > cseq) { pg = -2; deferred = true; break; }
+                gseq++;
+                g_next = g_first;
+                if (!stalled && !wait_ge(kCtlReady, gseq)) stalled = true;
+                g_end = ctl[kCtlItem + (gseq & 1)] >= n_items;
+                g_lim = g_end ? 0 : ctl[kCtlPages + (gseq & 1)];
+            }
+            if (pg < 0) g_lim = 0;   // end / handed back: the fast check above must keep failing
         }
         if (pg >= 0 && lane == 0) {
             const int buf = gseq & 1;
@@ -865,13 +875,13 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         else softmax_update(std::false_type{}, r, pg2, c2, pb2);
     };
 
-    // ---- prime the ring, then consume the stream.  Ring buffer 0 / 1 hold the pages at even /
-    // odd stream positions; (pg, sq) = page index within its item (-1: the stream has ended,
-    // -2: request handed back) and item number of the page a buffer holds.
-    int pg0 = grab(0), sq0 = gseq;
-    int pg1 = grab(1), sq1 = gseq;
+    // ---- prime the ring, then consume the stream.  The ring is a FIFO of two pages: (pgA, tagA)
+    // describe the page consumed next, (pgB, tagB) the one after it; tag = the page's item number,
+    // or the negative result of grab (-1: the stream has ended, -2: request handed back).
+    int pgA = grab(0), tagA = pgA < 0 ? pgA : gseq;
+    int pgB = grab(1), tagB = pgB < 0 ? pgB : gseq;
     reset_state();
-    bool ctx_ok = false;   // the query fragments / token count of item cseq are loaded
+    int want = -3;         // item number whose query fragments / token count are loaded (-3: none)
 
     // Software pipeline (one head half): K.Q^T of a page and P.V of the page before it are
     // independent and sit in one straight-line block.  One register set serves both: the
@@ -884,10 +894,8 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     bool pending = false;  // P.V of the previous page (values and weights in registers) is due
     int par = 0;           // ring buffer of the next page in the stream
     for (;;) {
-        const int sp = par ? pg1 : pg0;
-        const int ss = par ? sq1 : sq0;
         bool first = false;
-        if (sp < 0 || ss != cseq || !ctx_ok) {
+        if (tagA != want) {
             // rare path: item boundary, empty ring or end of stream (one copy of all of it)
             if constexpr (kPipelined) {
                 if (pending) {
@@ -897,27 +905,28 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             }
             // publish the finished items: up to the page's item; everything consumed when the
             // ring ran dry two items ahead of the published state (-2) or the stream ended (-1)
-            const int target = sp == -2 ? gseq + 1 : (sp == -1 ? gseq : ss);
+            const int target = tagA == -2 ? gseq + 1 : (tagA == -1 ? gseq : tagA);
             while (cseq < target) {
                 finish_item(cseq);
                 cseq++;
                 reset_state();
             }
-            if (sp == -1) break;
-            if (sp == -2) {
+            if (tagA == -1) break;
+            if (tagA == -2) {
                 // refill the (empty) ring in stream order, starting with this buffer
-                ctx_ok = false;
+                want = -3;
                 deferred = false;
-                const int a = grab(par), asq = gseq;
-                const int b = grab(par ^ 1), bsq = gseq;
-                if (par) { pg1 = a; sq1 = asq; pg0 = b; sq0 = bsq; }
-                else { pg0 = a; sq0 = asq; pg1 = b; sq1 = bsq; }
+                pgA = grab(par);
+                tagA = pgA < 0 ? pgA : gseq;
+                pgB = grab(par ^ 1);
+                tagB = pgB < 0 ? pgB : gseq;
                 continue;
             }
             load_ctx(cseq);
-            ctx_ok = true;
+            want = cseq;
             first = true;
         }
+        const int sp = pgA;
         const uint32_t page = my_ring + par * PAGE_BYTES;
         if (!stalled && !mbar_wait(my_bars + par * 8, (phase >> par) & 1u)) stalled = true;
         phase ^= 1u << par;
@@ -928,8 +937,10 @@ attn_stream_kernel(const AttnParams p, int n_items) {
                 qk_scores(r, c);
                 read_values(r, page);
                 __syncwarp();  // every lane has its slices: the buffer may be refilled
-                const int nx = grab(par);
-                if (par) { pg1 = nx; sq1 = gseq; } else { pg0 = nx; sq0 = gseq; }
+                pgA = pgB;
+                tagA = tagB;
+                pgB = grab(par);
+                tagB = pgB < 0 ? pgB : gseq;
                 softmax_update(std::false_type{}, r, sp, c, pb);
                 pending = true;
             } else {
@@ -937,15 +948,19 @@ attn_stream_kernel(const AttnParams p, int n_items) {
                 pv_accum(r.v, pb);
                 read_values(r, page);
                 __syncwarp();
-                const int nx = grab(par);
-                if (par) { pg1 = nx; sq1 = gseq; } else { pg0 = nx; sq0 = gseq; }
+                pgA = pgB;
+                tagA = tagB;
+                pgB = grab(par);
+                tagB = pgB < 0 ? pgB : gseq;
                 softmax_page(r, sp, c, pb);
             }
         } else {
             read_values(r, page);
             __syncwarp();
-            const int nx = grab(par);
-            if (par) { pg1 = nx; sq1 = gseq; } else { pg0 = nx; sq0 = gseq; }
+            pgA = pgB;
+            tagA = tagB;
+            pgB = grab(par);
+            tagB = pgB < 0 ? pgB : gseq;
             qk_scores(r, c);
             softmax_page(r, sp, c, pb);
             pv_accum(r.v, pb);
