@@ -499,7 +499,6 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     __syncthreads();
 
     // ---- per-warp stream state (all warp-uniform)
-    uint32_t phase = 0;                 // bit r = parity the next wait on ring buffer r expects
     int gseq = 0;                       // item the next page request belongs to
     int cseq = 0;                       // item number the arithmetic state belongs to
     bool g_end = ctl[kCtlItem + 0] >= n_items;
@@ -662,8 +661,10 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         }
         const float kna = half_bits_to_float(__byte_perm(r.kn.x, 0u, sel_own));
         const float knb = half_bits_to_float(__byte_perm(r.kn.y, 0u, sel_own));
-        float vna = half_bits_to_float(__byte_perm(r.vn.x, 0u, sel_own)) * p.inv_v_scale;
-        float vnb = half_bits_to_float(__byte_perm(r.vn.y, 0u, sel_own)) * p.inv_v_scale;
+        // (the factor that undoes the scaling of the value centroids is applied once per item,
+        // when the state is published)
+        float vna = half_bits_to_float(__byte_perm(r.vn.x, 0u, sel_own));
+        float vnb = half_bits_to_float(__byte_perm(r.vn.y, 0u, sel_own));
         if constexpr (!FULL) {
             vna = okA ? vna : 0.f;
             vnb = okB ? vnb : 0.f;
@@ -855,7 +856,8 @@ attn_stream_kernel(const AttnParams p, int n_items) {
 #pragma unroll
                 for (int mt = 0; mt < NMT; mt++)
                     my_xchg[(hh * NMT + mt) * 32 + lane] = make_float4(
-                        oacc[hh][mt][0], oacc[hh][mt][1], oacc[hh][mt][2], oacc[hh][mt][3]);
+                        oacc[hh][mt][0] * p.inv_v_scale, oacc[hh][mt][1] * p.inv_v_scale,
+                        oacc[hh][mt][2] * p.inv_v_scale, oacc[hh][mt][3] * p.inv_v_scale);
             }
             if (g == 0) {
                 xml[(hh * 2 + 0) * 4 + tg] = stalled ? __int_as_float(0x7fc00000) : m_run[hh];
@@ -892,8 +894,9 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     uint32_t pb[NH][2][2];
     float c[NH][2][4];
     bool pending = false;  // P.V of the previous page (values and weights in registers) is due
-    int par = 0;           // ring buffer of the next page in the stream
+    int n = 0;             // pages fetched so far: ring buffer n & 1, mbarrier parity (n >> 1) & 1
     for (;;) {
+        const int par = n & 1;
         bool first = false;
         if (tagA != want) {
             // rare path: item boundary, empty ring or end of stream (one copy of all of it)
@@ -928,8 +931,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         }
         const int sp = pgA;
         const uint32_t page = my_ring + par * PAGE_BYTES;
-        if (!stalled && !mbar_wait(my_bars + par * 8, (phase >> par) & 1u)) stalled = true;
-        phase ^= 1u << par;
+        if (!stalled && !mbar_wait(my_bars + par * 8, (n >> 1) & 1)) stalled = true;
         read_keys(r, page);
         if constexpr (kPipelined) {
             if (first) {
@@ -965,7 +967,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             softmax_page(r, sp, c, pb);
             pv_accum(r.v, pb);
         }
-        par ^= 1;
+        n++;
     }
 }
 
