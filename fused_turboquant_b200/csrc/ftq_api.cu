@@ -211,6 +211,56 @@ float search_v_scale(const float* levels, int bits, int head_dim) {
     return best;
 }
 
+// Factor s in [1, 2) for the K centroids of the tensor-core path: the key scores are sums of
+// q * centroid products, so what matters there is the SIZE of the centroids' fp16 rounding errors,
+// not their common bias: s minimises the probability-weighted mean square of
+// fp16(s * level) / s - level (cell probabilities of N(0, 1/D), cell edges = level midpoints).
+// 1 / s goes into the softmax scale, so the kernel needs nothing for it.
+float choose_k_scale(const float* levels, int bits, int head_dim) {
+    struct Entry { float levels[16]; int bits, head_dim; float scale; };
+    static std::mutex mu;
+    static Entry cache[16];
+    static int n_cached = 0, next_slot = 0;
+    const size_t nbytes = sizeof(float) << bits;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < n_cached; i++)
+            if (cache[i].bits == bits && cache[i].head_dim == head_dim &&
+                memcmp(cache[i].levels, levels, nbytes) == 0)
+                return cache[i].scale;
+    }
+    const int n = 1 << bits;
+    double prob[16];
+    const double inv_sigma = std::sqrt(static_cast<double>(head_dim));
+    double prev = 0.0;
+    for (int c = 0; c < n; c++) {
+        const double cdf = c == n - 1 ? 1.0
+            : 0.5 * std::erfc(-0.5 * (static_cast<double>(levels[c]) + levels[c + 1]) * inv_sigma /
+                              std::sqrt(2.0));
+        prob[c] = cdf - prev;
+        prev = cdf;
+    }
+    float best = 1.0f;
+    double best_cost = 1e30;
+    for (int i = 0; i < 8192; i++) {
+        const float sc = 1.0f + static_cast<float>(i) / 8192.0f;
+        double mse = 0.0;
+        for (int c = 0; c < n; c++) {
+            const double err = static_cast<double>(round_to_half(levels[c] * sc)) / sc - levels[c];
+            mse += prob[c] * err * err;
+        }
+        if (mse < best_cost) { best_cost = mse; best = sc; }
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    Entry& e = cache[next_slot];
+    memset(&e, 0, sizeof(e));
+    memcpy(e.levels, levels, nbytes);
+    e.bits = bits; e.head_dim = head_dim; e.scale = best;
+    next_slot = (next_slot + 1) % 16;
+    if (n_cached < 16) n_cached++;
+    return best;
+}
+
 struct ChunkPlan {
     int chunk_tokens, n_chunks, n_hpass;
 };
@@ -729,6 +779,10 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
         const float vs = choose_v_scale(levels_v_host, bits_v, head_dim);
         for (int i = 0; i < (1 << bits_v); i++) p.lv_scaled.v[i] = levels_v_host[i] * vs;
         p.inv_v_scale = 1.0f / vs;
+        // K centroids scaled for the smallest fp16 rounding error, undone through the softmax scale
+        const float ks = choose_k_scale(levels_k_host, bits_k, head_dim);
+        for (int i = 0; i < (1 << bits_k); i++) p.lk.v[i] = levels_k_host[i] * ks;
+        p.scale = scale / ks;
         // K and V can share one table only when the scaled V levels equal the K levels
         const bool shared_lut = bits_k == bits_v &&
             memcmp(p.lk.v, p.lv_scaled.v, sizeof(float) << bits_k) == 0;

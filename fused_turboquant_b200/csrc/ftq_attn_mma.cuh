@@ -90,6 +90,26 @@ __device__ __forceinline__ uint2 lut64(uint32_t addr) {
     return v;
 }
 
+#ifndef FTQ_LAZY_SLACK
+#define FTQ_LAZY_SLACK 3
+#endif
+// slack of the lazy reference maximum of the online softmax (base-2 exponent units)
+constexpr float kLazyMaxSlack = static_cast<float>(FTQ_LAZY_SLACK);
+// m16n8k16 with a zero accumulator input (saves clearing the accumulators of every page)
+__device__ __forceinline__ void mma_16816_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};\n"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+__device__ __forceinline__ uint32_t f2h_sat(float x) {
+    unsigned short h;
+    asm("cvt.rn.satfinite.f16.f32 %0, %1;\n" : "=h"(h) : "f"(x));
+    return h;
+}
+
 // ---- mbarrier + bulk-copy (TMA, 1-D, no multicast) helpers; all addresses are shared-window
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
@@ -637,12 +657,6 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         // S = K.Q^T of one page (two accumulator chains per head half)
         auto qk_scores = [&](const Regs& r, float (&c)[NH][2][4]) {
 #pragma unroll
-            for (int hh = 0; hh < NH; hh++)
-#pragma unroll
-                for (int z = 0; z < 2; z++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) c[hh][z][i] = 0.f;
-#pragma unroll
             for (int kb = 0; kb < NKB; kb++) {
                 const uint32_t a0 = lut32(entry_addr<C::IWK>(r.k[0], 2 * kb, lk_lane));
                 const uint32_t a1 = lut32(entry_addr<C::IWK>(r.k[1], 2 * kb, lk_lane));
@@ -650,12 +664,16 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 const uint32_t a3 = lut32(entry_addr<C::IWK>(r.k[1], 2 * kb + 1, lk_lane));
 #pragma unroll
                 for (int hh = 0; hh < NH; hh++) {
+                    uint32_t b0, b1;
                     if constexpr (C::QSMEM) {
                         const uint2 qv = lds64(qfrag + ((hh * NKB + kb) * 32 + lane) * 8);
-                        mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qv.x, qv.y);
+                        b0 = qv.x; b1 = qv.y;
                     } else {
-                        mma_16816(c[hh][kb & 1], a0, a1, a2, a3, qb[hh][kb][0], qb[hh][kb][1]);
+                        b0 = qb[hh][kb][0]; b1 = qb[hh][kb][1];
                     }
+                    // (the first MMA of each of the two accumulator chains starts from zero)
+                    if (kb < 2) mma_16816_z(c[hh][kb & 1], a0, a1, a2, a3, b0, b1);
+                    else mma_16816(c[hh][kb & 1], a0, a1, a2, a3, b0, b1);
                 }
             }
         };
@@ -689,14 +707,16 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                     sa = okA ? sa : -INFINITY;
                     sb = okB ? sb : -INFINITY;
                 }
-                float mx = fmaxf(sa, sb);
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                // mx is finite (page token 0 is valid).  The rescale is skipped by the whole warp
-                // when no head of this half saw a new maximum.
-                if (__any_sync(0xffffffffu, mx > m_run[hh])) {
-                    const float m_new = fmaxf(m_run[hh], mx);
+                // Lazy reference maximum: the cross-lane maximum and the rescale run only when a
+                // score exceeds the reference by more than kLazyMaxSlack (always on the first
+                // page of an item, where it is -inf); weights stay below 2^kLazyMaxSlack.
+                const float mloc = fmaxf(sa, sb);
+                if (__any_sync(0xffffffffu, mloc > m_run[hh] + kLazyMaxSlack)) {
+                    float mx = mloc;
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    const float m_new = fmaxf(m_run[hh], mx);  // finite: page token 0 is valid
                     const float corr = fast_exp2(m_run[hh] - m_new);  // 1 if unchanged, 0 from -inf
                     l_run[hh] *= corr;
 #pragma unroll
@@ -708,8 +728,8 @@ attn_mma_kernel(const AttnParams p, int n_items) {
                 const float pa = fast_exp2(sa - m_run[hh]);  // exp2(-inf) = 0 for masked tokens
                 const float pbv = fast_exp2(sb - m_run[hh]);
                 l_run[hh] += pa + pbv;
-                const uint32_t ha = __half_as_ushort(__float2half_rn(pa * vna));
-                const uint32_t hb = __half_as_ushort(__float2half_rn(pbv * vnb));
+                const uint32_t ha = f2h_sat(pa * vna);
+                const uint32_t hb = f2h_sat(pbv * vnb);
                 // M[token row][column n], both columns of a head equal; transposed, lane (g, tg)
                 // receives head g>>1, page tokens 4tg, 4tg+1 (first) and 4tg+2, 4tg+3 (second)
                 uint32_t t0w = movmatrix_trans(__byte_perm(ha, 0u, 0x1010u));

@@ -43,27 +43,8 @@
 
 namespace ftq {
 
-#ifndef FTQ_LAZY_SLACK
-#define FTQ_LAZY_SLACK 3
-#endif
-constexpr float kLazyMaxSlack = static_cast<float>(FTQ_LAZY_SLACK);
 constexpr int kStreamMaxChunkPages = 512;   // 8192 tokens
 constexpr int kFlagSpinLimit = 1 << 22;
-
-// m16n8k16 with a zero accumulator input (saves clearing the accumulators of every page)
-__device__ __forceinline__ void mma_16816_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                            uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%10,%10,%10};\n"
-        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-}
-
-__device__ __forceinline__ uint32_t f2h_sat(float x) {
-    unsigned short h;
-    asm("cvt.rn.satfinite.f16.f32 %0, %1;\n" : "=h"(h) : "f"(x));
-    return h;
-}
 
 template <int D, int BK, int BV, int NH>
 struct StreamCfg {
