@@ -5,7 +5,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cfloat>
+#include <atomic>
 #include <cstring>
+#include <random>
 #include <cstdlib>
 #include <mutex>
 
@@ -263,6 +265,11 @@ float choose_k_scale(const float* levels, int bits, int head_dim) {
 
 struct ChunkPlan {
     int chunk_tokens, n_chunks, n_hpass;
+    // streaming kernel only: units from bulk_units on are cut into tail_chunks chunks of
+    // tail_chunk_tokens instead (bulk_units < 0: one split for all units)
+    int64_t bulk_units = -1;
+    int tail_chunks = 0, tail_chunk_tokens = 0;
+    int row_chunks() const { return tail_chunks > n_chunks ? tail_chunks : n_chunks; }
 };
 
 // Split the context so that the grid fills the GPU a few times over.
@@ -320,10 +327,74 @@ ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers, int cta
     return pl;
 }
 
+// The streaming kernel's plan.  Measured on B200 (Llama-shaped K4V4 batches of 37..111
+// sequences, forced chunk counts): an item costs about 74 pages on top of its own pages (the
+// service warps' smaller page share, the publish / fold / prepare hand-overs), so long chunks
+// pay -- but whole waves of them rarely match the unit count.  The plan therefore has two
+// regions: as many units as fill whole waves of the grid are cut into few, long chunks; the
+// remaining units into more, shorter ones that share the last wave.  Items are handed out bulk
+// first, so the short ones also even out the CTAs' different speeds.
+ChunkPlan plan_chunks_stream(int B, int Hkv, int max_seq_len, int n_layers) {
+    ChunkPlan pl;
+    pl.n_hpass = 1;
+    const int64_t units = static_cast<int64_t>(B) * Hkv * n_layers;
+    const int64_t slots = ftq::sm_count();
+    const int seq = max_seq_len > 0 ? max_seq_len : 1;
+    const int c_min = (seq + 8191) / 8192;
+    const int c_max = (seq + 1023) / 1024 > c_min ? (seq + 1023) / 1024 : c_min;
+    const double item_cost = 74.0;
+    auto split = [&](int nc, int* ct, int* real) {
+        int t = ((seq + nc - 1) / nc + 63) / 64 * 64;
+        if (t > 8192) t = 8192;
+        *ct = t;
+        *real = (seq + t - 1) / t;
+    };
+    double best = -1.0;
+    for (int nc1 = c_min; nc1 <= c_max && nc1 < c_min + 16; nc1++) {
+        int ct1, r1;
+        split(nc1, &ct1, &r1);
+        const double cost1 = ct1 / 16.0 + item_cost;
+        // one split for all units
+        const double uniform = static_cast<double>((units * r1 + slots - 1) / slots) * cost1;
+        if (best < 0.0 || uniform < best * (1.0 - 1e-9)) {
+            best = uniform;
+            pl.chunk_tokens = ct1; pl.n_chunks = r1;
+            pl.bulk_units = -1; pl.tail_chunks = 0; pl.tail_chunk_tokens = 0;
+        }
+        // whole waves of this split, the rest of the units cut finer
+        const int64_t full = units * r1 / slots;
+        const int64_t bulk = full * slots / r1;
+        if (full == 0 || bulk >= units) continue;
+        for (int nc2 = nc1 + 1; nc2 <= c_max && nc2 <= nc1 + 16; nc2++) {
+            int ct2, r2;
+            split(nc2, &ct2, &r2);
+            if (r2 <= r1) continue;
+            const int64_t tail_waves = ((units - bulk) * r2 + slots - 1) / slots;
+            const double cost = static_cast<double>(full) * cost1 +
+                                static_cast<double>(tail_waves) * (ct2 / 16.0 + item_cost);
+            if (cost < best * (1.0 - 1e-9)) {
+                best = cost;
+                pl.chunk_tokens = ct1; pl.n_chunks = r1;
+                pl.bulk_units = bulk; pl.tail_chunks = r2; pl.tail_chunk_tokens = ct2;
+            }
+        }
+    }
+    return pl;
+}
+
+bool attn_mma_streams(int d, int bits_k, int bits_v, int group) {
+    switch (d) {
+        case 64: return ftq::attn_mma_streams_d64(bits_k, bits_v, group);
+        case 128: return ftq::attn_mma_streams_d128(bits_k, bits_v, group);
+        case 256: return ftq::attn_mma_streams_d256(bits_k, bits_v, group);
+    }
+    return false;
+}
+
 bool use_mma_path(int Hq, int Hkv, int q_dtype) { return Hq / Hkv <= 8 && q_dtype != FTQ_F32; }
 
 size_t partial_bytes(const ChunkPlan& pl, int B, int Hq, int d, int n_layers) {
-    return static_cast<size_t>(n_layers) * B * Hq * pl.n_chunks * (d + 4) * sizeof(float);
+    return static_cast<size_t>(n_layers) * B * Hq * pl.row_chunks() * (d + 4) * sizeof(float);
 }
 
 cudaError_t dispatch_split(int d, int bk, int bv, bool paged, const ftq::AttnParams& p, int n_lb,
@@ -595,9 +666,21 @@ int ftq_qk_scores(const float* q_rot, const uint8_t* k_codes, const void* k_norm
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_qk_scores launch");
 }
 
-// The tail of a decode workspace holds the counters of the tensor-core kernels: the work-item
-// counter (first word) and, from byte 256 on, one counter per (layer, sequence, KV head) unit
-// for the in-kernel split-KV merge.  The host zeroes the whole tail before every launch.
+// The tail of a decode workspace holds the counters of the tensor-core kernels: a 256-byte header
+// (work-item counter, count of finished CTAs, the 64-bit epoch word) and, from byte 256 on, one
+// counter per (layer, sequence, KV head) unit for the in-kernel split-KV merge.  The
+// barrier-synchronised kernel's launcher zeroes the header with a memset node; the streaming
+// kernel clears the tail itself under a per-launch epoch (see AttnParams), so one call is one
+// node in the stream and needs nothing from the call before it.
+static unsigned long long next_epoch() {
+    static std::atomic<unsigned long long> counter{[] {
+        std::random_device rd;
+        return (static_cast<unsigned long long>(rd()) << 32) | 1ull;
+    }()};
+    unsigned long long e = counter.fetch_add(1, std::memory_order_relaxed);
+    return e ? e : counter.fetch_add(1, std::memory_order_relaxed);
+}
+
 static size_t counter_bytes(int B, int Hkv, int n_layers) {
     const size_t units = static_cast<size_t>(n_layers > 0 ? n_layers : 0) * (B > 0 ? B : 0) *
                          (Hkv > 0 ? Hkv : 0);
@@ -611,7 +694,10 @@ size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_
     const ChunkPlan a = plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     const ChunkPlan m1 = plan_chunks_mma(B, Hkv, max_seq_len, n_layers, 1);
     const ChunkPlan m2 = plan_chunks_mma(B, Hkv, max_seq_len, n_layers, 2);
+    const ChunkPlan m3 = plan_chunks_stream(B, Hkv, max_seq_len, n_layers);
     size_t n = partial_bytes(a, B, Hq, head_dim, n_layers);
+    const size_t n3 = partial_bytes(m3, B, Hq, head_dim, n_layers);
+    if (n3 > n) n = n3;
     const size_t n1 = partial_bytes(m1, B, Hq, head_dim, n_layers);
     const size_t n2 = partial_bytes(m2, B, Hq, head_dim, n_layers);
     if (n1 > n) n = n1;
@@ -751,8 +837,10 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     const bool mma = use_mma_path(Hq, Hkv, q_dtype);
     // one CTA per SM (16 warps) when a 4-bit byte table is in use, else two (8 warps each)
     const int mma_ctas = (bits_k == 4 || bits_v == 4) ? 1 : 2;
-    const ChunkPlan pl = mma ? plan_chunks_mma(B, Hkv, max_seq_len, n_layers, mma_ctas)
-                             : plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
+    const bool streams = mma && attn_mma_streams(head_dim, bits_k, bits_v, Hq / Hkv);
+    const ChunkPlan pl = streams ? plan_chunks_stream(B, Hkv, max_seq_len, n_layers)
+                         : mma   ? plan_chunks_mma(B, Hkv, max_seq_len, n_layers, mma_ctas)
+                                 : plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     const size_t need = ftq_decode_workspace_bytes(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     if (!workspace || workspace_bytes < need)
         return fail(FTQ_ERR_WORKSPACE, "workspace needs %zu bytes, got %zu", need, workspace_bytes);
@@ -795,8 +883,18 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
         p.div_chunks = ftq::make_fastdiv(static_cast<uint32_t>(p.n_chunks));
         p.div_hkv = ftq::make_fastdiv(static_cast<uint32_t>(Hkv));
         p.div_b = ftq::make_fastdiv(static_cast<uint32_t>(B));
-        e = cudaMemsetAsync(p.work_counter, 0, tail, st);
-        if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn counter reset");
+        p.n_units = n_layers * B * Hkv;
+        p.epoch = next_epoch();
+        {
+            const bool two = pl.bulk_units >= 0;
+            p.bulk_units = two ? static_cast<int>(pl.bulk_units) : p.n_units;
+            p.tail_chunks = two ? pl.tail_chunks : pl.n_chunks;
+            p.tail_chunk_tokens = two ? pl.tail_chunk_tokens : pl.chunk_tokens;
+            p.row_chunks = pl.row_chunks();
+            p.bulk_items = p.bulk_units * pl.n_chunks;
+            p.total_items = p.bulk_items + (p.n_units - p.bulk_units) * p.tail_chunks;
+            p.div_tail_chunks = ftq::make_fastdiv(static_cast<uint32_t>(p.tail_chunks));
+        }
         bool merged = false;
         e = dispatch_mma(head_dim, bits_k, bits_v, shared_lut, p, n_layers * B, st, &merged);
         if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn launch");

@@ -44,10 +44,28 @@ struct AttnParams {
     int q_dtype;                // kF32 / kF16 / kBF16
     int cp16;                   // contiguous source: every span 16-byte aligned
     int chunk_tokens, n_chunks, n_hpass;
-    float* partials;            // [L*B*Hq][n_chunks][D + 4]
-    int* work_counter;          // tensor-core path: next work item (zeroed before the launch)
+    float* partials;            // [L*B*Hq][row_chunks][D + 4]
+    // Streaming kernel only: the first bulk_units (layer, sequence, KV head) units are cut into
+    // n_chunks chunks of chunk_tokens, the others into tail_chunks chunks of tail_chunk_tokens
+    // (smaller items for the last wave of the grid).  Items are numbered bulk first:
+    // [0, bulk_items) = unit * n_chunks + chunk, then (unit - bulk_units) * tail_chunks + chunk.
+    // row_chunks = max(n_chunks, tail_chunks) = chunk rows a unit owns in `partials`.  Every
+    // other kernel uses one split for all units (row_chunks == n_chunks).
+    int bulk_units, bulk_items, total_items;
+    int tail_chunks, tail_chunk_tokens, row_chunks;
+    FastDiv div_tail_chunks;
+    // Counters of the tensor-core path.  work_counter[0] = next work item.  The barrier-synchronised
+    // kernel has the host zero it before the launch.  The streaming kernel clears its counters
+    // itself: CTA 0 zeroes work_counter[0] (tickets), work_counter[1] (CTAs that have left) and
+    // the unit counters, then stores `epoch` (unique per launch, never 0) into the 64-bit word at
+    // work_counter + 2; everybody checks for it before the first atomic on a counter, and the
+    // last CTA to leave stores 0 there, so that a replay of the same launch does not find its
+    // own epoch.
+    int* work_counter;
     // streaming tensor-core kernel: it finishes the split-KV merge itself
-    int* unit_counter;          // [L*B*Hkv] chunks delivered per unit (zeroed before the launch)
+    int* unit_counter;          // [n_units = L*B*Hkv] chunks delivered per unit
+    int n_units;
+    unsigned long long epoch;
     void* out;                  // [L*B, Hq, D]
     int out_dtype;
     int64_t num_blocks;         // block ids are checked against it

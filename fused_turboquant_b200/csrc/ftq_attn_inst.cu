@@ -78,12 +78,29 @@ static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              S::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        const int64_t items = static_cast<int64_t>(p.n_chunks) * p.Hkv * n_lb;
+        const int64_t items = p.total_items;
         const int64_t slots = static_cast<int64_t>(sm_count()) * S::CTAS_PER_SM;
         const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
-        kern<<<grid, S::THREADS, S::SMEM_BYTES, stream>>>(p, static_cast<int>(items));
+        // One node per call: the kernel clears its own counters.  Programmatic stream
+        // serialisation lets the set-up of this launch (tables in shared memory) run while the
+        // kernel before it in the stream drains; the kernel waits for that kernel's completion
+        // (griddepcontrol.wait) before it touches anything in global memory.
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(S::THREADS);
+        cfg.dynamicSmemBytes = S::SMEM_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+#ifdef FTQ_NO_PDL
+        attr[0].val.programmaticStreamSerializationAllowed = 0;
+#else
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+#endif
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
         *merged = true;
-        return cudaGetLastError();
+        return cudaLaunchKernelEx(&cfg, kern, p, static_cast<int>(items));
     } else {
     *merged = false;
     using C = MmaCfg<D, BK, BV, NH>;
@@ -95,6 +112,8 @@ static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream
     const int64_t items = static_cast<int64_t>(p.n_chunks) * p.Hkv * n_lb;
     const int64_t slots = static_cast<int64_t>(sm_count()) * C::CTAS_PER_SM;
     const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
+    e = cudaMemsetAsync(p.work_counter, 0, 256, stream);   // this kernel counts from a zeroed word
+    if (e != cudaSuccess) return e;
     kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, static_cast<int>(items));
     return cudaGetLastError();
     }
@@ -137,6 +156,32 @@ cudaError_t FTQ_CAT(launch_attn_mma_d, FTQ_D)(int bits_k, int bits_v, bool share
         case 4: return mma_by_bv<4>(bits_v, shared_lut, p, n_lb, stream, merged);
     }
     return cudaErrorInvalidValue;
+}
+
+// does launch_attn_mma pick the streaming kernel for this configuration? (the host plans the
+// split of the context differently for it)
+template <int BK>
+static bool streams_by_bv(int bv, int nh) {
+#ifdef FTQ_ONLY_BITS
+    if (BK != FTQ_ONLY_BITS || bv != FTQ_ONLY_BITS) return false;
+    return nh == 1 ? use_stream_kernel<BK, BK, 1>() : use_stream_kernel<BK, BK, 2>();
+#else
+    switch (bv) {
+        case 2: return nh == 1 ? use_stream_kernel<BK, 2, 1>() : use_stream_kernel<BK, 2, 2>();
+        case 3: return nh == 1 ? use_stream_kernel<BK, 3, 1>() : use_stream_kernel<BK, 3, 2>();
+        case 4: return nh == 1 ? use_stream_kernel<BK, 4, 1>() : use_stream_kernel<BK, 4, 2>();
+    }
+    return false;
+#endif
+}
+bool FTQ_CAT(attn_mma_streams_d, FTQ_D)(int bits_k, int bits_v, int group) {
+    const int nh = group <= 4 ? 1 : 2;
+    switch (bits_k) {
+        case 2: return streams_by_bv<2>(bits_v, nh);
+        case 3: return streams_by_bv<3>(bits_v, nh);
+        case 4: return streams_by_bv<4>(bits_v, nh);
+    }
+    return false;
 }
 
 cudaError_t FTQ_CAT(launch_attn_merge_d, FTQ_D)(int out_dtype, const float* partials, void* out,

@@ -130,7 +130,7 @@ __device__ __forceinline__ void stream_merge_unit(const AttnParams& p, int lb, i
         const int h = h0 + o;
         const bool valid = h < group;
         const int64_t v = static_cast<int64_t>(lb) * p.Hq + hkv * group + (valid ? h : 0);
-        const float* rows = p.partials + v * p.n_chunks * ROW;
+        const float* rows = p.partials + v * p.row_chunks * ROW;
         float M = -INFINITY;
         bool nan = poison;
         for (int c = 0; c < nc; c++) {
@@ -227,6 +227,8 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     };
     auto gptr = [&](uint32_t saddr) { return smem_raw + (saddr - sbase); };
 
+    // the next kernel of the stream may start its own set-up as soon as every CTA got here
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
@@ -312,7 +314,22 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     const uint32_t lv_lane =
         C::V2BYTE ? (window | 128u | ((lane & 15) * 8))
                   : ((BV == 4 ? (window | (SHARED_LUT ? 0u : 128u)) : tv_small) | (lane * 4));
+    // Everything up to here touched shared memory only.  From here on the kernel reads and writes
+    // global memory that the kernel before it in the stream may still be using (the workspace).
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    unsigned long long* epoch_word = reinterpret_cast<unsigned long long*>(p.work_counter + 2);
+    if (blockIdx.x == 0) {
+        for (int i = tid; i < p.n_units; i += THREADS) p.unit_counter[i] = 0;
+        if (tid == 0) {
+            p.work_counter[0] = 0;
+            p.work_counter[1] = 0;
+        }
+    }
     __syncthreads();
+    if (blockIdx.x == 0 && tid == 0) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.u64 [%0], %1;\n" ::"l"(epoch_word), "l"(p.epoch) : "memory");
+    }
     if (ctl[kCtlLayout]) return;  // cannot happen for a configuration the launcher accepts
     const uint32_t my_ring = static_cast<uint32_t>(ctl[kCtlRingAddr + warp]);
     const uint32_t my_bars = my_ring + S::RING * PAGE_BYTES;
@@ -329,19 +346,30 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     struct Item { int chunk, hkv, lb, layer, b, t0, t1, n_pages, seq_len; };
     auto item_info = [&](int item) {
         Item it;
-        const int rest = static_cast<int>(fast_div(static_cast<uint32_t>(item), p.div_chunks));
-        it.chunk = item - rest * p.n_chunks;
+        // (bulk units first, then the units that are cut into smaller chunks)
+        int rest, ct;
+        if (item < p.bulk_items) {
+            rest = static_cast<int>(fast_div(static_cast<uint32_t>(item), p.div_chunks));
+            it.chunk = item - rest * p.n_chunks;
+            ct = p.chunk_tokens;
+        } else {
+            const int j = item - p.bulk_items;
+            rest = static_cast<int>(fast_div(static_cast<uint32_t>(j), p.div_tail_chunks));
+            it.chunk = j - rest * p.tail_chunks;
+            rest += p.bulk_units;
+            ct = p.tail_chunk_tokens;
+        }
         it.lb = static_cast<int>(fast_div(static_cast<uint32_t>(rest), p.div_hkv));
         it.hkv = rest - it.lb * p.Hkv;
         it.layer = static_cast<int>(fast_div(static_cast<uint32_t>(it.lb), p.div_b));
         it.b = it.lb - it.layer * p.B;
         it.seq_len = p.seq_lens[it.b];
-        it.t0 = it.chunk * p.chunk_tokens;
-        it.t1 = min(it.seq_len, it.t0 + p.chunk_tokens);
+        it.t0 = it.chunk * ct;
+        it.t1 = min(it.seq_len, it.t0 + ct);
         it.n_pages = (it.t1 - it.t0 + kPageTokens - 1) / kPageTokens;
         return it;
     };
-    const int64_t prow_head_stride = static_cast<int64_t>(p.n_chunks) * ROW;
+    const int64_t prow_head_stride = static_cast<int64_t>(p.row_chunks) * ROW;
     const uint32_t blk_stride = static_cast<uint32_t>(p.Hkv) * PAGE_BYTES;
 
     // bounded polls of a shared-memory word (all lanes read the same word)
@@ -358,6 +386,27 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     bool stalled = false;   // a bounded wait of this warp ran out: its results are replaced by NaN
     // states that must have been published in buffer seq & 1 once item number seq is complete
     auto arrivals_due = [&](int seq) { return WARPS * ((seq >> 1) + 1); };
+    // the counters are valid once CTA 0 has published this launch's epoch (checked before a warp's
+    // first atomic on any of them; by then it has normally been there for a long time)
+    bool epoch_seen = false;
+    auto await_epoch = [&]() {
+        if (epoch_seen) return;
+        epoch_seen = true;
+        for (int i = 0; i < kFlagSpinLimit; i++) {
+            unsigned long long v;
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];\n" : "=l"(v) : "l"(epoch_word) : "memory");
+            if (v == p.epoch) return;
+            __nanosleep(100);
+        }
+        stalled = true;
+    };
+    // work items: the first two of a CTA are fixed, the rest are drawn from the counter
+    auto draw_item = [&]() {
+        await_epoch();
+        int t = 0;
+        if (lane == 0) t = 2 * static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
+        return __shfl_sync(0xffffffffu, t, 0);
+    };
 
     // `qsw` is a scratch row block for the fp32 rotated queries (two exist, so that two warps
     // can run this at start-up).  With wait_seq >= 0 the buffer still belongs to item number
@@ -383,8 +432,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
                     }
                 }
             }
-            if (lane == 0) item = static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
-            item = __shfl_sync(0xffffffffu, item, 0);
+            item = draw_item();
         }
         if (wait_seq >= 0) {
             if (!stalled && !wait_ge(kCtlArrived + buf, arrivals_due(wait_seq))) stalled = true;
@@ -466,14 +514,10 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         __syncwarp();
     };
 
-    // ---- the first two items of this CTA: item blockIdx.x (warp 0) and one ticket from the
-    // counter (warp 1); everybody may start on them after the barrier
+    // ---- the first two items of this CTA: blockIdx.x (warp 0) and blockIdx.x + gridDim.x
+    // (warp 1); everybody may start on them after the barrier
     if (warp < 2) {
-        int t = static_cast<int>(blockIdx.x);
-        if (warp == 1) {
-            if (lane == 0) t = static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
-            t = __shfl_sync(0xffffffffu, t, 0);
-        }
+        const int t = static_cast<int>(blockIdx.x) + warp * static_cast<int>(gridDim.x);
         prepare(warp, t, qs + warp * (8 * (D + 16)), -1);
         __threadfence_block();
     }
@@ -729,7 +773,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         const int chunk = ctl[kCtlChunk + buf], hkv = ctl[kCtlHkv + buf], lb = ctl[kCtlLb + buf];
         const int seq_len = ctl[kCtlSeqLen + buf];
         float* prow = p.partials +
-            ((static_cast<int64_t>(lb) * p.Hq + hkv * group) * p.n_chunks + chunk) * ROW;
+            ((static_cast<int64_t>(lb) * p.Hq + hkv * group) * p.row_chunks + chunk) * ROW;
         // lane (g, tg) folds what it would own as a compute lane: O[head 4hh + tg][(D/8)g ..)
         float M[NH];
         bool nan = bad;
@@ -794,12 +838,15 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             }
         }
         // has every chunk of this (layer, sequence, KV head) unit been delivered?
-        const int nc = min(p.n_chunks, (seq_len + p.chunk_tokens - 1) / p.chunk_tokens);
+        const bool bulk = lb * p.Hkv + hkv < p.bulk_units;
+        const int ct = bulk ? p.chunk_tokens : p.tail_chunk_tokens;
+        const int nc = min(bulk ? p.n_chunks : p.tail_chunks, (seq_len + ct - 1) / ct);
         bool last = true;
         if (nc > 1) {
             __threadfence();
             __syncwarp();
             int old = 0;
+            await_epoch();
             if (lane == 0) old = atomicAdd(p.unit_counter + lb * p.Hkv + hkv, 1);
             last = __shfl_sync(0xffffffffu, old, 0) == nc - 1;
             if (last) __threadfence();
@@ -813,9 +860,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     // ---- prepare service for item number seq (warp 1, after it has published its own state):
     // once every warp is done with item seq, its metadata buffer takes item seq + 2
     auto serve_prepare = [&](int seq) {
-        int t = 0;
-        if (lane == 0) t = static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
-        t = __shfl_sync(0xffffffffu, t, 0);
+        const int t = draw_item();
         prepare(seq & 1, t, qs, seq);
         __threadfence_block();
         if (lane == 0) ctl[kCtlReady] = seq + 2;
@@ -949,6 +994,16 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             pv_accum(r.v, pb);
         }
         n++;
+    }
+    // the last CTA to leave takes the epoch out of the workspace: a replay of this very launch
+    // (a captured graph) must not find its own epoch there before CTA 0 has cleared the counters
+    __syncthreads();
+    if (warp == 0) {
+        await_epoch();
+        if (lane == 0 && atomicAdd(p.work_counter + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+            __threadfence();
+            asm volatile("st.release.gpu.global.u64 [%0], %1;\n" ::"l"(epoch_word), "l"(0ull) : "memory");
+        }
     }
 }
 

@@ -206,8 +206,8 @@ int ftq_paged_decode_attn(const void *q, int q_dtype, void *out, int out_dtype,
  *     (ftq_decode_workspace_bytes tells) is rejected with FTQ_ERR_WORKSPACE;
  *   - all calls on one GPU share the array and it keeps whatever the last call
  *     left (every partial row that is read is written first by the same call,
- *     and the counters in its tail are cleared by a memset node at the start
- *     of every call), so two calls that may run at the same time on one GPU
+ *     and the counters in its tail are cleared at the start of every call,
+ *     by the kernel itself or by a memset node), so two calls that may run at the same time on one GPU
  *     (different streams) corrupt each other: serialise them;
  *   - the device that owns q / out / pool must be the current device of the
  *     calling thread: the size check and the scratch address are per device;
