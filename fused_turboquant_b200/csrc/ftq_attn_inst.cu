@@ -52,11 +52,12 @@ cudaError_t FTQ_CAT(launch_attn_split_d, FTQ_D)(int bits_k, int bits_v, bool pag
 }
 
 // The streaming kernel (no CTA-wide barriers, merge included) serves the configurations in
-// which it was measured faster than the barrier-synchronised one: a 4-bit byte table (one
-// 16-warp CTA per SM) with one head half (GQA group <= 4).  Measured on B200: +5 % on the
-// Llama-shaped K4V4 batch; the 8-warp configurations (3- and 2-bit codes, where two service
-// warps are a quarter of the CTA) lose 2-6 % and keep attn_mma_kernel + the merge launch, as
-// does head_dim 256 (the per-warp exchange slots do not fit beside 16 page rings).
+// which it was measured faster than the barrier-synchronised one: a 4-bit byte table (one CTA
+// per SM) with one head half (GQA group <= 4) -- 16 warps at head_dim 64 / 128, 8 warps at
+// head_dim 256 (16 rings and exchange slots do not fit beside the table there).  Measured on
+// B200: +20 % on the Llama-shaped K4V4 batch, +5 % on the ragged head_dim-256 K4V2 batch.  With
+// 3- and 2-bit codes (two 8-warp CTAs per SM, or one 16-warp CTA) and with two head halves it
+// measured 0-17 % slower; those keep attn_mma_kernel + the merge launch.
 template <int BK, int BV, int NH>
 constexpr bool use_stream_kernel() {
     using S = StreamCfg<FTQ_D, BK, BV, NH>;
@@ -65,7 +66,7 @@ constexpr bool use_stream_kernel() {
 #elif defined(FTQ_ALL_STREAM)
     return S::FITS;
 #else
-    return S::FITS && S::WARPS == 16 && NH == 1;
+    return S::FITS && S::BYTE && NH == 1 && (S::WARPS == 16 || FTQ_D == 256);
 #endif
 }
 

@@ -63,7 +63,6 @@ struct StreamCfg {
     static constexpr int RING_W = RING * PAGE_BYTES + RING * 8;   // pages + their mbarriers
     static constexpr int XCHG_W = 32 * M::STATE_F4 * 16 + NH * 2 * 4 * 4;
     static constexpr int LIMIT = 227 * 1024;
-    static constexpr int CTAS_PER_SM = BYTE ? 1 : 2;
     // rounds of an item's page deal that the two service warps sit out (their share of the
     // pages shrinks by what their service work costs; measured optimum)
 #ifdef FTQ_SERVICE_SKIP
@@ -109,6 +108,9 @@ struct StreamCfg {
         }
         return worst + 128;
     }
+    // one CTA per SM around a 64 KB byte table (16 warps when their rings and exchange slots fit
+    // beside it, else 8); two 8-warp CTAs per SM with the small tables of 3- and 2-bit codes
+    static constexpr int CTAS_PER_SM = BYTE ? 1 : 2;
     static constexpr int LIMIT_CTA = BYTE ? LIMIT : LIMIT / 2 - 1024;
     static constexpr int WARPS = (BYTE && need(16) <= LIMIT_CTA) ? 16 : 8;
     static constexpr int THREADS = 32 * WARPS;
