@@ -380,7 +380,7 @@ def time_regions(setup, steps, regions, world, post=None, post_each=None):
 
 
 def time_calls(setup, reps):
-    """Mean CUDA-event duration of one decode call (one kernel + the counter memset node)."""
+    """Mean CUDA-event duration of one decode call (all the nodes the call puts into the stream)."""
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(setup.n_calls)]
     ms = []
@@ -818,9 +818,19 @@ def main():
         ms_step = ms_total / args.steps
         value = total_bytes_step / (ms_step * 1e-3) / 1e9
         bytes_call = s.bytes_layer * s.layers_per_call
-        achieved = bytes_call / (call_ms * 1e-3) / 1e9
         traffic, traffic_src = load_traffic(args.workload, s.layers_per_call)
-        fused = s.D != 256   # head_dim 256 keeps the separate merge launch
+        # 4-bit keys with a GQA group of at most 4 run the streaming kernel (merge and counter
+        # reset inside the kernel); the other configurations run attn_mma_kernel behind a memset
+        # node, followed by the merge kernel
+        fused = w["bk"] == 4 and w["Hq"] // w["Hkv"] <= 4
+        # Duration of the dominant kernel's launch.  Where a call is this one kernel and a step is
+        # nothing but such calls back to back, it is the timed region divided by its launches
+        # (gaps between launches included).  Otherwise (several nodes per call, or a collective
+        # inside the step) it is the event-timed duration of one call, timed call by call.
+        launch_ms = call_ms
+        if fused and gather is None:
+            launch_ms = float(np.median(regions)) / (args.steps * s.n_calls)
+        achieved = bytes_call / (launch_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -835,17 +845,19 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src,
                          "peak_source": peak_src, "frac_of_nominal_8000": achieved / 8000.0,
-                         "kernel": ("attn_stream_kernel (one ftq_paged_decode_attn call = this kernel "
-                                    "+ one memset node for its counters)" if fused else
-                                    "attn_mma_kernel + attn_merge_kernel (one ftq_paged_decode_attn call)")
+                         "kernel": ("attn_stream_kernel (one ftq_paged_decode_attn call = this one "
+                                    "kernel)" if fused else
+                                    "attn_mma_kernel + attn_merge_kernel behind one memset node "
+                                    "(one ftq_paged_decode_attn call)")
                                    + ", %d layer(s)" % s.layers_per_call,
-                         "bytes_per_launch": bytes_call, "ms_per_launch": call_ms},
+                         "bytes_per_launch": bytes_call, "ms_per_launch": launch_ms,
+                         "ms_per_call_timed_alone": call_ms},
             "e2e": {"value": total_bytes_step / (ms_e2e / args.steps * 1e-3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": int(s.q_host.numel() * 2),
                     "d2h_bytes_per_step": int(s.q_host.numel() * 2 * (world if head_sharded else 1)),
                     "ms_per_step": ms_e2e / args.steps, "copies": copies},
             "gpu_launches": int(args.steps * len(regions) * s.n_calls * (1 if fused else 2)),
-            "memset_nodes": int(args.steps * len(regions) * s.n_calls),
+            "memset_nodes": 0 if fused else int(args.steps * len(regions) * s.n_calls),
             "clocks": clocks, "parity": parity, "encode": enc,
         }
     del s
