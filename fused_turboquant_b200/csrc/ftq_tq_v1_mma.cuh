@@ -107,7 +107,9 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
     // (code - (2^VB - 1) / 2, exact in fp16) and the zero point moved accordingly: the weighted sums
     // of `code * scale` and of `zero` would otherwise be two large numbers of opposite sign, and
     // the fp16 rounding of the weights would be paid on their magnitude instead of the value's
-    constexpr float kCtr = 0.5f * ((1 << VB) - 1);
+    // (4-bit codes are centred on 8, not 7.5: the arithmetic dequantisation subtracts 1024 + centre
+    // in fp16, where only integers exist at that magnitude)
+    constexpr float kCtr = VB == 4 ? 8.f : 0.5f * ((1 << VB) - 1);
     if constexpr (C::BYTE) {
         uint32_t* tb = reinterpret_cast<uint32_t*>(gptr(window));
         for (int i = tid; i < 256 * 64; i += THREADS) {
@@ -117,11 +119,8 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
                     const __half2 h = __floats2half2_rn(p.centroids.v[e & 15], p.centroids.v[e >> 4]);
                     tb[i] = *reinterpret_cast<const uint32_t*>(&h);
                 }
-            } else if constexpr (VB == 4) {
-                const __half2 h = __floats2half2_rn(static_cast<float>(e & 15) - kCtr,
-                                                    static_cast<float>(e >> 4) - kCtr);
-                tb[i] = *reinterpret_cast<const uint32_t*>(&h);
             }
+            // (columns 32..63 of a row are free: 4-bit value codes are dequantised arithmetically)
         }
     }
     if constexpr (KB != 4) {
@@ -462,6 +461,44 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
             }
 
             // ---- O^T += V^T.P^T with the integer value codes as the A operand
+            if constexpr (VB == 4) {
+                // 4-bit codes are turned into fp16 arithmetically, no look-up: a nibble or-ed into
+                // the mantissa of 1024.0 (0x6400) is 1024 + code (or 1024 + 16 * code one nibble
+                // up), and one packed subtract / multiply-add centres it exactly.  A 32-bit word
+                // (coordinates 0..7 of the lane's slice) yields the pairs (0,4) (1,5) (2,6) (3,7):
+                // two m-tiles whose rows hold other coordinates than the table version's -- the
+                // write-out below knows.
+                const uint32_t kMagic = 0x64006400u;
+                const __half2 kSubLo = __floats2half2_rn(1024.f + kCtr, 1024.f + kCtr);
+                const __half2 kMulHi = __floats2half2_rn(0.0625f, 0.0625f);
+                const __half2 kSubHi = __floats2half2_rn(-(64.f + kCtr), -(64.f + kCtr));
+                auto dq = [&](uint32_t w, uint32_t (&t)[4]) {
+                    const uint32_t w8 = w >> 8;
+                    const uint32_t x0 = (w & 0x000F000Fu) | kMagic, x1 = (w & 0x00F000F0u) | kMagic;
+                    const uint32_t x2 = (w8 & 0x000F000Fu) | kMagic, x3 = (w8 & 0x00F000F0u) | kMagic;
+                    const __half2 h0 = __hsub2(*reinterpret_cast<const __half2*>(&x0), kSubLo);
+                    const __half2 h1 = __hfma2(*reinterpret_cast<const __half2*>(&x1), kMulHi, kSubHi);
+                    const __half2 h2 = __hsub2(*reinterpret_cast<const __half2*>(&x2), kSubLo);
+                    const __half2 h3 = __hfma2(*reinterpret_cast<const __half2*>(&x3), kMulHi, kSubHi);
+                    t[0] = *reinterpret_cast<const uint32_t*>(&h0);
+                    t[1] = *reinterpret_cast<const uint32_t*>(&h1);
+                    t[2] = *reinterpret_cast<const uint32_t*>(&h2);
+                    t[3] = *reinterpret_cast<const uint32_t*>(&h3);
+                };
+#pragma unroll
+                for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+                    for (int wd = 0; wd < NMT / 2; wd++) {
+                        uint32_t ta[4], tb4[4];
+                        dq(r.v[2 * ks][wd], ta);
+                        dq(r.v[2 * ks + 1][wd], tb4);
+#pragma unroll
+                        for (int hh = 0; hh < NH; hh++) {
+                            mma_16816(oacc[hh][2 * wd], ta[0], ta[1], tb4[0], tb4[1], pb[hh][ks][0], pb[hh][ks][1]);
+                            mma_16816(oacc[hh][2 * wd + 1], ta[2], ta[3], tb4[2], tb4[3], pb[hh][ks][0], pb[hh][ks][1]);
+                        }
+                    }
+            } else
 #pragma unroll
             for (int ks = 0; ks < 2; ks++)
 #pragma unroll
@@ -529,11 +566,21 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
                     // partial = (sum p * (code * scale + zero)) / sum p, lse in natural-log units
                     const float inv = 1.f / l;
                     float* dst = mid_row(cur_it, h);
-                    float* o4 = dst + (D / 8) * g_ + 4 * mt;
-                    o4[0] = (a.x + z) * inv;
-                    o4[1] = (a.y + z) * inv;
-                    o4[2] = (a.z + z) * inv;
-                    o4[3] = (a.w + z) * inv;
+                    if constexpr (VB == 4) {
+                        // rows of the arithmetic dequantisation: m-tile pair (2w, 2w + 1) covers
+                        // coordinates 8w..8w+7 of the slice as (0,4 | 1,5) and (2,6 | 3,7)
+                        float* o4 = dst + (D / 8) * g_ + 8 * (mt >> 1) + 2 * (mt & 1);
+                        o4[0] = (a.x + z) * inv;
+                        o4[4] = (a.y + z) * inv;
+                        o4[1] = (a.z + z) * inv;
+                        o4[5] = (a.w + z) * inv;
+                    } else {
+                        float* o4 = dst + (D / 8) * g_ + 4 * mt;
+                        o4[0] = (a.x + z) * inv;
+                        o4[1] = (a.y + z) * inv;
+                        o4[2] = (a.z + z) * inv;
+                        o4[3] = (a.w + z) * inv;
+                    }
                     if (g_ == 0 && mt == 0)
                         dst[D] = any_bad ? __int_as_float(0x7fc00000) : M * kLn2 + logf(l);
                 }
