@@ -37,6 +37,7 @@ SIGNATURES = {
                                    _i, _i, _i, _i, _i, _fp, _fp, _fp, _f, _vp, _sz, _vp]),
     "ftq_paged_decode_attn_static": (_i, [_vp, _i, _vp, _i, _vp, _i64, _i64, _i, _vp, _i, _vp, _i,
                                           _i, _i, _i, _i, _i, _i, _fp, _fp, _fp, _f, _vp]),
+    "ftq_paged_decode_status": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _c.POINTER(_c.c_int)]),
     "ftq_v0_store": (_i, [_vp, _vp, _i, _i64, _i, _i, _i64, _i64, _i, _i, _fp, _fp, _fp, _vp,
                           _i64, _i, _i, _vp, _vp]),
     "ftq_v0_gather": (_i, [_vp, _i64, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp]),

@@ -863,6 +863,10 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     p.rsqrt_d = rsqrt_dim(head_dim);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
+    {
+        const size_t tail = counter_bytes(B, Hkv, n_layers);
+        p.work_counter = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + need - tail);
+    }
     if (mma) {
         const float vs = choose_v_scale(levels_v_host, bits_v, head_dim);
         for (int i = 0; i < (1 << bits_v); i++) p.lv_scaled.v[i] = levels_v_host[i] * vs;
@@ -874,8 +878,6 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
         // K and V can share one table only when the scaled V levels equal the K levels
         const bool shared_lut = bits_k == bits_v &&
             memcmp(p.lk.v, p.lv_scaled.v, sizeof(float) << bits_k) == 0;
-        const size_t tail = counter_bytes(B, Hkv, n_layers);
-        p.work_counter = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + need - tail);
         p.unit_counter = p.work_counter + 64;
         p.out = out;
         p.out_dtype = out_dtype;
@@ -900,6 +902,8 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
         if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn launch");
         if (merged) return FTQ_OK;  // the streaming kernel finishes the merge itself
     } else {
+        e = cudaMemsetAsync(p.work_counter, 0, 256, st);   // the status word
+        if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn status reset");
         e = dispatch_split(head_dim, bits_k, bits_v, true, p, n_layers * B, st);
     }
     if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn split launch");
@@ -1038,6 +1042,34 @@ extern "C" int ftq_paged_decode_attn_static(
                                  n_layers, block_table, max_blocks, seq_lens, max_seq_len, B, Hq,
                                  Hkv, head_dim, bits_k, bits_v, levels_k_host, levels_v_host,
                                  signs_host, scale, scratch, FTQ_STATIC_SCRATCH_BYTES, stream);
+}
+
+extern "C" int ftq_paged_decode_status(const void* workspace, int B, int Hq, int Hkv, int head_dim,
+                                       int max_seq_len, int n_layers, void* stream,
+                                       int* status_bits) {
+    const size_t need = ftq_decode_workspace_bytes(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
+    if (need == 0) return fail(FTQ_ERR_INVALID, "bad shape");
+    const void* base = workspace;
+    if (!base) {
+        if (need > static_cast<size_t>(FTQ_STATIC_SCRATCH_BYTES))
+            return fail(FTQ_ERR_WORKSPACE, "no such call can have used the built-in scratch");
+        void* scratch = nullptr;
+        const int rc = static_scratch_address(&scratch);
+        if (rc) return rc;
+        base = scratch;
+    }
+    const uint8_t* word = static_cast<const uint8_t*>(base) + need - counter_bytes(B, Hkv, n_layers) +
+                          ftq::kStatusWord * sizeof(int);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int bits = 0;
+    cudaError_t e = cudaMemcpyAsync(&bits, word, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_status");
+    if (status_bits) *status_bits = bits;
+    if (bits == 0) return FTQ_OK;
+    return fail(FTQ_ERR_DEVICE, "the last decode call on this workspace reported%s%s",
+                (bits & FTQ_STATUS_BAD_BLOCK_ID) ? " a block id outside the pool" : "",
+                (bits & FTQ_STATUS_WAIT_EXPIRED) ? " a wait that ran out" : "");
 }
 
 // ------------------------------------------------------------------ vLLM-v1 slot format

@@ -61,6 +61,9 @@ struct AttnParams {
     // work_counter + 2; everybody checks for it before the first atomic on a counter, and the
     // last CTA to leave stores 0 there, so that a replay of the same launch does not find its
     // own epoch.
+    // work_counter[4] is the call's status word (kStatus* bits, cleared with the counters): what
+    // the kernels of this call met; the host reads it on request (ftq_paged_decode_status).
+    // nullptr for the contiguous entry points.
     int* work_counter;
     // streaming tensor-core kernel: it finishes the split-KV merge itself
     int* unit_counter;          // [n_units = L*B*Hkv] chunks delivered per unit
@@ -78,6 +81,10 @@ struct AttnParams {
     Codebook lv_scaled;
     float inv_v_scale;
 };
+
+constexpr int kStatusWord = 4;         // index into AttnParams::work_counter
+constexpr int kStatusBadBlock = 1;     // a block id outside [0, num_blocks) was met (its rows are NaN)
+constexpr int kStatusWaitExpired = 2;  // a bounded wait of a kernel ran out (its rows are NaN)
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, int src_bytes) {
     const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -444,7 +451,10 @@ attn_split_kernel(const AttnParams p) {
         }
         prow[h * prow_head_stride + d] = a;
         if (d == 0) {
-            if (bad_block) M = __int_as_float(0x7fc00000);
+            if (bad_block) {
+                M = __int_as_float(0x7fc00000);
+                if (h == 0 && p.work_counter) atomicOr(p.work_counter + kStatusWord, kStatusBadBlock);
+            }
             prow[h * prow_head_stride + D] = M;
             prow[h * prow_head_stride + D + 1] = l;
         }

@@ -499,7 +499,10 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         for (int i = tid - w0 * 32; i < it.n_pages; i += nw * 32) {
             const int32_t id = btab[i];
             const bool ok = static_cast<uint32_t>(id) < static_cast<uint64_t>(p.num_blocks);
-            if (!ok) s_bad[bad_slot] = 1;
+            if (!ok) {
+                s_bad[bad_slot] = 1;
+                atomicOr(p.work_counter + kStatusWord, kStatusBadBlock);
+            }
             sblk[i] = ok ? id : 0;
         }
         if (warp - w0 < 2) {  // warp-uniform
@@ -868,6 +871,7 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         if (stalled) {
 #pragma unroll
             for (int hh = 0; hh < NH; hh++) m_run[hh] = __int_as_float(0x7fc00000);
+            if (lane == 0) atomicOr(p.work_counter + kStatusWord, kStatusWaitExpired);
         }
         __syncthreads();  // every warp is done with the ring: it becomes the exchange area
 #pragma unroll

@@ -325,6 +325,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         if (tid == 0) {
             p.work_counter[0] = 0;
             p.work_counter[1] = 0;
+            p.work_counter[kStatusWord] = 0;
         }
     }
     __syncthreads();
@@ -460,6 +461,10 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             sblk[buf * kStreamMaxChunkPages + i] = ok ? id : 0;
         }
         bad = __any_sync(0xffffffffu, bad);
+        if (bad) {
+            await_epoch();   // (the status word is cleared with the counters)
+            if (lane == 0) atomicOr(p.work_counter + kStatusWord, kStatusBadBlock);
+        }
         const int t8 = lane & 7, o = lane >> 3;
 #pragma unroll
         for (int pass = 0; pass < NH; pass++) {
@@ -999,6 +1004,10 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     }
     // the last CTA to leave takes the epoch out of the workspace: a replay of this very launch
     // (a captured graph) must not find its own epoch there before CTA 0 has cleared the counters
+    if (stalled) {
+        await_epoch();
+        if (lane == 0) atomicOr(p.work_counter + kStatusWord, kStatusWaitExpired);
+    }
     __syncthreads();
     if (warp == 0) {
         await_epoch();

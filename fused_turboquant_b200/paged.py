@@ -10,6 +10,8 @@ tokens of one (block, head):  K codes | K norms fp16 | V codes | V norms fp16.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _lib, _trace, codebook, kernels
@@ -130,7 +132,26 @@ class PagedKVPool:
                 _lib.fptr(self.levels_v), _lib.fptr(self.signs), float(scale), _ptr(ws),
                 ws.numel(), _stream(q.device))
         _lib.check(rc, "ftq_paged_decode_attn")
+        self._last_decode = (ws, B, Hq, int(max_seq_len), L, q.device)
         return out
+
+    def decode_status(self) -> int:
+        """Status bits of this pool's last ``decode_attention`` call (0: nothing to report;
+        1: a block id outside the pool was met, 2: a bounded wait inside a kernel ran out -- the
+        rows concerned are NaN either way).  Copies one word back and synchronises the current
+        stream; the kernels themselves never trap on such input."""
+        last = getattr(self, "_last_decode", None)
+        if last is None:
+            return 0
+        ws, B, Hq, max_seq_len, L, device = last
+        bits = ctypes.c_int(0)
+        with torch.cuda.device(device):
+            rc = _lib.load().ftq_paged_decode_status(
+                _ptr(ws), B, Hq, self.num_kv_heads, self.head_dim, max_seq_len, L, _stream(device),
+                ctypes.byref(bits))
+        if rc not in (0, -5):
+            _lib.check(rc, "ftq_paged_decode_status")
+        return int(bits.value)
 
 
     def gather_sequence(self, layer: int, block_row: torch.Tensor, seq_len: int):

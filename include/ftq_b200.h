@@ -33,7 +33,8 @@ typedef enum {
     FTQ_ERR_INVALID = -1,     /* bad argument (shape, bits, alignment, NULL) */
     FTQ_ERR_UNSUPPORTED = -2, /* valid request this build has no kernel for  */
     FTQ_ERR_CUDA = -3,        /* a CUDA runtime call failed                  */
-    FTQ_ERR_WORKSPACE = -4    /* caller workspace missing or too small       */
+    FTQ_ERR_WORKSPACE = -4,   /* caller workspace missing or too small       */
+    FTQ_ERR_DEVICE = -5       /* a kernel reported a problem (ftq_paged_decode_status) */
 } ftq_status;
 
 typedef enum { FTQ_F32 = 0, FTQ_F16 = 1, FTQ_BF16 = 2 } ftq_dtype;
@@ -224,6 +225,26 @@ int ftq_paged_decode_attn_static(const void *q, int q_dtype, void *out, int out_
                                  int head_dim, int bits_k, int bits_v, const float *levels_k_host,
                                  const float *levels_v_host, const float *signs_host, float scale,
                                  void *stream);
+
+/*
+ * What the kernels of the LAST ftq_paged_decode_attn call on `workspace` met
+ * (`workspace` NULL: the last ftq_paged_decode_attn_static call on the current
+ * device).  The shape arguments are that call's: they locate the status word
+ * in the workspace tail.  *status_bits (may be NULL) receives
+ *   FTQ_STATUS_BAD_BLOCK_ID   a block-table id outside [0, num_blocks); the id
+ *                             was not dereferenced, the (sequence, KV head)
+ *                             rows it belongs to are NaN;
+ *   FTQ_STATUS_WAIT_EXPIRED   a bounded wait inside a kernel ran out; the rows
+ *                             concerned are NaN.
+ * Returns FTQ_OK when no bit is set, FTQ_ERR_DEVICE otherwise.  Copies four
+ * bytes back and SYNCHRONISES `stream`: meant for a host that wants to know
+ * without scanning the output for NaN, at a point where it can afford a sync.
+ * No counterpart in the reference (its Triton kernels do not check ids).
+ */
+#define FTQ_STATUS_BAD_BLOCK_ID 1
+#define FTQ_STATUS_WAIT_EXPIRED 2
+int ftq_paged_decode_status(const void *workspace, int B, int Hq, int Hkv, int head_dim,
+                            int max_seq_len, int n_layers, void *stream, int *status_bits);
 
 /* ------------------------------------------- reference v0 layout adaptors */
 

@@ -50,6 +50,7 @@ def test_block_id_outside_the_pool_poisons_only_its_sequence(d, G, bk, bv, qdtyp
 
     good = run(bt)
     assert np.isfinite(good).all()
+    assert pool.decode_status() == 0
     # the kernels are told the pool ends 8 blocks early; sequence 1 names a block in that tail
     # (allocated, zero-filled, never written), everything else stays below the limit
     pool.num_blocks = used
@@ -59,6 +60,10 @@ def test_block_id_outside_the_pool_poisons_only_its_sequence(d, G, bk, bv, qdtyp
     assert np.isnan(got[1]).all(), "a sequence with an out-of-range block id must come back as NaN"
     np.testing.assert_array_equal(got[0], good[0])
     np.testing.assert_array_equal(got[2], good[2])
+    # ... and the call's status word says so (the next clean call clears it)
+    assert pool.decode_status() == 1
+    run(bt)
+    assert pool.decode_status() == 0
     # negative ids are out of range too
     bad_bt[1, 3] = -1
     got = run(bad_bt)

@@ -63,6 +63,11 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         torch.cuda.synchronize()
         if call == 1:   # (the first call may load the kernel's module; the second must be clean)
             assert torch.cuda.mem_get_info(dev)[0] == free_before, "the call changed free device memory"
+        bits = ctypes.c_int(-1)
+        assert lib.ftq_paged_decode_status(None, B, Hkv * G, Hkv, D, max_seq, L,
+                                           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+                                           ctypes.byref(bits)) == 0
+        assert bits.value == 0
         a, b = got.float().cpu().numpy(), want.float().cpu().numpy()
         assert np.isfinite(a).all()
         # same gate the other decode tests use for bf16 outputs; in practice the bits agree
