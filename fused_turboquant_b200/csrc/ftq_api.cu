@@ -296,53 +296,18 @@ ChunkPlan plan_chunks(int B, int Hq, int Hkv, int d, int max_seq_len, int n_laye
 // lowest modelled cost wins.  Chunks hold at most 8192 tokens (short enough for the dynamic
 // hand-out of items to even out ragged batches; their block ids are staged in shared memory)
 // and at least 1024.
-ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers, int ctas_per_sm) {
+// The planner both tensor-core kernels share.  Cost of a plan = waves of items over the CTA slots
+// x (pages of an item + the fixed cost of an item, in pages); the cheapest plan wins, the fewest
+// chunks among equals.  A plan has up to two regions: as many units as fill whole waves of the
+// grid are cut into few, long chunks; the remaining units into more, shorter ones that share the
+// last wave.  Items are handed out bulk first, so the short ones also even out the CTAs'
+// different speeds.
+ChunkPlan plan_two_regions(int64_t units, int64_t slots, int max_seq_len, double item_cost) {
     ChunkPlan pl;
     pl.n_hpass = 1;
-    const int64_t units = static_cast<int64_t>(B) * Hkv * n_layers;
-    const int64_t slots = static_cast<int64_t>(ftq::sm_count()) * ctas_per_sm;
     const int seq = max_seq_len > 0 ? max_seq_len : 1;
     const int c_min = (seq + 8191) / 8192;
     const int c_max = (seq + 1023) / 1024 > c_min ? (seq + 1023) / 1024 : c_min;
-    // Cost of a plan = waves of items x (pages of an item + the fixed cost of an item, in
-    // pages).  The fixed cost (publish / fold / next item's queries) weighs about 15 pages for
-    // a 16-warp CTA and 30 for an 8-warp one (fitted to measured step times of the uniform
-    // benchmark shapes); the cheapest plan wins, the fewest chunks among equals.
-    const double item_cost = ctas_per_sm == 1 ? 15.0 : 30.0;
-    int best_nc = c_min, best_ct = 0;
-    double best_cost = -1.0;
-    for (int nc = c_min; nc <= c_max && nc < c_min + 64; nc++) {
-        int ct = ((seq + nc - 1) / nc + 63) / 64 * 64;
-        if (ct > 8192) ct = 8192;
-        const int real_nc = (seq + ct - 1) / ct;
-        const int64_t items = units * real_nc;
-        const int64_t waves = (items + slots - 1) / slots;
-        const double cost = static_cast<double>(waves) * (ct / 16.0 + item_cost);
-        if (best_cost < 0.0 || cost < best_cost * (1.0 - 1e-9)) {
-            best_cost = cost; best_nc = real_nc; best_ct = ct;
-        }
-    }
-    pl.chunk_tokens = best_ct;
-    pl.n_chunks = best_nc;
-    return pl;
-}
-
-// The streaming kernel's plan.  Measured on B200 (Llama-shaped K4V4 batches of 37..111
-// sequences, forced chunk counts): an item costs about 74 pages on top of its own pages (the
-// service warps' smaller page share, the publish / fold / prepare hand-overs), so long chunks
-// pay -- but whole waves of them rarely match the unit count.  The plan therefore has two
-// regions: as many units as fill whole waves of the grid are cut into few, long chunks; the
-// remaining units into more, shorter ones that share the last wave.  Items are handed out bulk
-// first, so the short ones also even out the CTAs' different speeds.
-ChunkPlan plan_chunks_stream(int B, int Hkv, int max_seq_len, int n_layers) {
-    ChunkPlan pl;
-    pl.n_hpass = 1;
-    const int64_t units = static_cast<int64_t>(B) * Hkv * n_layers;
-    const int64_t slots = ftq::sm_count();
-    const int seq = max_seq_len > 0 ? max_seq_len : 1;
-    const int c_min = (seq + 8191) / 8192;
-    const int c_max = (seq + 1023) / 1024 > c_min ? (seq + 1023) / 1024 : c_min;
-    const double item_cost = 74.0;
     auto split = [&](int nc, int* ct, int* real) {
         int t = ((seq + nc - 1) / nc + 63) / 64 * 64;
         if (t > 8192) t = 8192;
@@ -350,7 +315,7 @@ ChunkPlan plan_chunks_stream(int B, int Hkv, int max_seq_len, int n_layers) {
         *real = (seq + t - 1) / t;
     };
     double best = -1.0;
-    for (int nc1 = c_min; nc1 <= c_max && nc1 < c_min + 16; nc1++) {
+    for (int nc1 = c_min; nc1 <= c_max && nc1 < c_min + 64; nc1++) {
         int ct1, r1;
         split(nc1, &ct1, &r1);
         const double cost1 = ct1 / 16.0 + item_cost;
@@ -380,6 +345,24 @@ ChunkPlan plan_chunks_stream(int B, int Hkv, int max_seq_len, int n_layers) {
         }
     }
     return pl;
+}
+
+// attn_mma_kernel: the fixed cost of an item (publish / fold / next item's queries between
+// CTA-wide barriers) weighs about 15 pages for a 16-warp CTA and 30 for an 8-warp one (fitted to
+// measured step times of the uniform benchmark shapes).
+ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers, int ctas_per_sm) {
+    return plan_two_regions(static_cast<int64_t>(B) * Hkv * n_layers,
+                            static_cast<int64_t>(ftq::sm_count()) * ctas_per_sm, max_seq_len,
+                            ctas_per_sm == 1 ? 15.0 : 30.0);
+}
+
+// The streaming kernel (one CTA per SM).  Measured on B200 (Llama-shaped K4V4 batches of 37..111
+// sequences, forced chunk counts): an item costs about 74 pages on top of its own pages (the
+// service warps' smaller page share, the publish / fold / prepare hand-overs), so long chunks
+// pay -- but whole waves of them rarely match the unit count, hence the two regions.
+ChunkPlan plan_chunks_stream(int B, int Hkv, int max_seq_len, int n_layers) {
+    return plan_two_regions(static_cast<int64_t>(B) * Hkv * n_layers, ftq::sm_count(), max_seq_len,
+                            74.0);
 }
 
 bool attn_mma_streams(int d, int bits_k, int bits_v, int group) {
@@ -418,19 +401,26 @@ cudaError_t dispatch_mma(int d, int bk, int bv, bool shared_lut, const ftq::Attn
 }
 
 cudaError_t dispatch_merge(int d, int out_dtype, const float* partials, void* out,
-                           const int32_t* seq_lens, int S, int B, int Hq, const ChunkPlan& pl,
-                           int64_t n_vec, const ftq::SignBits& signs, cudaStream_t st) {
+                           const int32_t* seq_lens, int S, int B, int Hq, int Hkv,
+                           const ChunkPlan& pl, int64_t n_vec, const ftq::SignBits& signs,
+                           cudaStream_t st) {
     const float r = rsqrt_dim(d);
+    const bool two = pl.bulk_units >= 0;
+    const int bulk = two ? static_cast<int>(pl.bulk_units) : 0x7fffffff;
+    const int tc = two ? pl.tail_chunks : pl.n_chunks, tt = two ? pl.tail_chunk_tokens : pl.chunk_tokens;
     switch (d) {
         case 64:
             return ftq::launch_attn_merge_d64(out_dtype, partials, out, seq_lens, S, B, Hq,
-                                              pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, st);
+                                              pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, Hkv,
+                                              bulk, tc, tt, pl.row_chunks(), st);
         case 128:
             return ftq::launch_attn_merge_d128(out_dtype, partials, out, seq_lens, S, B, Hq,
-                                               pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, st);
+                                               pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, Hkv,
+                                               bulk, tc, tt, pl.row_chunks(), st);
         case 256:
             return ftq::launch_attn_merge_d256(out_dtype, partials, out, seq_lens, S, B, Hq,
-                                               pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, st);
+                                               pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, Hkv,
+                                               bulk, tc, tt, pl.row_chunks(), st);
     }
     return cudaErrorInvalidValue;
 }
@@ -758,7 +748,7 @@ int ftq_flash_decode(const void* q, int q_dtype, int q_is_rotated, const uint8_t
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = dispatch_split(head_dim, bits_k, bits_v, false, p, B, st);
     if (e != cudaSuccess) return cuda_fail(e, "ftq_flash_decode split launch");
-    e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, S, B, Hq, pl,
+    e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, S, B, Hq, Hkv, pl,
                        static_cast<int64_t>(B) * Hq, p.signs, st);
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_flash_decode merge launch");
 }
@@ -907,7 +897,7 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
         e = dispatch_split(head_dim, bits_k, bits_v, true, p, n_layers * B, st);
     }
     if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn split launch");
-    e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, 0, B, Hq, pl,
+    e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, 0, B, Hq, Hkv, pl,
                        static_cast<int64_t>(n_layers) * B * Hq, p.signs, st);
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_paged_decode_attn merge launch");
 }

@@ -468,7 +468,8 @@ template <int D, typename OT>
 __global__ void __launch_bounds__(128)
 attn_merge_kernel(const float* __restrict__ partials, OT* __restrict__ out,
                   const int32_t* __restrict__ seq_lens, int S, int B, int Hq, int n_chunks,
-                  int chunk_tokens, int64_t n_vec, SignBits signs, float rsqrt_d) {
+                  int chunk_tokens, int64_t n_vec, SignBits signs, float rsqrt_d, int Hkv,
+                  int bulk_units, int tail_chunks, int tail_chunk_tokens, int row_chunks) {
     constexpr int E = D / kOctet;
     constexpr int ROW = D + 4;
     const int lane = threadIdx.x & 31;
@@ -479,9 +480,14 @@ attn_merge_kernel(const float* __restrict__ partials, OT* __restrict__ out,
     if (valid) {
         const int b = static_cast<int>((v / Hq) % B);
         const int len = seq_lens ? (S > 0 ? min(seq_lens[b], S) : seq_lens[b]) : S;
-        nc = min(n_chunks, (len + chunk_tokens - 1) / chunk_tokens);
+        // (layer, sequence, KV head) units from bulk_units on were cut into tail_chunks chunks
+        // of tail_chunk_tokens (see AttnParams); a unit owns row_chunks chunk rows either way
+        const int64_t unit = (v / Hq) * Hkv + (v % Hq) / (Hq / Hkv);
+        const bool bulk = unit < bulk_units;
+        const int ct = bulk ? chunk_tokens : tail_chunk_tokens;
+        nc = min(bulk ? n_chunks : tail_chunks, (len + ct - 1) / ct);
     }
-    const float* rows = partials + (valid ? v : 0) * n_chunks * ROW;
+    const float* rows = partials + (valid ? v : 0) * row_chunks * ROW;
     float M = -INFINITY;
     for (int c = 0; c < nc; c++) M = fmaxf(M, rows[c * ROW + D]);
     float a[E];
