@@ -1066,8 +1066,22 @@ extern "C" int ftq_paged_decode_status(const void* workspace, int B, int Hq, int
 
 namespace {
 // key_bits 8 = FP8 (e4m3) keys, as in vLLM's stock TurboQuantConfig
-bool tq_bits_ok(int kb, int vb) { return ((kb >= 1 && kb <= 4) || kb == 8) && ((vb >= 1 && vb <= 4) || vb == 8); }
-int tq_key_bytes(int d, int kb) { return kb == 8 ? d : d * kb / 8 + 2; }
+// key_bits: 1..4 = Lloyd-Max codes, 8 = FP8, FTQ_TQ_KEY_BITS_MSE8 = 8-bit Lloyd-Max codes
+bool tq_bits_ok(int kb, int vb) {
+    return ((kb >= 1 && kb <= 4) || kb == 8 || kb == FTQ_TQ_KEY_BITS_MSE8) && ((vb >= 1 && vb <= 4) || vb == 8);
+}
+int tq_key_bytes(int d, int kb) {
+    return kb == 8 ? d : (kb == FTQ_TQ_KEY_BITS_MSE8 ? d + 2 : d * kb / 8 + 2);
+}
+static_assert(FTQ_TQ_KEY_BITS_MSE8 == ftq::kTqKeyBitsMse8, "header and kernels agree on the marker");
+// strictly ascending table of n floats -> the kernels' 256-entry parameter block
+int pack_table256(const float* host, int n, bool ascending_strictly, ftq::TqTable256* t) {
+    for (int i = 0; i < 256; i++) t->v[i] = i < n ? host[i] : FLT_MAX;
+    for (int i = 1; i < n; i++)
+        if (ascending_strictly ? !(host[i] > host[i - 1]) : !(host[i] >= host[i - 1]))
+            return fail(FTQ_ERR_INVALID, "the 8-bit key table must be ascending");
+    return FTQ_OK;
+}
 bool even(int64_t v) { return (v & 1) == 0; }
 }  // namespace
 
@@ -1085,7 +1099,7 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
                             int block_size, const int64_t* slot_mapping, void* stream) {
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
-        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 or 8 = FP8 / 1,2,3,4,8)", key_bits,
+        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4, 8 = FP8 or FTQ_TQ_KEY_BITS_MSE8 / 1,2,3,4,8)", key_bits,
                     value_bits);
     if (!dtype_ok(dtype)) return fail(FTQ_ERR_INVALID, "bad dtype %d", dtype);
     if (rotate_values && value_bits == 8)
@@ -1094,8 +1108,9 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
     if (n_tokens * Hkv >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "n_tokens * Hkv must be below 2^31");
     if (n_tokens == 0) return FTQ_OK;
     const bool key_fp8 = key_bits == 8;  // no codebook: midpoints_host may be NULL
-    if (key_fp8 && value_lloyd_max && value_bits == 4)
-        return fail(FTQ_ERR_UNSUPPORTED, "Lloyd-Max value codes need a key codebook (FP8 keys have none)");
+    const bool key_mse8 = key_bits == FTQ_TQ_KEY_BITS_MSE8;  // midpoints_host: 255 entries
+    if ((key_fp8 || key_mse8) && value_lloyd_max && value_bits == 4)
+        return fail(FTQ_ERR_UNSUPPORTED, "Lloyd-Max value codes need a 4-bit key codebook");
     if (!key || !value || !kv_cache || !slot_mapping || (!key_fp8 && !midpoints_host))
         return fail(FTQ_ERR_INVALID, "NULL pointer argument");
     const int64_t es = static_cast<int64_t>(dtype_size(dtype));
@@ -1119,11 +1134,18 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
     p.block_size = block_size;
     p.div_block = ftq::make_fastdiv(static_cast<uint32_t>(block_size));
     p.slot_mapping = slot_mapping;
-    const int nmid = key_fp8 ? 0 : (1 << key_bits) - 1;
+    const int nmid = (key_fp8 || key_mse8) ? 0 : (1 << key_bits) - 1;
     for (int i = 0; i < ftq::kTqMaxMid; i++) p.midpoints[i] = i < nmid ? midpoints_host[i] : FLT_MAX;
     for (int i = 1; i < nmid; i++)
         if (!(midpoints_host[i] > midpoints_host[i - 1]))
             return fail(FTQ_ERR_INVALID, "midpoints must be strictly ascending");
+    ftq::TqTable256 mid8;
+    if (key_mse8) {
+        const int rc = pack_table256(midpoints_host, 255, true, &mid8);
+        if (rc) return rc;
+    }
+    const ftq::TqTable256* t8 = key_mse8 ? &mid8 : nullptr;
+    const int kb = key_mse8 ? 8 : key_bits;
     p.rsqrt_d = 1.0f / sqrtf(static_cast<float>(head_dim));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t n_vec = n_tokens * Hkv;
@@ -1132,9 +1154,9 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
                       (value_lloyd_max && value_bits == 4 ? ftq::kTqLloydMaxValues : 0);
     cudaError_t e = cudaErrorInvalidValue;
     switch (head_dim) {
-        case 64: e = ftq::launch_tq_store_d64(key_bits, value_bits, dtype, p, vmode, n_vec, st); break;
-        case 128: e = ftq::launch_tq_store_d128(key_bits, value_bits, dtype, p, vmode, n_vec, st); break;
-        case 256: e = ftq::launch_tq_store_d256(key_bits, value_bits, dtype, p, vmode, n_vec, st); break;
+        case 64: e = ftq::launch_tq_store_d64(kb, value_bits, dtype, p, vmode, n_vec, t8, st); break;
+        case 128: e = ftq::launch_tq_store_d128(kb, value_bits, dtype, p, vmode, n_vec, t8, st); break;
+        case 256: e = ftq::launch_tq_store_d256(kb, value_bits, dtype, p, vmode, n_vec, t8, st); break;
     }
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "tq_store launch");
 }
@@ -1175,7 +1197,7 @@ extern "C" int ftq_tq_decode_layers(const void* q, int q_dtype, int B, int Hq, i
     B = B * n_layers;   // rows of q / mid_o / out
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
-        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4 or 8 = FP8 / 1,2,3,4,8)", key_bits,
+        return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4, 8 = FP8 or FTQ_TQ_KEY_BITS_MSE8 / 1,2,3,4,8)", key_bits,
                     value_bits);
     if (!dtype_ok(q_dtype) || !dtype_ok(out_dtype)) return fail(FTQ_ERR_INVALID, "bad dtype");
     if ((prefix_out != nullptr) != (prefix_lse != nullptr))
@@ -1189,8 +1211,9 @@ extern "C" int ftq_tq_decode_layers(const void* q, int q_dtype, int B, int Hq, i
     if (B == 0) return FTQ_OK;
     if (B > 65535) return fail(FTQ_ERR_INVALID, "B must be at most 65535 per call");
     const bool key_fp8 = key_bits == 8;  // no codebook: centroids_host may be NULL
-    if (key_fp8 && value_lloyd_max && value_bits == 4)
-        return fail(FTQ_ERR_UNSUPPORTED, "Lloyd-Max value codes need a key codebook (FP8 keys have none)");
+    const bool key_mse8 = key_bits == FTQ_TQ_KEY_BITS_MSE8;  // centroids_host: 256 entries
+    if ((key_fp8 || key_mse8) && value_lloyd_max && value_bits == 4)
+        return fail(FTQ_ERR_UNSUPPORTED, "Lloyd-Max value codes need a 4-bit key codebook");
     if (!q || !kv_cache || !block_table || !seq_lens || (!key_fp8 && !centroids_host) || !mid_o || !out)
         return fail(FTQ_ERR_INVALID, "NULL pointer argument");
     if (!aligned(q, 16) || !aligned(out, 4) || !aligned(mid_o, 4))
@@ -1225,7 +1248,14 @@ extern "C" int ftq_tq_decode_layers(const void* q, int q_dtype, int B, int Hq, i
     p.n_hpass = (Hq / Hkv + gh - 1) / gh;
     if (static_cast<int64_t>(Hkv) * p.n_hpass > 65535) return fail(FTQ_ERR_INVALID, "too many heads");
     p.rsqrt_d = 1.0f / sqrtf(static_cast<float>(head_dim));
-    if (key_fp8) {
+    ftq::TqTable256 cent8;
+    if (key_mse8) {
+        const int rc = pack_table256(centroids_host, 256, false, &cent8);
+        if (rc) return rc;
+    }
+    const ftq::TqTable256* t8 = key_mse8 ? &cent8 : nullptr;
+    const int kb = key_mse8 ? 8 : key_bits;
+    if (key_fp8 || key_mse8) {
         memset(&p.centroids, 0, sizeof(p.centroids));
     } else {
         const int rc = pack_levels(centroids_host, key_bits, &p.centroids);
@@ -1252,9 +1282,9 @@ extern "C" int ftq_tq_decode_layers(const void* q, int q_dtype, int B, int Hq, i
             e = ftq::launch_tq_mma_d128(key_bits, value_bits, nh, p, static_cast<int>(items), st);
     } else {
         switch (head_dim) {
-            case 64: e = ftq::launch_tq_split_d64(key_bits, value_bits, p, st); break;
-            case 128: e = ftq::launch_tq_split_d128(key_bits, value_bits, p, st); break;
-            case 256: e = ftq::launch_tq_split_d256(key_bits, value_bits, p, st); break;
+            case 64: e = ftq::launch_tq_split_d64(kb, value_bits, p, t8, st); break;
+            case 128: e = ftq::launch_tq_split_d128(kb, value_bits, p, t8, st); break;
+            case 256: e = ftq::launch_tq_split_d256(kb, value_bits, p, t8, st); break;
         }
     }
     if (e != cudaSuccess) return cuda_fail(e, "tq_decode stage 1 launch");

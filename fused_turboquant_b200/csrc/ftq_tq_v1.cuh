@@ -28,6 +28,7 @@
 
 #include <cuda_fp8.h>
 
+#include <cfloat>
 #include <type_traits>
 
 #include "ftq_attn.cuh"
@@ -36,6 +37,17 @@
 namespace ftq {
 
 constexpr int kTqMaxMid = 15;  // key codes of 1..4 bits
+
+// 8-bit Lloyd-Max key codes (256 centroids, one byte per coordinate + the fp16 norm; the
+// reference's BoundaryTurboQuantConfig with key_use_fp8_at_8bit = False,
+// vllm_plugin/boundary_tq_config.py:26-35): the kernels are instantiated with KB = 8 and K8M =
+// true and get their table -- 255 midpoints for the store, 256 centroids for the decode -- as a
+// second kernel parameter (1 KB of constant bank, no device allocation); everybody else passes
+// an empty struct.
+constexpr int kTqKeyBitsMse8 = 264;  // the host-side key_bits value that selects it
+struct TqTable256 { float v[256]; };
+struct TqNoTable { int unused; };
+template <bool K8M> using TqTable = std::conditional_t<K8M, TqTable256, TqNoTable>;
 
 struct TqStoreParams {
     const void* key;       // [n_tokens, Hkv, D], strides in elements
@@ -129,22 +141,24 @@ template <> __device__ __forceinline__ float round_as<__nv_bfloat16>(float v) {
 // where the scale would and the zero point is 0.  The squares are added in register order per
 // lane, then pairwise over the octet -- in whichever layout the values sit (after the fused
 // rotation: lane l holds the coordinates l + 8k).
-template <int D, int KB, int VB, typename T, bool ROTV, bool LMV = false>
+template <int D, int KB, int VB, typename T, bool ROTV, bool LMV = false, bool K8M = false>
 __global__ void __launch_bounds__(256)
-tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
+tq_store_kernel(const TqStoreParams p, int64_t n_vec, const TqTable<K8M> t8) {
+    static_assert(!K8M || KB == 8, "the 256-entry table belongs to 8-bit keys");
     static_assert(!ROTV || VB != 8, "rotated 8-bit values are rotated by the caller");
     static_assert(!LMV || VB == 4, "Lloyd-Max value codes are 4-bit");
     constexpr int E = D / kOctet;
     constexpr int NCH = E / 8;
-    constexpr bool KFP8 = KB == 8;
-    static_assert(!(KFP8 && LMV), "Lloyd-Max value codes use the key midpoints");
-    constexpr int MSE = D * KB / 8;                      // (FP8 keys: D bytes)
+    constexpr bool KBYTE = KB == 8;             // one byte per coordinate: FP8 or an 8-bit code
+    constexpr bool KFP8 = KBYTE && !K8M;
+    static_assert(!(KBYTE && LMV), "Lloyd-Max value codes use a 4-bit key codebook");
+    constexpr int MSE = D * KB / 8;                      // (8-bit keys: D bytes)
     constexpr int KPS = MSE + (KFP8 ? 0 : 2);
     constexpr int VDB = tq_value_bytes(D, VB);
     constexpr int VMAX = (1 << VB) - 1;
-    constexpr int NMID = KFP8 ? 0 : (1 << KB) - 1;
-    constexpr int NW = KB == 2 ? (E + 15) / 16 : E / 8;  // (unused for 1-bit codes and FP8 keys)
-    constexpr int KT = (KB == 1 || KFP8) ? 2 : KB;       // transposition constants: 2..4 bits only
+    constexpr int NMID = KBYTE ? 0 : (1 << KB) - 1;
+    constexpr int NW = KB == 2 ? (E + 15) / 16 : E / 8;  // (unused for 1-bit codes and 8-bit keys)
+    constexpr int KT = (KB == 1 || KBYTE) ? 2 : KB;      // transposition constants: 2..4 bits only
     constexpr int VT = (ROTV && VB != 1) ? VB : 4;
 
     const int lane = threadIdx.x & 31;
@@ -155,6 +169,22 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
     const TransposeConsts<VT> tcv = transpose_consts<VT>(lane);
     (void)tc;
     (void)tcv;
+    // 8-bit codes: the 255 midpoints in shared memory (lanes search at different places)
+    __shared__ float smid[K8M ? 256 : 1];
+    if constexpr (K8M) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) smid[i] = i < 255 ? t8.v[i] : FLT_MAX;
+        __syncthreads();
+    }
+    // code = number of midpoints <= y (what the reference's binary search returns,
+    // triton_inkernel_store.py:92-100, for strictly ascending midpoints)
+    auto code8 = [&](float yv) {
+        uint32_t idx = 0;
+#pragma unroll
+        for (int step = 128; step >= 1; step >>= 1)
+            if (yv >= smid[K8M ? idx + step - 1 : 0]) idx += step;
+        return idx;
+    };
+    (void)code8;
 
     for (int64_t base = warp * 4; base < n_vec; base += n_warps * 4) {
         const int64_t v = base + sub;
@@ -204,16 +234,22 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
         for (int r = 0; r < E; r++) y[r] = __fdiv_rn(y[r], den);
         octet_fwht<E>(y, lane);  // -> (lane l, register k) = coordinate l + 8k
 
-        if constexpr (KFP8) {
+        if constexpr (KBYTE) {
             // lane l holds the coordinates l + 8k: neighbouring lanes trade bytes so that each
             // stores 16-bit pairs (the even lane those of even k, the odd lane those of odd k)
             const bool odd = lane & 1;
 #pragma unroll
             for (int k = 0; k < E; k += 2) {
-                const uint32_t a = __nv_cvt_float_to_fp8(
-                    __fmul_rn(__fmul_rn(y[k], p.rsqrt_d), norm), __NV_SATFINITE, __NV_E4M3);
-                const uint32_t b = __nv_cvt_float_to_fp8(
-                    __fmul_rn(__fmul_rn(y[k + 1], p.rsqrt_d), norm), __NV_SATFINITE, __NV_E4M3);
+                uint32_t a, b;
+                if constexpr (KFP8) {
+                    a = __nv_cvt_float_to_fp8(__fmul_rn(__fmul_rn(y[k], p.rsqrt_d), norm),
+                                              __NV_SATFINITE, __NV_E4M3);
+                    b = __nv_cvt_float_to_fp8(__fmul_rn(__fmul_rn(y[k + 1], p.rsqrt_d), norm),
+                                              __NV_SATFINITE, __NV_E4M3);
+                } else {
+                    a = code8(__fmul_rn(y[k], p.rsqrt_d));
+                    b = code8(__fmul_rn(y[k + 1], p.rsqrt_d));
+                }
                 const uint32_t recv = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
                 const uint32_t pair = odd ? (recv | (b << 8)) : (a | (recv << 8));
                 const int coord = odd ? t - 1 + 8 * (k + 1) : t + 8 * k;
@@ -224,9 +260,9 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
 #pragma unroll
         for (int i = 0; i < NW; i++) w[i] = 0u;
 #pragma unroll
-        for (int k = 0; k < (KFP8 ? 0 : E); k++) {
+        for (int k = 0; k < (KBYTE ? 0 : E); k++) {
             const float yv = __fmul_rn(y[k], p.rsqrt_d);
-            constexpr int SB = KFP8 ? 1 : KB;  // (no codes with FP8 keys)
+            constexpr int SB = KBYTE ? 1 : KB;  // (8-bit keys were stored above)
             if constexpr (KB == 1) {
                 tq_or_code<SB>(yv, p.midpoints, w[0], k);
             } else if constexpr (KB == 2) {
@@ -238,7 +274,7 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
         }
         if constexpr (KB == 1) emit_bits1<E>(w[0], dst, store, lane);
 #pragma unroll
-        for (int i = 0; i < ((KB == 1 || KFP8) ? 0 : NW); i++) {
+        for (int i = 0; i < ((KB == 1 || KBYTE) ? 0 : NW); i++) {
             const uint32_t o = octet_transpose_items<KT>(w[i], tc);
             if constexpr (KB == 3) {
                 const int g0 = (4 * t) / 3;
@@ -302,7 +338,7 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec) {
         auto vcode = [&](float x) -> uint32_t {
             if constexpr (LMV) {
                 uint32_t c = 0;
-                tq_or_code<(KFP8 ? 1 : KB)>(__fdiv_rn(x, vden), p.midpoints, c, 0);
+                tq_or_code<(KBYTE ? 1 : KB)>(__fdiv_rn(x, vden), p.midpoints, c, 0);
                 return c;
             } else {
                 const float f = __fadd_rn(__fdiv_rn(__fsub_rn(x, mn), scale), 0.5f);
@@ -424,12 +460,13 @@ __host__ __device__ constexpr int tq_row_stride(int bytes, int nb) {
     return tq_gcd((bytes + unit) / 4, 32) < tq_gcd(bytes / 4, 32) ? bytes + unit : bytes;
 }
 
-template <int D, int KB, int VB>
+template <int D, int KB, int VB, bool K8M = false>
 __global__ void __launch_bounds__(kAttnThreads)
-tq_split_kernel(const TqDecodeParams p) {
+tq_split_kernel(const TqDecodeParams p, const TqTable<K8M> t8) {
+    static_assert(!K8M || KB == 8, "the 256-entry table belongs to 8-bit keys");
     constexpr int E = AttnCfg<D>::E;
     constexpr int GH = AttnCfg<D>::GH;
-    constexpr bool KFP8 = KB == 8;   // D bytes of e4m3, no norm field
+    constexpr bool KFP8 = KB == 8 && !K8M;   // D bytes of e4m3, no norm field
     constexpr int MSE = D * KB / 8;
     constexpr int NU = KFP8 ? 0 : 1;  // 16-bit units of the key norm
     constexpr int VDB = tq_value_bytes(D, VB);
@@ -447,7 +484,7 @@ tq_split_kernel(const TqDecodeParams p) {
     float* meta = reinterpret_cast<float*>(smem_raw + BUF_BYTES);   // [3][64]: key norm, value scale, zero
     const uint8_t** slots = reinterpret_cast<const uint8_t**>(meta + 3 * kTqTileTokens);  // [64]
     float* qs = reinterpret_cast<float*>(slots + kTqTileTokens);    // [GH][D]
-    float* lut = qs + GH * D;                                       // [16]
+    float* lut = qs + GH * D;                                       // [16], 8-bit key codes: [256]
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -480,7 +517,11 @@ tq_split_kernel(const TqDecodeParams p) {
     }
 
     // ---- prologue: centroids and the rotated (no signs), pre-scaled queries of this pass
-    if (tid < kMaxLevels) lut[tid] = p.centroids.v[tid];
+    if constexpr (K8M) {
+        for (int i = tid; i < 256; i += kAttnThreads) lut[i] = t8.v[i];
+    } else {
+        if (tid < kMaxLevels) lut[tid] = p.centroids.v[tid];
+    }
     {
         const int hh = warp * 4 + o;
         const bool hv = hh < nh;
@@ -805,12 +846,13 @@ tq_split_kernel(const TqDecodeParams p) {
 }
 
 template <int D>
-constexpr int tq_split_smem_bytes(int kb, int vb) {
+constexpr int tq_split_smem_bytes(int kb, int vb, bool k8m = false) {
     const int mse = D * kb / 8, vdb = tq_value_bytes(D, vb);
     const int tile = kTqTileTokens * (tq_row_stride(mse, mse / kOctet) + tq_row_stride(vdb, vdb / kOctet));
     const int merge = 4 * AttnCfg<D>::GH * (D + 2) * 4;
     const int buf = ((tile > merge ? tile : merge) + 15) / 16 * 16;
-    return buf + 3 * kTqTileTokens * 4 + kTqTileTokens * 8 + AttnCfg<D>::GH * D * 4 + kMaxLevels * 4;
+    return buf + 3 * kTqTileTokens * 4 + kTqTileTokens * 8 + AttnCfg<D>::GH * D * 4 +
+           (k8m ? 256 : kMaxLevels) * 4;
 }
 
 struct TqMergeParams {

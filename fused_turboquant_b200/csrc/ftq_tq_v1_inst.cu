@@ -23,63 +23,68 @@
 namespace ftq {
 
 #ifdef FTQ_TQ_STORE
-template <int KB, int VB, typename T>
-static cudaError_t store_run(const TqStoreParams& p, int value_mode, int64_t n_vec, cudaStream_t stream) {
+template <int KB, int VB, typename T, bool K8M>
+static cudaError_t store_run(const TqStoreParams& p, int value_mode, int64_t n_vec,
+                             const TqTable<K8M>& t8, cudaStream_t stream) {
     const int64_t want = (n_vec + 31) / 32;  // 8 warps x 4 vectors per CTA pass
     const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     const unsigned gx = static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
     const bool rotate_v = (value_mode & kTqRotateValues) != 0;
     if constexpr (VB == 4 && KB != 8) {
         if (value_mode & kTqLloydMaxValues) {
-            if (rotate_v) tq_store_kernel<FTQ_D, KB, VB, T, true, true><<<gx, 256, 0, stream>>>(p, n_vec);
-            else tq_store_kernel<FTQ_D, KB, VB, T, false, true><<<gx, 256, 0, stream>>>(p, n_vec);
+            if (rotate_v) tq_store_kernel<FTQ_D, KB, VB, T, true, true><<<gx, 256, 0, stream>>>(p, n_vec, t8);
+            else tq_store_kernel<FTQ_D, KB, VB, T, false, true><<<gx, 256, 0, stream>>>(p, n_vec, t8);
             return cudaGetLastError();
         }
     }
     if constexpr (VB != 8) {
         if (rotate_v) {
-            tq_store_kernel<FTQ_D, KB, VB, T, true><<<gx, 256, 0, stream>>>(p, n_vec);
+            tq_store_kernel<FTQ_D, KB, VB, T, true, false, K8M><<<gx, 256, 0, stream>>>(p, n_vec, t8);
             return cudaGetLastError();
         }
     } else if (rotate_v) {
         return cudaErrorInvalidValue;  // 8-bit values are rotated by the caller
     }
-    tq_store_kernel<FTQ_D, KB, VB, T, false><<<gx, 256, 0, stream>>>(p, n_vec);
+    tq_store_kernel<FTQ_D, KB, VB, T, false, false, K8M><<<gx, 256, 0, stream>>>(p, n_vec, t8);
     return cudaGetLastError();
 }
 
-template <int KB, int VB>
+template <int KB, int VB, bool K8M>
 static cudaError_t store_by_dtype(int dtype, const TqStoreParams& p, int vmode, int64_t n_vec,
-                                  cudaStream_t s) {
+                                  const TqTable<K8M>& t8, cudaStream_t s) {
     switch (dtype) {
-        case kF32: return store_run<KB, VB, float>(p, vmode, n_vec, s);
-        case kF16: return store_run<KB, VB, __half>(p, vmode, n_vec, s);
-        case kBF16: return store_run<KB, VB, __nv_bfloat16>(p, vmode, n_vec, s);
+        case kF32: return store_run<KB, VB, float, K8M>(p, vmode, n_vec, t8, s);
+        case kF16: return store_run<KB, VB, __half, K8M>(p, vmode, n_vec, t8, s);
+        case kBF16: return store_run<KB, VB, __nv_bfloat16, K8M>(p, vmode, n_vec, t8, s);
     }
     return cudaErrorInvalidValue;
 }
 
-template <int KB>
+template <int KB, bool K8M = false>
 static cudaError_t store_by_vb(int vb, int dtype, const TqStoreParams& p, int vmode, int64_t n_vec,
-                               cudaStream_t s) {
+                               const TqTable<K8M>& t8, cudaStream_t s) {
     switch (vb) {
-        case 1: return store_by_dtype<KB, 1>(dtype, p, vmode, n_vec, s);
-        case 2: return store_by_dtype<KB, 2>(dtype, p, vmode, n_vec, s);
-        case 3: return store_by_dtype<KB, 3>(dtype, p, vmode, n_vec, s);
-        case 4: return store_by_dtype<KB, 4>(dtype, p, vmode, n_vec, s);
-        case 8: return store_by_dtype<KB, 8>(dtype, p, vmode, n_vec, s);
+        case 1: return store_by_dtype<KB, 1, K8M>(dtype, p, vmode, n_vec, t8, s);
+        case 2: return store_by_dtype<KB, 2, K8M>(dtype, p, vmode, n_vec, t8, s);
+        case 3: return store_by_dtype<KB, 3, K8M>(dtype, p, vmode, n_vec, t8, s);
+        case 4: return store_by_dtype<KB, 4, K8M>(dtype, p, vmode, n_vec, t8, s);
+        case 8: return store_by_dtype<KB, 8, K8M>(dtype, p, vmode, n_vec, t8, s);
     }
     return cudaErrorInvalidValue;
 }
 
 cudaError_t FTQ_CAT(launch_tq_store_d, FTQ_D)(int kb, int vb, int dtype, const TqStoreParams& p,
-                                             int value_mode, int64_t n_vec, cudaStream_t stream) {
+                                             int value_mode, int64_t n_vec, const TqTable256* mid8,
+                                             cudaStream_t stream) {
+    const TqNoTable none{};
     switch (kb) {
-        case 1: return store_by_vb<1>(vb, dtype, p, value_mode, n_vec, stream);
-        case 2: return store_by_vb<2>(vb, dtype, p, value_mode, n_vec, stream);
-        case 3: return store_by_vb<3>(vb, dtype, p, value_mode, n_vec, stream);
-        case 4: return store_by_vb<4>(vb, dtype, p, value_mode, n_vec, stream);
-        case 8: return store_by_vb<8>(vb, dtype, p, value_mode, n_vec, stream);  // FP8 keys
+        case 1: return store_by_vb<1>(vb, dtype, p, value_mode, n_vec, none, stream);
+        case 2: return store_by_vb<2>(vb, dtype, p, value_mode, n_vec, none, stream);
+        case 3: return store_by_vb<3>(vb, dtype, p, value_mode, n_vec, none, stream);
+        case 4: return store_by_vb<4>(vb, dtype, p, value_mode, n_vec, none, stream);
+        case 8:   // 8-bit Lloyd-Max codes with a table, FP8 keys without
+            return mid8 ? store_by_vb<8, true>(vb, dtype, p, value_mode, n_vec, *mid8, stream)
+                        : store_by_vb<8>(vb, dtype, p, value_mode, n_vec, none, stream);
     }
     return cudaErrorInvalidValue;
 }
@@ -87,35 +92,39 @@ cudaError_t FTQ_CAT(launch_tq_store_d, FTQ_D)(int kb, int vb, int dtype, const T
 #endif  // FTQ_TQ_STORE
 
 #ifdef FTQ_TQ_DECODE
-template <int KB, int VB>
-static cudaError_t split_run(const TqDecodeParams& p, cudaStream_t stream) {
-    constexpr int smem = tq_split_smem_bytes<FTQ_D>(KB, VB);
+template <int KB, int VB, bool K8M>
+static cudaError_t split_run(const TqDecodeParams& p, const TqTable<K8M>& t8, cudaStream_t stream) {
+    constexpr int smem = tq_split_smem_bytes<FTQ_D>(KB, VB, K8M);
     static_assert(smem <= 48 * 1024, "tile does not fit the default shared-memory carve-out");
     const dim3 grid(p.splits, p.Hkv * p.n_hpass, p.B);
-    tq_split_kernel<FTQ_D, KB, VB><<<grid, kAttnThreads, smem, stream>>>(p);
+    tq_split_kernel<FTQ_D, KB, VB, K8M><<<grid, kAttnThreads, smem, stream>>>(p, t8);
     return cudaGetLastError();
 }
 
-template <int KB>
-static cudaError_t split_by_vb(int vb, const TqDecodeParams& p, cudaStream_t s) {
+template <int KB, bool K8M = false>
+static cudaError_t split_by_vb(int vb, const TqDecodeParams& p, const TqTable<K8M>& t8,
+                               cudaStream_t s) {
     switch (vb) {
-        case 1: return split_run<KB, 1>(p, s);
-        case 2: return split_run<KB, 2>(p, s);
-        case 3: return split_run<KB, 3>(p, s);
-        case 4: return split_run<KB, 4>(p, s);
-        case 8: return split_run<KB, 8>(p, s);
+        case 1: return split_run<KB, 1, K8M>(p, t8, s);
+        case 2: return split_run<KB, 2, K8M>(p, t8, s);
+        case 3: return split_run<KB, 3, K8M>(p, t8, s);
+        case 4: return split_run<KB, 4, K8M>(p, t8, s);
+        case 8: return split_run<KB, 8, K8M>(p, t8, s);
     }
     return cudaErrorInvalidValue;
 }
 
 cudaError_t FTQ_CAT(launch_tq_split_d, FTQ_D)(int kb, int vb, const TqDecodeParams& p,
-                                             cudaStream_t stream) {
+                                             const TqTable256* cent8, cudaStream_t stream) {
+    const TqNoTable none{};
     switch (kb) {
-        case 1: return split_by_vb<1>(vb, p, stream);
-        case 2: return split_by_vb<2>(vb, p, stream);
-        case 3: return split_by_vb<3>(vb, p, stream);
-        case 4: return split_by_vb<4>(vb, p, stream);
-        case 8: return split_by_vb<8>(vb, p, stream);  // FP8 keys
+        case 1: return split_by_vb<1>(vb, p, none, stream);
+        case 2: return split_by_vb<2>(vb, p, none, stream);
+        case 3: return split_by_vb<3>(vb, p, none, stream);
+        case 4: return split_by_vb<4>(vb, p, none, stream);
+        case 8:   // 8-bit Lloyd-Max codes with a table, FP8 keys without
+            return cent8 ? split_by_vb<8, true>(vb, p, *cent8, stream)
+                         : split_by_vb<8>(vb, p, none, stream);
     }
     return cudaErrorInvalidValue;
 }

@@ -7,14 +7,17 @@
 
 namespace ftq {
 
+// kb = 8 with a table (mid8 / cent8 not NULL) = 8-bit Lloyd-Max key codes, without = FP8 keys.
 // value_mode of the store launchers
 constexpr int kTqRotateValues = 1;    // Hadamard-transform the values in the kernel
 constexpr int kTqLloydMaxValues = 2;  // 4-bit values: Lloyd-Max codes against the key midpoints
 
 #define FTQ_DECLARE_TQ_LAUNCHERS(DD)                                                              \
     cudaError_t launch_tq_store_d##DD(int kb, int vb, int dtype, const TqStoreParams& p,          \
-                                      int value_mode, int64_t n_vec, cudaStream_t stream);        \
-    cudaError_t launch_tq_split_d##DD(int kb, int vb, const TqDecodeParams& p, cudaStream_t stream); \
+                                      int value_mode, int64_t n_vec, const TqTable256* mid8,      \
+                                      cudaStream_t stream);                                       \
+    cudaError_t launch_tq_split_d##DD(int kb, int vb, const TqDecodeParams& p,                    \
+                                      const TqTable256* cent8, cudaStream_t stream);              \
     cudaError_t launch_tq_mma_d##DD(int kb, int vb, int nh, const TqDecodeParams& p, int n_items,   \
                                     cudaStream_t stream);                                         \
     cudaError_t launch_tq_merge_d##DD(int out_dtype, const TqMergeParams& p, cudaStream_t stream);

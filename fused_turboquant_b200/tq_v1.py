@@ -28,15 +28,18 @@ from .kernels import _DT, _host_table, _ptr, _require_cuda, _stream, rht
 class TurboQuantSlotConfig:
     """Slot layout of one (token, KV head): key codes | key norm f16 | value codes | scale f16 | zero f16.
 
-    ``key_quant_bits == 8`` selects FP8 (e4m3) keys as vLLM's stock ``TurboQuantConfig`` does: the
-    key field is ``head_dim`` bytes with no norm behind it.  (The reference's 8-bit Lloyd-Max keys,
-    ``BoundaryTurboQuantConfig(key_use_fp8_at_8bit=False)``, are not supported.)
+    ``key_quant_bits == 8`` selects FP8 (e4m3) keys as vLLM's stock ``TurboQuantConfig`` does (the
+    key field is ``head_dim`` bytes with no norm behind it) unless ``key_use_fp8_at_8bit`` is
+    False: then the 8 bits are Lloyd-Max codes of a 256-entry table, one byte per coordinate plus
+    the fp16 norm, as the reference's boundary layers store them
+    (``BoundaryTurboQuantConfig(key_use_fp8_at_8bit=False)``, vllm_plugin/boundary_tq_config.py:26-35).
     """
 
     head_dim: int
-    key_quant_bits: int       # 1..4: Lloyd-Max codes; 8: FP8 keys
+    key_quant_bits: int       # 1..4: Lloyd-Max codes; 8: FP8 keys or 8-bit Lloyd-Max codes
     value_quant_bits: int     # 1, 2, 3, 4 or 8: per-vector uniform codes
     norm_correction: bool = True
+    key_use_fp8_at_8bit: bool = True
 
     def __post_init__(self):
         if self.head_dim not in (64, 128, 256):
@@ -48,7 +51,7 @@ class TurboQuantSlotConfig:
 
     @property
     def key_fp8(self) -> bool:
-        return self.key_quant_bits == 8
+        return self.key_quant_bits == 8 and self.key_use_fp8_at_8bit
 
     @property
     def key_mse_bits(self) -> int:
@@ -98,11 +101,15 @@ def midpoints_of(centroids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return c, (c[:-1] + c[1:]) / 2
 
 
+KEY_BITS_MSE8 = 264   # FTQ_TQ_KEY_BITS_MSE8 of the C ABI: 8-bit Lloyd-Max key codes
+
+
 def _key_bits(tq_config) -> int:
-    """key_quant_bits of a (possibly duck-typed) config; 8 must mean FP8 keys."""
+    """The C ABI's key_bits of a (possibly duck-typed) config: 8 bits that are not FP8 are 8-bit
+    Lloyd-Max codes."""
     kb = int(tq_config.key_quant_bits)
     if kb == 8 and not getattr(tq_config, "key_fp8", True):
-        raise ValueError("8-bit Lloyd-Max key codes are not supported (8 key bits = FP8 keys)")
+        return KEY_BITS_MSE8
     return kb
 
 

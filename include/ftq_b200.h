@@ -287,9 +287,14 @@ int ftq_v0_gather(const uint8_t *kv_cache, int64_t num_blocks, int block_size, i
  * triton_inkernel_store.py:80-91): the key field is then D bytes of e4m3 (rotated key * norm,
  * round to nearest even, saturating) with NO norm field, and midpoints_host / centroids_host
  * may be NULL; value_bits 1/2/3/4/8 (per-vector uniform codes; 4-bit values optionally
- * Lloyd-Max codes).  The reference's 8-bit Lloyd-Max key codes (256 centroids, boundary
- * layers only) are not available.
+ * Lloyd-Max codes).  key_bits = FTQ_TQ_KEY_BITS_MSE8 selects the reference's 8-bit
+ * Lloyd-Max key codes (256 centroids, its boundary layers: BoundaryTurboQuantConfig with
+ * key_use_fp8_at_8bit = False, vllm_plugin/boundary_tq_config.py:26-35; store branch
+ * triton_inkernel_store.py:132-137): the key field is D code bytes + the fp16 norm,
+ * midpoints_host holds 255 and centroids_host 256 ascending entries; such caches are decoded
+ * by the fp32 kernel, and Lloyd-Max value codes are not available with them.
  */
+#define FTQ_TQ_KEY_BITS_MSE8 264
 int ftq_tq_slot_bytes(int head_dim, int key_bits, int value_bits);
 
 /*

@@ -539,7 +539,11 @@ void ftq_oracle_tq_store(const float *key, const float *value, int64_t n_tokens,
                          int64_t stride_block, int64_t stride_pos, int64_t stride_head,
                          int block_size, const int64_t *slot_mapping, float *y_out,
                          int value_lloyd_max, int value_sum_order) {
-    const int key_fp8 = key_bits == 8; /* FP8 keys: d bytes of e4m3(y * norm), no norm field */
+    /* key_bits 264 = 8-bit Lloyd-Max codes (256 centroids, one byte per coordinate + norm:
+     * triton_inkernel_store.py:132-137, boundary_tq_config.py:26-35); 8 = FP8 keys */
+    const int key_mse8 = key_bits == 264;
+    if (key_mse8) key_bits = 8;
+    const int key_fp8 = key_bits == 8 && !key_mse8; /* d bytes of e4m3(y * norm), no norm field */
     const int n_cent = key_fp8 ? 1 : 1 << key_bits;
     const int mse_bytes = d * key_bits / 8;
     const int kps = mse_bytes + (key_fp8 ? 0 : 2);
@@ -639,7 +643,9 @@ void ftq_oracle_tq_decode(const float *q, int B, int Hq, int Hkv, int d, const u
                           float *out, float *lse, int value_lloyd_max) {
     const int v_lm = value_lloyd_max && value_bits == 4; /* triton_decode_offset.py:399-423 */
     const int group = Hq / Hkv;
-    const int key_fp8 = key_bits == 8; /* triton_decode_offset.py:175-194 */
+    const int key_mse8 = key_bits == 264; /* 8-bit Lloyd-Max codes: the generic MSE branch */
+    if (key_mse8) key_bits = 8;
+    const int key_fp8 = key_bits == 8 && !key_mse8; /* triton_decode_offset.py:175-194 */
     const int mse_bytes = d * key_bits / 8;
     const int kps = mse_bytes + (key_fp8 ? 0 : 2);
     const int vdb = value_bits == 8 ? d : d * value_bits / 8;

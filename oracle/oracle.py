@@ -207,9 +207,10 @@ def v0_gather(kv_cache: np.ndarray, kv_type: int, pd: int, block_tables, seq_len
 # ---------------------------------------------------------------- vLLM-v1 slot format
 
 def tq_slot_bytes(d: int, key_bits: int, value_bits: int) -> int:
-    """key codes + fp16 norm (key_bits 8 = FP8 keys: d bytes, no norm) + value codes + fp16 scale
-    + fp16 zero, rounded up to even."""
-    s = (d if key_bits == 8 else d * key_bits // 8 + 2) + (d if value_bits == 8 else d * value_bits // 8) + 4
+    """key codes + fp16 norm (key_bits 8 = FP8 keys: d bytes, no norm; 264 = 8-bit Lloyd-Max codes:
+    d bytes + norm) + value codes + fp16 scale + fp16 zero, rounded up to even."""
+    kbytes = d if key_bits == 8 else (d + 2 if key_bits == 264 else d * key_bits // 8 + 2)
+    s = kbytes + (d if value_bits == 8 else d * value_bits // 8) + 4
     return s + s % 2
 
 

@@ -55,11 +55,24 @@ CASES = [
     ("d256_k8v3", 256, 1, 2, 8, 3, 0, (19, 8), (0, 0), 2, 8),
 ]
 
+# `--set k8mse` (written to tq_v1_k8mse.npz, own seed): key bits 8 = 8-bit Lloyd-Max codes, 256
+# centroids, one byte per coordinate + the fp16 norm (BoundaryTurboQuantConfig with
+# key_use_fp8_at_8bit = False, vllm_plugin/boundary_tq_config.py:26-35; store branch
+# triton_inkernel_store.py:132-137)
+CASES_K8MSE = [
+    ("d128_k8mse_v4_nc", 128, 2, 4, 8, 4, 1, (45, 18), (0, 0), 3, 16),
+    ("d64_k8mse_v3", 64, 2, 2, 8, 3, 0, (27, 11), (0, 3), 2, 16),
+    ("d256_k8mse_v2_nc", 256, 1, 2, 8, 2, 1, (19, 8), (0, 0), 2, 8),
+]
+
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference repository")
+    ap.add_argument("--set", default="main", choices=["main", "k8mse"],
+                    help="main: tq_v1.npz; k8mse: the 8-bit Lloyd-Max key cases, tq_v1_k8mse.npz")
     args = ap.parse_args()
+    k8mse = args.set == "k8mse"
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from vllm.model_executor.layers.quantization.turboquant.centroids import get_centroids
     from vllm.v1.attention.ops.triton_decode_attention import _fwd_kernel_stage2
@@ -74,11 +87,11 @@ def main() -> None:
     store_mod._use_fp8_e4b15 = lambda device: False
 
     torch.set_num_threads(1)
-    gen = torch.Generator("cpu").manual_seed(20251)
+    gen = torch.Generator("cpu").manual_seed(20252 if k8mse else 20251)
     out = {}
-    for name, D, Hkv, G, kb, vb, nc, seq_lens, kv_start, splits, bs in CASES:
+    for name, D, Hkv, G, kb, vb, nc, seq_lens, kv_start, splits, bs in (CASES_K8MSE if k8mse else CASES):
         cfg = BoundaryTurboQuantConfig(head_dim=D, key_quant_bits=kb, value_quant_bits=vb,
-                                       norm_correction=bool(nc), key_use_fp8_at_8bit=True)
+                                       norm_correction=bool(nc), key_use_fp8_at_8bit=not k8mse)
         slot = cfg.key_packed_size + cfg.value_data_bytes + 4
         slot += slot % 2
         B, Hq = len(seq_lens), Hkv * G
@@ -160,7 +173,7 @@ def main() -> None:
         out[f"{name}_meta"] = np.array([D, Hkv, G, kb, vb, nc, splits, bs, slot, nb], np.int32)
         print(name, "slot", slot, flush=True)
 
-    path = os.path.join(HERE, "tq_v1.npz")
+    path = os.path.join(HERE, "tq_v1_k8mse.npz" if k8mse else "tq_v1.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path))
 

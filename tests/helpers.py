@@ -103,7 +103,10 @@ def tq_v1_compare_cache(cache, ref, slot_mapping, y, midpoints, d, key_bits, val
     `key_fp8_vs_rne` counts bytes of `cache` that differ from torch's round-to-nearest-even cast
     of `y` although `y` is farther than 1e-6 (relative) from the tie between the two candidates.
     """
-    key_fp8 = key_bits == 8
+    key_mse8 = key_bits == 264          # 8-bit Lloyd-Max codes: one byte per coordinate + norm
+    if key_mse8:
+        key_bits = 8
+    key_fp8 = key_bits == 8 and not key_mse8
     mse = d * key_bits // 8
     kps = mse + (0 if key_fp8 else 2)
     vdb = d if value_bits == 8 else d * value_bits // 8

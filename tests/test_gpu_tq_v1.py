@@ -23,6 +23,10 @@ CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8",
          "d128_k1v1_nc", "d64_k1v3", "d256_k3v1_nc",
          "d128_k4v4_nc_vlm", "d64_k4v4_vlm", "d128_k3v4_nc_vlm",   # _vlm: Lloyd-Max value codes
          "d128_k8v4", "d64_k8v2", "d256_k8v3"]                     # k8: FP8 (e4m3) keys
+# 8-bit Lloyd-Max key codes (tq_v1_k8mse.npz; the reference's boundary layers): the fixtures' meta
+# says 8 key bits like the FP8 cases; the oracle / helpers tell the two apart by key bits = 264,
+# the host mirror by key_use_fp8_at_8bit
+K8MSE = ["d128_k8mse_v4_nc", "d64_k8mse_v3", "d256_k8mse_v2_nc"]
 cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
@@ -30,12 +34,23 @@ def _meta(g, name):
     return (int(v) for v in g[f"{name}_meta"])
 
 
-@pytest.mark.parametrize("name", CASES)
+def _case(golden, name):
+    """(fixtures, meta with the oracle's key bits, host-mirror config) of a store / decode case."""
+    from fused_turboquant_b200 import tq_v1
+    mse8 = name in K8MSE
+    g = golden("tq_v1_k8mse.npz" if mse8 else "tq_v1.npz")
+    meta = [int(v) for v in g[f"{name}_meta"]]
+    cfg = tq_v1.TurboQuantSlotConfig(meta[0], meta[3], meta[4], bool(meta[5]),
+                                     key_use_fp8_at_8bit=not mse8)
+    if mse8:
+        meta[3] = 264
+    return g, meta, cfg
+
+
+@pytest.mark.parametrize("name", CASES + K8MSE)
 def test_store_vs_reference_kernel_and_oracle(oracle, golden, name):
     from fused_turboquant_b200 import tq_v1
-    g = golden("tq_v1.npz")
-    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = _meta(g, name)
-    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
+    g, (D, Hkv, G, kb, vb, nc, splits, bs, slot, nb), cfg = _case(golden, name)
     assert cfg.slot_size_aligned == slot
     cache = torch.zeros((nb, bs, Hkv, slot), dtype=torch.uint8, device="cuda")
     vlm = name.endswith("_vlm")    # (the fixture's V is already rotated for these cases)
@@ -55,12 +70,10 @@ def test_store_vs_reference_kernel_and_oracle(oracle, golden, name):
     np.testing.assert_array_equal(got, ref)
 
 
-@pytest.mark.parametrize("name", CASES)
+@pytest.mark.parametrize("name", CASES + K8MSE)
 def test_decode_vs_reference_kernels(oracle, golden, name):
     from fused_turboquant_b200 import tq_v1
-    g = golden("tq_v1.npz")
-    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = _meta(g, name)
-    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, bool(nc))
+    g, (D, Hkv, G, kb, vb, nc, splits, bs, slot, nb), cfg = _case(golden, name)
     B, Hq = g[f"{name}_q"].shape[:2]
     mid_o = torch.empty((B, Hq, splits, D + 1), dtype=torch.float32, device="cuda")
     lse = torch.empty((B, Hq), dtype=torch.float32, device="cuda")

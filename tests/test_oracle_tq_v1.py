@@ -12,10 +12,22 @@ CASES = ["d128_k4v4", "d128_k3v4_nc", "d64_k3v3_g7", "d256_k4v2", "d128_k2v8",
          "d128_k8v4", "d64_k8v2", "d256_k8v3"]                     # k8: FP8 (e4m3) keys
 
 
-@pytest.mark.parametrize("name", CASES)
+# 8-bit Lloyd-Max key codes (tq_v1_k8mse.npz): the fixtures' meta says 8 key bits like the FP8
+# cases; the oracle and the C ABI tell the two apart by key_bits = 264
+K8MSE = ["d128_k8mse_v4_nc", "d64_k8mse_v3", "d256_k8mse_v2_nc"]
+
+
+def _case(golden, name):
+    g = golden("tq_v1_k8mse.npz" if name in K8MSE else "tq_v1.npz")
+    meta = [int(v) for v in g[f"{name}_meta"]]
+    if name in K8MSE:
+        meta[3] = 264
+    return g, meta
+
+
+@pytest.mark.parametrize("name", CASES + K8MSE)
 def test_store_matches_reference_store_kernel(oracle, golden, name):
-    g = golden("tq_v1.npz")
-    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = (int(v) for v in g[f"{name}_meta"])
+    g, (D, Hkv, G, kb, vb, nc, splits, bs, slot, nb) = _case(golden, name)
     assert slot == oracle.tq_slot_bytes(D, kb, vb)
     cache = np.zeros((nb, bs, Hkv, slot), np.uint8)
     vlm = name.endswith("_vlm")
@@ -40,10 +52,9 @@ def test_store_matches_reference_store_kernel(oracle, golden, name):
     np.testing.assert_allclose(y[sm >= 0], g[f"{name}_y"][sm >= 0], atol=2e-6)
 
 
-@pytest.mark.parametrize("name", CASES)
+@pytest.mark.parametrize("name", CASES + K8MSE)
 def test_decode_matches_reference_decode_kernels(oracle, golden, name):
-    g = golden("tq_v1.npz")
-    D, Hkv, G, kb, vb, nc, splits, bs, slot, nb = (int(v) for v in g[f"{name}_meta"])
+    g, (D, Hkv, G, kb, vb, nc, splits, bs, slot, nb) = _case(golden, name)
     out, mid_o, lse = oracle.tq_decode(g[f"{name}_q"], g[f"{name}_cache"], g[f"{name}_block_table"],
                                        g[f"{name}_seq_lens"], g[f"{name}_centroids"], kb, vb,
                                        D ** -0.5, splits, norm_correction=bool(nc),

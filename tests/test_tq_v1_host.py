@@ -35,13 +35,22 @@ def test_config_rejects_what_the_kernels_do_not_cover():
             tq_v1.TurboQuantSlotConfig(*bad)
 
 
-def test_eight_bit_lloyd_max_keys_are_refused():
-    """A duck-typed reference config with 8 key bits that are NOT FP8 must not be taken for FP8."""
+def test_eight_bit_lloyd_max_keys_are_not_taken_for_fp8(golden):
+    """8 key bits that are NOT FP8 (the reference's boundary layers) are 8-bit Lloyd-Max codes:
+    another key_bits value at the C ABI, another slot size."""
     class Cfg:
         head_dim, key_quant_bits, value_quant_bits, norm_correction, key_fp8 = 128, 8, 4, True, False
-    with pytest.raises(ValueError):
-        tq_v1._key_bits(Cfg())
+    assert tq_v1._key_bits(Cfg()) == tq_v1.KEY_BITS_MSE8
     assert tq_v1._key_bits(tq_v1.TurboQuantSlotConfig(128, 8, 4)) == 8
+    cfg = tq_v1.TurboQuantSlotConfig(128, 8, 4, key_use_fp8_at_8bit=False)
+    assert tq_v1._key_bits(cfg) == tq_v1.KEY_BITS_MSE8
+    assert not cfg.key_fp8 and cfg.key_mse_bits == 8 and cfg.n_centroids == 256
+    assert cfg.key_packed_size == 130
+    g = golden("tq_v1_k8mse.npz")
+    for name, d, vb in (("d128_k8mse_v4_nc", 128, 4), ("d64_k8mse_v3", 64, 3), ("d256_k8mse_v2_nc", 256, 2)):
+        c = tq_v1.TurboQuantSlotConfig(d, 8, vb, key_use_fp8_at_8bit=False)
+        assert int(g[f"{name}_meta"][8]) == c.slot_size_aligned
+        assert g[f"{name}_centroids"].shape == (256,) and g[f"{name}_midpoints"].shape == (255,)
 
 
 def test_midpoints_follow_the_reference_recipe(golden):
