@@ -118,10 +118,9 @@ __device__ __forceinline__ uint32_t octet_transpose_items(uint32_t w, const Tran
 // arithmetic so that the store at the end does not wait for it.
 __device__ __forceinline__ int64_t load_slot(const EncodeSink& sink, int64_t v, bool valid) {
     if (sink.mode == kSinkFlat || !valid) return -1;
-    const int64_t slot = sink.slot_mapping[fast_div(static_cast<uint32_t>(v), sink.div_hkv)];
-    // negative = padding (the reference's `slot < 0` skip, triton_inkernel_store.py:398-399);
-    // a slot outside the cache is dropped the same way instead of being written out of bounds
-    return slot < sink.slot_limit ? slot : -1;
+    // (the value is not looked at before emit_vector: a compare here would make the warp wait for
+    // the load before the arithmetic instead of after it)
+    return sink.slot_mapping[fast_div(static_cast<uint32_t>(v), sink.div_hkv)];
 }
 
 // Store one encoded vector: `w` holds this lane's codes (coordinates l + 8k) packed as
@@ -144,7 +143,10 @@ __device__ __forceinline__ void emit_vector(const uint32_t (&w)[NW], float norm,
     } else if (valid) {
         const uint32_t token = fast_div(static_cast<uint32_t>(v), sink.div_hkv);
         const int head = static_cast<int>(static_cast<uint32_t>(v) - token * sink.Hkv);
-        if (slot < 0) {
+        // negative = padding (the reference's `slot < 0` skip, triton_inkernel_store.py:398-399);
+        // a slot at or beyond the cache's end is dropped the same way instead of being written
+        // out of bounds (one unsigned compare covers both)
+        if (static_cast<uint64_t>(slot) >= static_cast<uint64_t>(sink.slot_limit)) {
             store = false;
         } else if (sink.mode == kSinkPaged) {
             // slot >= 0 here; pages per layer and bytes per page both fit 32 bits
