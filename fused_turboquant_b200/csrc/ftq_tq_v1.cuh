@@ -191,22 +191,9 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec, const TqTable<K8M> t8) {
         const bool valid = v < n_vec;
         const uint32_t token = valid ? fast_div(static_cast<uint32_t>(v), p.div_hkv) : 0u;
         const int head = valid ? static_cast<int>(static_cast<uint32_t>(v) - token * p.Hkv) : 0;
+        // (requested here, looked at only after the key's arithmetic: the warp does not wait for it)
         const int64_t slot = valid ? p.slot_mapping[token] : -1;
-        const bool store = valid && slot >= 0;
         const int64_t row_off = static_cast<int64_t>(token) * p.token_stride + head * p.head_stride;
-        uint8_t* dst = nullptr;
-        if (store) {
-            int64_t blk, off;
-            if (slot < (1ll << 31)) {
-                const uint32_t b32 = fast_div(static_cast<uint32_t>(slot), p.div_block);
-                blk = b32;
-                off = static_cast<uint32_t>(slot) - b32 * p.block_size;
-            } else {
-                blk = slot / p.block_size;
-                off = slot - blk * p.block_size;
-            }
-            dst = p.kv_cache + blk * p.stride_block + off * p.stride_pos + head * p.stride_head;
-        }
 
         // ---- key: raw norm, normalise, butterfly, midpoint search
         float y[E];
@@ -233,6 +220,21 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec, const TqTable<K8M> t8) {
 #pragma unroll
         for (int r = 0; r < E; r++) y[r] = __fdiv_rn(y[r], den);
         octet_fwht<E>(y, lane);  // -> (lane l, register k) = coordinate l + 8k
+
+        const bool store = valid && slot >= 0;
+        uint8_t* dst = nullptr;
+        if (store) {
+            int64_t blk, off;
+            if (slot < (1ll << 31)) {
+                const uint32_t b32 = fast_div(static_cast<uint32_t>(slot), p.div_block);
+                blk = b32;
+                off = static_cast<uint32_t>(slot) - b32 * p.block_size;
+            } else {
+                blk = slot / p.block_size;
+                off = slot - blk * p.block_size;
+            }
+            dst = p.kv_cache + blk * p.stride_block + off * p.stride_pos + head * p.stride_head;
+        }
 
         if constexpr (KBYTE) {
             // lane l holds the coordinates l + 8k: neighbouring lanes trade bytes so that each
