@@ -68,7 +68,7 @@ struct StreamCfg {
 #ifdef FTQ_SERVICE_SKIP
     static constexpr int SKIP = FTQ_SERVICE_SKIP;
 #else
-    static constexpr int SKIP = 8;
+    static constexpr int SKIP = 7;
 #endif
     // service warps: 2 = warp 0 folds and finishes units, warp 1 prepares; 1 = warp 0 does both
 #ifdef FTQ_SERVICE_WARPS
@@ -546,6 +546,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     constexpr int WC = S::SKIP > 0 ? WARPS - NSVC : WARPS;
     constexpr int THR = S::SKIP > 0 ? WC * (S::SKIP - 1) : 0;
     const int g_first = S::SKIP > 0 ? (warp < NSVC ? WC * S::SKIP + warp : warp - NSVC) : warp;
+    const uint64_t page_policy = l2_evict_first_policy();
     int g_next = g_first;                                   // next page of item gseq for this warp
     int g_lim = g_end ? 0 : ctl[kCtlPages + 0];             // its page count (0: nothing to take)
     // request the next page of the stream into ring buffer rb; returns its index within item
@@ -582,7 +583,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             const uint8_t* page = reinterpret_cast<const uint8_t*>(base) +
                 static_cast<uint64_t>(static_cast<uint32_t>(sblk[buf * kStreamMaxChunkPages + pg])) * blk_stride;
             mbar_expect_tx(my_bars + rb * 8, PAGE_BYTES);
-            bulk_g2s(my_ring + rb * PAGE_BYTES, page, PAGE_BYTES, my_bars + rb * 8);
+            bulk_g2s_hint(my_ring + rb * PAGE_BYTES, page, PAGE_BYTES, my_bars + rb * 8, page_policy);
         }
         return pg;
     };
