@@ -624,11 +624,11 @@ tq_split_kernel(const TqDecodeParams p, const TqTable<K8M> t8) {
                 uint32_t v = 0u;
                 if (live && b0 < hi) {
                     if (b0 < lo)
-                        v = static_cast<uint32_t>(__ldg(reinterpret_cast<const uint16_t*>(al + b0 + 2))) << 16;
+                        v = static_cast<uint32_t>(__ldcs(reinterpret_cast<const uint16_t*>(al + b0 + 2))) << 16;
                     else if (b0 + 4 > hi)
-                        v = __ldg(reinterpret_cast<const uint16_t*>(al + b0));
+                        v = __ldcs(reinterpret_cast<const uint16_t*>(al + b0));
                     else
-                        v = __ldg(reinterpret_cast<const uint32_t*>(al + b0));
+                        v = __ldcs(reinterpret_cast<const uint32_t*>(al + b0));
                 }
                 raw[i] = v;
             }
@@ -663,7 +663,7 @@ tq_split_kernel(const TqDecodeParams p, const TqTable<K8M> t8) {
                     const int idx = base + u * kAttnThreads;
                     const int tk = idx / SLOT_U16, j = idx - tk * SLOT_U16;
                     v[u] = idx < ntile * SLOT_U16
-                               ? __ldg(reinterpret_cast<const uint16_t*>(slots[tk]) + j) : uint16_t(0);
+                               ? __ldcs(reinterpret_cast<const uint16_t*>(slots[tk]) + j) : uint16_t(0);
                 }
 #pragma unroll
                 for (int u = 0; u < 8; u++) {

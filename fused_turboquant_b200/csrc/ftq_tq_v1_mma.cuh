@@ -299,10 +299,11 @@ tq_mma_kernel(const TqDecodeParams p, int n_items) {
                     unsigned long long entry;
                     asm volatile("ld.shared.b64 %0, [%1];\n" : "=l"(entry) : "r"(my_page + C::OFF_AL + 8 * tok));
                     const uint8_t* al = reinterpret_cast<const uint8_t*>(entry & ~3ull);
+                    // (streaming loads: a slot is read once per decode step)
                     if (w == NWR - 1 && !(entry & 1ull))
-                        v = __ldg(reinterpret_cast<const uint16_t*>(al + 4 * w));
+                        v = __ldcs(reinterpret_cast<const uint16_t*>(al + 4 * w));
                     else
-                        v = __ldg(reinterpret_cast<const uint32_t*>(al + 4 * w));
+                        v = __ldcs(reinterpret_cast<const uint32_t*>(al + 4 * w));
                 }
                 raw[i] = v;
             }
