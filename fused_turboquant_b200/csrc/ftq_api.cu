@@ -265,12 +265,52 @@ float choose_k_scale(const float* levels, int bits, int head_dim) {
 
 struct ChunkPlan {
     int chunk_tokens, n_chunks, n_hpass;
-    // streaming kernel only: units from bulk_units on are cut into tail_chunks chunks of
-    // tail_chunk_tokens instead (bulk_units < 0: one split for all units)
+    // tensor-core kernels: units from bulk_units on are cut into tail_chunks chunks of
+    // tail_chunk_tokens instead, and the last tail_b_units of them into one chunk more
+    // (bulk_units < 0: one split for all units)
     int64_t bulk_units = -1;
     int tail_chunks = 0, tail_chunk_tokens = 0;
-    int row_chunks() const { return tail_chunks > n_chunks ? tail_chunks : n_chunks; }
+    int64_t tail_b_units = 0;
+    int tail_b_chunks = 0, tail_b_chunk_tokens = 0;
+    int row_chunks() const {
+        int m = n_chunks;
+        if (tail_chunks > m) m = tail_chunks;
+        if (tail_b_units > 0 && tail_b_chunks > m) m = tail_b_chunks;
+        return m;
+    }
 };
+
+// The device-side description of a plan over `units` units (n_regions = 0 for the fp32 kernels'
+// single split).
+ftq::SplitPlan make_split(const ChunkPlan& pl, int64_t units, bool tensor_core) {
+    ftq::SplitPlan sp{};
+    if (!tensor_core) return sp;
+    auto put = [&](int k, int64_t first_unit, int64_t first_item, int chunks, int tokens) {
+        sp.r[k].first_unit = static_cast<int>(first_unit);
+        sp.r[k].first_item = static_cast<int>(first_item);
+        sp.r[k].chunks = chunks;
+        sp.r[k].chunk_tokens = tokens;
+        sp.r[k].div_chunks = ftq::make_fastdiv(static_cast<uint32_t>(chunks));
+    };
+    const int64_t bulk = pl.bulk_units >= 0 ? pl.bulk_units : units;
+    put(0, 0, 0, pl.n_chunks, pl.chunk_tokens);
+    sp.n_regions = 1;
+    int64_t items = bulk * pl.n_chunks;
+    if (bulk < units) {
+        const int64_t a_units = units - bulk - pl.tail_b_units;
+        if (a_units > 0) {
+            put(sp.n_regions++, bulk, items, pl.tail_chunks, pl.tail_chunk_tokens);
+            items += a_units * pl.tail_chunks;
+        }
+        if (pl.tail_b_units > 0) {
+            put(sp.n_regions++, bulk + a_units, items, pl.tail_b_chunks, pl.tail_b_chunk_tokens);
+            items += pl.tail_b_units * pl.tail_b_chunks;
+        }
+    }
+    sp.row_chunks = pl.row_chunks();
+    sp.total_items = static_cast<int>(items);
+    return sp;
+}
 
 // Split the context so that the grid fills the GPU a few times over.
 ChunkPlan plan_chunks(int B, int Hq, int Hkv, int d, int max_seq_len, int n_layers) {
@@ -344,6 +384,23 @@ ChunkPlan plan_two_regions(int64_t units, int64_t slots, int max_seq_len, double
             }
         }
     }
+    // The CTAs differ in speed by a few percent on identical items (measured), and a last wave
+    // with fewer items than CTAs leaves the fastest ones idle.  So some of the tail units get
+    // one chunk more, enough for the last wave to hold an item for every CTA: the ticket order
+    // hands the longer items to the CTAs that arrive first and the shorter ones to the late ones.
+    pl.tail_b_units = 0;
+    if (pl.bulk_units >= 0) {
+        const int64_t tail_units = units - pl.bulk_units;
+        const int64_t items = tail_units * pl.tail_chunks;
+        const int64_t missing = (items + slots - 1) / slots * slots - items;
+        int ct3, r3;
+        split(pl.tail_chunks + 1, &ct3, &r3);
+        if (missing > 0 && missing <= tail_units && r3 == pl.tail_chunks + 1 && r3 <= c_max) {
+            pl.tail_b_units = missing;
+            pl.tail_b_chunks = r3;
+            pl.tail_b_chunk_tokens = ct3;
+        }
+    }
     return pl;
 }
 
@@ -402,25 +459,22 @@ cudaError_t dispatch_mma(int d, int bk, int bv, bool shared_lut, const ftq::Attn
 
 cudaError_t dispatch_merge(int d, int out_dtype, const float* partials, void* out,
                            const int32_t* seq_lens, int S, int B, int Hq, int Hkv,
-                           const ChunkPlan& pl, int64_t n_vec, const ftq::SignBits& signs,
-                           cudaStream_t st) {
+                           const ChunkPlan& pl, const ftq::SplitPlan& split, int64_t n_vec,
+                           const ftq::SignBits& signs, cudaStream_t st) {
     const float r = rsqrt_dim(d);
-    const bool two = pl.bulk_units >= 0;
-    const int bulk = two ? static_cast<int>(pl.bulk_units) : 0x7fffffff;
-    const int tc = two ? pl.tail_chunks : pl.n_chunks, tt = two ? pl.tail_chunk_tokens : pl.chunk_tokens;
     switch (d) {
         case 64:
             return ftq::launch_attn_merge_d64(out_dtype, partials, out, seq_lens, S, B, Hq,
                                               pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, Hkv,
-                                              bulk, tc, tt, pl.row_chunks(), st);
+                                              split, st);
         case 128:
             return ftq::launch_attn_merge_d128(out_dtype, partials, out, seq_lens, S, B, Hq,
                                                pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, Hkv,
-                                               bulk, tc, tt, pl.row_chunks(), st);
+                                               split, st);
         case 256:
             return ftq::launch_attn_merge_d256(out_dtype, partials, out, seq_lens, S, B, Hq,
                                                pl.n_chunks, pl.chunk_tokens, n_vec, signs, r, Hkv,
-                                               bulk, tc, tt, pl.row_chunks(), st);
+                                               split, st);
     }
     return cudaErrorInvalidValue;
 }
@@ -749,7 +803,7 @@ int ftq_flash_decode(const void* q, int q_dtype, int q_is_rotated, const uint8_t
     cudaError_t e = dispatch_split(head_dim, bits_k, bits_v, false, p, B, st);
     if (e != cudaSuccess) return cuda_fail(e, "ftq_flash_decode split launch");
     e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, S, B, Hq, Hkv, pl,
-                       static_cast<int64_t>(B) * Hq, p.signs, st);
+                       ftq::SplitPlan{}, static_cast<int64_t>(B) * Hq, p.signs, st);
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_flash_decode merge launch");
 }
 
@@ -877,16 +931,7 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
         p.div_b = ftq::make_fastdiv(static_cast<uint32_t>(B));
         p.n_units = n_layers * B * Hkv;
         p.epoch = next_epoch();
-        {
-            const bool two = pl.bulk_units >= 0;
-            p.bulk_units = two ? static_cast<int>(pl.bulk_units) : p.n_units;
-            p.tail_chunks = two ? pl.tail_chunks : pl.n_chunks;
-            p.tail_chunk_tokens = two ? pl.tail_chunk_tokens : pl.chunk_tokens;
-            p.row_chunks = pl.row_chunks();
-            p.bulk_items = p.bulk_units * pl.n_chunks;
-            p.total_items = p.bulk_items + (p.n_units - p.bulk_units) * p.tail_chunks;
-            p.div_tail_chunks = ftq::make_fastdiv(static_cast<uint32_t>(p.tail_chunks));
-        }
+        p.split = make_split(pl, p.n_units, true);
         bool merged = false;
         e = dispatch_mma(head_dim, bits_k, bits_v, shared_lut, p, n_layers * B, st, &merged);
         if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn launch");
@@ -898,7 +943,7 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     }
     if (e != cudaSuccess) return cuda_fail(e, "ftq_paged_decode_attn split launch");
     e = dispatch_merge(head_dim, out_dtype, p.partials, out, seq_lens, 0, B, Hq, Hkv, pl,
-                       static_cast<int64_t>(n_layers) * B * Hq, p.signs, st);
+                       p.split, static_cast<int64_t>(n_layers) * B * Hq, p.signs, st);
     return e == cudaSuccess ? FTQ_OK : cuda_fail(e, "ftq_paged_decode_attn merge launch");
 }
 

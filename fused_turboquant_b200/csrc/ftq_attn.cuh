@@ -24,6 +24,33 @@
 
 namespace ftq {
 
+// How the tensor-core decode kernels cut the (layer, sequence, KV head) units into work items: up
+// to three regions of consecutive units, each with its own chunk length -- few long chunks for
+// the units that fill whole waves of the grid, shorter ones for the rest, sized so that the last
+// wave has an item for every CTA (the longer ones first: the CTAs that arrive last get the short
+// ones).  Items are numbered region by region: item = r.first_item + (unit - r.first_unit) *
+// r.chunks + chunk.  A unit owns row_chunks chunk rows of the partials buffer whatever its region.
+struct SplitRegion {
+    int first_unit, first_item, chunks, chunk_tokens;
+    FastDiv div_chunks;
+};
+struct SplitPlan {
+    SplitRegion r[3];
+    int n_regions, row_chunks, total_items;
+};
+__host__ __device__ __forceinline__ const SplitRegion& region_of_item(const SplitPlan& s, int item) {
+    int k = 0;
+    if (s.n_regions > 1 && item >= s.r[1].first_item) k = 1;
+    if (s.n_regions > 2 && item >= s.r[2].first_item) k = 2;
+    return s.r[k];
+}
+__host__ __device__ __forceinline__ const SplitRegion& region_of_unit(const SplitPlan& s, int unit) {
+    int k = 0;
+    if (s.n_regions > 1 && unit >= s.r[1].first_unit) k = 1;
+    if (s.n_regions > 2 && unit >= s.r[2].first_unit) k = 2;
+    return s.r[k];
+}
+
 struct AttnParams {
     const void* q;              // [L*B, Hq, D]
     // paged source
@@ -45,15 +72,9 @@ struct AttnParams {
     int cp16;                   // contiguous source: every span 16-byte aligned
     int chunk_tokens, n_chunks, n_hpass;
     float* partials;            // [L*B*Hq][row_chunks][D + 4]
-    // Streaming kernel only: the first bulk_units (layer, sequence, KV head) units are cut into
-    // n_chunks chunks of chunk_tokens, the others into tail_chunks chunks of tail_chunk_tokens
-    // (smaller items for the last wave of the grid).  Items are numbered bulk first:
-    // [0, bulk_items) = unit * n_chunks + chunk, then (unit - bulk_units) * tail_chunks + chunk.
-    // row_chunks = max(n_chunks, tail_chunks) = chunk rows a unit owns in `partials`.  Every
-    // other kernel uses one split for all units (row_chunks == n_chunks).
-    int bulk_units, bulk_items, total_items;
-    int tail_chunks, tail_chunk_tokens, row_chunks;
-    FastDiv div_tail_chunks;
+    // Tensor-core kernels: how the (layer, sequence, KV head) units are cut into work items (see
+    // SplitPlan).  The fp32 kernels use one split for all units: n_chunks / chunk_tokens above.
+    SplitPlan split;
     // Counters of the tensor-core path.  work_counter[0] = next work item.  The barrier-synchronised
     // kernel has the host zero it before the launch.  The streaming kernel clears its counters
     // itself: CTA 0 zeroes work_counter[0] (tickets), work_counter[1] (CTAs that have left) and
@@ -469,7 +490,7 @@ __global__ void __launch_bounds__(128)
 attn_merge_kernel(const float* __restrict__ partials, OT* __restrict__ out,
                   const int32_t* __restrict__ seq_lens, int S, int B, int Hq, int n_chunks,
                   int chunk_tokens, int64_t n_vec, SignBits signs, float rsqrt_d, int Hkv,
-                  int bulk_units, int tail_chunks, int tail_chunk_tokens, int row_chunks) {
+                  const SplitPlan split) {
     constexpr int E = D / kOctet;
     constexpr int ROW = D + 4;
     const int lane = threadIdx.x & 31;
@@ -480,14 +501,19 @@ attn_merge_kernel(const float* __restrict__ partials, OT* __restrict__ out,
     if (valid) {
         const int b = static_cast<int>((v / Hq) % B);
         const int len = seq_lens ? (S > 0 ? min(seq_lens[b], S) : seq_lens[b]) : S;
-        // (layer, sequence, KV head) units from bulk_units on were cut into tail_chunks chunks
-        // of tail_chunk_tokens (see AttnParams); a unit owns row_chunks chunk rows either way
-        const int64_t unit = (v / Hq) * Hkv + (v % Hq) / (Hq / Hkv);
-        const bool bulk = unit < bulk_units;
-        const int ct = bulk ? chunk_tokens : tail_chunk_tokens;
-        nc = min(bulk ? n_chunks : tail_chunks, (len + ct - 1) / ct);
+        // the unit's region tells how many chunks it was cut into (split.n_regions == 0: one
+        // split for all units, n_chunks / chunk_tokens)
+        int ncr = n_chunks, ct = chunk_tokens;
+        if (split.n_regions > 0) {
+            const int unit = static_cast<int>((v / Hq) * Hkv + (v % Hq) / (Hq / Hkv));
+            const SplitRegion& rg = region_of_unit(split, unit);
+            ncr = rg.chunks;
+            ct = rg.chunk_tokens;
+        }
+        nc = min(ncr, (len + ct - 1) / ct);
     }
-    const float* rows = partials + (valid ? v : 0) * row_chunks * ROW;
+    const float* rows =
+        partials + (valid ? v : 0) * (split.n_regions > 0 ? split.row_chunks : n_chunks) * ROW;
     float M = -INFINITY;
     for (int c = 0; c < nc; c++) M = fmaxf(M, rows[c * ROW + D]);
     float a[E];

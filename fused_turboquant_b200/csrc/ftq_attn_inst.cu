@@ -79,7 +79,7 @@ static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              S::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        const int64_t items = p.total_items;
+        const int64_t items = p.split.total_items;
         const int64_t slots = static_cast<int64_t>(sm_count()) * S::CTAS_PER_SM;
         const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
         // One node per call: the kernel clears its own counters.  Programmatic stream
@@ -110,7 +110,7 @@ static cudaError_t run_mma_nh(const AttnParams& p, int n_lb, cudaStream_t stream
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    const int64_t items = p.total_items;
+    const int64_t items = p.split.total_items;
     const int64_t slots = static_cast<int64_t>(sm_count()) * C::CTAS_PER_SM;
     const unsigned grid = static_cast<unsigned>(items < slots ? items : slots);
     e = cudaMemsetAsync(p.work_counter, 0, 256, stream);   // this kernel counts from a zeroed word
@@ -189,27 +189,24 @@ cudaError_t FTQ_CAT(launch_attn_merge_d, FTQ_D)(int out_dtype, const float* part
                                                 const int32_t* seq_lens, int S, int B, int Hq,
                                                 int n_chunks, int chunk_tokens, int64_t n_vec,
                                                 const SignBits& signs, float rsqrt_d, int Hkv,
-                                                int bulk_units, int tail_chunks,
-                                                int tail_chunk_tokens, int row_chunks,
-                                                cudaStream_t stream) {
+                                                const SplitPlan& split, cudaStream_t stream) {
     constexpr int D = FTQ_D;
     const unsigned grid = static_cast<unsigned>((n_vec + 15) / 16);
     switch (out_dtype) {
         case kF32:
             attn_merge_kernel<D, float><<<grid, 128, 0, stream>>>(
                 partials, static_cast<float*>(out), seq_lens, S, B, Hq, n_chunks, chunk_tokens,
-                n_vec, signs, rsqrt_d, Hkv, bulk_units, tail_chunks, tail_chunk_tokens, row_chunks);
+                n_vec, signs, rsqrt_d, Hkv, split);
             break;
         case kF16:
             attn_merge_kernel<D, __half><<<grid, 128, 0, stream>>>(
                 partials, static_cast<__half*>(out), seq_lens, S, B, Hq, n_chunks, chunk_tokens,
-                n_vec, signs, rsqrt_d, Hkv, bulk_units, tail_chunks, tail_chunk_tokens, row_chunks);
+                n_vec, signs, rsqrt_d, Hkv, split);
             break;
         case kBF16:
             attn_merge_kernel<D, __nv_bfloat16><<<grid, 128, 0, stream>>>(
                 partials, static_cast<__nv_bfloat16*>(out), seq_lens, S, B, Hq, n_chunks,
-                chunk_tokens, n_vec, signs, rsqrt_d, Hkv, bulk_units, tail_chunks,
-                tail_chunk_tokens, row_chunks);
+                chunk_tokens, n_vec, signs, rsqrt_d, Hkv, split);
             break;
         default:
             return cudaErrorInvalidValue;

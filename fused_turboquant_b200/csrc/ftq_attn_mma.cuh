@@ -461,18 +461,12 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     struct Item { int chunk, hkv, lb, layer, b, t0, t1, n_pages; };
     auto item_info = [&](int item) {
         Item it;
-        // (bulk units first, then the units that are cut into shorter chunks: see AttnParams)
-        int rest, ct;
-        if (item < p.bulk_items) {
-            it.chunk = item % p.n_chunks;
-            rest = item / p.n_chunks;
-            ct = p.chunk_tokens;
-        } else {
-            const int j = item - p.bulk_items;
-            it.chunk = j % p.tail_chunks;
-            rest = p.bulk_units + j / p.tail_chunks;
-            ct = p.tail_chunk_tokens;
-        }
+        // (items are numbered region by region: see SplitPlan)
+        const SplitRegion& rg = region_of_item(p.split, item);
+        const int j = item - rg.first_item;
+        it.chunk = j % rg.chunks;
+        const int rest = rg.first_unit + j / rg.chunks;
+        const int ct = rg.chunk_tokens;
         it.hkv = rest % p.Hkv;
         it.lb = rest / p.Hkv;
         it.layer = it.lb / p.B;
@@ -482,10 +476,10 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         it.n_pages = (it.t1 - it.t0 + kPageTokens - 1) / kPageTokens;
         return it;
     };
-    const int64_t prow_head_stride = static_cast<int64_t>(p.row_chunks) * ROW;
+    const int64_t prow_head_stride = static_cast<int64_t>(p.split.row_chunks) * ROW;
     auto partial_row = [&](const Item& it) {
         return p.partials +
-               ((static_cast<int64_t>(it.lb) * p.Hq + it.hkv * group) * p.row_chunks + it.chunk) * ROW;
+               ((static_cast<int64_t>(it.lb) * p.Hq + it.hkv * group) * p.split.row_chunks + it.chunk) * ROW;
     };
     // Work items are handed out by a global counter (zeroed by the host before the launch), one
     // at a time and in index order, so that CTAs that drew short items come back for more: with

@@ -132,7 +132,7 @@ __device__ __forceinline__ void stream_merge_unit(const AttnParams& p, int lb, i
         const int h = h0 + o;
         const bool valid = h < group;
         const int64_t v = static_cast<int64_t>(lb) * p.Hq + hkv * group + (valid ? h : 0);
-        const float* rows = p.partials + v * p.row_chunks * ROW;
+        const float* rows = p.partials + v * p.split.row_chunks * ROW;
         float M = -INFINITY;
         bool nan = poison;
         for (int c = 0; c < nc; c++) {
@@ -349,19 +349,13 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     struct Item { int chunk, hkv, lb, layer, b, t0, t1, n_pages, seq_len; };
     auto item_info = [&](int item) {
         Item it;
-        // (bulk units first, then the units that are cut into smaller chunks)
-        int rest, ct;
-        if (item < p.bulk_items) {
-            rest = static_cast<int>(fast_div(static_cast<uint32_t>(item), p.div_chunks));
-            it.chunk = item - rest * p.n_chunks;
-            ct = p.chunk_tokens;
-        } else {
-            const int j = item - p.bulk_items;
-            rest = static_cast<int>(fast_div(static_cast<uint32_t>(j), p.div_tail_chunks));
-            it.chunk = j - rest * p.tail_chunks;
-            rest += p.bulk_units;
-            ct = p.tail_chunk_tokens;
-        }
+        // (items are numbered region by region: see SplitPlan)
+        const SplitRegion& rg = region_of_item(p.split, item);
+        const int j = item - rg.first_item;
+        const int q = static_cast<int>(fast_div(static_cast<uint32_t>(j), rg.div_chunks));
+        it.chunk = j - q * rg.chunks;
+        const int rest = rg.first_unit + q;
+        const int ct = rg.chunk_tokens;
         it.lb = static_cast<int>(fast_div(static_cast<uint32_t>(rest), p.div_hkv));
         it.hkv = rest - it.lb * p.Hkv;
         it.layer = static_cast<int>(fast_div(static_cast<uint32_t>(it.lb), p.div_b));
@@ -372,7 +366,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         it.n_pages = (it.t1 - it.t0 + kPageTokens - 1) / kPageTokens;
         return it;
     };
-    const int64_t prow_head_stride = static_cast<int64_t>(p.row_chunks) * ROW;
+    const int64_t prow_head_stride = static_cast<int64_t>(p.split.row_chunks) * ROW;
     const uint32_t blk_stride = static_cast<uint32_t>(p.Hkv) * PAGE_BYTES;
 
     // bounded polls of a shared-memory word (all lanes read the same word)
@@ -781,7 +775,7 @@ attn_stream_kernel(const AttnParams p, int n_items) {
         const int chunk = ctl[kCtlChunk + buf], hkv = ctl[kCtlHkv + buf], lb = ctl[kCtlLb + buf];
         const int seq_len = ctl[kCtlSeqLen + buf];
         float* prow = p.partials +
-            ((static_cast<int64_t>(lb) * p.Hq + hkv * group) * p.row_chunks + chunk) * ROW;
+            ((static_cast<int64_t>(lb) * p.Hq + hkv * group) * p.split.row_chunks + chunk) * ROW;
         // lane (g, tg) folds what it would own as a compute lane: O[head 4hh + tg][(D/8)g ..)
         float M[NH];
         bool nan = bad;
@@ -846,9 +840,8 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             }
         }
         // has every chunk of this (layer, sequence, KV head) unit been delivered?
-        const bool bulk = lb * p.Hkv + hkv < p.bulk_units;
-        const int ct = bulk ? p.chunk_tokens : p.tail_chunk_tokens;
-        const int nc = min(bulk ? p.n_chunks : p.tail_chunks, (seq_len + ct - 1) / ct);
+        const SplitRegion& rg = region_of_unit(p.split, lb * p.Hkv + hkv);
+        const int nc = min(rg.chunks, (seq_len + rg.chunk_tokens - 1) / rg.chunk_tokens);
         bool last = true;
         if (nc > 1) {
             __threadfence();

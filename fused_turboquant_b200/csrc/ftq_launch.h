@@ -23,8 +23,7 @@ namespace ftq {
                                         const int32_t* seq_lens, int S, int B, int Hq,          \
                                         int n_chunks, int chunk_tokens, int64_t n_vec,          \
                                         const SignBits& signs, float rsqrt_d, int Hkv,          \
-                                        int bulk_units, int tail_chunks, int tail_chunk_tokens, \
-                                        int row_chunks, cudaStream_t stream);
+                                        const SplitPlan& split, cudaStream_t stream);
 
 FTQ_DECLARE_LAUNCHERS(64)
 FTQ_DECLARE_LAUNCHERS(128)
