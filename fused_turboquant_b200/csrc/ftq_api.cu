@@ -413,22 +413,22 @@ ChunkPlan plan_chunks_mma(int B, int Hkv, int max_seq_len, int n_layers, int cta
                             ctas_per_sm == 1 ? 15.0 : 30.0);
 }
 
-// The streaming kernel (one CTA per SM).  Measured on B200 (Llama-shaped K4V4 batches of 37..111
+// The streaming kernel.  Measured on B200 (Llama-shaped K4V4 batches of 37..111
 // sequences, forced chunk counts): an item costs about 74 pages on top of its own pages (the
 // service warps' smaller page share, the publish / fold / prepare hand-overs), so long chunks
 // pay -- but whole waves of them rarely match the unit count, hence the two regions.
-ChunkPlan plan_chunks_stream(int B, int Hkv, int max_seq_len, int n_layers) {
-    return plan_two_regions(static_cast<int64_t>(B) * Hkv * n_layers, ftq::sm_count(), max_seq_len,
-                            74.0);
+ChunkPlan plan_chunks_stream(int B, int Hkv, int max_seq_len, int n_layers, int ctas_per_sm) {
+    return plan_two_regions(static_cast<int64_t>(B) * Hkv * n_layers,
+                            static_cast<int64_t>(ftq::sm_count()) * ctas_per_sm, max_seq_len, 74.0);
 }
 
-bool attn_mma_streams(int d, int bits_k, int bits_v, int group) {
+int attn_mma_stream_ctas(int d, int bits_k, int bits_v, int group) {
     switch (d) {
-        case 64: return ftq::attn_mma_streams_d64(bits_k, bits_v, group);
-        case 128: return ftq::attn_mma_streams_d128(bits_k, bits_v, group);
-        case 256: return ftq::attn_mma_streams_d256(bits_k, bits_v, group);
+        case 64: return ftq::attn_mma_stream_ctas_d64(bits_k, bits_v, group);
+        case 128: return ftq::attn_mma_stream_ctas_d128(bits_k, bits_v, group);
+        case 256: return ftq::attn_mma_stream_ctas_d256(bits_k, bits_v, group);
     }
-    return false;
+    return 0;
 }
 
 bool use_mma_path(int Hq, int Hkv, int q_dtype) { return Hq / Hkv <= 8 && q_dtype != FTQ_F32; }
@@ -738,10 +738,13 @@ size_t ftq_decode_workspace_bytes(int B, int Hq, int Hkv, int head_dim, int max_
     const ChunkPlan a = plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     const ChunkPlan m1 = plan_chunks_mma(B, Hkv, max_seq_len, n_layers, 1);
     const ChunkPlan m2 = plan_chunks_mma(B, Hkv, max_seq_len, n_layers, 2);
-    const ChunkPlan m3 = plan_chunks_stream(B, Hkv, max_seq_len, n_layers);
+    const ChunkPlan m3 = plan_chunks_stream(B, Hkv, max_seq_len, n_layers, 1);
+    const ChunkPlan m4 = plan_chunks_stream(B, Hkv, max_seq_len, n_layers, 2);
     size_t n = partial_bytes(a, B, Hq, head_dim, n_layers);
     const size_t n3 = partial_bytes(m3, B, Hq, head_dim, n_layers);
+    const size_t n4 = partial_bytes(m4, B, Hq, head_dim, n_layers);
     if (n3 > n) n = n3;
+    if (n4 > n) n = n4;
     const size_t n1 = partial_bytes(m1, B, Hq, head_dim, n_layers);
     const size_t n2 = partial_bytes(m2, B, Hq, head_dim, n_layers);
     if (n1 > n) n = n1;
@@ -881,8 +884,9 @@ int ftq_paged_decode_attn(const void* q, int q_dtype, void* out, int out_dtype,
     const bool mma = use_mma_path(Hq, Hkv, q_dtype);
     // one CTA per SM (16 warps) when a 4-bit byte table is in use, else two (8 warps each)
     const int mma_ctas = (bits_k == 4 || bits_v == 4) ? 1 : 2;
-    const bool streams = mma && attn_mma_streams(head_dim, bits_k, bits_v, Hq / Hkv);
-    const ChunkPlan pl = streams ? plan_chunks_stream(B, Hkv, max_seq_len, n_layers)
+    const int stream_ctas = mma ? attn_mma_stream_ctas(head_dim, bits_k, bits_v, Hq / Hkv) : 0;
+    const bool streams = stream_ctas > 0;
+    const ChunkPlan pl = streams ? plan_chunks_stream(B, Hkv, max_seq_len, n_layers, stream_ctas)
                          : mma   ? plan_chunks_mma(B, Hkv, max_seq_len, n_layers, mma_ctas)
                                  : plan_chunks(B, Hq, Hkv, head_dim, max_seq_len, n_layers);
     const size_t need = ftq_decode_workspace_bytes(B, Hq, Hkv, head_dim, max_seq_len, n_layers);

@@ -159,30 +159,35 @@ cudaError_t FTQ_CAT(launch_attn_mma_d, FTQ_D)(int bits_k, int bits_v, bool share
     return cudaErrorInvalidValue;
 }
 
-// does launch_attn_mma pick the streaming kernel for this configuration? (the host plans the
-// split of the context differently for it)
+// CTAs per SM of the streaming kernel where launch_attn_mma picks it for this configuration, 0
+// where it picks the barrier-synchronised kernel (the host plans the split of the context
+// differently for the two)
+template <int BK, int BV, int NH>
+static constexpr int stream_ctas() {
+    return use_stream_kernel<BK, BV, NH>() ? StreamCfg<FTQ_D, BK, BV, NH>::CTAS_PER_SM : 0;
+}
 template <int BK>
-static bool streams_by_bv(int bv, int nh) {
+static int stream_ctas_by_bv(int bv, int nh) {
 #ifdef FTQ_ONLY_BITS
-    if (BK != FTQ_ONLY_BITS || bv != FTQ_ONLY_BITS) return false;
-    return nh == 1 ? use_stream_kernel<BK, BK, 1>() : use_stream_kernel<BK, BK, 2>();
+    if (BK != FTQ_ONLY_BITS || bv != FTQ_ONLY_BITS) return 0;
+    return nh == 1 ? stream_ctas<BK, BK, 1>() : stream_ctas<BK, BK, 2>();
 #else
     switch (bv) {
-        case 2: return nh == 1 ? use_stream_kernel<BK, 2, 1>() : use_stream_kernel<BK, 2, 2>();
-        case 3: return nh == 1 ? use_stream_kernel<BK, 3, 1>() : use_stream_kernel<BK, 3, 2>();
-        case 4: return nh == 1 ? use_stream_kernel<BK, 4, 1>() : use_stream_kernel<BK, 4, 2>();
+        case 2: return nh == 1 ? stream_ctas<BK, 2, 1>() : stream_ctas<BK, 2, 2>();
+        case 3: return nh == 1 ? stream_ctas<BK, 3, 1>() : stream_ctas<BK, 3, 2>();
+        case 4: return nh == 1 ? stream_ctas<BK, 4, 1>() : stream_ctas<BK, 4, 2>();
     }
-    return false;
+    return 0;
 #endif
 }
-bool FTQ_CAT(attn_mma_streams_d, FTQ_D)(int bits_k, int bits_v, int group) {
+int FTQ_CAT(attn_mma_stream_ctas_d, FTQ_D)(int bits_k, int bits_v, int group) {
     const int nh = group <= 4 ? 1 : 2;
     switch (bits_k) {
-        case 2: return streams_by_bv<2>(bits_v, nh);
-        case 3: return streams_by_bv<3>(bits_v, nh);
-        case 4: return streams_by_bv<4>(bits_v, nh);
+        case 2: return stream_ctas_by_bv<2>(bits_v, nh);
+        case 3: return stream_ctas_by_bv<3>(bits_v, nh);
+        case 4: return stream_ctas_by_bv<4>(bits_v, nh);
     }
-    return false;
+    return 0;
 }
 
 cudaError_t FTQ_CAT(launch_attn_merge_d, FTQ_D)(int out_dtype, const float* partials, void* out,

@@ -18,7 +18,7 @@ namespace ftq {
                                         int n_lb, cudaStream_t stream);                         \
     cudaError_t launch_attn_mma_d##DD(int bits_k, int bits_v, bool shared_lut, const AttnParams& p, \
                                       int n_lb, cudaStream_t stream, bool* merged);            \
-    bool attn_mma_streams_d##DD(int bits_k, int bits_v, int group);                             \
+    int attn_mma_stream_ctas_d##DD(int bits_k, int bits_v, int group);                          \
     cudaError_t launch_attn_merge_d##DD(int out_dtype, const float* partials, void* out,        \
                                         const int32_t* seq_lens, int S, int B, int Hq,          \
                                         int n_chunks, int chunk_tokens, int64_t n_vec,          \
