@@ -19,6 +19,13 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libftq_b200.so")
+# A second library for ONE test (tests/test_gpu_wait_expiry.py): the same objects, except that the
+# head_dim-128 decode unit is compiled with FTQ_TEST_WAIT_EXPIRY (one page copy of one warp is
+# never issued and the poll limit is small), so that a bounded wait runs out and the give-up path
+# (NaN rows, status word, the context stays usable) executes.  Never loaded by the package.
+TEST_LIB_PATH = os.path.join(PKG_DIR, "libftq_b200_waittest.so")
+TEST_UNIT = ("ftq_attn_inst.cu", "attn_d128_waittest",
+             ["-DFTQ_D=128", "-DFTQ_ONLY_BITS=4", "-DFTQ_TEST_WAIT_EXPIRY"])
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -76,8 +83,10 @@ def _unit_stale(src: str, obj: str) -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile and link the library if it is missing or older than its sources."""
-    if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _sources_mtime():
+    """Compile and link the library (and the wait-expiry test library) if missing or older than
+    the sources."""
+    if not force and all(os.path.exists(l) and os.path.getmtime(l) >= _sources_mtime()
+                         for l in (LIB_PATH, TEST_LIB_PATH)):
         return LIB_PATH
     nvcc = _nvcc()
     os.makedirs(OBJ_DIR, exist_ok=True)
@@ -97,11 +106,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return obj
 
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
-        objs = list(ex.map(compile_one, UNITS))
-    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcudart"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        objs = list(ex.map(compile_one, UNITS + [TEST_UNIT]))
+    test_obj = objs.pop()
+    for lib, members in ((LIB_PATH, objs),
+                         (TEST_LIB_PATH, [test_obj if o.endswith("attn_d128.o") else o for o in objs])):
+        cmd = [nvcc, "-shared", "-o", lib, *members, "-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     return LIB_PATH
 
 

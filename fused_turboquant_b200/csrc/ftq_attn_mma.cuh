@@ -143,7 +143,14 @@ __device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void* src, uin
 }
 // Bounded wait: gives up after kMbarSpinLimit polls (each poll may itself block for a
 // hardware-defined slice) and reports failure instead of hanging the SM.
+// FTQ_TEST_WAIT_EXPIRY (only the test library of build.py defines it): warp 5 of CTA 0 announces its
+// first page copy to the mbarrier but does not issue it, and the poll limit is small -- the wait
+// runs out, which is the one way to execute the give-up path (NaN rows, status word) on purpose.
+#ifdef FTQ_TEST_WAIT_EXPIRY
+constexpr int kMbarSpinLimit = 1 << 6;
+#else
 constexpr int kMbarSpinLimit = 1 << 20;
+#endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (int i = 0; i < kMbarSpinLimit; i++) {
         uint32_t ok;
@@ -553,6 +560,9 @@ attn_mma_kernel(const AttnParams p, int n_items) {
     // left over they run the next item's prologue at the same time
     constexpr int NRED = (NH * NMT <= WARPS - 2) ? NH * NMT : WARPS;
 
+#ifdef FTQ_TEST_WAIT_EXPIRY
+    bool test_drop = blockIdx.x == 0 && warp == 5;
+#endif
     draw_ticket();
     if (tid == 0) {
         s_next[1] = resolve_ticket(ticket);
@@ -643,6 +653,12 @@ attn_mma_kernel(const AttnParams p, int n_items) {
             const uint8_t* page =
                 head_base + static_cast<uint64_t>(static_cast<uint32_t>(sblk[pg])) * blk_stride;
             mbar_expect_tx(my_bars + rb * 8, C::PAGE_BYTES);
+#ifdef FTQ_TEST_WAIT_EXPIRY
+            if (test_drop) {   // (see kMbarSpinLimit)
+                test_drop = false;
+                return;
+            }
+#endif
             bulk_g2s_hint(my_ring + rb * C::PAGE_BYTES, page, C::PAGE_BYTES, my_bars + rb * 8, page_policy);
         };
         // same, for the first pages of a later item, whose block ids are not staged yet
@@ -802,7 +818,9 @@ attn_mma_kernel(const AttnParams p, int n_items) {
         // Software pipeline: K.Q^T of page i+1 and P.V of page i are independent and sit in one
         // straight-line block, so their look-ups and MMAs overlap each other's latencies.
         {
-            if (lane == 0 && !primed) {
+            // (a warp whose wait has run out requests nothing any more: the mbarrier of the lost
+            // copy never completes its phase, and arriving on it again would be an error)
+            if (lane == 0 && !primed && !stalled) {
                 // (when the exchange area aliases the ring, the previous item's merge wrote it
                 // with ordinary stores)
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");

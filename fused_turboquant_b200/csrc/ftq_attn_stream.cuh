@@ -541,6 +541,9 @@ attn_stream_kernel(const AttnParams p, int n_items) {
     constexpr int THR = S::SKIP > 0 ? WC * (S::SKIP - 1) : 0;
     const int g_first = S::SKIP > 0 ? (warp < NSVC ? WC * S::SKIP + warp : warp - NSVC) : warp;
     const uint64_t page_policy = l2_evict_first_policy();
+#ifdef FTQ_TEST_WAIT_EXPIRY
+    bool test_drop = blockIdx.x == 0 && warp == 5;   // (see kMbarSpinLimit)
+#endif
     int g_next = g_first;                                   // next page of item gseq for this warp
     int g_lim = g_end ? 0 : ctl[kCtlPages + 0];             // its page count (0: nothing to take)
     // request the next page of the stream into ring buffer rb; returns its index within item
@@ -570,15 +573,23 @@ attn_stream_kernel(const AttnParams p, int n_items) {
             }
             if (pg < 0) g_lim = 0;   // end / handed back: the fast check above must keep failing
         }
-        if (pg >= 0 && lane == 0) {
+        // (a warp whose wait has run out requests nothing any more: the mbarrier of the lost copy
+        // never completes its phase, and arriving on it again would be an error)
+        if (pg >= 0 && lane == 0 && !stalled) {
             const int buf = gseq & 1;
             const unsigned long long base =
                 *reinterpret_cast<volatile unsigned long long*>(const_cast<int*>(ctl + kCtlBase + 2 * buf));
             const uint8_t* page = reinterpret_cast<const uint8_t*>(base) +
                 static_cast<uint64_t>(static_cast<uint32_t>(sblk[buf * kStreamMaxChunkPages + pg])) * blk_stride;
             mbar_expect_tx(my_bars + rb * 8, PAGE_BYTES);
+#ifdef FTQ_TEST_WAIT_EXPIRY
+            if (!test_drop)
+#endif
             bulk_g2s_hint(my_ring + rb * PAGE_BYTES, page, PAGE_BYTES, my_bars + rb * 8, page_policy);
         }
+#ifdef FTQ_TEST_WAIT_EXPIRY
+        if (pg >= 0) test_drop = false;
+#endif
         return pg;
     };
 
