@@ -1322,6 +1322,13 @@ extern "C" int ftq_tq_decode_layers(const void* q, int q_dtype, int B, int Hq, i
                      value_bits != 8 && head_dim != 256 && aligned(kv_cache, 4) &&
                      !p.value_lloyd_max;
     if (mma) {
+        // key centroids scaled for the smallest fp16 rounding error of the table (see
+        // choose_k_scale).  With norm correction the factor cancels by itself (the centroid
+        // vector is re-normalised with the scaled centroids); without, it goes into the
+        // softmax scale.
+        const float ks = choose_k_scale(centroids_host, key_bits, head_dim);
+        for (int i = 0; i < (1 << key_bits); i++) p.centroids.v[i] *= ks;
+        if (!p.norm_correction) p.scale = scale / ks;
         const int64_t items = static_cast<int64_t>(B) * Hkv * num_kv_splits;
         if (items >= (1ll << 31)) return fail(FTQ_ERR_INVALID, "too many (sequence, head, split) items");
         const int nh = group <= 4 ? 1 : 2;

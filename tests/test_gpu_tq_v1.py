@@ -178,14 +178,20 @@ def test_tensor_core_decode_vs_reference_fixture(oracle, golden, name, qdtype):
     np.testing.assert_array_equal(np.isfinite(m[..., D]), live)
     assert np.all(m[..., :D][~live] == 0)
     np.testing.assert_allclose(m[..., D][live], m_ref[..., D][live], rtol=2e-3, atol=5e-3)
-    # fp16 centroids / weights on keys with x12 outlier channels: a few elements in a thousand sit
-    # just outside the 2e-3 / 1e-3 gate in fp32 (all far inside one bf16 ulp of the output)
+    # fp16 queries / weights on keys with x12 outlier channels: up to 2 elements in a thousand
+    # sit just outside the 2e-3 / 1e-3 gate in fp32 (measured: 0-16 of 3 072-8 192 partial
+    # elements, max |err| 2.8e-3; 0-3 of 1 024-2 048 output elements, max |err| 1.7e-3; all far
+    # inside one bf16 ulp of the output)
     part, ref_part = m[..., :D][live], m_ref[..., :D][live]
-    assert gate(part, ref_part) <= part.size // 150, gate(part, ref_part)
-    assert np.abs(part - ref_part).max() < 8e-3
+    print(f"\n[tq tensor-core stage 1] {name} {qdtype}: partials outside 2e-3/1e-3: "
+          f"{gate(part, ref_part)} of {part.size}, max |err| {np.abs(part - ref_part).max():.2e}; "
+          f"outputs outside: {gate(out.cpu().numpy(), o_ref)} of {o_ref.size}, "
+          f"max |err| {np.abs(out.cpu().numpy() - o_ref).max():.2e}")
+    assert gate(part, ref_part) <= part.size // 300, gate(part, ref_part)
+    assert np.abs(part - ref_part).max() < 4e-3
     o = out.cpu().numpy()
-    assert gate(o, o_ref) <= o.size // 300, gate(o, o_ref)
-    assert np.abs(o - o_ref).max() < 5e-3
+    assert gate(o, o_ref) <= o.size // 400, gate(o, o_ref)
+    assert np.abs(o - o_ref).max() < 2.5e-3
 
 
 def test_llama_shape_sampled(oracle):
