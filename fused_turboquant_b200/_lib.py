@@ -44,6 +44,8 @@ SIGNATURES = {
     "ftq_tq_slot_bytes": (_i, [_i, _i, _i]),
     "ftq_tq_store": (_i, [_vp, _vp, _i, _i64, _i, _i, _i64, _i64, _i, _i, _i, _i, _fp, _vp, _i64,
                           _i64, _i64, _i, _vp, _vp]),
+    "ftq_tq_store_layers": (_i, [_vp, _vp, _i, _i64, _i, _i, _i64, _i64, _i, _i, _i, _i, _fp, _vp,
+                                 _i64, _i64, _i64, _i, _vp, _i, _i64, _i64, _i64, _vp]),
     "ftq_tq_decode": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i64, _i64, _i64, _i, _vp, _i, _vp, _vp,
                            _i, _i, _i, _i, _i, _fp, _c.c_float, _i, _vp, _vp, _i, _vp, _vp, _i, _vp,
                            _vp]),

@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cfloat>
 #include <atomic>
+#include <cstdint>
 #include <cstring>
 #include <random>
 #include <cstdlib>
@@ -1146,6 +1147,23 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
                             const float* midpoints_host, uint8_t* kv_cache,
                             int64_t stride_block, int64_t stride_pos, int64_t stride_head,
                             int block_size, const int64_t* slot_mapping, void* stream) {
+    return ftq_tq_store_layers(key, value, dtype, n_tokens, Hkv, head_dim, token_stride, head_stride,
+                               key_bits, value_bits, rotate_values, value_lloyd_max, midpoints_host,
+                               kv_cache, stride_block, stride_pos, stride_head, block_size,
+                               slot_mapping, 1, 0, 0, 0, stream);
+}
+
+extern "C" int ftq_tq_store_layers(const void* key, const void* value, int dtype, int64_t n_tokens,
+                                   int Hkv, int head_dim, int64_t token_stride, int64_t head_stride,
+                                   int key_bits, int value_bits, int rotate_values,
+                                   int value_lloyd_max, const float* midpoints_host,
+                                   uint8_t* kv_cache, int64_t stride_block, int64_t stride_pos,
+                                   int64_t stride_head, int block_size,
+                                   const int64_t* slot_mapping, int n_layers,
+                                   int64_t kv_layer_stride, int64_t cache_layer_stride,
+                                   int64_t num_blocks, void* stream) {
+    if (n_layers <= 0 || n_layers > 65535 || !even(cache_layer_stride) || num_blocks < 0)
+        return fail(FTQ_ERR_INVALID, "bad n_layers / cache_layer_stride / num_blocks");
     if (!dim_ok(head_dim)) return fail(FTQ_ERR_UNSUPPORTED, "head_dim %d (need 64/128/256)", head_dim);
     if (!tq_bits_ok(key_bits, value_bits))
         return fail(FTQ_ERR_UNSUPPORTED, "key_bits %d / value_bits %d (need 1..4, 8 = FP8 or FTQ_TQ_KEY_BITS_MSE8 / 1,2,3,4,8)", key_bits,
@@ -1163,13 +1181,18 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
     if (!key || !value || !kv_cache || !slot_mapping || (!key_fp8 && !midpoints_host))
         return fail(FTQ_ERR_INVALID, "NULL pointer argument");
     const int64_t es = static_cast<int64_t>(dtype_size(dtype));
-    if (!aligned(key, 16) || !aligned(value, 16) || (token_stride * es) % 16 || (head_stride * es) % 16)
+    if (!aligned(key, 16) || !aligned(value, 16) || (token_stride * es) % 16 || (head_stride * es) % 16 ||
+        (kv_layer_stride * es) % 16)
         return fail(FTQ_ERR_INVALID, "key/value rows must be 16-byte aligned");
     if (!aligned(kv_cache, 2) || !even(stride_block) || !even(stride_pos) || !even(stride_head))
         return fail(FTQ_ERR_INVALID, "kv_cache base and strides must be even");
     if (stride_head < ftq_tq_slot_bytes(head_dim, key_bits, value_bits) - 1)
         return fail(FTQ_ERR_INVALID, "stride_head smaller than the slot");
     ftq::TqStoreParams p{};
+    p.kv_layer_stride = kv_layer_stride;
+    p.cache_layer_stride = cache_layer_stride;
+    // (num_blocks = 0: the cache's extent is not known, only negative slots are skipped)
+    p.slot_limit = num_blocks > 0 ? num_blocks * block_size : INT64_MAX;
     p.key = key;
     p.value = value;
     p.token_stride = token_stride;
@@ -1200,7 +1223,8 @@ extern "C" int ftq_tq_store(const void* key, const void* value, int dtype, int64
     const int64_t n_vec = n_tokens * Hkv;
     // (as in the reference, the Lloyd-Max flag only changes 4-bit values)
     const int vmode = (rotate_values ? ftq::kTqRotateValues : 0) |
-                      (value_lloyd_max && value_bits == 4 ? ftq::kTqLloydMaxValues : 0);
+                      (value_lloyd_max && value_bits == 4 ? ftq::kTqLloydMaxValues : 0) |
+                      (n_layers << 8);
     cudaError_t e = cudaErrorInvalidValue;
     switch (head_dim) {
         case 64: e = ftq::launch_tq_store_d64(kb, value_bits, dtype, p, vmode, n_vec, t8, st); break;

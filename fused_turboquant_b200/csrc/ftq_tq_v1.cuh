@@ -62,6 +62,11 @@ struct TqStoreParams {
     const int64_t* slot_mapping;
     float midpoints[kTqMaxMid];
     float rsqrt_d;  // 1.0f / sqrtf(D), as the reference computes it
+    // layers in one launch (blockIdx.y = layer): element / byte distances between the layers'
+    // key / value tensors and caches; every layer uses the same slot_mapping
+    int64_t kv_layer_stride, cache_layer_stride;
+    // slots at or beyond it (a stale or corrupt mapping) are skipped like negative ones
+    int64_t slot_limit;
 };
 
 __host__ __device__ constexpr int tq_value_bytes(int d, int vb) { return vb == 8 ? d : d * vb / 8; }
@@ -193,7 +198,8 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec, const TqTable<K8M> t8) {
         const int head = valid ? static_cast<int>(static_cast<uint32_t>(v) - token * p.Hkv) : 0;
         // (requested here, looked at only after the key's arithmetic: the warp does not wait for it)
         const int64_t slot = valid ? p.slot_mapping[token] : -1;
-        const int64_t row_off = static_cast<int64_t>(token) * p.token_stride + head * p.head_stride;
+        const int64_t row_off = blockIdx.y * p.kv_layer_stride +
+                                static_cast<int64_t>(token) * p.token_stride + head * p.head_stride;
 
         // ---- key: raw norm, normalise, butterfly, midpoint search
         float y[E];
@@ -221,7 +227,9 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec, const TqTable<K8M> t8) {
         for (int r = 0; r < E; r++) y[r] = __fdiv_rn(y[r], den);
         octet_fwht<E>(y, lane);  // -> (lane l, register k) = coordinate l + 8k
 
-        const bool store = valid && slot >= 0;
+        // negative = padding (triton_inkernel_store.py:398-399); a slot at or beyond the cache's
+        // end is dropped the same way instead of being written out of bounds
+        const bool store = valid && static_cast<uint64_t>(slot) < static_cast<uint64_t>(p.slot_limit);
         uint8_t* dst = nullptr;
         if (store) {
             int64_t blk, off;
@@ -233,7 +241,8 @@ tq_store_kernel(const TqStoreParams p, int64_t n_vec, const TqTable<K8M> t8) {
                 blk = slot / p.block_size;
                 off = slot - blk * p.block_size;
             }
-            dst = p.kv_cache + blk * p.stride_block + off * p.stride_pos + head * p.stride_head;
+            dst = p.kv_cache + blockIdx.y * p.cache_layer_stride + blk * p.stride_block +
+                  off * p.stride_pos + head * p.stride_head;
         }
 
         if constexpr (KBYTE) {

@@ -27,8 +27,9 @@ template <int KB, int VB, typename T, bool K8M>
 static cudaError_t store_run(const TqStoreParams& p, int value_mode, int64_t n_vec,
                              const TqTable<K8M>& t8, cudaStream_t stream) {
     const int64_t want = (n_vec + 31) / 32;  // 8 warps x 4 vectors per CTA pass
-    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
-    const unsigned gx = static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
+    const int layers = value_mode >> 8;      // (the launcher packs the layer count above the flags)
+    const int64_t cap = (static_cast<int64_t>(sm_count()) * 8 + layers - 1) / layers;
+    const dim3 gx(static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap)), layers);
     const bool rotate_v = (value_mode & kTqRotateValues) != 0;
     if constexpr (VB == 4 && KB != 8) {
         if (value_mode & kTqLloydMaxValues) {

@@ -11,6 +11,7 @@ namespace ftq {
 // value_mode of the store launchers
 constexpr int kTqRotateValues = 1;    // Hadamard-transform the values in the kernel
 constexpr int kTqLloydMaxValues = 2;  // 4-bit values: Lloyd-Max codes against the key midpoints
+// bits 8.. of value_mode: the number of layers stored by the launch (grid y; at least 1)
 
 #define FTQ_DECLARE_TQ_LAUNCHERS(DD)                                                              \
     cudaError_t launch_tq_store_d##DD(int kb, int vb, int dtype, const TqStoreParams& p,          \

@@ -131,7 +131,10 @@ def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
                  slot_mapping: torch.Tensor, midpoints, tq_config: TurboQuantSlotConfig,
                  head_size: int | None = None, v_rotate: bool = False,
                  v_lloyd_max: bool = False) -> None:
-    """Quantise ``key``/``value`` ``[N, Hkv, D]`` into the slots ``slot_mapping`` names (< 0: skipped).
+    """Quantise ``key``/``value`` ``[N, Hkv, D]`` into the slots ``slot_mapping`` names (< 0: skipped,
+    and so are slots beyond the cache's end).  ``key``/``value`` ``[L, N, Hkv, D]`` with a cache
+    ``[L, num_blocks, block_size, Hkv, slot]`` stores all layers in one launch (same
+    ``slot_mapping`` for every layer).
 
     ``v_lloyd_max`` (the reference's TURBOQUANT_V_LLOYD_MAX switch; 4-bit values only, ignored
     otherwise as in the reference): values become Lloyd-Max codes against the key midpoints, their
@@ -140,7 +143,13 @@ def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
     """
     _require_cuda(key, "key")
     _require_cuda(kv_cache, "kv_cache")
-    n, hkv, d = key.shape
+    layered = key.dim() == 4
+    if layered != (kv_cache.dim() == 5):
+        raise ValueError("key/value [L, N, Hkv, D] go with a cache [L, num_blocks, block_size, Hkv, slot]")
+    n_layers = key.shape[0] if layered else 1
+    if layered and kv_cache.shape[0] != n_layers:
+        raise ValueError("key/value and kv_cache disagree on the number of layers")
+    n, hkv, d = key.shape[-3:]
     if head_size is not None and head_size != d:
         raise ValueError(f"head_size {head_size} does not match key.shape[-1] {d}")
     if d != tq_config.head_dim:
@@ -155,22 +164,23 @@ def launch_store(key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
     if v_rotate and not rotate_in_kernel:
         # 8-bit values: rotate here (the kernel fuses the rotation for 1..4-bit values only)
         value = rht(value.float().contiguous(), None).to(key.dtype)
-    if key.stride(2) != 1 or value.stride() != key.stride():
+    if key.stride(-1) != 1 or value.stride() != key.stride():
         key, value = key.contiguous(), value.contiguous()
     if kv_cache.dtype != torch.uint8:
         kv_cache = kv_cache.view(torch.uint8)
-    sb, sp, sh = _cache_strides(kv_cache)
-    if kv_cache.shape[3] < tq_config.slot_size:
-        raise ValueError(f"kv_cache slots of {kv_cache.shape[3]} bytes are smaller than {tq_config.slot_size}")
+    sb, sp, sh = _cache_strides(kv_cache[0] if layered else kv_cache)
+    if kv_cache.shape[-1] < tq_config.slot_size:
+        raise ValueError(f"kv_cache slots of {kv_cache.shape[-1]} bytes are smaller than {tq_config.slot_size}")
     sm = slot_mapping.to(device=key.device, dtype=torch.int64).contiguous()
     kb = _key_bits(tq_config)
     with torch.cuda.device(key.device):
-        rc = _lib.load().ftq_tq_store(
-            _ptr(key), _ptr(value), _DT[key.dtype], n, hkv, d, key.stride(0), key.stride(1),
+        rc = _lib.load().ftq_tq_store_layers(
+            _ptr(key), _ptr(value), _DT[key.dtype], n, hkv, d, key.stride(-3), key.stride(-2),
             kb, tq_config.value_quant_bits, int(rotate_in_kernel),
-            int(bool(v_lloyd_max)), _table_ptr(midpoints, kb == 8), _ptr(kv_cache), sb, sp, sh, kv_cache.shape[1],
-            _ptr(sm), _stream(key.device))
-    _lib.check(rc, "ftq_tq_store")
+            int(bool(v_lloyd_max)), _table_ptr(midpoints, kb == 8), _ptr(kv_cache), sb, sp, sh,
+            kv_cache.shape[-3], _ptr(sm), n_layers, key.stride(0) if layered else 0,
+            kv_cache.stride(0) if layered else 0, kv_cache.shape[-4], _stream(key.device))
+    _lib.check(rc, "ftq_tq_store_layers")
 
 
 def decode_attention(query: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor,

@@ -323,6 +323,23 @@ int ftq_tq_store(const void *key, const void *value, int dtype, int64_t n_tokens
                  const int64_t *slot_mapping, void *stream);
 
 /*
+ * ftq_tq_store for the caches of n_layers layers in ONE launch: key / value are
+ * [n_layers, n_tokens, Hkv, head_dim] (kv_layer_stride elements between layers), the caches
+ * lie cache_layer_stride bytes apart and every layer uses the same slot_mapping (vLLM gives all
+ * layers the same one).  The reference stores per layer (v1_backend.py:727-760); small models
+ * are launch-bound that way.  num_blocks > 0 additionally skips every slot at or beyond
+ * num_blocks * block_size (a stale or corrupt mapping) like a negative one, instead of writing
+ * out of bounds.  With n_layers = 1, strides 0, num_blocks = 0 this is ftq_tq_store.
+ */
+int ftq_tq_store_layers(const void *key, const void *value, int dtype, int64_t n_tokens, int Hkv,
+                        int head_dim, int64_t token_stride, int64_t head_stride, int key_bits,
+                        int value_bits, int rotate_values, int value_lloyd_max,
+                        const float *midpoints_host, uint8_t *kv_cache, int64_t stride_block,
+                        int64_t stride_pos, int64_t stride_head, int block_size,
+                        const int64_t *slot_mapping, int n_layers, int64_t kv_layer_stride,
+                        int64_t cache_layer_stride, int64_t num_blocks, void *stream);
+
+/*
  * Replaces _decode_attention_offset_only (vllm_plugin/v1_backend.py:975-1093): query
  * rotation q @ H, _tq_decode_stage1_offset (vllm_plugin/triton_decode_offset.py:42-444)
  * and the stage-2 merge, in two launches.  q: [B, Hq, head_dim] of q_dtype in the original

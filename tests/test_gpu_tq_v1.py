@@ -415,3 +415,53 @@ def test_all_layers_in_one_call_equals_per_layer_calls(D, kb, vb, G, qdtype):
     assert torch.isnan(got[:, 2]).all()
     keep = [0, 1, 3]
     assert torch.equal(got[:, keep], one[:, keep])
+
+
+@pytest.mark.parametrize("D,kb,vb,fp8", [(128, 4, 4, True), (64, 3, 3, True), (256, 8, 2, False), (128, 8, 8, True)])
+def test_store_of_all_layers_in_one_call_equals_per_layer_calls(D, kb, vb, fp8):
+    """[L, N, Hkv, D] keys / values into a [L, nb, bs, Hkv, slot] cache in one launch: the same bytes as
+    one launch per layer (4-bit, 3-bit, 8-bit Lloyd-Max and FP8 keys)."""
+    from fused_turboquant_b200 import tq_v1
+    L, N, Hkv, bs, nb = 3, 150, 2, 16, 12
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, True, key_use_fp8_at_8bit=fp8)
+    g = torch.Generator("cpu").manual_seed(D + kb)
+    K = torch.randn(L, N, Hkv, D, generator=g).bfloat16().cuda()
+    V = (torch.randn(L, N, Hkv, D, generator=g) * 1.3 - 0.2).bfloat16().cuda()
+    n_cent = 256 if (kb == 8 and not fp8) else 1 << min(kb, 4)
+    cent, mids = tq_v1.midpoints_of(torch.sort(torch.randn(n_cent, generator=g)).values / D ** 0.5)
+    slots = torch.randperm(nb * bs, generator=g)[:N]
+    slots[5] = -1
+    one = torch.zeros((L, nb, bs, Hkv, cfg.slot_size_aligned), dtype=torch.uint8, device="cuda")
+    tq_v1.launch_store(K, V, one, slots.cuda(), mids, cfg, v_rotate=vb != 8)
+    per = torch.zeros_like(one)
+    for l in range(L):
+        tq_v1.launch_store(K[l], V[l], per[l], slots.cuda(), mids, cfg, v_rotate=vb != 8)
+    assert torch.equal(one, per)
+    assert one.any()
+
+
+def test_store_skips_slots_beyond_the_cache():
+    """A slot at or beyond num_blocks * block_size is dropped like a negative one.  The cache the
+    call is given is a view of a larger allocation, so a missing guard would show as bytes
+    written behind the view, not as an out-of-bounds write."""
+    from fused_turboquant_b200 import tq_v1
+    D, kb, vb, Hkv, bs, nb = 128, 4, 4, 2, 16, 6
+    cfg = tq_v1.TurboQuantSlotConfig(D, kb, vb, True)
+    g = torch.Generator("cpu").manual_seed(77)
+    N = 40
+    K = torch.randn(N, Hkv, D, generator=g).bfloat16().cuda()
+    V = torch.randn(N, Hkv, D, generator=g).bfloat16().cuda()
+    cent, mids = tq_v1.midpoints_of(torch.sort(torch.randn(16, generator=g)).values / D ** 0.5)
+    big = torch.zeros((nb + 4, bs, Hkv, cfg.slot_size_aligned), dtype=torch.uint8, device="cuda")
+    slots = torch.randperm(nb * bs, generator=g)[:N]
+    good = big.clone()
+    tq_v1.launch_store(K, V, good[:nb], slots.cuda(), mids, cfg)
+    bad = slots.clone()
+    bad[3] = nb * bs + 1            # inside `big`, outside the view the call is given
+    bad[17] = (nb + 3) * bs + 15
+    tq_v1.launch_store(K, V, big[:nb], bad.cuda(), mids, cfg)
+    assert not big[nb:].any(), "the store wrote behind the cache it was given"
+    want = good.clone()
+    for tok in (3, 17):
+        want[int(slots[tok]) // bs, int(slots[tok]) % bs] = 0
+    assert torch.equal(big, want)
