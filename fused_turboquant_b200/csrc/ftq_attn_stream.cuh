@@ -24,17 +24,26 @@
 //     for that.  Item metadata is double buffered; a warp can never be more
 //     than two items ahead of the slowest one.
 //   * The split-KV merge is part of the kernel: the CTA that delivers the last
-//     chunk of a (layer, sequence, KV head) unit (a counter per unit, zeroed by
-//     the host before the launch) merges the unit's partial rows, applies the
-//     inverse rotation (core/hadamard.py:93-100) and stores the output (warp 0,
-//     right after the fold).  No CTA ever waits for another CTA.
+//     chunk of a (layer, sequence, KV head) unit (a counter per unit) merges
+//     the unit's partial rows, applies the inverse rotation
+//     (core/hadamard.py:93-100) and stores the output (warp 0, right after the
+//     fold).  No CTA ever waits for another CTA's work.
+//   * The kernel clears its own counters: CTA 0 zeroes them and publishes the
+//     launch's epoch, everybody checks for the epoch before the first atomic
+//     on a counter (the first two items of a CTA are fixed, so that check is
+//     long satisfied when it comes), the last CTA to leave takes the epoch out
+//     again.  The launch is a programmatic dependent of whatever kernel
+//     precedes it in the stream: the tables are built before
+//     griddepcontrol.wait, global memory is touched only after it.
 //   * The online softmax keeps a lazy reference maximum: the cross-lane maximum
 //     and the rescale run only when some score exceeds the reference by more
 //     than kLazyMaxSlack (base-2 exponent units); weights stay below
 //     2^kLazyMaxSlack and are converted to fp16 with saturation.
 //
-// Every wait (mbarrier, shared-memory flags) is bounded; a wait that runs out
-// marks the warp's state with NaN, which reaches the output instead of a hang.
+// Every wait (mbarrier, shared-memory flags, epoch) is bounded; a wait that runs
+// out marks the warp's state with NaN, which reaches the output instead of a
+// hang, sets a bit in the call's status word, and the warp requests no further
+// pages (the lost copy's mbarrier must not be arrived on again).
 // Block ids outside [0, num_blocks) are never dereferenced: the item is
 // computed on block 0 and its result replaced by NaN.
 #pragma once
