@@ -316,7 +316,7 @@ class Setup:
     """One workload resident on this rank: pools, page table, queries, workspace."""
 
     def __init__(self, name, w, seq_lens, Hkv_local, Hq_local, device, seed, gen,
-                 force_per_layer=False):
+                 force_per_layer=False, force_one_call=False):
         self.name, self.w, self.seq_lens, self.device = name, w, seq_lens, device
         self.Hkv, self.Hq, self.L, self.D = Hkv_local, Hq_local, w["layers"], w["D"]
         self.B = len(seq_lens)
@@ -332,7 +332,10 @@ class Setup:
         # A layer that moves less than 64 MB is launch-bound on its own: such workloads run all
         # layers in ONE call (layer is a dimension of the kernel's work items).  Larger layers
         # get one call per layer, as an inference engine would issue them.
-        self.layers_per_call = self.L if (self.bytes_layer < (64 << 20) and not force_per_layer) else 1
+        # (force_one_call: the record that gathers once per step runs the step as one call at
+        # every rank count, not only where a rank's share of a layer is small)
+        self.layers_per_call = self.L if (force_one_call or (self.bytes_layer < (64 << 20)
+                                                              and not force_per_layer)) else 1
         self.n_calls = self.L // self.layers_per_call
         self.ws = torch.empty(self.pool.workspace_bytes(self.B, Hq_local, self.max_seq,
                                                         self.layers_per_call),
@@ -504,8 +507,8 @@ def head_sharded_record(device, rank, world, steps):
     """Configuration 4 as stated: KV heads split over the ranks (Hkv / world each, with the query
     heads of those groups), every rank holds all four 131 072-token sequences of its heads, and
     the outputs are all-gathered along the head axis over NCCL inside the timed region -- once per
-    step (all layers' outputs in one collective) and, second figure, once per layer (what a model
-    with dependent layers has to do).  Strong scaling: the total work is fixed."""
+    step (all layers in one call, their outputs in one collective) and, second figure, once per
+    layer (one call and one collective per layer: what a model with dependent layers has to do).  Strong scaling: the total work is fixed."""
     from fused_turboquant_b200 import sharding
 
     w = dict(WORKLOADS["cfg4"])
@@ -520,7 +523,7 @@ def head_sharded_record(device, rank, world, steps):
     total_bytes_step = decode_bytes(seq_lens, w["Hq"], w["Hkv"], w["D"], w["bk"], w["bv"]) * w["layers"]
     for mode in ("per_step", "per_layer"):
         s = Setup("cfg4", w, seq_lens, len(kvr), len(qr), device, seed=41 + rank, gen=gen,
-                  force_per_layer=(mode == "per_layer"))
+                  force_per_layer=(mode == "per_layer"), force_one_call=(mode == "per_step"))
         gather = sharding.all_gather_heads
         post, post_each = (gather, None) if mode == "per_step" else (None, gather)
         for _ in range(3):
