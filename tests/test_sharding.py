@@ -93,13 +93,17 @@ def _absent_rank_worker(rank, world, port, q, done):
     """Rank 1 joins the group but never enters the collective; rank 0 must get an error, not hang."""
     import datetime
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    # (the rendezvous gets a generous limit -- a loaded machine starts the two interpreters many
+    # seconds apart --, the short limit belongs to the group the collective runs on)
     dist.init_process_group("gloo", rank=rank, world_size=world,
-                            timeout=datetime.timedelta(seconds=4))
+                            timeout=datetime.timedelta(seconds=180))
+    short = dist.new_group(ranks=list(range(world)), backend="gloo",
+                           timeout=datetime.timedelta(seconds=4))
     if rank == 1:
-        done.wait(60)          # stays alive (a crashed peer is a different failure), skips the call
+        done.wait(120)         # stays alive (a crashed peer is a different failure), skips the call
         os._exit(0)
     try:
-        sharding.all_gather_heads(torch.zeros(1, 2, 2, 4))
+        sharding.all_gather_heads(torch.zeros(1, 2, 2, 4), group=short)
         q.put("returned")
     except Exception as e:     # gloo reports the timeout as a RuntimeError / DistBackendError
         q.put(f"{type(e).__name__}: {e}"[:300])
@@ -115,9 +119,9 @@ def test_all_gather_with_an_absent_rank_times_out_cleanly():
     procs = [ctx.Process(target=_absent_rank_worker, args=(r, 2, port, q, done)) for r in range(2)]
     for p in procs:
         p.start()
-    msg = q.get(timeout=90)
+    msg = q.get(timeout=300)
     for p in procs:
-        p.join(timeout=60)
+        p.join(timeout=120)
         assert p.exitcode == 0
     assert msg != "returned", "the collective returned although a rank never joined it"
     assert "Error" in msg or "Timed out" in msg or "timeout" in msg.lower(), msg
